@@ -1,0 +1,93 @@
+"""Builds the CPU checkers (test infrastructure, never the product).
+
+* ``_build/libthor_oracle.so``  — the plain-C restatement in ``thor_oracle.c`` (gcc, OpenMP).
+* ``_ref/libthor_ref_cast.so``   — the REFERENCE's own CPU cast path, compiled from the reference
+  checkout where it lies (only when that checkout is present; the output is git-ignored and is
+  carried to the GPU machine as a built file).  Nothing is copied out of the reference tree.
+
+Run as ``python oracle/build.py``.  The reference checkout is looked up in
+``$THOR_REFERENCE_DIR`` (default: ``/root/reference``).
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import site
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+BUILD = HERE / "_build"
+REF_OUT = HERE / "_ref"
+REFERENCE_DIR = Path(os.environ.get("THOR_REFERENCE_DIR", "/root/reference"))
+CUDA_INCLUDE = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+
+
+def _run(cmd: list[str]) -> None:
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(map(str, cmd)), proc.stdout, proc.stderr))
+
+
+def _stale(out: Path, deps: list[Path]) -> bool:
+    return not out.exists() or out.stat().st_mtime < max(p.stat().st_mtime for p in deps)
+
+
+def build_oracle(force: bool = False) -> Path:
+    BUILD.mkdir(exist_ok=True)
+    out = BUILD / "libthor_oracle.so"
+    srcs = sorted(HERE.glob("*.c"))
+    if force or _stale(out, srcs):
+        _run(["gcc", "-O3", "-fopenmp", "-fPIC", "-shared", "-fvisibility=hidden", "-ffp-contract=off",
+              *map(str, srcs), "-o", str(out), "-lm"])
+    return out
+
+
+def _site_include_dirs() -> list[Path]:
+    dirs = []
+    for sp in site.getsitepackages() + [sysconfig.get_paths()["purelib"]]:
+        base = Path(sp)
+        for rel in ("include/cudnn_frontend/thirdparty", "include", "nvidia/cudnn/include", "nvidia/cublas/include"):
+            if (base / rel).is_dir():
+                dirs.append(base / rel)
+    return dirs
+
+
+def build_reference_cast(force: bool = False) -> Path | None:
+    """Compile the reference's CPU TypeConverter into _ref/; returns None when it cannot be built here."""
+    out = REF_OUT / "libthor_ref_cast.so"
+    src = HERE / "ref_cast.cpp"
+    ref_src = REFERENCE_DIR / "Utilities/TensorOperations/DataTypeConversions/TypeConverter.cpp"
+    if not ref_src.exists():
+        return out if out.exists() else None
+    REF_OUT.mkdir(exist_ok=True)
+    if not force and not _stale(out, [src, ref_src]):
+        return out
+    verdir = REF_OUT / "generated"
+    verdir.mkdir(exist_ok=True)
+    # ThorVersion.h is produced by the reference's cmake from ThorVersion.h.in; give it the same two macros.
+    (verdir / "ThorVersion.h").write_text('#pragma once\n#define THOR_VERSION "0.0.33"\n#define THOR_GIT_VERSION "unknown"\n')
+    cmd = ["g++", "-std=c++23", "-O2", "-fopenmp", "-fPIC", "-shared", "-fvisibility=hidden", "-ffunction-sections", "-fdata-sections",
+           "-Wl,--gc-sections", "-Wl,-z,defs", "-I", str(REFERENCE_DIR), "-I", str(verdir), "-I", str(CUDA_INCLUDE)]
+    for d in _site_include_dirs():
+        cmd += ["-I", str(d)]
+    cmd += [str(src), "-o", str(out)]
+    _run(cmd)
+    return out
+
+
+def build_all(force: bool = False) -> dict:
+    result = {"oracle": str(build_oracle(force))}
+    try:
+        ref = build_reference_cast(force)
+        result["reference_cast"] = str(ref) if ref else None
+    except RuntimeError as exc:  # the reference needs headers this machine lacks
+        result["reference_cast"] = None
+        result["reference_cast_error"] = str(exc)[-2000:]
+    return result
+
+
+if __name__ == "__main__":
+    print(build_all(force="--force" in sys.argv))

@@ -1,0 +1,118 @@
+"""GPU parity of the cast seam (thor_b200_cast_launch) against the CPU oracle, bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from thor_b200 import DataType, TypeConverter
+from thor_b200._native import ThorB200InvalidArgument
+from thor_b200.workloads import cast_input
+
+pytestmark = pytest.mark.gpu
+
+_TORCH_STORAGE = {o.BF16: torch.uint16, o.FP8_E4M3: torch.uint8, o.FP8_E5M2: torch.uint8}
+
+
+def _to_dev(a: np.ndarray) -> torch.Tensor:
+    if a.dtype == np.bool_:
+        return torch.from_numpy(a.view(np.uint8).copy()).cuda()
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _gpu_cast(src: np.ndarray, sdt: int, ddt: int) -> np.ndarray:
+    d_src = _to_dev(src)
+    n = src.size
+    d_dst = torch.empty(n * np.dtype(o.STORAGE[ddt]).itemsize, dtype=torch.uint8, device="cuda")
+    guard = torch.full((64,), 0xAB, dtype=torch.uint8, device="cuda")
+    buf = torch.cat([d_dst, guard])  # guard bytes right behind the output: must stay untouched
+    out = buf[: d_dst.numel()]
+    TypeConverter.convert_type_raw(d_src.data_ptr(), out.data_ptr(), DataType(sdt), DataType(ddt), n)
+    torch.cuda.synchronize()
+    assert bool((buf[d_dst.numel():] == 0xAB).all()), "cast wrote past n elements"
+    return out.cpu().numpy().view(o.STORAGE[ddt] if ddt != o.BOOLEAN else np.uint8)
+
+
+def _assert_same(got, want, ddt):
+    got = np.ascontiguousarray(got).view(np.uint8)
+    want = np.ascontiguousarray(want).view(np.uint8)
+    if ddt in (o.FP8_E4M3, o.FP8_E5M2):
+        keep = ~np.isnan(o.to_float64(want, ddt))
+        got, want = got[keep], want[keep]
+    bad = np.flatnonzero(got != want)
+    assert bad.size == 0, f"{bad.size} byte mismatches, first at byte {bad[:5]}"
+
+
+def test_configuration_1_bit_exact():
+    """fp32 -> fp16, n = 2^24, U(-4,4) with +-0 / subnormal / tie / overflow edge values at 0.1 %."""
+    x = cast_input(1 << 24, seed=0)
+    got = _gpu_cast(x, o.FP32, o.FP16)
+    want = o.cast(x, o.FP32, o.FP16)
+    _assert_same(got, want, o.FP16)
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 255, 2049, 65537, (1 << 20) + 3])
+def test_ragged_sizes_and_no_overrun(n):
+    x = cast_input(n, seed=n, edge_density=0.05)
+    _assert_same(_gpu_cast(x, o.FP32, o.FP16), o.cast(x, o.FP32, o.FP16), o.FP16)
+    _assert_same(_gpu_cast(x, o.FP32, o.BF16), o.cast(x, o.FP32, o.BF16), o.BF16)
+
+
+def test_nan_inputs_map_to_canonical_nan():
+    x = np.array([np.nan, -np.nan, 1.0, np.inf] * 5, np.float32)
+    assert [int(v) for v in _gpu_cast(x, o.FP32, o.FP16).view(np.uint16)[:4]] == [0x7FFF, 0x7FFF, 0x3C00, 0x7C00]
+
+
+@pytest.mark.parametrize("src", o.ALL_DTYPES, ids=lambda d: o.NAMES[d])
+def test_all_pairs_on_representable_values(src):
+    """Mirrors the reference's all-pairs test (TypeConverterTest.cpp:10-765): values representable in every dtype."""
+    rng = np.random.default_rng(src)
+    grid = rng.integers(0, 9, 4099).astype(np.float32)
+    s = o.cast(grid, o.FP32, src) if src != o.FP32 else grid
+    for dst in o.ALL_DTYPES:
+        if dst == src:
+            continue
+        _assert_same(_gpu_cast(s, src, dst), o.cast(s, src, dst), dst)
+
+
+@pytest.mark.parametrize("src,dst", [(o.FP32, o.FP8_E4M3), (o.FP32, o.FP8_E5M2), (o.FP64, o.FP16), (o.FP64, o.BF16), (o.FP16, o.BF16),
+                                     (o.BF16, o.FP16), (o.FP16, o.FP8_E4M3), (o.BF16, o.FP8_E5M2), (o.FP64, o.FP32), (o.FP16, o.FP32),
+                                     (o.FP8_E4M3, o.FP16), (o.FP8_E5M2, o.BF16), (o.INT32, o.FP16), (o.INT64, o.FP32), (o.INT64, o.BF16)])
+def test_float_family_rounding(src, dst):
+    rng = np.random.default_rng(7)
+    base = (rng.standard_normal(1 << 16) * 2.0 ** rng.integers(-20, 18, 1 << 16)).astype(np.float64)
+    if src in (o.INT32, o.INT64):
+        s = (base * 1000).astype(np.int64).astype(o.STORAGE[src])
+    else:
+        s = o.cast(base, o.FP64, src) if src != o.FP64 else base
+    _assert_same(_gpu_cast(s, src, dst), o.cast(s, src, dst), dst)
+
+
+def test_float_to_int_truncates_toward_zero():
+    x = np.array([-2.75, -1.5, -0.25, 0.25, 1.5, 2.75, 100.9, -100.9] * 33, np.float32)
+    for dst in (o.INT8, o.INT16, o.INT32, o.INT64):
+        _assert_same(_gpu_cast(x, o.FP32, dst), o.cast(x, o.FP32, dst), dst)
+
+
+def test_same_dtype_and_overlap_are_rejected():
+    a = torch.zeros(64, dtype=torch.float32, device="cuda")
+    with pytest.raises(ThorB200InvalidArgument):
+        TypeConverter.convert_type_raw(a.data_ptr(), a.data_ptr() + 256, DataType.fp32, DataType.fp32, 8)
+    with pytest.raises(ThorB200InvalidArgument, match="overlap"):
+        TypeConverter.convert_type_raw(a.data_ptr(), a.data_ptr() + 8, DataType.fp32, DataType.fp16, 16)
+
+
+def test_in_place_same_size():
+    x = np.arange(-500, 524, dtype=np.int32)
+    d = torch.from_numpy(x.copy()).cuda()
+    TypeConverter.convert_type_raw(d.data_ptr(), d.data_ptr(), DataType.int32, DataType.fp32, x.size)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.cpu().numpy().view(np.float32), x.astype(np.float32))
+
+
+def test_unaligned_views_use_the_scalar_path():
+    x = cast_input(5000, seed=11)
+    d = torch.from_numpy(x).cuda()
+    out = torch.empty(5001, dtype=torch.float16, device="cuda")
+    TypeConverter.convert_type_raw(d.data_ptr() + 4, out.data_ptr() + 2, DataType.fp32, DataType.fp16, 4999)
+    torch.cuda.synchronize()
+    assert np.array_equal(out[1:].cpu().numpy().view(np.uint16), o.cast(x[1:], o.FP32, o.FP16).view(np.uint16))
