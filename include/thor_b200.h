@@ -80,6 +80,185 @@ THOR_B200_API uint64_t thor_b200_launch_count(void);
  * ------------------------------------------------------------------------------------------- */
 THOR_B200_API int thor_b200_cast_launch(const void* src, void* dst, int src_dtype, int dst_dtype, int64_t n, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * S3  fused elementwise / broadcast expression stage
+ * Replaces EquationCompiler::compileFusedStage / compileSpecializedBroadcastStage
+ * (Utilities/Expression/EquationCompiler.h:36-75; emitter CudaSourceEmitter.cpp:6749-6859 and
+ * :7794-7944) and EquationRunner::run (Utilities/Expression/EquationRunner.h:14-18,
+ * EquationRunner.cpp:34-290).
+ *
+ * A stage is a topologically ordered SSA node list, as in ThorImplementation::PhysicalExpression
+ * (Expression.h:231-371): node k may only name parents < k.  `op` carries the integer value of
+ * ThorImplementation::ExprOp (Expression.h:32-148); the subset a fused stage may contain is
+ * listed in thor_b200_expr_op.  Every node arrives with its dtypes already resolved by the
+ * caller (ExpressionDTypeResolution.cpp:1012-1148): the node computes in compute_dtype and
+ * materialises its value in output_dtype; parents are converted to the consumer's compute dtype.
+ * ------------------------------------------------------------------------------------------- */
+typedef enum thor_b200_expr_op {
+    THOR_B200_OP_INPUT = 3, THOR_B200_OP_RUNTIME_SCALAR = 4, THOR_B200_OP_TENSOR_RUNTIME_SCALAR = 5, THOR_B200_OP_SCALAR_FP = 6,
+    THOR_B200_OP_ADD = 7, THOR_B200_OP_SUB = 8, THOR_B200_OP_MUL = 9, THOR_B200_OP_DIV = 10, THOR_B200_OP_POW = 11,
+    THOR_B200_OP_EQUAL = 12, THOR_B200_OP_NOT_EQUAL = 13, THOR_B200_OP_LESS = 14, THOR_B200_OP_LESS_EQUAL = 15,
+    THOR_B200_OP_GREATER = 16, THOR_B200_OP_GREATER_EQUAL = 17, THOR_B200_OP_LOGICAL_AND = 18, THOR_B200_OP_LOGICAL_OR = 19,
+    THOR_B200_OP_LOGICAL_NOT = 20, THOR_B200_OP_CAST = 21, THOR_B200_OP_WHERE = 22, THOR_B200_OP_NEG = 23, THOR_B200_OP_ABS = 24,
+    THOR_B200_OP_CEIL = 25, THOR_B200_OP_FLOOR = 26, THOR_B200_OP_ROUND = 27, THOR_B200_OP_TRUNC = 28, THOR_B200_OP_SIN = 29,
+    THOR_B200_OP_COS = 30, THOR_B200_OP_TAN = 31, THOR_B200_OP_ASIN = 32, THOR_B200_OP_ACOS = 33, THOR_B200_OP_ATAN = 34,
+    THOR_B200_OP_SINH = 35, THOR_B200_OP_COSH = 36, THOR_B200_OP_ASINH = 37, THOR_B200_OP_ACOSH = 38, THOR_B200_OP_ATANH = 39,
+    THOR_B200_OP_ERF = 40, THOR_B200_OP_ERFC = 41, THOR_B200_OP_ERFCX = 42, THOR_B200_OP_ERFINV = 43, THOR_B200_OP_ERFCINV = 44,
+    THOR_B200_OP_TGAMMA = 45, THOR_B200_OP_LGAMMA = 46, THOR_B200_OP_DIGAMMA = 47, THOR_B200_OP_EXP = 48, THOR_B200_OP_EXPM1 = 49,
+    THOR_B200_OP_EXP2 = 50, THOR_B200_OP_EXP10 = 51, THOR_B200_OP_LN = 52, THOR_B200_OP_LOG1P = 53, THOR_B200_OP_LOG2 = 54,
+    THOR_B200_OP_LOG10 = 55, THOR_B200_OP_SQRT = 56, THOR_B200_OP_TANH = 57, THOR_B200_OP_NORMCDF = 58,
+    THOR_B200_OP_MIN = 69, THOR_B200_OP_MAX = 70, THOR_B200_OP_MIN_GRAD_LEFT = 71, THOR_B200_OP_MIN_GRAD_RIGHT = 72,
+    THOR_B200_OP_MAX_GRAD_LEFT = 73, THOR_B200_OP_MAX_GRAD_RIGHT = 74,
+    /* stage-boundary ops: never inside a fused stage, listed for the host layer and the reduction seam */
+    THOR_B200_OP_REDUCE_SUM = 83, THOR_B200_OP_REDUCE_PROD = 84, THOR_B200_OP_REDUCE_MIN = 85, THOR_B200_OP_REDUCE_MAX = 86,
+    THOR_B200_OP_REDUCE_ARGMIN = 87, THOR_B200_OP_REDUCE_ARGMAX = 88, THOR_B200_OP_REDUCE_AVG = 95, THOR_B200_OP_REDUCE_NORM1 = 96,
+    THOR_B200_OP_REDUCE_NORM2 = 97
+} thor_b200_expr_op;
+
+#define THOR_B200_NO_NODE 0xFFFFFFFFu
+#define THOR_B200_MAX_RANK 8
+
+typedef struct thor_b200_expr_node {
+    uint16_t op;            /* thor_b200_expr_op */
+    uint16_t output_dtype;  /* thor_b200_dtype the node's value is stored in */
+    uint16_t compute_dtype; /* thor_b200_dtype the node computes in */
+    uint16_t input_dtype;   /* INPUT / *_RUNTIME_SCALAR nodes: dtype of the bound value; 0 otherwise */
+    uint32_t lhs, rhs, aux; /* parent node indices, THOR_B200_NO_NODE when unused (WHERE: lhs=cond, rhs=true, aux=false) */
+    uint32_t input_slot;    /* INPUT / *_RUNTIME_SCALAR nodes: index into the stage's input list */
+    double scalar_fp;       /* SCALAR_FP nodes: the literal */
+} thor_b200_expr_node;
+
+typedef enum thor_b200_input_kind {
+    THOR_B200_INPUT_TENSOR = 0,               /* device pointer to a tensor of the stage's shape (or a broadcast view of it) */
+    THOR_B200_INPUT_RUNTIME_SCALAR_FP32 = 1,  /* float passed by value at launch (Expression::runtimeScalar) */
+    THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR = 2 /* device pointer to one element (Expression::tensorRuntimeScalar) */
+} thor_b200_input_kind;
+
+typedef struct thor_b200_expr_input {
+    int32_t kind;  /* thor_b200_input_kind */
+    int32_t dtype; /* thor_b200_dtype of the bound value */
+} thor_b200_expr_input;
+
+typedef struct thor_b200_expr_output {
+    uint32_t node;  /* node whose value is written */
+    int32_t dtype;  /* must equal that node's output_dtype */
+} thor_b200_expr_output;
+
+/* Broadcast geometry of a stage, the information the reference bakes into specialised broadcast
+ * kernels (SpecializedBroadcastGroup, FusedEquation.cpp:5802-6020).  Outputs are dense row-major
+ * tensors of shape dims[0..rank).  input_strides[slot][d] is the element stride of tensor input
+ * `slot` along output axis d, 0 where that input is broadcast (ignored for scalar inputs). */
+typedef struct thor_b200_expr_broadcast {
+    uint32_t rank;
+    uint64_t dims[THOR_B200_MAX_RANK];
+    const int64_t* input_strides; /* [n_inputs][THOR_B200_MAX_RANK], row-major */
+} thor_b200_expr_broadcast;
+
+typedef struct thor_b200_expr_options {
+    int32_t use_fast_math; /* NVRTC --use_fast_math, off by default like FusedEquation::compile (FusedEquation.cpp:7014-7016) */
+    int32_t compile_only;  /* 1: emit + compile to a cubin but do not load it (usable without a GPU or driver) */
+    int32_t reserved[6];   /* must be zero */
+} thor_b200_expr_options;
+
+typedef struct thor_b200_expr thor_b200_expr;
+
+/* Emits CUDA C++ for the stage, compiles it with NVRTC for sm_100a and (unless compile_only) loads
+ * it on the current device.  broadcast == NULL compiles a flat stage: every tensor input and
+ * output has the same number of elements, given at launch.  Identical stages share one compiled
+ * module (process-wide cache keyed by the emitted source), like the reference's LRU caches
+ * (EquationCompiler.cpp:123-157).  Thread-safe.  The handle is immutable and may be launched
+ * from any thread on any stream of the device it was compiled on. */
+THOR_B200_API int thor_b200_expr_compile(const thor_b200_expr_node* nodes, uint32_t n_nodes, const thor_b200_expr_input* inputs,
+                                         uint32_t n_inputs, const thor_b200_expr_output* outputs, uint32_t n_outputs,
+                                         const thor_b200_expr_broadcast* broadcast, const thor_b200_expr_options* options,
+                                         thor_b200_expr** out_expr);
+/* Launches the stage.  input_ptrs[slot] is the device pointer for tensor and tensor-runtime-scalar
+ * inputs (ignored for fp32 runtime scalars, whose values are read from runtime_scalars[slot]).
+ * numel is the element count of a flat stage (ignored for broadcast stages, whose shape is baked
+ * in).  Performs no allocation and no compilation except the first use of the unaligned-pointer
+ * variant of a stage.  An output may alias an input only if it is that input's whole tensor. */
+THOR_B200_API int thor_b200_expr_launch(thor_b200_expr* expr, const void* const* input_ptrs, const float* runtime_scalars,
+                                        void* const* output_ptrs, uint64_t numel, void* stream);
+/* The CUDA C++ source emitted for the stage (owned by the handle). */
+THOR_B200_API const char* thor_b200_expr_source(const thor_b200_expr* expr);
+/* "flat_v2", "flat_scalar", "bcast_tiled_v2", "bcast_tiled_scalar" or "bcast_generic": which kernel shape was chosen. */
+THOR_B200_API const char* thor_b200_expr_launch_kind(const thor_b200_expr* expr);
+THOR_B200_API void thor_b200_expr_destroy(thor_b200_expr* expr);
+
+/* ---------------------------------------------------------------------------------------------
+ * Device memory for stamped plans.  Replaces the allocation half of ThorImplementation::Tensor
+ * (DeepLearning/Implementation/Tensor/Tensor.cpp:232-281) for the intermediates and outputs that
+ * FusedEquation::stamp / CubReduction::stamp create; run-time entry points never allocate.
+ * ------------------------------------------------------------------------------------------- */
+THOR_B200_API int thor_b200_device_alloc(size_t bytes, void** out_ptr);
+THOR_B200_API int thor_b200_device_free(void* ptr);
+
+/* ---------------------------------------------------------------------------------------------
+ * S2  dense value reductions and arg reductions
+ * Replaces CubReductionInternal::query*ReductionBytes / launch*Reduction and the ArgMin/ArgMax
+ * variants (Utilities/TensorOperations/Cub/CubReductionInternal.h:9-176; dispatch
+ * CubReductionOperation.cuh:2966-3054, CubArgReductionOperation.cuh:1119-1178), i.e. what
+ * CubReduction::stampValidated (CubReduction.cpp:935-968) and StampedCub{,Arg}Reduction::runOn
+ * (CubReduction.cpp:1405,1441) call.
+ *
+ * The input is a dense tensor viewed as [outer, reduction, inner]: the geometry that
+ * CubReduction::analyzeGeometry (CubReduction.cpp:755-912) produces for the DeviceTransformReduce
+ * (outer = inner = 1), ContiguousFixedSegment (inner = 1) and TiledFixedSegment paths.  Every
+ * input element is converted to fp32, transformed (identity / |x| / x^2), combined in fp32
+ * (NaN-propagating min / max), finalised in fp32 (mean divides by the count, L2 takes the square
+ * root), multiplied by output_scale and converted once to the output dtype
+ * (CubReductionOperation.cuh:60-129,186-198).  Results are deterministic: a given plan combines
+ * partial results in a fixed order.
+ * ------------------------------------------------------------------------------------------- */
+typedef enum thor_b200_reduce_op { /* = ThorImplementation::CubReductionOp (CubReduction.h:17-25) */
+    THOR_B200_REDUCE_SUM = 0, THOR_B200_REDUCE_MIN = 1, THOR_B200_REDUCE_MAX = 2, THOR_B200_REDUCE_PRODUCT = 3,
+    THOR_B200_REDUCE_MEAN = 4, THOR_B200_REDUCE_L1NORM = 5, THOR_B200_REDUCE_L2NORM = 6
+} thor_b200_reduce_op;
+
+typedef struct thor_b200_reduce_desc {
+    int32_t op;           /* thor_b200_reduce_op */
+    int32_t input_dtype;  /* fp8 / fp16 / bf16 / fp32 */
+    int32_t output_dtype; /* fp8 / fp16 / bf16 / fp32 */
+    uint32_t flags;       /* must be zero */
+    uint64_t outer, reduction, inner;
+    /* Element strides of output[o, i]; both zero selects the natural dense [outer, inner] layout.
+     * (outer_stride = 1, inner_stride = outer) writes the permuted [inner, outer] layout of
+     * CubReductionGeometry::tiled_output_permuted (CubReduction.h:139-147). */
+    uint64_t out_stride_outer, out_stride_inner;
+} thor_b200_reduce_desc;
+
+typedef struct thor_b200_reduce_plan thor_b200_reduce_plan;
+
+/* Plans the reduction (kernel choice, split of the reduction axis, workspace size).  May be
+ * called without a GPU.  workspace_bytes is always >= 1, like the reference's convention
+ * (CubReductionOperation.cuh:2941-2945). */
+THOR_B200_API int thor_b200_reduce_plan_create(const thor_b200_reduce_desc* desc, thor_b200_reduce_plan** out_plan, size_t* workspace_bytes);
+/* Runs the planned reduction; no allocation, no planning.  `workspace` must hold workspace_bytes
+ * bytes, be 16-byte aligned and must not be shared by launches that overlap in time. */
+THOR_B200_API int thor_b200_reduce_launch(const thor_b200_reduce_plan* plan, const void* input, void* output, void* workspace,
+                                          size_t workspace_bytes, float output_scale, void* stream);
+/* "full", "rows_warp", "rows_cta", "rows_split", "cols" ...: the kernel family the plan selected. */
+THOR_B200_API const char* thor_b200_reduce_plan_kind(const thor_b200_reduce_plan* plan);
+THOR_B200_API void thor_b200_reduce_plan_destroy(thor_b200_reduce_plan* plan);
+
+typedef struct thor_b200_argreduce_desc {
+    int32_t op;          /* 0 = argmin, 1 = argmax (CubArgReductionOp, CubReduction.h:27-30) */
+    int32_t input_dtype; /* fp8 / fp16 / bf16 / fp32 */
+    int32_t value_dtype; /* dtype of the optional value output, 0 if none is produced */
+    int32_t index_dtype; /* THOR_B200_UINT32 or THOR_B200_UINT64 */
+    uint64_t outer, reduction, inner;
+} thor_b200_argreduce_desc;
+
+typedef struct thor_b200_argreduce_plan thor_b200_argreduce_plan;
+
+/* Arg reductions: values are compared in fp32; NaN beats every number; among equal candidates
+ * (NaNs included) the lowest index wins; the index is the position inside the reduction domain
+ * (CubArgReductionOperation.cuh:31-73,127-151; CubReduction.h:405-411). */
+THOR_B200_API int thor_b200_argreduce_plan_create(const thor_b200_argreduce_desc* desc, thor_b200_argreduce_plan** out_plan, size_t* workspace_bytes);
+THOR_B200_API int thor_b200_argreduce_launch(const thor_b200_argreduce_plan* plan, const void* input, void* value_output, void* index_output,
+                                             void* workspace, size_t workspace_bytes, void* stream);
+THOR_B200_API void thor_b200_argreduce_plan_destroy(thor_b200_argreduce_plan* plan);
+
 #ifdef __cplusplus
 }
 #endif

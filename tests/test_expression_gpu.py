@@ -1,0 +1,178 @@
+"""GPU parity of fused elementwise / broadcast expression stages against the eager oracle.
+
+Tolerances (stated per test): fp32 elementwise <= 2 ulp; fp16 / bf16 outputs <= 1 output ulp for
+correctly-rounded ops, and a small documented slack where the reference itself uses approximate
+pair intrinsics (h2exp, __h2div) whose results are not correctly rounded."""
+import numpy as np
+import pytest
+
+import oracle as o
+from _exprutil import assert_ulp, make_inputs, run_both
+
+pytestmark = pytest.mark.gpu
+
+FLOATS = [o.FP32, o.FP16, o.BF16]
+
+
+@pytest.mark.parametrize("dtype", FLOATS, ids=lambda d: o.NAMES[d])
+def test_add_sub_mul_div(dtype):
+    """((x + y) - 2) * (x / (y + 1)) -- the reference's test_add_sub_mul_div_numerical."""
+    ins = make_inputs({"x": ((4099,), dtype, 1, 6), "y": ((4099,), dtype, 2, 7)}, seed=1)
+    plan, res = run_both(lambda ns: ((ns.input("x") + ns.input("y")) - 2.0) * (ns.input("x") / (ns.input("y") + 1.0)), ins)
+    got, want = res["output"]
+    # fp32: <= 2 ulp.  16-bit: __h2div is not correctly rounded (<= 1 ulp off) and the product can double that.
+    assert_ulp(got, want, 2.0, frac_within_1=0.97)
+    assert plan.stage_kind_names() == ["FusedKernel"]
+    assert plan.physical_stage_names()[0] == ("flat_scalar" if dtype == o.FP32 else "flat_v2")
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 1000, 2048 * 3 + 5])
+def test_flat_ragged_sizes(n):
+    ins = make_inputs({"x": ((n,), o.FP16, -3, 3), "y": ((n,), o.FP16, -3, 3)}, seed=n)
+    _, res = run_both(lambda ns: ns.input("x") * ns.input("y") + ns.input("x"), ins)
+    got, want = res["output"]
+    # mul + add may contract to one fma on the GPU (the reference compiles with -fmad=true): up to 1 ulp of the sum
+    assert_ulp(got, want, 1.0, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", FLOATS, ids=lambda d: o.NAMES[d])
+def test_unary_functions(dtype):
+    ins = make_inputs({"x": ((3001,), dtype, 0.1, 3.0)}, seed=2)
+    fns = {
+        "exp": lambda x: x.exp(), "ln": lambda x: x.ln(), "sqrt": lambda x: x.sqrt(), "tanh": lambda x: x.tanh(), "abs": lambda x: (-x).abs(),
+        "sin": lambda x: x.sin(), "cos": lambda x: x.cos(), "erf": lambda x: x.erf(), "log1p": lambda x: x.log1p(), "expm1": lambda x: x.expm1(),
+        "floor": lambda x: (x * 3.0).floor(), "ceil": lambda x: (x * 3.0).ceil(), "round": lambda x: (x * 3.0).round(), "normcdf": lambda x: x.normcdf(),
+        "log2": lambda x: x.log2(), "exp2": lambda x: x.exp2(), "atan": lambda x: x.atan(), "sinh": lambda x: x.sinh(), "lgamma": lambda x: x.lgamma(),
+        "digamma": lambda x: x.digamma(),
+    }
+    for name, f in fns.items():
+        _, res = run_both(lambda ns, f=f: f(ns.input("x")), ins)
+        got, want = res["output"]
+        # libdevice fp32 functions are within 1-4 ulp; pair intrinsics on 16-bit types within 1-2 ulp of the 16-bit result
+        try:
+            assert_ulp(got, want, 6.0 if dtype == o.FP32 else 2.0, atol=1e-6)
+        except AssertionError as e:
+            raise AssertionError(f"{name}: {e}")
+
+
+@pytest.mark.parametrize("dtype", FLOATS, ids=lambda d: o.NAMES[d])
+def test_stable_activations(dtype):
+    """sigmoid / softplus / gelu / swish at large |x| (the reference's test_expression_stable_activations)."""
+    vals = np.array([-80, -30, -10, -3, -1, -0.5, 0, 0.5, 1, 3, 10, 30, 80] * 17, np.float32)
+    ins = {"x": (o.from_float32(vals, dtype), dtype)}
+    for name, f in {"sigmoid": lambda x: x.sigmoid(), "softplus": lambda x: x.softplus(), "gelu": lambda x: x.gelu(), "swish": lambda x: x.swish(),
+                    "elu": lambda x: x.elu(1.5), "selu": lambda x: x.selu(), "relu6": lambda x: x.relu6(), "hard_tanh": lambda x: x.hard_tanh(-2.0, 2.0)}.items():
+        _, res = run_both(lambda ns, f=f: f(ns.input("x")), ins)
+        got, want = res["output"]
+        assert np.isfinite(got).all(), name
+        try:
+            assert_ulp(got, want, 4.0 if dtype == o.FP32 else 3.0, atol=1e-7 if dtype == o.FP32 else 6e-8)
+        except AssertionError as e:
+            raise AssertionError(f"{name}: {e}")
+
+
+def test_mixed_dtype_promotion_and_cast():
+    """fp16 * bf16 promotes to fp32; cast is an explicit boundary (ExpressionDTypeResolution.cpp:277-307, 939-941)."""
+    ins = make_inputs({"h": ((1024,), o.FP16, -2, 2), "b": ((1024,), o.BF16, -2, 2), "f": ((1024,), o.FP32, -2, 2)}, seed=3)
+    _, res = run_both(lambda ns: {"p": ns.input("h") * ns.input("b"), "q": ns.cast(ns.input("h") + ns.input("f"), o.BF16),
+                                  "r": ns.input("b") * 0.3 + ns.input("b")}, ins)
+    assert res["p"][1].dtype == o.FP32 and res["q"][1].dtype == o.BF16 and res["r"][1].dtype == o.BF16
+    assert_ulp(*res["p"], 1.0)
+    assert_ulp(*res["q"], 1.0)
+    assert_ulp(*res["r"], 1.0, atol=1e-2)
+
+
+def test_comparison_where_and_logical():
+    ins = make_inputs({"x": ((2050,), o.FP32, -2, 2), "y": ((2050,), o.FP32, -2, 2)}, seed=4)
+
+    def f(ns):
+        x, y = ns.input("x"), ns.input("y")
+        return {"w": ns.where((x > y).logical_and(x > 0.0), x * 2.0, y - 1.0), "m": x.min(y), "t": ns.where(x > 0.25, x, 0.0)}
+
+    _, res = run_both(f, ins)
+    for k in ("w", "m", "t"):
+        assert_ulp(*res[k], 1.0)
+
+
+def test_runtime_scalar_can_change_between_runs():
+    import torch
+
+    from thor_b200.expression import Expression as ex
+
+    x = torch.arange(16, dtype=torch.float32, device="cuda")
+    eq = ex.compile(ex.input("x") * ex.runtime_scalar("s") + 1.0)
+    plan = eq.stamp({"x": x, "s": 2.0})
+    plan.run()
+    torch.cuda.synchronize()
+    assert torch.equal(plan.output(), x * 2 + 1)
+    plan.set_runtime_scalar("s", -3.0)
+    plan.run()
+    torch.cuda.synchronize()
+    assert torch.equal(plan.output(), x * -3 + 1)
+
+
+# ---- broadcast ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", FLOATS, ids=lambda d: o.NAMES[d])
+@pytest.mark.parametrize("shape", [(64, 256), (33, 40), (5, 7), (3, 16, 128)])
+def test_row_and_column_broadcast(dtype, shape):
+    cols = shape[-1]
+    ins = make_inputs({"x": (shape, dtype, -2, 2), "c": ((cols,), dtype, 0.5, 1.5), "r": (shape[:-1] + (1,), dtype, -1, 1)}, seed=5)
+    plan, res = run_both(lambda ns: (ns.input("x") * ns.input("c") - ns.input("r")).max(0.0), ins)
+    assert_ulp(*res["output"], 1.0, atol=4e-3 if dtype != o.FP32 else 1e-6)
+    kind = plan.physical_stage_names()[0]
+    vec = 4 if dtype == o.FP32 else 8
+    assert kind.startswith("bcast_tiled" if cols % vec == 0 else "bcast_generic"), kind
+
+
+def test_middle_axis_broadcast_uses_row_offsets():
+    ins = make_inputs({"x": ((6, 5, 64), o.FP32, -2, 2), "m": ((6, 1, 64), o.FP32, -2, 2), "s": ((1, 5, 1), o.FP32, 1, 2)}, seed=6)
+    plan, res = run_both(lambda ns: (ns.input("x") - ns.input("m")) / ns.input("s"), ins)
+    assert_ulp(*res["output"], 2.0)
+    assert plan.physical_stage_names()[0] == "bcast_tiled_scalar"
+
+
+def test_configuration_2_small():
+    """y = relu(a*x + b) * sigmoid(z), fp16, a per column, b an fp32 runtime scalar (small rows x 8192 cols)."""
+    ins = make_inputs({"x": ((64, 8192), o.FP16, -3, 3), "z": ((64, 8192), o.FP16, -3, 3), "a": ((8192,), o.FP16, 0.5, 1.5)}, seed=0)
+    plan, res = run_both(lambda ns: ((ns.input("a") * ns.input("x") + ns.runtime_scalar("b")).max(0.0)) * ns.input("z").sigmoid(), ins, {"b": 0.1})
+    got, want = res["output"]
+    # a*x+b may be one fma on the GPU (result within 1 ulp of a*x+b at the magnitude of the sum, i.e. an
+    # absolute slack near cancellation); h2exp / __h2div add up to ~2 ulp on the sigmoid factor
+    assert_ulp(got, want, 3.0, frac_within_1=0.95, atol=2e-3)
+    assert plan.physical_stage_names() == ["bcast_tiled_v2"]
+    assert "__hmax2" in plan.stage_sources()[0] and "h2exp" in plan.stage_sources()[0]
+
+
+def test_multiple_outputs_share_one_stage():
+    ins = make_inputs({"x": ((1000,), o.FP32, -2, 2)}, seed=7)
+    plan, res = run_both(lambda ns: {"a": ns.input("x").exp(), "b": ns.input("x") * ns.input("x")}, ins)
+    assert plan.stage_kind_names() == ["FusedKernel"]
+    assert_ulp(*res["a"], 2.0)
+    assert_ulp(*res["b"], 0.0)
+
+
+def test_unaligned_pointers_fall_back_to_the_generic_kernel():
+    import torch
+
+    from thor_b200.expression import Expression as ex
+
+    base = torch.randn(4097, device="cuda", dtype=torch.float32)
+    x = base[1:]  # 4-byte aligned only
+    out = torch.empty(4096, device="cuda", dtype=torch.float32)
+    eq = ex.compile(ex.input("x") * 2.0 + 1.0)
+    eq.run({"x": x.contiguous() if False else x}, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, x * 2.0 + 1.0)
+
+
+def test_run_rejects_multi_stage_expressions():
+    import torch
+
+    from thor_b200._native import ThorB200InvalidArgument
+    from thor_b200.expression import Expression as ex
+
+    x = torch.randn(8, 16, device="cuda")
+    eq = ex.compile(ex.input("x") - ex.input("x").reduce_max([1]))
+    with pytest.raises(ThorB200InvalidArgument):
+        eq.run({"x": x}, torch.empty_like(x))

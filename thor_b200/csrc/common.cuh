@@ -95,9 +95,20 @@ struct alignas(BYTES >= 16 ? 16 : BYTES) Pack {
     unsigned char b[BYTES];
 };
 
-template <int BYTES>
+// 256-bit global load (sm_100 LDG.256); the address must be 32-byte aligned.
+__device__ __forceinline__ void load256(uint4& lo, uint4& hi, const void* p) {
+    asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
+}
+
+template <int BYTES, bool WIDE = false>
 __device__ __forceinline__ void loadPack(Pack<BYTES>& dst, const void* src) {
-    if constexpr (BYTES >= 16) {
+    if constexpr (WIDE && (BYTES % 32) == 0) {
+#pragma unroll
+        for (int i = 0; i < BYTES / 32; ++i)
+            load256(reinterpret_cast<uint4*>(&dst)[2 * i], reinterpret_cast<uint4*>(&dst)[2 * i + 1], reinterpret_cast<const char*>(src) + 32 * i);
+    } else if constexpr (BYTES >= 16) {
 #pragma unroll
         for (int i = 0; i < BYTES / 16; ++i)
             reinterpret_cast<uint4*>(&dst)[i] = __ldcs(reinterpret_cast<const uint4*>(src) + i);

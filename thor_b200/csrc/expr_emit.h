@@ -1,0 +1,49 @@
+// Fused-stage emitter: turns a validated SSA node list (+ optional broadcast geometry) into the
+// CUDA C++ source of one single-pass kernel and the launch geometry that goes with it.
+#pragma once
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "thor_b200.h"
+
+namespace tb::expr {
+
+struct Stage {
+    std::vector<thor_b200_expr_node> nodes;
+    std::vector<thor_b200_expr_input> inputs;
+    std::vector<thor_b200_expr_output> outputs;
+    bool broadcast = false;
+    uint32_t rank = 0;
+    std::vector<uint64_t> dims;                 // [rank]
+    std::vector<std::vector<int64_t>> strides;  // [n_inputs][rank] (tensor inputs only)
+    bool fast_math = false;
+};
+
+enum class Kind { FlatV2, FlatScalar, TiledV2, TiledScalar, Generic };
+
+struct Emitted {
+    std::string source;
+    Kind kind = Kind::FlatScalar;
+    int vec = 1;        // elements per pack
+    int unroll = 1;     // packs (flat) or rows (tiled) per thread
+    int threads = 256;
+    // tiled / generic geometry (baked into the source as literals)
+    uint64_t rows = 0, cols = 0, numel = 0;
+    int tx = 0, ty = 0;
+    // pointer alignment (bytes) the kernel assumes for each tensor input / output; 1 = none
+    std::vector<int> input_align;
+    std::vector<int> output_align;
+};
+
+// Validates the stage.  Returns "" when it is well formed, else the reason.
+std::string validate(const Stage& stage);
+
+// Emits the fastest kernel shape the stage admits, or (force_generic) the element-wise fallback that
+// makes no alignment or divisibility assumption.  Returns "" on success, else the reason.
+std::string emit(const Stage& stage, bool force_generic, Emitted* out);
+
+const char* kindName(Kind k);
+
+}  // namespace tb::expr

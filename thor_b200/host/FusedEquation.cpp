@@ -1,0 +1,696 @@
+// Planner + stamper of the host layer: DAG -> stages -> C-ABI handles -> launch list.
+#include "FusedEquation.h"
+
+#include <algorithm>
+#include <cstring>
+#include <functional>
+#include <set>
+#include <sstream>
+#include <stdexcept>
+
+#include "AutoDiff.h"
+#include "RowFusion.h"
+#include "thor_b200.h"
+
+namespace ThorB200 {
+
+namespace {
+
+[[noreturn]] void throwFromStatus(int status, const char* what) {
+    const std::string msg = std::string(what) + ": " + thor_b200_last_error();
+    if (status == THOR_B200_INVALID_ARGUMENT || status == THOR_B200_UNSUPPORTED) throw std::logic_error(msg);
+    throw std::runtime_error(msg);
+}
+void check(int status, const char* what) {
+    if (status != THOR_B200_OK) throwFromStatus(status, what);
+}
+
+uint64_t numelOf(const std::vector<uint64_t>& dims) {
+    uint64_t n = 1;
+    for (uint64_t d : dims) n *= d;
+    return n;
+}
+
+std::vector<uint64_t> broadcastDims(const std::vector<uint64_t>& a, const std::vector<uint64_t>& b) {
+    const size_t r = std::max(a.size(), b.size());
+    std::vector<uint64_t> out(r, 1);
+    for (size_t i = 0; i < r; ++i) {
+        const uint64_t da = i < r - a.size() ? 1 : a[i - (r - a.size())];
+        const uint64_t db = i < r - b.size() ? 1 : b[i - (r - b.size())];
+        if (da != db && da != 1 && db != 1) throw std::logic_error("Expression: operand shapes do not broadcast");
+        out[i] = da == 1 ? db : da;
+    }
+    return out;
+}
+
+int reduceOpFor(ExprOp op) {
+    switch (op) {
+        case ExprOp::REDUCE_SUM: return THOR_B200_REDUCE_SUM;
+        case ExprOp::REDUCE_PROD: return THOR_B200_REDUCE_PRODUCT;
+        case ExprOp::REDUCE_MIN: return THOR_B200_REDUCE_MIN;
+        case ExprOp::REDUCE_MAX: return THOR_B200_REDUCE_MAX;
+        case ExprOp::REDUCE_AVG: return THOR_B200_REDUCE_MEAN;
+        case ExprOp::REDUCE_NORM1: return THOR_B200_REDUCE_L1NORM;
+        case ExprOp::REDUCE_NORM2: return THOR_B200_REDUCE_L2NORM;
+        default: throw std::logic_error("not a value reduction");
+    }
+}
+
+struct ExprHandle {
+    thor_b200_expr* h = nullptr;
+    ~ExprHandle() { thor_b200_expr_destroy(h); }
+};
+struct ReducePlanHandle {
+    thor_b200_reduce_plan* h = nullptr;
+    ~ReducePlanHandle() { thor_b200_reduce_plan_destroy(h); }
+};
+struct ArgReducePlanHandle {
+    thor_b200_argreduce_plan* h = nullptr;
+    ~ArgReducePlanHandle() { thor_b200_argreduce_plan_destroy(h); }
+};
+
+}  // namespace
+
+std::vector<std::vector<uint64_t>> inferNodeShapes(const PhysicalExpression& expr, const std::vector<std::vector<uint64_t>>& input_dims) {
+    std::vector<std::vector<uint64_t>> shape(expr.nodes.size());
+    for (size_t k = 0; k < expr.nodes.size(); ++k) {
+        const ExprNode& n = expr.nodes[k];
+        if (n.op == ExprOp::INPUT) {
+            shape[k] = input_dims.at(n.input_slot);
+        } else if (isScalarLeafOp(n.op)) {
+            shape[k] = {};
+        } else if (isReductionOp(n.op)) {
+            const auto& in = shape[n.lhs];
+            std::vector<bool> reduced(in.size(), n.reduction_axes.empty());
+            for (uint64_t ax : n.reduction_axes) {
+                if (ax >= in.size()) throw std::logic_error("reduction axis out of range");
+                reduced[ax] = true;
+            }
+            std::vector<uint64_t> kept(in);
+            for (size_t i = 0; i < in.size(); ++i)
+                if (reduced[i]) kept[i] = 1;
+            std::vector<uint64_t> out;
+            const bool squeeze_all = n.squeeze_axes.size() == 1 && n.squeeze_axes[0] == kSqueezeAll;
+            for (size_t i = 0; i < kept.size(); ++i) {
+                bool drop = squeeze_all ? kept[i] == 1 : std::find(n.squeeze_axes.begin(), n.squeeze_axes.end(), i) != n.squeeze_axes.end();
+                if (drop && kept[i] != 1) throw std::logic_error("squeeze axis is not a singleton");
+                if (!drop) out.push_back(kept[i]);
+            }
+            if (out.empty()) out.push_back(1);
+            shape[k] = out;
+        } else if (n.op == ExprOp::RESHAPE) {
+            if (numelOf(n.reshape_dims) != numelOf(shape[n.lhs])) throw std::logic_error("reshape changes the element count");
+            shape[k] = n.reshape_dims;
+        } else if (n.op == ExprOp::UNSQUEEZE) {
+            std::vector<uint64_t> out = shape[n.lhs];
+            std::vector<uint64_t> axes = n.unsqueeze_axes;
+            std::sort(axes.begin(), axes.end());
+            for (uint64_t ax : axes) {
+                if (ax > out.size()) throw std::logic_error("unsqueeze axis out of range");
+                out.insert(out.begin() + static_cast<long>(ax), 1);
+            }
+            shape[k] = out;
+        } else if (n.op == ExprOp::SQUEEZE) {
+            std::vector<uint64_t> out;
+            const auto& in = shape[n.lhs];
+            const bool squeeze_all = n.squeeze_axes.size() == 1 && n.squeeze_axes[0] == kSqueezeAll;
+            for (size_t i = 0; i < in.size(); ++i) {
+                const bool drop = squeeze_all ? in[i] == 1 : std::find(n.squeeze_axes.begin(), n.squeeze_axes.end(), i) != n.squeeze_axes.end();
+                if (drop && in[i] != 1) throw std::logic_error("squeeze axis is not a singleton");
+                if (!drop) out.push_back(in[i]);
+            }
+            if (out.empty()) out.push_back(1);
+            shape[k] = out;
+        } else {
+            std::vector<uint64_t> out;
+            for (uint32_t p : {n.lhs, n.rhs, n.aux})
+                if (p != UINT32_MAX) out = broadcastDims(out, shape[p]);
+            shape[k] = out;
+        }
+    }
+    return shape;
+}
+
+// ---- stamped plan ---------------------------------------------------------------------------------
+
+struct PhysicalStage {
+    StageKind kind = StageKind::FusedKernel;
+    std::string physical_name;
+    std::string source;
+    // FusedKernel
+    std::shared_ptr<ExprHandle> expr;
+    std::vector<const void*> input_ptrs;
+    std::vector<float> scalars;
+    std::vector<std::string> scalar_names;  // per slot, "" for tensors
+    std::vector<void*> output_ptrs;
+    uint64_t numel = 0;
+    // Reduction / ArgMinMax
+    std::shared_ptr<ReducePlanHandle> reduce;
+    std::shared_ptr<ArgReducePlanHandle> argreduce;
+    const void* in = nullptr;
+    void* out = nullptr;
+    Tensor workspace;
+    size_t workspace_bytes = 0;
+    // FusedRows
+    std::function<void(void* stream)> custom_launch;
+    uint64_t launches = 1;
+};
+
+struct StampedExecutionPlan::Impl {
+    Stream stream;
+    std::vector<PhysicalStage> stages;
+    std::vector<std::string> logical_stage_names;
+    std::map<std::string, Tensor> outputs;
+    std::vector<Tensor> keep_alive;
+    uint64_t intermediate_bytes = 0;
+};
+
+void StampedExecutionPlan::run() { runOn(impl_->stream); }
+
+void StampedExecutionPlan::runOn(const Stream& stream) {
+    if (!impl_) throw std::logic_error("StampedExecutionPlan is empty");
+    for (PhysicalStage& s : impl_->stages) {
+        switch (s.kind) {
+            case StageKind::FusedKernel:
+                check(thor_b200_expr_launch(s.expr->h, s.input_ptrs.data(), s.scalars.data(), s.output_ptrs.data(), s.numel, stream.handle),
+                      "StampedExecutionPlan::run fused stage");
+                break;
+            case StageKind::Reduction:
+                check(thor_b200_reduce_launch(s.reduce->h, s.in, s.out, s.workspace.getMemPtr(), s.workspace_bytes, 1.0f, stream.handle),
+                      "StampedExecutionPlan::run reduction");
+                break;
+            case StageKind::ArgMinMax:
+                check(thor_b200_argreduce_launch(s.argreduce->h, s.in, nullptr, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream.handle),
+                      "StampedExecutionPlan::run arg reduction");
+                break;
+            case StageKind::FusedRows: s.custom_launch(stream.handle); break;
+            case StageKind::View: break;
+        }
+    }
+}
+
+Tensor StampedExecutionPlan::getOutput(const std::string& name) const {
+    auto it = impl_->outputs.find(name);
+    if (it == impl_->outputs.end()) throw std::logic_error("StampedExecutionPlan has no output named '" + name + "'");
+    return it->second;
+}
+std::vector<std::string> StampedExecutionPlan::getOutputNames() const {
+    std::vector<std::string> names;
+    for (const auto& kv : impl_->outputs) names.push_back(kv.first);
+    return names;
+}
+void StampedExecutionPlan::setRuntimeScalar(const std::string& name, float value) {
+    bool found = false;
+    for (PhysicalStage& s : impl_->stages)
+        for (size_t i = 0; i < s.scalar_names.size(); ++i)
+            if (s.scalar_names[i] == name) {
+                s.scalars[i] = value;
+                found = true;
+            }
+    if (!found) throw std::logic_error("StampedExecutionPlan has no runtime scalar named '" + name + "'");
+}
+std::vector<std::string> StampedExecutionPlan::stageKindNames() const { return impl_->logical_stage_names; }
+std::vector<std::string> StampedExecutionPlan::physicalStageNames() const {
+    std::vector<std::string> out;
+    for (const auto& s : impl_->stages) out.push_back(s.physical_name);
+    return out;
+}
+std::vector<std::string> StampedExecutionPlan::stageSources() const {
+    std::vector<std::string> out;
+    for (const auto& s : impl_->stages) out.push_back(s.source);
+    return out;
+}
+uint64_t StampedExecutionPlan::intermediateBytes() const { return impl_->intermediate_bytes; }
+uint64_t StampedExecutionPlan::kernelLaunchesPerRun() const {
+    uint64_t n = 0;
+    for (const auto& s : impl_->stages)
+        if (s.kind != StageKind::View) n += s.launches;
+    return n;
+}
+
+// ---- FusedEquation ----------------------------------------------------------------------------------
+
+struct FusedEquation::Deferred {
+    Outputs forward;
+    std::vector<std::string> wrt;
+    std::string upstream_prefix;
+};
+
+FusedEquation FusedEquation::compile(const Outputs& outputs, int device_num, FusedEquationOptions options) {
+    if (!outputs.expression()) throw std::logic_error("FusedEquation::compile requires outputs");
+    FusedEquation eq;
+    eq.outputs_ = outputs;
+    eq.device_num_ = device_num;
+    eq.options_ = options;
+    return eq;
+}
+
+FusedEquation FusedEquation::compile(const Expression& expr, int device_num, FusedEquationOptions options) {
+    return compile(Expression::outputs({{"output", expr}}), device_num, options);
+}
+
+FusedEquation FusedEquation::compileBackward(const std::vector<std::string>& wrt_names, const std::string& upstream_prefix) const {
+    FusedEquation eq;
+    eq.device_num_ = device_num_;
+    eq.options_ = options_;
+    eq.deferred_backward_ = std::make_shared<Deferred>(Deferred{outputs_, wrt_names, upstream_prefix});
+    return eq;
+}
+
+namespace {
+
+struct Planner {
+    const PhysicalExpression& g;
+    const std::vector<NamedOutput>& outs;
+    const std::vector<std::vector<uint64_t>>& shape;
+    std::vector<int> level;          // stage level at which the node's value exists
+    std::vector<bool> materialize;   // elementwise nodes that must be written to memory
+    std::vector<bool> needed;        // reachable from the outputs
+
+    Planner(const PhysicalExpression& graph, const std::vector<NamedOutput>& outputs, const std::vector<std::vector<uint64_t>>& shapes)
+        : g(graph), outs(outputs), shape(shapes) {
+        const size_t n = g.nodes.size();
+        needed.assign(n, false);
+        for (const auto& o : outs) needed[o.node_idx] = true;
+        for (size_t k = n; k-- > 0;) {
+            if (!needed[k]) continue;
+            for (uint32_t p : {g.nodes[k].lhs, g.nodes[k].rhs, g.nodes[k].aux})
+                if (p != UINT32_MAX) needed[p] = true;
+        }
+        level.assign(n, 0);
+        materialize.assign(n, false);
+        for (size_t k = 0; k < n; ++k) {
+            if (!needed[k]) continue;
+            const ExprNode& nd = g.nodes[k];
+            int lv = 0;
+            for (uint32_t p : {nd.lhs, nd.rhs, nd.aux})
+                if (p != UINT32_MAX) lv = std::max(lv, level[p]);
+            if (isBoundary(k)) {
+                lv += 1;  // a boundary op consumes a tensor that exists after level lv's fused stages
+                if (isElementwise(nd.lhs)) materialize[nd.lhs] = true;
+            }
+            level[k] = lv;
+        }
+        for (const auto& o : outs)
+            if (isElementwise(o.node_idx)) materialize[o.node_idx] = true;
+    }
+    bool isBoundary(size_t k) const { return isReductionOp(g.nodes[k].op) || isViewOp(g.nodes[k].op); }
+    bool isElementwise(size_t k) const { return !isBoundary(k) && !isLeafOp(g.nodes[k].op); }
+};
+
+}  // namespace
+
+StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, RuntimeInputValue>& inputs, const Stream& stream,
+                                          const std::unordered_map<std::string, Tensor>& preallocated_outputs) {
+    Outputs outputs = outputs_;
+    if (deferred_backward_) {
+        // shapes are known only now: build the backward DAG for these forward shapes
+        std::unordered_map<std::string, std::vector<uint64_t>> dims;
+        for (const auto& kv : inputs)
+            if (!kv.second.is_scalar) dims[kv.first] = kv.second.tensor.getDimensions();
+        outputs = buildBackwardOutputs(deferred_backward_->forward, deferred_backward_->wrt, deferred_backward_->upstream_prefix, dims);
+    }
+    PhysicalOutputs phys = outputs.physicalOutputs();
+    // private copy: dtype resolution writes into the graph
+    phys.expr = std::make_shared<PhysicalExpression>(*phys.expr);
+    PhysicalExpression& g = *phys.expr;
+
+    // bind inputs
+    std::vector<DataType> in_dtypes(g.inputs.size(), DataType::FP32);
+    std::vector<std::vector<uint64_t>> in_dims(g.inputs.size());
+    std::vector<RuntimeInputValue> bound(g.inputs.size());
+    for (const NamedInput& in : g.inputs) {
+        auto it = inputs.find(in.name);
+        if (it == inputs.end()) throw std::logic_error("FusedEquation::stamp: missing input '" + in.name + "'");
+        const RuntimeInputValue& v = it->second;
+        if (in.kind == NamedInput::Kind::RuntimeScalarFp32) {
+            if (!v.is_scalar) throw std::logic_error("FusedEquation::stamp: input '" + in.name + "' must be an fp32 scalar value");
+            in_dtypes[in.slot] = DataType::FP32;
+        } else {
+            if (v.is_scalar || !v.tensor.isInitialized()) throw std::logic_error("FusedEquation::stamp: input '" + in.name + "' must be a tensor");
+            if (v.tensor.getGpuNum() != device_num_) throw std::logic_error("FusedEquation::stamp: input '" + in.name + "' lives on another device");
+            in_dtypes[in.slot] = v.tensor.getDataType();
+            in_dims[in.slot] = v.tensor.getDimensions();
+            if (in.kind == NamedInput::Kind::TensorRuntimeScalar && v.tensor.getTotalNumElements() != 1)
+                throw std::logic_error("FusedEquation::stamp: tensor runtime scalar '" + in.name + "' must hold one element");
+        }
+        bound[in.slot] = v;
+    }
+    resolveOutputsDTypesInPlace(phys, in_dtypes);
+    std::vector<std::vector<uint64_t>> shape_inputs = in_dims;
+    for (const NamedInput& in : g.inputs)
+        if (in.kind == NamedInput::Kind::TensorRuntimeScalar) shape_inputs[in.slot] = {};
+    const auto shape = inferNodeShapes(g, shape_inputs);
+    // tensor-runtime-scalar leaves are rank-0 in shape inference (handled by isScalarLeafOp)
+
+    Planner plan(g, phys.outputs, shape);
+    auto impl = std::make_shared<StampedExecutionPlan::Impl>();
+    impl->stream = stream;
+
+    // tensor that holds each materialised node (inputs, boundary outputs, materialised elementwise nodes)
+    std::vector<Tensor> node_tensor(g.nodes.size());
+    for (size_t k = 0; k < g.nodes.size(); ++k)
+        if (g.nodes[k].op == ExprOp::INPUT || g.nodes[k].op == ExprOp::TENSOR_RUNTIME_SCALAR) {
+            if (g.nodes[k].output_dtype != g.nodes[k].input_tensor_dtype)
+                continue;  // an input with an output-dtype override is converted inside the consuming fused stage
+            node_tensor[k] = bound[g.nodes[k].input_slot].tensor;
+        }
+    std::map<uint32_t, std::string> output_name_of;
+    for (const auto& o : phys.outputs) output_name_of[o.node_idx] = o.name;
+
+    auto allocateFor = [&](uint32_t node, bool is_output) -> Tensor {
+        const DataType dt = *g.nodes[node].output_dtype;
+        if (is_output) {
+            auto it = preallocated_outputs.find(output_name_of.at(node));
+            if (it != preallocated_outputs.end()) {
+                if (it->second.getDataType() != dt) throw std::logic_error("FusedEquation::stamp: preallocated output '" + it->first + "' has the wrong dtype");
+                if (it->second.getTotalNumElements() != numelOf(shape[node])) throw std::logic_error("FusedEquation::stamp: preallocated output '" + it->first + "' has the wrong size");
+                return it->second;
+            }
+        }
+        Tensor t = Tensor::allocate(dt, shape[node], device_num_);
+        if (!is_output) impl->intermediate_bytes += t.getArraySizeInBytes();
+        return t;
+    };
+
+    int max_level = 0;
+    for (size_t k = 0; k < g.nodes.size(); ++k)
+        if (plan.needed[k]) max_level = std::max(max_level, plan.level[k]);
+
+    // Logical stage list first (what the reference's planner would run); the row-fusion pass may then
+    // replace runs of logical stages by one physical super-stage.
+    struct LogicalStage {
+        StageKind kind;
+        std::vector<uint32_t> nodes;  // FusedKernel: materialised nodes it produces; others: the boundary node
+    };
+    std::vector<LogicalStage> logical;
+    for (int lv = 0; lv <= max_level; ++lv) {
+        // fused groups of this level, grouped by output shape
+        std::vector<std::pair<std::vector<uint64_t>, std::vector<uint32_t>>> groups;
+        for (uint32_t k = 0; k < g.nodes.size(); ++k) {
+            if (!plan.needed[k] || !plan.materialize[k] || plan.level[k] != lv) continue;
+            bool placed = false;
+            for (auto& grp : groups)
+                if (grp.first == shape[k]) {
+                    grp.second.push_back(k);
+                    placed = true;
+                    break;
+                }
+            if (!placed) groups.push_back({shape[k], {k}});
+        }
+        for (auto& grp : groups) logical.push_back({StageKind::FusedKernel, grp.second});
+        for (uint32_t k = 0; k < g.nodes.size(); ++k) {
+            if (!plan.needed[k] || !plan.isBoundary(k) || plan.level[k] != lv + 1) continue;
+            const ExprOp op = g.nodes[k].op;
+            logical.push_back({isViewOp(op) ? StageKind::View : (isArgReductionOp(op) ? StageKind::ArgMinMax : StageKind::Reduction), {k}});
+        }
+    }
+    for (const auto& ls : logical) {
+        impl->logical_stage_names.push_back(ls.kind == StageKind::FusedKernel ? "FusedKernel" : ls.kind == StageKind::Reduction ? "Reduction"
+                                            : ls.kind == StageKind::ArgMinMax ? "ArgMinMax" : "View");
+    }
+
+    // Optional physical fusion of row-reduction chains (softmax / LayerNorm class).
+    std::vector<bool> covered(g.nodes.size(), false);  // nodes whose values a super-stage already produced or made unnecessary
+    if (options_.fuse_row_reductions) {
+        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_};
+        std::vector<RowFusionMatch> matches = matchRowFusions(ctx);
+        for (RowFusionMatch& m : matches) {
+            PhysicalStage st;
+            st.kind = StageKind::FusedRows;
+            st.physical_name = m.name;
+            st.launches = m.launches;
+            for (auto& [node, is_out] : m.produced) {
+                Tensor t = allocateFor(node, is_out);
+                node_tensor[node] = t;
+                if (is_out) impl->outputs[output_name_of.at(node)] = t;
+                covered[node] = true;
+            }
+            for (uint32_t node : m.absorbed) covered[node] = true;
+            st.custom_launch = m.bind(node_tensor, impl->keep_alive, impl->intermediate_bytes);
+            impl->stages.push_back(std::move(st));
+        }
+    }
+
+    auto needsRun = [&](const LogicalStage& ls) {
+        for (uint32_t k : ls.nodes)
+            if (!covered[k]) return true;
+        return false;
+    };
+
+    for (const LogicalStage& ls : logical) {
+        if (!needsRun(ls)) continue;
+        if (ls.kind == StageKind::View) {
+            const uint32_t k = ls.nodes[0];
+            const Tensor& src = node_tensor[g.nodes[k].lhs];
+            if (!src.isInitialized()) throw std::logic_error("FusedEquation::stamp: view of a value that is not materialised");
+            node_tensor[k] = Tensor::wrap(src.getMemPtr(), src.getDataType(), shape[k], device_num_);
+            impl->keep_alive.push_back(src);
+            PhysicalStage st;
+            st.kind = StageKind::View;
+            st.physical_name = "view";
+            impl->stages.push_back(std::move(st));
+            if (output_name_of.count(k)) impl->outputs[output_name_of[k]] = node_tensor[k];
+            continue;
+        }
+        if (ls.kind == StageKind::Reduction || ls.kind == StageKind::ArgMinMax) {
+            const uint32_t k = ls.nodes[0];
+            const ExprNode& nd = g.nodes[k];
+            const Tensor& src = node_tensor[nd.lhs];
+            if (!src.isInitialized()) throw std::logic_error("FusedEquation::stamp: reduction input is not materialised");
+            const auto& in_shape = shape[nd.lhs];
+            std::vector<bool> reduced(in_shape.size(), nd.reduction_axes.empty());
+            for (uint64_t ax : nd.reduction_axes) reduced[ax] = true;
+            // [outer, reduction, inner] needs the non-singleton reduced axes to form one contiguous block
+            uint64_t outer = 1, red = 1, inner = 1;
+            int phase = 0;
+            for (size_t i = 0; i < in_shape.size(); ++i) {
+                if (in_shape[i] == 1) continue;
+                if (reduced[i]) {
+                    if (phase == 2) throw std::logic_error("FusedEquation::stamp: reduction over non-adjacent axes is not provided (StridedFixedSegment path)");
+                    phase = 1;
+                    red *= in_shape[i];
+                } else if (phase == 0) {
+                    outer *= in_shape[i];
+                } else {
+                    phase = 2;
+                    inner *= in_shape[i];
+                }
+            }
+            const bool is_out = output_name_of.count(k) != 0;
+            Tensor dst = allocateFor(k, is_out);
+            node_tensor[k] = dst;
+            if (is_out) impl->outputs[output_name_of[k]] = dst;
+            PhysicalStage st;
+            st.kind = ls.kind;
+            st.in = src.getMemPtr();
+            st.out = dst.getMemPtr();
+            impl->keep_alive.push_back(src);
+            size_t ws = 1;
+            if (ls.kind == StageKind::Reduction) {
+                thor_b200_reduce_desc d{};
+                d.op = reduceOpFor(nd.op);
+                d.input_dtype = static_cast<int>(src.getDataType());
+                d.output_dtype = static_cast<int>(*nd.output_dtype);
+                d.outer = outer;
+                d.reduction = red;
+                d.inner = inner;
+                st.reduce = std::make_shared<ReducePlanHandle>();
+                check(thor_b200_reduce_plan_create(&d, &st.reduce->h, &ws), "FusedEquation::stamp reduction plan");
+                st.physical_name = thor_b200_reduce_plan_kind(st.reduce->h);
+                st.launches = st.physical_name.find("split") != std::string::npos || st.physical_name == "full" ? 2 : 1;
+            } else {
+                thor_b200_argreduce_desc d{};
+                d.op = nd.op == ExprOp::REDUCE_ARGMAX ? 1 : 0;
+                d.input_dtype = static_cast<int>(src.getDataType());
+                d.value_dtype = 0;
+                d.index_dtype = static_cast<int>(*nd.output_dtype);
+                d.outer = outer;
+                d.reduction = red;
+                d.inner = inner;
+                st.argreduce = std::make_shared<ArgReducePlanHandle>();
+                check(thor_b200_argreduce_plan_create(&d, &st.argreduce->h, &ws), "FusedEquation::stamp arg-reduction plan");
+                st.physical_name = "arg_reduce";
+            }
+            st.workspace_bytes = ws;
+            st.workspace = Tensor::allocate(DataType::UINT8, {static_cast<uint64_t>(ws)}, device_num_);
+            if (ws > 1) impl->intermediate_bytes += ws;
+            impl->stages.push_back(std::move(st));
+            continue;
+        }
+
+        // ---- fused elementwise / broadcast stage -------------------------------------------------
+        std::vector<uint32_t> stage_outputs;
+        for (uint32_t k : ls.nodes)
+            if (!covered[k]) stage_outputs.push_back(k);
+        // ancestors back to materialised roots
+        std::vector<bool> in_stage(g.nodes.size(), false);
+        std::vector<uint32_t> stack(stage_outputs.begin(), stage_outputs.end());
+        while (!stack.empty()) {
+            const uint32_t k = stack.back();
+            stack.pop_back();
+            if (in_stage[k]) continue;
+            in_stage[k] = true;
+            const bool root = node_tensor[k].isInitialized() || isLeafOp(g.nodes[k].op);
+            if (root) continue;
+            for (uint32_t p : {g.nodes[k].lhs, g.nodes[k].rhs, g.nodes[k].aux})
+                if (p != UINT32_MAX) stack.push_back(p);
+        }
+        std::vector<thor_b200_expr_node> nodes;
+        std::vector<thor_b200_expr_input> ins;
+        std::vector<const void*> in_ptrs;
+        std::vector<float> scalars;
+        std::vector<std::string> scalar_names;
+        std::vector<std::vector<uint64_t>> in_shapes;
+        std::map<uint32_t, uint32_t> remap;
+        std::map<const void*, uint32_t> slot_of_ptr;
+        std::map<std::string, uint32_t> slot_of_scalar;
+        const std::vector<uint64_t>& out_dims = shape[stage_outputs[0]];
+        for (uint32_t k = 0; k < g.nodes.size(); ++k) {
+            if (!in_stage[k]) continue;
+            const ExprNode& nd = g.nodes[k];
+            thor_b200_expr_node cn{};
+            cn.lhs = cn.rhs = cn.aux = THOR_B200_NO_NODE;
+            cn.input_slot = THOR_B200_NO_NODE;
+            cn.output_dtype = static_cast<uint16_t>(*nd.output_dtype);
+            cn.compute_dtype = static_cast<uint16_t>(nd.compute_dtype.value_or(*nd.output_dtype));
+            const bool is_stage_output = std::find(stage_outputs.begin(), stage_outputs.end(), k) != stage_outputs.end();
+            if (node_tensor[k].isInitialized() && !(is_stage_output && plan.isElementwise(k))) {
+                // materialised tensor (external input, reduction result, view): a stage input
+                const Tensor& t = node_tensor[k];
+                const bool one_elem_scalar = nd.op == ExprOp::TENSOR_RUNTIME_SCALAR;
+                uint32_t slot;
+                auto it = slot_of_ptr.find(t.getMemPtr());
+                if (it != slot_of_ptr.end() && static_cast<int>(t.getDataType()) == ins[it->second].dtype) {
+                    slot = it->second;
+                } else {
+                    slot = static_cast<uint32_t>(ins.size());
+                    ins.push_back({one_elem_scalar ? THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR : THOR_B200_INPUT_TENSOR, static_cast<int>(t.getDataType())});
+                    in_ptrs.push_back(t.getMemPtr());
+                    scalars.push_back(0.0f);
+                    scalar_names.push_back("");
+                    in_shapes.push_back(one_elem_scalar ? std::vector<uint64_t>{} : shape[k]);
+                    slot_of_ptr[t.getMemPtr()] = slot;
+                    impl->keep_alive.push_back(t);
+                }
+                cn.op = one_elem_scalar ? THOR_B200_OP_TENSOR_RUNTIME_SCALAR : THOR_B200_OP_INPUT;
+                cn.input_slot = slot;
+                cn.input_dtype = static_cast<uint16_t>(t.getDataType());
+                // a materialised value is read back in its storage dtype
+                cn.output_dtype = static_cast<uint16_t>(nd.op == ExprOp::INPUT || one_elem_scalar ? *nd.output_dtype : t.getDataType());
+            } else if (nd.op == ExprOp::INPUT || nd.op == ExprOp::TENSOR_RUNTIME_SCALAR) {
+                // input whose output dtype differs from its storage dtype: converted on load
+                const Tensor& t = bound[nd.input_slot].tensor;
+                const bool one_elem_scalar = nd.op == ExprOp::TENSOR_RUNTIME_SCALAR;
+                const uint32_t slot = static_cast<uint32_t>(ins.size());
+                ins.push_back({one_elem_scalar ? THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR : THOR_B200_INPUT_TENSOR, static_cast<int>(t.getDataType())});
+                in_ptrs.push_back(t.getMemPtr());
+                scalars.push_back(0.0f);
+                scalar_names.push_back("");
+                in_shapes.push_back(one_elem_scalar ? std::vector<uint64_t>{} : shape[k]);
+                impl->keep_alive.push_back(t);
+                cn.op = one_elem_scalar ? THOR_B200_OP_TENSOR_RUNTIME_SCALAR : THOR_B200_OP_INPUT;
+                cn.input_slot = slot;
+                cn.input_dtype = static_cast<uint16_t>(t.getDataType());
+            } else if (nd.op == ExprOp::RUNTIME_SCALAR) {
+                const std::string& name = g.inputs[nd.input_slot].name;
+                uint32_t slot;
+                auto it = slot_of_scalar.find(name);
+                if (it != slot_of_scalar.end()) {
+                    slot = it->second;
+                } else {
+                    slot = static_cast<uint32_t>(ins.size());
+                    ins.push_back({THOR_B200_INPUT_RUNTIME_SCALAR_FP32, THOR_B200_FP32});
+                    in_ptrs.push_back(nullptr);
+                    scalars.push_back(bound[nd.input_slot].scalar);
+                    scalar_names.push_back(name);
+                    in_shapes.push_back({});
+                    slot_of_scalar[name] = slot;
+                }
+                cn.op = THOR_B200_OP_RUNTIME_SCALAR;
+                cn.input_slot = slot;
+                cn.input_dtype = THOR_B200_FP32;
+            } else if (nd.op == ExprOp::SCALAR_FP) {
+                cn.op = THOR_B200_OP_SCALAR_FP;
+                cn.scalar_fp = nd.scalar_fp;
+            } else {
+                cn.op = static_cast<uint16_t>(nd.op);
+                if (nd.lhs != UINT32_MAX) cn.lhs = remap.at(nd.lhs);
+                if (nd.rhs != UINT32_MAX) cn.rhs = remap.at(nd.rhs);
+                if (nd.aux != UINT32_MAX) cn.aux = remap.at(nd.aux);
+            }
+            remap[k] = static_cast<uint32_t>(nodes.size());
+            nodes.push_back(cn);
+        }
+        std::vector<thor_b200_expr_output> outs;
+        std::vector<void*> out_ptrs;
+        for (uint32_t k : stage_outputs) {
+            const bool is_out = output_name_of.count(k) != 0;
+            Tensor dst = allocateFor(k, is_out);
+            node_tensor[k] = dst;
+            if (is_out) impl->outputs[output_name_of[k]] = dst;
+            outs.push_back({remap.at(k), static_cast<int>(*g.nodes[k].output_dtype)});
+            out_ptrs.push_back(dst.getMemPtr());
+        }
+        // broadcast geometry: flat when every tensor input covers the whole output
+        const uint64_t out_numel = numelOf(out_dims);
+        bool flat = true;
+        for (size_t s = 0; s < ins.size(); ++s)
+            if (ins[s].kind == THOR_B200_INPUT_TENSOR && numelOf(in_shapes[s]) != out_numel) flat = false;
+        thor_b200_expr_broadcast bc{};
+        std::vector<int64_t> strides(ins.size() * THOR_B200_MAX_RANK, 0);
+        if (!flat) {
+            if (out_dims.size() > THOR_B200_MAX_RANK) throw std::logic_error("FusedEquation::stamp: broadcast rank above 8");
+            bc.rank = static_cast<uint32_t>(out_dims.size());
+            for (size_t d = 0; d < out_dims.size(); ++d) bc.dims[d] = out_dims[d];
+            for (size_t s = 0; s < ins.size(); ++s) {
+                if (ins[s].kind != THOR_B200_INPUT_TENSOR) continue;
+                const auto& d = in_shapes[s];
+                const size_t pad = out_dims.size() - d.size();
+                int64_t stride = 1;
+                for (size_t i = d.size(); i-- > 0;) {
+                    strides[s * THOR_B200_MAX_RANK + pad + i] = (d[i] == 1 && out_dims[pad + i] != 1) ? 0 : (d[i] == 1 ? 0 : stride);
+                    stride *= static_cast<int64_t>(d[i]);
+                }
+            }
+            bc.input_strides = strides.data();
+        }
+        thor_b200_expr_options opt{};
+        opt.use_fast_math = options_.use_fast_math;
+        PhysicalStage st;
+        st.kind = StageKind::FusedKernel;
+        st.expr = std::make_shared<ExprHandle>();
+        check(thor_b200_expr_compile(nodes.data(), static_cast<uint32_t>(nodes.size()), ins.data(), static_cast<uint32_t>(ins.size()), outs.data(),
+                                     static_cast<uint32_t>(outs.size()), flat ? nullptr : &bc, &opt, &st.expr->h),
+              "FusedEquation::stamp fused stage");
+        st.physical_name = thor_b200_expr_launch_kind(st.expr->h);
+        st.source = thor_b200_expr_source(st.expr->h);
+        st.input_ptrs = in_ptrs;
+        st.scalars = scalars;
+        st.scalar_names = scalar_names;
+        st.output_ptrs = out_ptrs;
+        st.numel = out_numel;
+        impl->stages.push_back(std::move(st));
+    }
+
+    // outputs that are plain inputs or were produced by boundary stages
+    for (const auto& o : phys.outputs) {
+        if (impl->outputs.count(o.name)) continue;
+        if (!node_tensor[o.node_idx].isInitialized()) throw std::logic_error("FusedEquation::stamp: output '" + o.name + "' was not produced");
+        impl->outputs[o.name] = node_tensor[o.node_idx];
+    }
+    for (auto& t : node_tensor)
+        if (t.isInitialized()) impl->keep_alive.push_back(t);
+    return StampedExecutionPlan(impl);
+}
+
+void FusedEquation::run(const std::unordered_map<std::string, RuntimeInputValue>& inputs, const std::unordered_map<std::string, Tensor>& outputs,
+                        const Stream& stream) {
+    StampedExecutionPlan plan = stamp(inputs, stream, outputs);
+    const auto kinds = plan.stageKindNames();
+    if (kinds.size() != 1 || kinds[0] != "FusedKernel")
+        throw std::logic_error("FusedEquation::run supports single fused-stage expressions only; use stamp() for staged reductions");
+    plan.run();
+}
+
+}  // namespace ThorB200

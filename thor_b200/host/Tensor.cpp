@@ -1,0 +1,33 @@
+#include "Tensor.h"
+
+#include <stdexcept>
+#include <string>
+
+#include "thor_b200.h"
+
+namespace ThorB200 {
+
+Tensor Tensor::wrap(void* device_ptr, DataType dtype, std::vector<uint64_t> dims, int gpu_num) {
+    Tensor t;
+    t.ptr_ = device_ptr;
+    t.dtype_ = dtype;
+    t.dims_ = std::move(dims);
+    t.gpu_num_ = gpu_num;
+    return t;
+}
+
+Tensor Tensor::allocate(DataType dtype, std::vector<uint64_t> dims, int gpu_num) {
+    Tensor t;
+    t.dtype_ = dtype;
+    t.dims_ = std::move(dims);
+    t.gpu_num_ = gpu_num;
+    void* p = nullptr;
+    // the caller has made gpu_num current (the reference wraps allocation in ScopedGpu)
+    if (thor_b200_device_alloc(t.getArraySizeInBytes(), &p) != THOR_B200_OK)
+        throw std::runtime_error(std::string("Tensor::allocate: ") + thor_b200_last_error());
+    t.ptr_ = p;
+    t.owner_ = std::shared_ptr<void>(p, [](void* q) { thor_b200_device_free(q); });
+    return t;
+}
+
+}  // namespace ThorB200

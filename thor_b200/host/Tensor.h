@@ -1,0 +1,51 @@
+// Minimal stand-ins for the reference's boundary types Tensor and Stream
+// (DeepLearning/Implementation/Tensor/Tensor.h:56-266, Utilities/Common/Stream.h:35-118): a device
+// pointer with dtype + dense row-major dimensions, and a cudaStream_t with its device ordinal.
+// Device memory comes from the C ABI (thor_b200_device_alloc); the host layer never links CUDA.
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <vector>
+
+#include "DataType.h"
+
+namespace ThorB200 {
+
+struct Stream {
+    void* handle = nullptr;  // cudaStream_t
+    int gpu_num = 0;
+    Stream() = default;
+    Stream(void* h, int gpu) : handle(h), gpu_num(gpu) {}
+    int getGpuNum() const { return gpu_num; }
+};
+
+class Tensor {
+   public:
+    Tensor() = default;
+    // Adopts memory owned by the caller (a torch tensor, a Thor tensor, ...).
+    static Tensor wrap(void* device_ptr, DataType dtype, std::vector<uint64_t> dims, int gpu_num = 0);
+    // Allocates dense device memory on gpu_num (used at stamp time for intermediates and outputs).
+    static Tensor allocate(DataType dtype, std::vector<uint64_t> dims, int gpu_num = 0);
+
+    bool isInitialized() const { return ptr_ != nullptr; }
+    void* getMemPtr() const { return ptr_; }
+    DataType getDataType() const { return dtype_; }
+    const std::vector<uint64_t>& getDimensions() const { return dims_; }
+    int getGpuNum() const { return gpu_num_; }
+    uint64_t getTotalNumElements() const {
+        uint64_t n = 1;
+        for (uint64_t d : dims_) n *= d;
+        return n;
+    }
+    uint64_t getArraySizeInBytes() const { return getTotalNumElements() * dataTypeSize(dtype_); }
+
+   private:
+    void* ptr_ = nullptr;
+    DataType dtype_ = DataType::FP32;
+    std::vector<uint64_t> dims_;
+    int gpu_num_ = 0;
+    std::shared_ptr<void> owner_;
+};
+
+}  // namespace ThorB200

@@ -1,0 +1,156 @@
+"""Binding of the reduction seam, named after the reference's CubReduction / CubArgReduction
+(Utilities/TensorOperations/Cub/CubReduction.h:176-447): describe, stamp (plan + allocate), run."""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Optional, Sequence, Union
+
+import torch
+
+from . import _native
+from .dtypes import DataType, from_torch, to_torch
+from .expression import _Binding, _bind_tensor, _check, _host
+
+_lib = _native.lib
+
+
+class _ReduceDesc(C.Structure):
+    _fields_ = [("op", C.c_int32), ("input_dtype", C.c_int32), ("output_dtype", C.c_int32), ("flags", C.c_uint32), ("outer", C.c_uint64),
+                ("reduction", C.c_uint64), ("inner", C.c_uint64), ("out_stride_outer", C.c_uint64), ("out_stride_inner", C.c_uint64)]
+
+
+class _ArgDesc(C.Structure):
+    _fields_ = [("op", C.c_int32), ("input_dtype", C.c_int32), ("value_dtype", C.c_int32), ("index_dtype", C.c_int32), ("outer", C.c_uint64),
+                ("reduction", C.c_uint64), ("inner", C.c_uint64)]
+
+
+_lib.thor_b200_reduce_plan_create.argtypes = [C.POINTER(_ReduceDesc), C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
+_lib.thor_b200_reduce_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
+_lib.thor_b200_reduce_plan_kind.argtypes = [C.c_void_p]
+_lib.thor_b200_reduce_plan_kind.restype = C.c_char_p
+_lib.thor_b200_reduce_plan_destroy.argtypes = [C.c_void_p]
+_lib.thor_b200_reduce_plan_destroy.restype = None
+_lib.thor_b200_argreduce_plan_create.argtypes = [C.POINTER(_ArgDesc), C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
+_lib.thor_b200_argreduce_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+_lib.thor_b200_argreduce_plan_destroy.argtypes = [C.c_void_p]
+_lib.thor_b200_argreduce_plan_destroy.restype = None
+
+
+class CubReductionOp(enum.IntEnum):
+    Sum = 0
+    Min = 1
+    Max = 2
+    Product = 3
+    Mean = 4
+    L1Norm = 5
+    L2Norm = 6
+
+
+class CubArgReductionOp(enum.IntEnum):
+    ArgMin = 0
+    ArgMax = 1
+
+
+class CubReductionPath(enum.IntEnum):
+    DeviceTransformReduce = 0
+    ContiguousFixedSegment = 1
+    TiledFixedSegment = 2
+    StridedFixedSegment = 3
+
+
+def analyze_geometry(dims: Sequence[int], axes: Sequence[int]):
+    """(outer, reduction, inner, path) like CubReduction::analyzeGeometry (CubReduction.cpp:755-912); needs no GPU."""
+    d = (C.c_uint64 * max(1, len(dims)))(*dims)
+    a = (C.c_uint32 * max(1, len(axes)))(*axes)
+    ori = (C.c_uint64 * 3)()
+    path = C.c_int32()
+    _check(_host.thb_reduction_geometry(d, len(dims), a, len(axes), ori, C.byref(path)))
+    return int(ori[0]), int(ori[1]), int(ori[2]), CubReductionPath(path.value)
+
+
+def empty_reduction_value(op: CubReductionOp) -> float:
+    return float(_host.thb_cub_empty_value(int(op)))
+
+
+class StampedCubReduction:
+    def __init__(self, handle, input_t, output_t):
+        self._h, self._in, self.output = handle, input_t, output_t
+
+    def __del__(self):
+        try:
+            _host.thb_cub_reduction_free(self._h)
+        except Exception:
+            pass
+
+    def run(self) -> None:
+        _check(_host.thb_cub_reduction_run(self._h))
+
+    def kernel_kind(self) -> str:
+        return _host.thb_cub_reduction_kind(self._h).decode()
+
+    def workspace_bytes(self) -> int:
+        return int(_host.thb_cub_reduction_workspace_bytes(self._h))
+
+
+class CubReduction:
+    def __init__(self, op: CubReductionOp, axes: Union[int, Sequence[int]], output_dtype: Optional[DataType] = None, output_scale: float = 1.0):
+        self.op = CubReductionOp(op)
+        self.axes = [axes] if isinstance(axes, int) else list(axes)
+        self.output_dtype = output_dtype
+        self.output_scale = float(output_scale)
+
+    def stamp(self, input_t: torch.Tensor, stream=None, input_dtype: Optional[DataType] = None, output: Optional[torch.Tensor] = None) -> StampedCubReduction:
+        in_dt = DataType(input_dtype) if input_dtype is not None else from_torch(input_t.dtype)
+        out_dt = DataType(self.output_dtype) if self.output_dtype is not None else in_dt
+        out_shape = [1 if i in self.axes else d for i, d in enumerate(input_t.shape)]
+        if output is None:
+            output = torch.empty(out_shape, dtype=to_torch(out_dt), device=input_t.device)
+        ib = _bind_tensor("input", input_t, in_dt)
+        ob = _bind_tensor("output", output, out_dt)
+        axes = (C.c_uint32 * max(1, len(self.axes)))(*self.axes)
+        h = C.c_void_p()
+        with torch.cuda.device(input_t.device):
+            _check(_host.thb_cub_reduction_stamp(int(self.op), axes, len(self.axes), int(self.output_dtype or 0), C.c_float(self.output_scale),
+                                                 C.byref(ib), C.byref(ob), _native.stream_handle(stream), input_t.device.index or 0, C.byref(h)))
+        return StampedCubReduction(h, input_t, output)
+
+
+class StampedCubArgReduction:
+    def __init__(self, plan, input_t, index, value, workspace, ws_bytes, stream):
+        self._plan, self._in, self.index, self.value, self._ws, self._ws_bytes, self._stream = plan, input_t, index, value, workspace, ws_bytes, stream
+
+    def __del__(self):
+        try:
+            _lib.thor_b200_argreduce_plan_destroy(self._plan)
+        except Exception:
+            pass
+
+    def run(self) -> None:
+        _native.check(_lib.thor_b200_argreduce_launch(self._plan, self._in.data_ptr(), self.value.data_ptr() if self.value is not None else None,
+                                                      self.index.data_ptr() if self.index is not None else None, self._ws.data_ptr(), self._ws_bytes,
+                                                      _native.stream_handle(self._stream)))
+
+
+class CubArgReduction:
+    def __init__(self, op: CubArgReductionOp, axes: Union[int, Sequence[int]], produce_value: bool = True, produce_index: bool = True,
+                 index_dtype: DataType = DataType.uint32):
+        self.op = CubArgReductionOp(op)
+        self.axes = [axes] if isinstance(axes, int) else list(axes)
+        self.produce_value, self.produce_index, self.index_dtype = produce_value, produce_index, DataType(index_dtype)
+
+    def stamp(self, input_t: torch.Tensor, stream=None, input_dtype: Optional[DataType] = None) -> StampedCubArgReduction:
+        in_dt = DataType(input_dtype) if input_dtype is not None else from_torch(input_t.dtype)
+        outer, red, inner, path = analyze_geometry(list(input_t.shape), self.axes)
+        if path == CubReductionPath.StridedFixedSegment:
+            raise _native.ThorB200InvalidArgument("CubArgReduction: reductions over non-adjacent axes are not provided by this build")
+        desc = _ArgDesc(int(self.op), int(in_dt), int(in_dt) if self.produce_value else 0, int(self.index_dtype), outer, red, inner)
+        plan = C.c_void_p()
+        ws = C.c_size_t()
+        with torch.cuda.device(input_t.device):
+            _native.check(_lib.thor_b200_argreduce_plan_create(C.byref(desc), C.byref(plan), C.byref(ws)))
+        out_shape = [1 if i in self.axes else d for i, d in enumerate(input_t.shape)]
+        index = torch.empty(out_shape, dtype=to_torch(self.index_dtype), device=input_t.device) if self.produce_index else None
+        value = torch.empty(out_shape, dtype=input_t.dtype, device=input_t.device) if self.produce_value else None
+        workspace = torch.empty(max(16, ws.value), dtype=torch.uint8, device=input_t.device)
+        return StampedCubArgReduction(plan, input_t, index, value, workspace, ws.value, stream)
