@@ -1,0 +1,543 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: fused expression / reduction / cast kernels on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2] [--no-extras]
+
+A step is one pass of the hot path over one batch of synthetic input resident in HBM.  The headline
+workload is configuration 2 (y = relu(a*x + b) * sigmoid(z), fp16 [8192, 8192], a per column, b an
+fp32 runtime scalar); with N > 1 every rank owns its own [8192, 8192] row shard of a [8192*N, 8192]
+problem (weak scaling, no data-path collective).  The other configurations are timed the same way
+and reported under "all_configs" (their full-reduction / dgamma partials are combined with one NCCL
+allreduce when N > 1).
+
+Timing: W >= 3 warm-up steps, then exactly K steps between a barrier + synchronize on both sides,
+bracketed by CUDA events on the launching stream; the max over ranks is reported.  Buffers rotate
+over several disjoint sets whose total size is several times the 126 MB L2, so no step finds its
+inputs in cache.  SM clocks and throttle reasons are sampled with nvidia-smi during the timed region.
+
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ---------------------------------------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------------------------------------
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def sample_count(self) -> int:
+        try:
+            return sum(1 for _ in open(self.path))
+        except Exception:
+            return 0
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        try:
+            rows = [r.split(",") for r in Path(self.path).read_text().strip().splitlines() if r.strip()]
+            os.unlink(self.path)
+        except Exception:
+            rows = []
+        clocks, reasons = [], set()
+        for r in rows:
+            try:
+                clocks.append(float(r[0]))
+                out["sm_max_mhz"] = float(r[1])
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                    if v.strip().lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        if clocks:
+            clocks.sort()
+            # median of the upper half: the samples taken while the kernels were running
+            busy = clocks[len(clocks) // 2:]
+            out["sm_mhz"] = busy[len(busy) // 2]
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(clocks)
+        return out
+
+
+class Dist:
+    def __init__(self, n_gpus: int):
+        import torch
+
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.enabled = self.world > 1
+        torch.cuda.set_device(self.local_rank if self.enabled else 0)
+        if self.enabled:
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+
+    def barrier(self):
+        import torch
+
+        if self.enabled:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max(self, v: float) -> float:
+        import torch
+
+        if not self.enabled:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_reduce(self, t, op="sum"):
+        if self.enabled:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM if op == "sum" else self.dist.ReduceOp.MAX)
+
+    def close(self):
+        if self.enabled:
+            self.dist.destroy_process_group()
+
+
+def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler | None = None):
+    """W untimed + K timed calls of step(i); returns (device ms per step as max over ranks, wall ms per step)."""
+    import torch
+
+    for i in range(warmup):
+        step(i)
+    dist.barrier()
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        step(warmup + i)
+    e1.record()
+    dist.barrier()
+    wall = (time.perf_counter() - t0) * 1e3 / steps
+    clocks = None
+    if sampler:
+        # nvidia-smi cannot sample faster than every few ms: when the timed region was shorter than that, keep the
+        # identical load running (untimed) until a handful of samples under load exist
+        extended = 0
+        t_ext = time.perf_counter()
+        while not dist.enabled and sampler.sample_count() < 5 and time.perf_counter() - t_ext < 2.0:
+            for i in range(steps):
+                step(warmup + steps + extended + i)
+            extended += steps
+            torch.cuda.synchronize()
+        clocks = sampler.stop()
+        clocks["untimed_extension_steps"] = extended
+    ms = dist.max(e0.elapsed_time(e1) / steps)
+    return ms, wall, clocks
+
+
+# ---------------------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------------------
+class Workload:
+    name = ""
+    description = ""
+    dtype = ""
+    unit_name = "elements"
+
+    def __init__(self, dist: Dist, scale: float = 1.0):
+        self.dist = dist
+        self.scale = scale  # fraction of the leading dimension (profiling captures use a smaller case)
+        self.sets = []
+        self.launches_per_step = 0
+        for attr in ("ROWS", "N"):
+            if hasattr(self, attr) and scale != 1.0:
+                setattr(self, attr, max(8, int(getattr(type(self), attr) * scale) // 8 * 8))
+
+    def algorithmic_bytes(self) -> int: raise NotImplementedError
+    def units(self) -> int: raise NotImplementedError
+    def setup(self): raise NotImplementedError
+    def step(self, i: int): raise NotImplementedError
+    def n_sets(self, bytes_per_set: int) -> int:
+        return max(2, min(8, -(-4 * L2_BYTES // max(1, bytes_per_set))))
+
+
+class C1Cast(Workload):
+    name = "c1_cast_fp32_fp16"
+    description = "TypeConverter fp32->fp16, 1-D, n=2^24, U(-4,4) with edge values at 0.1% (per GPU)"
+    dtype = "f32->f16"
+    N = 1 << 24
+
+    def setup(self):
+        import torch
+
+        from thor_b200 import TypeConverter
+        from thor_b200.workloads import cast_input
+
+        self.n = self.N
+        host = torch.from_numpy(cast_input(self.n, seed=self.dist.rank))
+        k = self.n_sets(self.algorithmic_bytes())
+        self.sets = [(host.cuda(), torch.empty(self.n, dtype=torch.float16, device="cuda")) for _ in range(k)]
+        self.convert = TypeConverter.convert_type
+        self.launches_per_step = 1
+        self.host_in = host.pin_memory()
+        self.host_out = torch.empty(self.n, dtype=torch.float16).pin_memory()
+
+    def algorithmic_bytes(self): return self.N * 6
+    def units(self): return self.N
+    def step(self, i):
+        src, dst = self.sets[i % len(self.sets)]
+        self.convert(src, dst)
+
+    def e2e_step(self, i):
+        src, dst = self.sets[i % len(self.sets)]
+        src.copy_(self.host_in, non_blocking=True)
+        self.convert(src, dst)
+        self.host_out.copy_(dst, non_blocking=True)
+
+    def e2e_bytes(self): return self.N * 4, self.N * 2
+
+
+class C2FusedExpr(Workload):
+    name = "c2_fused_relu_axb_sigmoid"
+    description = "y = relu(a*x + b) * sigmoid(z): x,z,y fp16 [8192,8192] per GPU, a fp16 [8192] per column, b fp32 runtime scalar 0.1"
+    dtype = "f16"
+    ROWS, COLS = 8192, 8192
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(1234 + self.dist.rank)
+        self.a = torch.empty(C, device="cuda", dtype=torch.float32).uniform_(0.5, 1.5, generator=gen).half()
+        eq = ex.compile(((ex.input("a") * ex.input("x") + ex.runtime_scalar("b")).max(0.0)) * ex.input("z").sigmoid())
+        self.eq = eq
+        k = self.n_sets(self.algorithmic_bytes())
+        self.sets = []
+        for _ in range(k):
+            x = torch.randn(R, C, device="cuda", dtype=torch.float32, generator=gen).half()
+            z = torch.randn(R, C, device="cuda", dtype=torch.float32, generator=gen).half()
+            y = torch.empty(R, C, device="cuda", dtype=torch.float16)
+            plan = eq.stamp({"a": self.a, "x": x, "z": z, "b": 0.1}, outputs={"output": y})
+            self.sets.append((plan, x, z, y))
+        self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
+        self.kernel_kind = self.sets[0][0].physical_stage_names()
+        self.host_x = self.sets[0][1].cpu().pin_memory()
+        self.host_z = self.sets[0][2].cpu().pin_memory()
+        self.host_y = torch.empty(R, C, dtype=torch.float16).pin_memory()
+
+    def algorithmic_bytes(self): return 3 * self.ROWS * self.COLS * 2 + self.COLS * 2
+    def units(self): return self.ROWS * self.COLS
+    def step(self, i): self.sets[i % len(self.sets)][0].run()
+
+    def e2e_step(self, i):
+        plan, x, z, y = self.sets[i % len(self.sets)]
+        x.copy_(self.host_x, non_blocking=True)
+        z.copy_(self.host_z, non_blocking=True)
+        plan.run()
+        self.host_y.copy_(y, non_blocking=True)
+
+    def e2e_bytes(self): return 2 * self.ROWS * self.COLS * 2, self.ROWS * self.COLS * 2
+
+    # CPU baseline: the oracle's C port of the same per-node-fp16 arithmetic on a row sample
+    def cpu_sample(self, rows: int, threads: int):
+        import numpy as np
+
+        import oracle
+
+        x = self.host_x[:rows].numpy()
+        z = self.host_z[:rows].numpy()
+        a = self.a.cpu().numpy()
+        t0 = time.perf_counter()
+        oracle.c2_fused(a, x, 0.1, z, True, threads)
+        dt = time.perf_counter() - t0
+        return (3 * rows * self.COLS * 2 + self.COLS * 2) / dt / 1e9, f"{rows} of {self.ROWS} rows x {self.COLS} cols, one pass"
+
+
+class C3Softmax(Workload):
+    name = "c3_softmax_rows_fp32"
+    description = "exp(x - max_row) / sum_row(exp(x - max_row)) on fp32 [65536,4096] per GPU (composed expression)"
+    dtype = "f32"
+    ROWS, COLS = 65536, 4096
+
+    def build(self, ex):
+        x = ex.input("x")
+        e = (x - x.reduce_max([1])).exp()
+        return {"y": e / e.reduce_sum([1])}
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(77 + self.dist.rank)
+        eq = ex.compile(self.build(ex))
+        self.sets = []
+        for _ in range(2):
+            x = torch.randn(R, C, device="cuda", generator=gen) * 3.0
+            y = torch.empty(R, C, device="cuda")
+            self.sets.append((eq.stamp({"x": x}, outputs={"y": y}), x, y))
+        self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
+        self.kernel_kind = self.sets[0][0].physical_stage_names()
+
+    def algorithmic_bytes(self): return 2 * self.ROWS * self.COLS * 4
+    def units(self): return self.ROWS * self.COLS
+    def step(self, i): self.sets[i % len(self.sets)][0].run()
+
+
+class C3Argmax(C3Softmax):
+    name = "c3_row_argmax_fp32"
+    description = "row argmax of fp32 [65536,4096] per GPU -> uint32 [65536]"
+
+    def build(self, ex):
+        return {"idx": ex.input("x").argmax([1], [1])}
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(78 + self.dist.rank)
+        eq = ex.compile(self.build(ex))
+        self.sets = []
+        for _ in range(2):
+            x = torch.randn(R, C, device="cuda", generator=gen) * 3.0
+            self.sets.append((eq.stamp({"x": x}), x))
+        self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
+        self.kernel_kind = self.sets[0][0].physical_stage_names()
+
+    def algorithmic_bytes(self): return self.ROWS * self.COLS * 4 + self.ROWS * 4
+
+
+class C4FullReduce(Workload):
+    name = "c4_full_reductions_bf16"
+    description = "sum, sum of squares ((x*x).reduce_sum()) and max over bf16 n=2^31 per GPU, fp32 accumulation"
+    dtype = "bf16->f32"
+    N = 1 << 31
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        gen = torch.Generator(device="cuda").manual_seed(99 + self.dist.rank)
+        self.x = torch.empty(self.N, device="cuda", dtype=torch.bfloat16)
+        chunk = min(self.N, 1 << 28)
+        for s in range(0, self.N, chunk):
+            n = min(chunk, self.N - s)
+            self.x[s:s + n] = (torch.randn(n, device="cuda", generator=gen) + 0.01).bfloat16()
+        x = ex.input("x")
+        eq = ex.compile({"sum": x.reduce_sum(), "sumsq": (x * x).reduce_sum(), "max": x.reduce_max()})
+        self.plan = eq.stamp({"x": self.x})
+        self.launches_per_step = self.plan.kernel_launches_per_run()
+        self.kernel_kind = self.plan.physical_stage_names()
+        self.outs = [self.plan.output(n) for n in ("sum", "sumsq", "max")]
+
+    def algorithmic_bytes(self): return self.N * 2
+    def units(self): return self.N
+    def step(self, i):
+        self.plan.run()
+        if self.dist.enabled:
+            # per-GPU fp32 partials -> one allreduce each (sum for the additive statistics, max for the maximum)
+            packed = torch_cat(self.outs[:2])
+            self.dist.all_reduce(packed, "sum")
+            self.dist.all_reduce(self.outs[2], "max")
+
+
+def torch_cat(ts):
+    import torch
+
+    return torch.cat([t.reshape(-1) for t in ts])
+
+
+WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c4": C4FullReduce}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# arms
+# ---------------------------------------------------------------------------------------------------------
+def reference_arm(args):
+    """The reference's own CPU implementation of the path, on the host cores of this machine.
+
+    The reference has a CPU path only for casts (TypeConverter::cpuConvertTypeImpl); its expressions and
+    reductions exist on the GPU only, so for the headline workload (configuration 2) this arm times the
+    CPU restatement of the reference's per-node arithmetic (oracle port), each step a bounded row sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+
+    import oracle
+
+    threads = oracle.host_threads()
+    rows, cols = 512, 8192
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((rows, cols)).astype(np.float16)
+    z = rng.standard_normal((rows, cols)).astype(np.float16)
+    a = rng.uniform(0.5, 1.5, cols).astype(np.float16)
+    bytes_per_step = 3 * rows * cols * 2 + cols * 2
+    for _ in range(max(1, args.warmup)):
+        oracle.c2_fused(a, x, 0.1, z, True, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.c2_fused(a, x, 0.1, z, True, threads)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = bytes_per_step / dt / 1e9
+    sample = f"{rows} of 8192 rows x {cols} cols per step (oracle C port, OpenMP)"
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_expr_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": {"workload": C2FusedExpr.name, "description": C2FusedExpr.description, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
+    }))
+
+
+def run_workload(dist: Dist, cls, steps: int, warmup: int, sample_clocks: bool, scale: float = 1.0):
+    import thor_b200
+
+    wl = cls(dist, scale)
+    wl.setup()
+    before = thor_b200.launch_count()
+    sampler = ClockSampler(dist.local_rank if dist.enabled else 0) if (sample_clocks and dist.rank == 0) else None
+    ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler)
+    launches = (thor_b200.launch_count() - before) * steps // (steps + warmup)
+    return wl, ms, wall, clocks, launches
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations, the end-to-end leg and the CPU baseline")
+    ap.add_argument("--scale", type=float, default=1.0, help="fraction of the workload's leading dimension (smaller cases for profiler captures only)")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+
+    import thor_b200
+
+    dist = Dist(args.gpus)
+    peak, peak_kind = measured_peak()
+    wl, ms, wall, clocks, launches = run_workload(dist, WORKLOADS[args.workload], args.steps, args.warmup, True, args.scale)
+    world = dist.world
+    total_bytes = wl.algorithmic_bytes() * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+    per_gpu_gbs = wl.algorithmic_bytes() / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "fused_expr_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "description": wl.description, "sharding": f"rows x{world}, no collective" if world > 1 else "single GPU",
+                   "cache": f"{len(wl.sets) or 1} rotating buffer sets, {wl.algorithmic_bytes() * max(1, len(wl.sets)) >> 20} MiB per GPU > 4 x L2",
+                   "kernel": getattr(wl, "kernel_kind", None), "scale": args.scale},
+        "elements_per_s": wl.units() * world / (ms * 1e-3),
+        "wall_ms_per_step": wall,
+        "clocks": clocks,
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
+                     "traffic": TRAFFIC_BYTES.get(wl.name), "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": wl.algorithmic_bytes(),
+                     "launch_us": ms * 1e3 / max(1, wl.launches_per_step)},
+    }
+
+    if not args.no_extras:
+        # end to end: pinned host buffers -> H2D -> kernel -> D2H inside the timed region
+        if hasattr(wl, "e2e_step"):
+            k = max(3, min(10, args.steps))
+            e_ms, _, _ = time_steps(dist, wl.e2e_step, k, 3)
+            h2d, d2h = wl.e2e_bytes()
+            line["e2e"] = {"value": total_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                           "ms_per_step": e_ms}
+        # CPU baseline on rank 0 at N = 1: bounded sample of the same workload
+        if world == 1 and hasattr(wl, "cpu_sample"):
+            import oracle
+
+            threads = oracle.host_threads()
+            wl.cpu_sample(64, threads)  # warm
+            v, sample = wl.cpu_sample(1024, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample}
+        del wl
+        torch.cuda.empty_cache()
+        extras = {}
+        for key, cls in WORKLOADS.items():
+            if key == args.workload:
+                continue
+            try:
+                w2, ms2, _, _, l2 = run_workload(dist, cls, max(5, args.steps // 5), 3, False)
+                g = w2.algorithmic_bytes() / (ms2 * 1e-3) / 1e9
+                extras[w2.name] = {"ms_per_step": ms2, "gbps_per_gpu": g, "gbps_total": g * world, "frac_of_peak": g / peak, "launches_per_step": w2.launches_per_step,
+                                   "kernels": getattr(w2, "kernel_kind", None), "algorithmic_bytes": w2.algorithmic_bytes(),
+                                   "elements_per_s": w2.units() * world / (ms2 * 1e-3)}
+                del w2
+                torch.cuda.empty_cache()
+            except Exception as exc:  # a configuration that cannot run must not hide the headline number
+                extras[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        line["all_configs"] = extras
+    if dist.rank == 0:
+        print(json.dumps(line))
+    dist.close()
+
+
+# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.
+TRAFFIC_BYTES = {}
+
+if __name__ == "__main__":
+    main()

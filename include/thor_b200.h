@@ -157,7 +157,10 @@ typedef struct thor_b200_expr_broadcast {
 typedef struct thor_b200_expr_options {
     int32_t use_fast_math; /* NVRTC --use_fast_math, off by default like FusedEquation::compile (FusedEquation.cpp:7014-7016) */
     int32_t compile_only;  /* 1: emit + compile to a cubin but do not load it (usable without a GPU or driver) */
-    int32_t reserved[6];   /* must be zero */
+    int32_t rows_per_thread;  /* tiled broadcast kernels: rows each thread walks (1, 2, 4 or 8); 0 = chosen by the emitter */
+    int32_t min_ctas_per_sm;  /* second argument of __launch_bounds__ (caps registers per thread); 0 = none */
+    int32_t packs_per_thread; /* flat kernels: 16-byte packs each thread handles (1, 2 or 4); 0 = chosen by the emitter */
+    int32_t reserved[3];      /* must be zero */
 } thor_b200_expr_options;
 
 typedef struct thor_b200_expr thor_b200_expr;
@@ -258,6 +261,51 @@ THOR_B200_API int thor_b200_argreduce_plan_create(const thor_b200_argreduce_desc
 THOR_B200_API int thor_b200_argreduce_launch(const thor_b200_argreduce_plan* plan, const void* input, void* value_output, void* index_output,
                                              void* workspace, size_t workspace_bytes, void* stream);
 THOR_B200_API void thor_b200_argreduce_plan_destroy(thor_b200_argreduce_plan* plan);
+
+/* ---------------------------------------------------------------------------------------------
+ * Row programs: "elementwise -> row reduction -> elementwise" chains as ONE single-pass kernel.
+ * No counterpart in the reference, which makes every reduction a stage boundary
+ * (EquationCompiler.cpp:684-688) and therefore runs a composed softmax as 4 kernels and a composed
+ * LayerNorm through materialised fp32 temporaries.  A row program takes the same SSA node list as
+ * thor_b200_expr_compile, extended with REDUCE_* nodes, over tensors that are [rows, cols] (FULL),
+ * [rows, 1] (ROW), [cols] (COL) or one element (SCALAR):
+ *   - REDUCE_{SUM,AVG,MIN,MAX,PROD,NORM1,NORM2} with input_slot = 0 reduces along the columns of a FULL
+ *     value and yields a ROW value that later nodes may consume (softmax max / sum, mean, variance);
+ *   - REDUCE_{SUM,AVG} with input_slot = 1 reduces along the rows of a FULL value and yields a COL value
+ *     that must be an output (LayerNorm dgamma / dbeta): persistent CTAs keep per-column fp32
+ *     partials in registers, write them to the workspace and a second kernel folds them in order.
+ * One CTA (or one warp for short rows) owns a row, keeps it in registers, and every node keeps the
+ * per-node dtype rule of the fused stages; reductions convert to fp32, accumulate in fp32 and
+ * round once to the node's output dtype, like the reduction seam.
+ * ------------------------------------------------------------------------------------------- */
+typedef enum thor_b200_row_shape {
+    THOR_B200_SHAPE_FULL = 0, THOR_B200_SHAPE_ROW = 1, THOR_B200_SHAPE_COL = 2, THOR_B200_SHAPE_SCALAR = 3
+} thor_b200_row_shape;
+
+typedef struct thor_b200_rowprog_desc {
+    const thor_b200_expr_node* nodes;
+    uint32_t n_nodes;
+    const thor_b200_expr_input* inputs;
+    const int32_t* input_shapes; /* thor_b200_row_shape per input (ignored for fp32 runtime scalars) */
+    uint32_t n_inputs;
+    const thor_b200_expr_output* outputs;
+    uint32_t n_outputs;
+    uint64_t rows, cols;
+    thor_b200_expr_options options;
+} thor_b200_rowprog_desc;
+
+typedef struct thor_b200_rowprog thor_b200_rowprog;
+
+/* Returns THOR_B200_UNSUPPORTED (and leaves *out_prog NULL) when the node list is valid but does not
+ * fit a row program (row too long for one CTA, a ROW value reduced again, ...): the caller then runs
+ * its ordinary stage list. */
+THOR_B200_API int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* desc, thor_b200_rowprog** out_prog, size_t* workspace_bytes);
+THOR_B200_API int thor_b200_rowprog_launch(thor_b200_rowprog* prog, const void* const* input_ptrs, const float* runtime_scalars,
+                                           void* const* output_ptrs, void* workspace, size_t workspace_bytes, void* stream);
+THOR_B200_API const char* thor_b200_rowprog_source(const thor_b200_rowprog* prog);
+/* Kernels one launch of the program runs (1, or 2 when column reductions need the fold kernel). */
+THOR_B200_API uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* prog);
+THOR_B200_API void thor_b200_rowprog_destroy(thor_b200_rowprog* prog);
 
 #ifdef __cplusplus
 }

@@ -109,3 +109,80 @@ def to_float64(a: np.ndarray, dtype: int) -> np.ndarray:
 def from_float32(a: np.ndarray, dtype: int) -> np.ndarray:
     """Encode float32 values into the storage array of dtype with one RNE rounding."""
     return cast(np.ascontiguousarray(a, dtype=np.float32), FP32, dtype) if dtype != FP32 else np.ascontiguousarray(a, dtype=np.float32)
+
+
+# ---- workload-sized loops of thor_oracle.c --------------------------------------------------------
+def _setup_workloads():
+    L = lib()
+    if getattr(L, "_workloads_ready", False):
+        return L
+    c = ctypes
+    L.tor_c2_fused.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_int64, c.c_int64, c.c_int, c.c_int]
+    L.tor_c2_fused.restype = None
+    L.tor_softmax_rows_f32.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int64, c.c_int64, c.c_int]
+    L.tor_softmax_rows_f32.restype = None
+    L.tor_c4_stats_bf16.argtypes = [c.c_void_p, c.c_int64, c.POINTER(c.c_double), c.POINTER(c.c_double), c.POINTER(c.c_float), c.c_int]
+    L.tor_c4_stats_bf16.restype = None
+    L.tor_layernorm_fwd_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int64, c.c_int64, c.c_int]
+    L.tor_layernorm_fwd_bf16.restype = None
+    L.tor_layernorm_bwd_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int64, c.c_int64, c.c_int]
+    L.tor_layernorm_bwd_bf16.restype = None
+    L._workloads_ready = True
+    return L
+
+
+def host_threads() -> int:
+    import os
+
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def c2_fused(a: np.ndarray, x: np.ndarray, b: float, z: np.ndarray, fuse_mul_add: bool = False, threads: int = 0) -> np.ndarray:
+    """relu(a*x + b) * sigmoid(z), every node fp16; arrays are np.float16 ([cols], [rows, cols], [rows, cols])."""
+    L = _setup_workloads()
+    rows, cols = x.shape
+    a, x, z = (np.ascontiguousarray(v, dtype=np.float16) for v in (a, x, z))
+    y = np.empty((rows, cols), np.float16)
+    L.tor_c2_fused(_ptr(a), _ptr(x), float(b), _ptr(z), _ptr(y), rows, cols, int(fuse_mul_add), threads or host_threads())
+    return y
+
+
+def softmax_rows(x: np.ndarray, want_softmax: bool = True, want_argmax: bool = True, threads: int = 0):
+    L = _setup_workloads()
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    y = np.empty_like(x) if want_softmax else None
+    idx = np.empty(rows, np.uint32) if want_argmax else None
+    L.tor_softmax_rows_f32(_ptr(x), _ptr(y) if y is not None else None, _ptr(idx) if idx is not None else None, rows, cols, threads or host_threads())
+    return y, idx
+
+
+def c4_stats(x_bf16: np.ndarray, threads: int = 0):
+    """(sum, sum of bf16-rounded squares, max) of a bf16 vector given as uint16 storage; fp64 accumulation."""
+    L = _setup_workloads()
+    x = np.ascontiguousarray(x_bf16, dtype=np.uint16)
+    s, q, m = ctypes.c_double(), ctypes.c_double(), ctypes.c_float()
+    L.tor_c4_stats_bf16(_ptr(x), x.size, ctypes.byref(s), ctypes.byref(q), ctypes.byref(m), threads or host_threads())
+    return s.value, q.value, m.value
+
+
+def layernorm_fwd(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float = 1e-5, threads: int = 0):
+    """bf16 storage (uint16) in, bf16 y out plus fp32 mean / rstd per row."""
+    L = _setup_workloads()
+    rows, cols = x.shape
+    y = np.empty((rows, cols), np.uint16)
+    mean, rstd = np.empty(rows, np.float32), np.empty(rows, np.float32)
+    L.tor_layernorm_fwd_bf16(_ptr(np.ascontiguousarray(x)), _ptr(np.ascontiguousarray(gamma)), _ptr(np.ascontiguousarray(beta)), eps, _ptr(y), _ptr(mean),
+                             _ptr(rstd), rows, cols, threads or host_threads())
+    return y, mean, rstd
+
+
+def layernorm_bwd(x: np.ndarray, gamma: np.ndarray, dy: np.ndarray, eps: float = 1e-5, threads: int = 0):
+    """bf16 storage in; returns dx (bf16 storage), dgamma, dbeta (float64)."""
+    L = _setup_workloads()
+    rows, cols = x.shape
+    dx = np.empty((rows, cols), np.uint16)
+    dg, db = np.empty(cols, np.float64), np.empty(cols, np.float64)
+    L.tor_layernorm_bwd_bf16(_ptr(np.ascontiguousarray(x)), _ptr(np.ascontiguousarray(gamma)), _ptr(np.ascontiguousarray(dy)), eps, _ptr(dx), _ptr(dg),
+                             _ptr(db), rows, cols, threads or host_threads())
+    return dx, dg, db

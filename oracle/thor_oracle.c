@@ -223,3 +223,206 @@ API void tor_cast_f32_f16(const float* src, uint16_t* dst, int64_t n, int thread
 #pragma omp parallel for schedule(static) num_threads(threads)
     for (int64_t i = 0; i < n; ++i) dst[i] = tor_f32_to_f16(src[i]);
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Fast fp32 <-> fp16 / bf16 for the workload-sized loops below (bit tricks, RNE, NaN -> 0x7FFF);
+ * checked against encode_rne / decode over all inputs classes by tests/test_oracle_cast.py.
+ * ---------------------------------------------------------------------------------------- */
+static inline uint16_t fast_f32_to_f16(float f) {
+    uint32_t x = f32_bits(f);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t a = x & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return 0x7FFF;                    /* NaN */
+    if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u); /* >= 65520 rounds to inf (also inf) */
+    if (a < 0x38800000u) {                                   /* below the smallest normal half: subnormal or zero */
+        if (a < 0x33000000u) return (uint16_t)sign;          /* < 2^-25: rounds to zero (2^-25 itself ties to even = 0) */
+        /* add the magic constant 0.5f: the float adder performs the RNE rounding to the 2^-24 grid */
+        float m = bits_f32(a) + 0.5f;
+        return (uint16_t)(sign | (f32_bits(m) - 0x3F000000u));
+    }
+    uint32_t mant_odd = (a >> 13) & 1u;
+    a += 0xC8000FFFu + mant_odd; /* rebias exponent (-112 << 23) and round to nearest even */
+    return (uint16_t)(sign | (a >> 13));
+}
+static inline float fast_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t em = h & 0x7FFFu;
+    if (em >= 0x7C00u) return bits_f32(sign | 0x7F800000u | ((em & 0x3FFu) << 13));
+    if (em < 0x0400u) { /* subnormal: value = em * 2^-24 */
+        float v = (float)em * 5.9604644775390625e-8f;
+        return sign ? -v : v;
+    }
+    return bits_f32(sign | ((em + 0x1C000u) << 13));
+}
+static inline uint16_t fast_f32_to_bf16(float f) {
+    uint32_t x = f32_bits(f);
+    if ((x & 0x7FFFFFFFu) > 0x7F800000u) return 0x7FFF;
+    x += 0x7FFFu + ((x >> 16) & 1u);
+    return (uint16_t)(x >> 16);
+}
+static inline float rh(float v) { return fast_f16_to_f32(fast_f32_to_f16(v)); }   /* round through fp16 */
+static inline float rb(float v) { return bits_f32((uint32_t)fast_f32_to_bf16(v) << 16); } /* round through bf16 */
+
+API uint16_t tor_fast_f32_to_f16(float f) { return fast_f32_to_f16(f); }
+API float tor_fast_f16_to_f32(uint16_t h) { return fast_f16_to_f32(h); }
+API uint16_t tor_fast_f32_to_bf16(float f) { return fast_f32_to_bf16(f); }
+
+/* ------------------------------------------------------------------------------------------
+ * Configuration 2: y = relu(a*x + b) * sigmoid(z) with every node in fp16
+ * (dtype assignment ExpressionDTypeResolution.cpp:1012-1128; sigmoid composite Expression.h:1077-1088;
+ * relu = max(x, 0), DeepLearning/Api/Layers/Activations/Relu.h:21-22).  Every node result is rounded
+ * to fp16; b is first rounded to fp16 (scalars take the stage's 16-bit compute type,
+ * CudaSourceEmitter.cpp:4034-4043).  fuse_mul_add = 1 evaluates a*x+b as one fused multiply-add
+ * (what -fmad=true lets the compiler do with __hmul2 + __hadd2); 0 rounds the product first.
+ * x, z, y: [rows, cols]; a: [cols].
+ * ---------------------------------------------------------------------------------------- */
+API void tor_c2_fused(const uint16_t* a, const uint16_t* x, float b, const uint16_t* z, uint16_t* y, int64_t rows, int64_t cols, int fuse_mul_add,
+                      int threads) {
+    const float bh = rh(b);
+    if (threads < 1) threads = 1;
+#pragma omp parallel for schedule(static) num_threads(threads)
+    for (int64_t r = 0; r < rows; ++r) {
+        for (int64_t c = 0; c < cols; ++c) {
+            const float av = fast_f16_to_f32(a[c]), xv = fast_f16_to_f32(x[r * cols + c]), zv = fast_f16_to_f32(z[r * cols + c]);
+            float lin;
+            if (fuse_mul_add) lin = rh((float)((double)av * (double)xv + (double)bh)); /* exact product + one rounding */
+            else lin = rh(rh(av * xv) + bh);
+            const float relu = lin > 0.0f ? lin : 0.0f;             /* max(lin, 0) */
+            const float neg = -zv;
+            const float num = rh(expf(-(neg > 0.0f ? neg : 0.0f))); /* exp(-max(-z, 0)) */
+            const float den = rh(1.0f + rh(expf(-fabsf(zv))));      /* 1 + exp(-|z|) */
+            const float sig = rh(num / den);
+            y[r * cols + c] = fast_f32_to_f16(relu * sig);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Configuration 3: composed softmax over the last axis of fp32 [rows, cols] plus row argmax.
+ * m = reduce_max (exact), e = expf(x - m) per element in fp32, s = sum(e) accumulated in fp64
+ * (CubReductionOperation.cuh:60-129 accumulates in fp32; the fp64 sum is the accuracy reference
+ * both are compared to), y = e / s in fp32.  argmax: NaN wins, lowest index wins ties
+ * (CubArgReductionOperation.cuh:31-73).
+ * ---------------------------------------------------------------------------------------- */
+API void tor_softmax_rows_f32(const float* x, float* y, uint32_t* argmax, int64_t rows, int64_t cols, int threads) {
+    if (threads < 1) threads = 1;
+#pragma omp parallel for schedule(static) num_threads(threads)
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* p = x + r * cols;
+        float m = -INFINITY;
+        int64_t best = 0;
+        int has_nan = 0;
+        for (int64_t c = 0; c < cols; ++c) {
+            const float v = p[c];
+            if (v != v) { if (!has_nan) { has_nan = 1; best = c; m = v; } continue; }
+            if (!has_nan && (c == 0 || v > m)) { m = v; best = c; }
+        }
+        if (argmax) argmax[r] = (uint32_t)best;
+        if (!y) continue;
+        double s = 0.0;
+        for (int64_t c = 0; c < cols; ++c) { const float e = expf(p[c] - m); y[r * cols + c] = e; s += e; }
+        const float sf = (float)s;
+        for (int64_t c = 0; c < cols; ++c) y[r * cols + c] = y[r * cols + c] / sf;
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Configuration 4: sum, sum of squares and max of a bf16 vector.  sum-of-squares is spelled
+ * (x*x).reduce_sum() (cf. DeepLearning/Implementation/Layers/Optimizers/Lamb.cpp:106): the product
+ * node is a bf16 node, so it is rounded to bf16 before the fp32 conversion of the reduction.
+ * Accumulation here is fp64 over those rounded operands.
+ * ---------------------------------------------------------------------------------------- */
+API void tor_c4_stats_bf16(const uint16_t* x, int64_t n, double* sum, double* sumsq, float* maxv, int threads) {
+    double s = 0.0, q = 0.0;
+    float m = -INFINITY;
+    int has_nan = 0;
+    if (threads < 1) threads = 1;
+#pragma omp parallel for schedule(static) num_threads(threads) reduction(+ : s, q) reduction(max : m) reduction(| : has_nan)
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = bits_f32((uint32_t)x[i] << 16);
+        s += v;
+        q += rb(v * v);
+        if (v != v) has_nan = 1;
+        else if (v > m) m = v;
+    }
+    *sum = s;
+    *sumsq = q;
+    *maxv = has_nan ? NAN : m;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Configuration 5: LayerNorm written as an Expression DAG over bf16 [rows, cols]:
+ *   mean = x.reduce_mean({1}); xc = x - mean; var = (xc*xc).reduce_mean({1});
+ *   rstd = 1 / sqrt(var + eps); y = (xc * rstd * gamma + beta).cast(BF16)
+ * Everything from xc onward is fp32 (bf16 - fp32 promotes, ExpressionDTypeResolution.cpp:277-307);
+ * reductions accumulate here in fp64 and are rounded to fp32 like every reduction output.
+ * Backward (reverse-mode of that DAG, AutoDiff.cpp:3690-5930), with g = dy * gamma, xhat = xc * rstd:
+ *   dx = rstd * (g - mean_row(g) - xhat * mean_row(g * xhat)),
+ *   dgamma = sum_rows(dy * xhat), dbeta = sum_rows(dy)       (fp32 outputs)
+ * ---------------------------------------------------------------------------------------- */
+API void tor_layernorm_fwd_bf16(const uint16_t* x, const uint16_t* gamma, const uint16_t* beta, float eps, uint16_t* y, float* mean_out,
+                                float* rstd_out, int64_t rows, int64_t cols, int threads) {
+    if (threads < 1) threads = 1;
+#pragma omp parallel for schedule(static) num_threads(threads)
+    for (int64_t r = 0; r < rows; ++r) {
+        const uint16_t* p = x + r * cols;
+        double s = 0.0;
+        for (int64_t c = 0; c < cols; ++c) s += bits_f32((uint32_t)p[c] << 16);
+        const float mean = (float)s / (float)cols;
+        double q = 0.0;
+        for (int64_t c = 0; c < cols; ++c) { const float xc = bits_f32((uint32_t)p[c] << 16) - mean; q += (double)(xc * xc); }
+        const float var = (float)q / (float)cols;
+        const float rstd = 1.0f / sqrtf(var + eps);
+        if (mean_out) mean_out[r] = mean;
+        if (rstd_out) rstd_out[r] = rstd;
+        if (y)
+            for (int64_t c = 0; c < cols; ++c) {
+                const float xc = bits_f32((uint32_t)p[c] << 16) - mean;
+                const float v = xc * rstd * bits_f32((uint32_t)gamma[c] << 16) + bits_f32((uint32_t)beta[c] << 16);
+                y[r * cols + c] = fast_f32_to_bf16(v);
+            }
+    }
+}
+
+API void tor_layernorm_bwd_bf16(const uint16_t* x, const uint16_t* gamma, const uint16_t* dy, float eps, uint16_t* dx, double* dgamma, double* dbeta,
+                                int64_t rows, int64_t cols, int threads) {
+    if (threads < 1) threads = 1;
+    for (int64_t c = 0; c < cols; ++c) { dgamma[c] = 0.0; dbeta[c] = 0.0; }
+#pragma omp parallel num_threads(threads)
+    {
+        double* lg = (double*)calloc((size_t)cols, sizeof(double));
+        double* lb = (double*)calloc((size_t)cols, sizeof(double));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            const uint16_t* p = x + r * cols;
+            const uint16_t* d = dy + r * cols;
+            double s = 0.0;
+            for (int64_t c = 0; c < cols; ++c) s += bits_f32((uint32_t)p[c] << 16);
+            const float mean = (float)s / (float)cols;
+            double q = 0.0;
+            for (int64_t c = 0; c < cols; ++c) { const float xc = bits_f32((uint32_t)p[c] << 16) - mean; q += (double)(xc * xc); }
+            const float rstd = 1.0f / sqrtf((float)q / (float)cols + eps);
+            double sg = 0.0, sgx = 0.0;
+            for (int64_t c = 0; c < cols; ++c) {
+                const double xhat = (double)(bits_f32((uint32_t)p[c] << 16) - mean) * rstd;
+                const double dyv = bits_f32((uint32_t)d[c] << 16);
+                const double g = dyv * bits_f32((uint32_t)gamma[c] << 16);
+                sg += g;
+                sgx += g * xhat;
+                lg[c] += dyv * xhat;
+                lb[c] += dyv;
+            }
+            const double mg = sg / (double)cols, mgx = sgx / (double)cols;
+            if (dx)
+                for (int64_t c = 0; c < cols; ++c) {
+                    const double xhat = (double)(bits_f32((uint32_t)p[c] << 16) - mean) * rstd;
+                    const double g = (double)bits_f32((uint32_t)d[c] << 16) * bits_f32((uint32_t)gamma[c] << 16);
+                    dx[r * cols + c] = fast_f32_to_bf16((float)(rstd * (g - mg - xhat * mgx)));
+                }
+        }
+#pragma omp critical
+        for (int64_t c = 0; c < cols; ++c) { dgamma[c] += lg[c]; dbeta[c] += lb[c]; }
+        free(lg);
+        free(lb);
+    }
+}

@@ -79,7 +79,7 @@ def test_mixed_dtype_promotion_and_cast():
     assert res["p"][1].dtype == o.FP32 and res["q"][1].dtype == o.BF16 and res["r"][1].dtype == o.BF16
     assert_ulp(*res["p"], 1.0)
     assert_ulp(*res["q"], 1.0)
-    assert_ulp(*res["r"], 1.0, atol=1e-2)
+    assert_ulp(*res["r"], 1.0, atol=2e-2)
 
 
 def test_comparison_where_and_logical():
@@ -119,7 +119,9 @@ def test_row_and_column_broadcast(dtype, shape):
     cols = shape[-1]
     ins = make_inputs({"x": (shape, dtype, -2, 2), "c": ((cols,), dtype, 0.5, 1.5), "r": (shape[:-1] + (1,), dtype, -1, 1)}, seed=5)
     plan, res = run_both(lambda ns: (ns.input("x") * ns.input("c") - ns.input("r")).max(0.0), ins)
-    assert_ulp(*res["output"], 1.0, atol=4e-3 if dtype != o.FP32 else 1e-6)
+    # x*c - r may contract to one fma on the GPU (-fmad=true, as in the reference): the two forms differ by up
+    # to half an ulp of the PRODUCT (|x*c| < 4), an absolute slack when the difference is small
+    assert_ulp(*res["output"], 1.0, atol={o.FP32: 1e-6, o.FP16: 4e-3, o.BF16: 2e-2}[dtype])
     kind = plan.physical_stage_names()[0]
     vec = 4 if dtype == o.FP32 else 8
     assert kind.startswith("bcast_tiled" if cols % vec == 0 else "bcast_generic"), kind
@@ -133,15 +135,39 @@ def test_middle_axis_broadcast_uses_row_offsets():
 
 
 def test_configuration_2_small():
-    """y = relu(a*x + b) * sigmoid(z), fp16, a per column, b an fp32 runtime scalar (small rows x 8192 cols)."""
-    ins = make_inputs({"x": ((64, 8192), o.FP16, -3, 3), "z": ((64, 8192), o.FP16, -3, 3), "a": ((8192,), o.FP16, 0.5, 1.5)}, seed=0)
-    plan, res = run_both(lambda ns: ((ns.input("a") * ns.input("x") + ns.runtime_scalar("b")).max(0.0)) * ns.input("z").sigmoid(), ins, {"b": 0.1})
-    got, want = res["output"]
-    # a*x+b may be one fma on the GPU (result within 1 ulp of a*x+b at the magnitude of the sum, i.e. an
-    # absolute slack near cancellation); h2exp / __h2div add up to ~2 ulp on the sigmoid factor
-    assert_ulp(got, want, 3.0, frac_within_1=0.95, atol=2e-3)
+    """y = relu(a*x + b) * sigmoid(z), fp16, a per column, b an fp32 runtime scalar (512 rows x 8192 cols).
+
+    Checked against the C restatement with a*x+b evaluated as ONE fused multiply-add: the reference compiles
+    its kernels with -fmad=true (EquationCompiler.cpp:1875) and its pair intrinsics __hmul2 / __hadd2 may be
+    contracted, which is what the compiler does with this pattern.  Tolerance: 1 fp16 ulp."""
+    import torch
+
+    from thor_b200.expression import Expression as ex
+
+    rng = np.random.default_rng(0)
+    rows, cols = 512, 8192
+    x = rng.standard_normal((rows, cols)).astype(np.float16)
+    z = rng.standard_normal((rows, cols)).astype(np.float16)
+    a = rng.uniform(0.5, 1.5, cols).astype(np.float16)
+    eq = ex.compile(((ex.input("a") * ex.input("x") + ex.runtime_scalar("b")).max(0.0)) * ex.input("z").sigmoid())
+    plan = eq.stamp({"a": torch.from_numpy(a).cuda(), "x": torch.from_numpy(x).cuda(), "z": torch.from_numpy(z).cuda(), "b": 0.1})
+    plan.run()
+    torch.cuda.synchronize()
+    got = plan.output().cpu().numpy().astype(np.float64)
+    want = o.c2_fused(a, x, 0.1, z, fuse_mul_add=True).astype(np.float64)
+    from oracle import expr_oracle as eo
+
+    d = eo.ulp_distance(got, want, o.FP16)
+    assert d.max() <= 1.0, d.max()
+    assert (d == 0).mean() > 0.9999
     assert plan.physical_stage_names() == ["bcast_tiled_v2"]
     assert "__hmax2" in plan.stage_sources()[0] and "h2exp" in plan.stage_sources()[0]
+    # the literal spelling Expression(0.1) gives the same bits as the runtime scalar
+    eq2 = ex.compile(((ex.input("a") * ex.input("x") + 0.1).max(0.0)) * ex.input("z").sigmoid())
+    plan2 = eq2.stamp({"a": torch.from_numpy(a).cuda(), "x": torch.from_numpy(x).cuda(), "z": torch.from_numpy(z).cuda()})
+    plan2.run()
+    torch.cuda.synchronize()
+    assert torch.equal(plan2.output(), plan.output())
 
 
 def test_multiple_outputs_share_one_stage():

@@ -1,0 +1,169 @@
+"""Row programs (softmax / LayerNorm class) against the staged execution and the CPU oracle.
+
+Tolerances: fp32-accumulated row statistics 1e-5 relative; fp32 elementwise results <= 2 ulp given
+identical row statistics (so the end-to-end bound on softmax values is 1e-5 relative); bf16 outputs
+<= 1 bf16 ulp plus the fp32 rounding noise of the terms that cancel (stated per test)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from oracle import expr_oracle as eo
+from thor_b200 import DataType
+from thor_b200.expression import Expression as ex
+
+pytestmark = pytest.mark.gpu
+
+
+def _softmax_expr():
+    x = ex.input("x")
+    e = (x - x.reduce_max([1])).exp()
+    return e / e.reduce_sum([1])
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 1000), (257, 128), (5, 32768), (1000, 36)])
+def test_softmax_row_program_matches_staged_and_oracle(rows, cols):
+    x = (torch.randn(rows, cols, device="cuda") * 3.0).contiguous()
+    fused = ex.compile(_softmax_expr(), fuse_row_reductions=True).stamp({"x": x})
+    staged = ex.compile(_softmax_expr(), fuse_row_reductions=False).stamp({"x": x})
+    fused.run()
+    staged.run()
+    torch.cuda.synchronize()
+    assert fused.physical_stage_names() == ["row_program"], fused.physical_stage_names()
+    assert staged.physical_stage_names()[0].startswith("rows_")
+    # the logical stage list is what the reference's planner reports (Reduction, Fused, Reduction, Fused)
+    assert fused.stage_kind_names() == staged.stage_kind_names() == ["Reduction", "FusedKernel", "Reduction", "FusedKernel"]
+    want, _ = o.softmax_rows(x.cpu().numpy(), want_argmax=False)
+    for plan in (fused, staged):
+        got = plan.output().cpu().numpy()
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-12)
+    assert fused.kernel_launches_per_run() == 1 and staged.kernel_launches_per_run() == 4
+    assert fused.intermediate_bytes() <= 1 and staged.intermediate_bytes() >= rows * cols * 4
+
+
+def test_softmax_rows_with_nan_and_inf_follow_the_staged_semantics():
+    x = torch.randn(8, 256, device="cuda")
+    x[1, 5] = float("inf")
+    x[2, 7] = float("nan")
+    x[3, :] = -float("inf")
+    fused = ex.compile(_softmax_expr()).stamp({"x": x})
+    staged = ex.compile(_softmax_expr(), fuse_row_reductions=False).stamp({"x": x})
+    fused.run()
+    staged.run()
+    torch.cuda.synchronize()
+    a, b = fused.output().cpu().numpy(), staged.output().cpu().numpy()
+    assert np.array_equal(np.isnan(a), np.isnan(b))
+    np.testing.assert_allclose(a[~np.isnan(a)], b[~np.isnan(b)], rtol=1e-5)
+
+
+def _layernorm(dtype_out=DataType.bf16, eps=1e-5):
+    x, gamma, beta = ex.input("x"), ex.input("gamma"), ex.input("beta")
+    mean = x.reduce_mean([1])
+    xc = x - mean
+    var = (xc * xc).reduce_mean([1])
+    rstd = 1.0 / (var + eps).sqrt()
+    return (xc * rstd * gamma + beta).cast(dtype_out)
+
+
+def _bf16(t):
+    return t.view(torch.uint16).cpu().numpy()
+
+
+def _ln_inputs(rows, cols, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    gamma = (torch.rand(cols, device="cuda", generator=g) * 0.2 + 0.9).bfloat16()
+    beta = (torch.randn(cols, device="cuda", generator=g) * 0.02).bfloat16()
+    dy = (torch.randn(rows, cols, device="cuda", generator=g) * 1e-2).bfloat16()
+    return x, gamma, beta, dy
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 8192), (300, 1024), (17, 256), (1024, 64)])
+def test_layernorm_forward_row_program(rows, cols):
+    x, gamma, beta, _ = _ln_inputs(rows, cols)
+    fused = ex.compile(_layernorm()).stamp({"x": x, "gamma": gamma, "beta": beta})
+    staged = ex.compile(_layernorm(), fuse_row_reductions=False).stamp({"x": x, "gamma": gamma, "beta": beta})
+    fused.run()
+    staged.run()
+    torch.cuda.synchronize()
+    assert fused.physical_stage_names() == ["row_program"]
+    assert len(staged.physical_stage_names()) >= 4
+    want, _, _ = o.layernorm_fwd(_bf16(x), _bf16(gamma), _bf16(beta), 1e-5)
+    wantf = o.to_float64(want.reshape(-1), o.BF16).reshape(rows, cols)
+    for plan in (fused, staged):
+        got = o.to_float64(_bf16(plan.output()).reshape(-1), o.BF16).reshape(rows, cols)
+        d = eo.ulp_distance(got, wantf, o.BF16)
+        assert d.max() <= 1.0, d.max()
+        assert (d == 0).mean() > 0.99
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 8192), (300, 1024), (48, 256)])
+def test_layernorm_backward_from_autodiff(rows, cols):
+    """dx, dgamma, dbeta of the LayerNorm DAG produced by compile_backward, as a row program with column
+    reductions, against the staged plan and the fp64 oracle."""
+    x, gamma, beta, dy = _ln_inputs(rows, cols, seed=3)
+    fwd = ex.compile({"y": _layernorm()})
+    bwd = fwd.compile_backward(["x", "gamma", "beta"])
+    binds = {"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy}
+    fused = bwd.stamp(binds)
+    fused.run()
+    torch.cuda.synchronize()
+    assert fused.physical_stage_names() == ["row_program"], fused.physical_stage_names()
+    dx_w, dg_w, db_w = o.layernorm_bwd(_bf16(x), _bf16(gamma), _bf16(dy), 1e-5)
+    dxw = o.to_float64(dx_w.reshape(-1), o.BF16).reshape(rows, cols)
+    dx = fused.output("x_grad")
+    assert dx.dtype == torch.bfloat16
+    got = o.to_float64(_bf16(dx).reshape(-1), o.BF16).reshape(rows, cols)
+    # dx = rstd * (g - mean(g) - xhat * mean(g * xhat)): the three terms are O(|dy|) and cancel partly, so the
+    # fp32 noise of the terms (a few 1e-7 of |dy| ~ 1e-2) adds to the 1-ulp bf16 rounding of the result
+    d = eo.ulp_distance(got, dxw, o.BF16)
+    d = np.where(np.abs(got - dxw) <= 2e-8, 0.0, d)
+    assert d.max() <= 1.0, d.max()
+    dg = fused.output("gamma_grad").float().cpu().numpy().astype(np.float64).reshape(-1)
+    db = fused.output("beta_grad").float().cpu().numpy().astype(np.float64).reshape(-1)
+    scale_g = np.abs(dg_w) + 1e-3 * np.sqrt(rows) * 1e-2
+    assert fused.output("gamma_grad").dtype == torch.float32
+    assert (np.abs(dg - dg_w) <= 1e-5 * scale_g + 2e-7 * rows * 1e-2).all()
+    assert (np.abs(db - db_w) <= 1e-5 * np.abs(db_w) + 2e-7 * rows * 1e-2).all()
+
+
+def test_layernorm_backward_staged_plan_agrees():
+    rows, cols = 96, 512
+    x, gamma, beta, dy = _ln_inputs(rows, cols, seed=5)
+    fwd_f = ex.compile({"y": _layernorm()}, fuse_row_reductions=True)
+    fwd_s = ex.compile({"y": _layernorm()}, fuse_row_reductions=False)
+    binds = {"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy}
+    pf = fwd_f.compile_backward(["x", "gamma", "beta"]).stamp(binds)
+    ps = fwd_s.compile_backward(["x", "gamma", "beta"]).stamp(binds)
+    pf.run()
+    ps.run()
+    torch.cuda.synchronize()
+    assert len(ps.physical_stage_names()) > 4 and "row_program" not in ps.physical_stage_names()
+    for name in ("x_grad", "gamma_grad", "beta_grad"):
+        a, b = pf.output(name).float(), ps.output(name).float()
+        assert torch.allclose(a.reshape(-1), b.reshape(-1), rtol=2e-2 if name == "x_grad" else 1e-4, atol=1e-6), name
+
+
+def test_autodiff_elementwise_chain():
+    """d/dx sum(tanh(x) * y) = (1 - tanh(x)^2) * y, d/dy = tanh(x)."""
+    x = torch.randn(4, 256, device="cuda")
+    y = torch.randn(4, 256, device="cuda")
+    g = torch.ones(4, 256, device="cuda")
+    eq = ex.compile({"out": ex.input("x").tanh() * ex.input("y")})
+    plan = eq.compile_backward(["x", "y"]).stamp({"x": x, "y": y, "__grad_output": g})
+    plan.run()
+    torch.cuda.synchronize()
+    assert torch.allclose(plan.output("x_grad"), (1 - torch.tanh(x) ** 2) * y, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(plan.output("y_grad"), torch.tanh(x), rtol=1e-5, atol=1e-6)
+
+
+def test_autodiff_unbroadcasts_with_reduce_sum():
+    x = torch.randn(32, 128, device="cuda")
+    w = torch.randn(128, device="cuda")
+    g = torch.randn(32, 128, device="cuda")
+    eq = ex.compile({"out": ex.input("x") * ex.input("w")})
+    plan = eq.compile_backward(["w"]).stamp({"x": x, "w": w, "__grad_output": g})
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.output("w_grad").shape == (128,)
+    assert torch.allclose(plan.output("w_grad"), (g * x).sum(0), rtol=1e-5, atol=1e-5)

@@ -203,14 +203,14 @@ void decideV2(Plan& p) {
 std::string nodeVar(size_t k) { return "v" + std::to_string(k); }
 
 // ---- scalar body -------------------------------------------------------------------------------
-std::string scalarNodeExpr(const Plan& p, size_t k) {
-    const auto& nd = p.st.nodes[k];
+std::string scalarNodeExprImpl(const std::vector<thor_b200_expr_node>& nodes, const std::vector<thor_b200_expr_input>& inputs, size_t k) {
+    const auto& nd = nodes[k];
     const int C = nd.compute_dtype, O = nd.output_dtype;
-    auto parent = [&](uint32_t idx, int to) { return cvt(nodeVar(idx), p.st.nodes[idx].output_dtype, to); };
+    auto parent = [&](uint32_t idx, int to) { return cvt(nodeVar(idx), nodes[idx].output_dtype, to); };
     switch (nd.op) {
-        case THOR_B200_OP_INPUT: return cvt("x" + std::to_string(nd.input_slot), p.st.inputs[nd.input_slot].dtype, O);
+        case THOR_B200_OP_INPUT: return cvt("x" + std::to_string(nd.input_slot), inputs[nd.input_slot].dtype, O);
         case THOR_B200_OP_RUNTIME_SCALAR: return cvt("s" + std::to_string(nd.input_slot), THOR_B200_FP32, O);
-        case THOR_B200_OP_TENSOR_RUNTIME_SCALAR: return cvt("s" + std::to_string(nd.input_slot), p.st.inputs[nd.input_slot].dtype, O);
+        case THOR_B200_OP_TENSOR_RUNTIME_SCALAR: return cvt("s" + std::to_string(nd.input_slot), inputs[nd.input_slot].dtype, O);
         case THOR_B200_OP_SCALAR_FP: return cvt(floatLiteral(nd.scalar_fp), THOR_B200_FP32, O);
         case THOR_B200_OP_CAST: return parent(nd.lhs, O);
         case THOR_B200_OP_WHERE:
@@ -254,6 +254,8 @@ std::string scalarNodeExpr(const Plan& p, size_t k) {
     }
     return cvt(r, C, O);
 }
+
+std::string scalarNodeExpr(const Plan& p, size_t k) { return scalarNodeExprImpl(p.st.nodes, p.st.inputs, k); }
 
 // ---- half2 / bfloat162 body --------------------------------------------------------------------
 std::string v2NodeExpr(const Plan& p, size_t k) {
@@ -353,6 +355,11 @@ std::string kernelParams(const Stage& st, bool with_numel) {
     return os.str();
 }
 
+std::string launchBounds(const Stage& st) {
+    if (st.min_ctas_per_sm > 0) return "__launch_bounds__(256, " + std::to_string(st.min_ctas_per_sm) + ")";
+    return "__launch_bounds__(256)";
+}
+
 // Loads of one-element tensor scalars, once per thread.
 void emitScalarLoads(const Stage& st, std::ostringstream& os) {
     for (size_t s = 0; s < st.inputs.size(); ++s)
@@ -406,12 +413,13 @@ void emitFlat(const Plan& p, Emitted* out, std::ostringstream& os) {
     const int lanes = p.v2 ? VEC / 2 : VEC;
     size_t in_bytes = 0;
     for (const auto& in : st.inputs) if (in.kind == THOR_B200_INPUT_TENSOR) in_bytes += dtypeSize(in.dtype) * VEC;
-    const int U = in_bytes >= 48 ? 1 : 2;
+    int U = in_bytes >= 48 ? 1 : 2;
+    if (st.packs_per_thread == 1 || st.packs_per_thread == 2 || st.packs_per_thread == 4) U = st.packs_per_thread;
     out->kind = p.v2 ? Kind::FlatV2 : Kind::FlatScalar;
     out->vec = VEC;
     out->unroll = U;
     out->threads = 256;
-    os << "extern \"C\" __global__ void __launch_bounds__(256) fused_kernel(" << kernelParams(st, true) << ") {\n";
+    os << "extern \"C\" __global__ void " << launchBounds(st) << " fused_kernel(" << kernelParams(st, true) << ") {\n";
     os << "    constexpr int VEC = " << VEC << ", U = " << U << ";\n";
     os << "    const tb_u64 n_packs = numel / VEC;\n";
     os << "    const tb_u64 base = (tb_u64)blockIdx.x * (256 * U) + threadIdx.x;\n";
@@ -555,6 +563,7 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
         dense += cls[s] == Dense;
     }
     int U = dense <= 2 ? 4 : (dense <= 4 ? 2 : 1);
+    if (st.rows_per_thread == 1 || st.rows_per_thread == 2 || st.rows_per_thread == 4 || st.rows_per_thread == 8) U = st.rows_per_thread;
     while (U > 1 && static_cast<uint64_t>(ty) * (U / 2) >= rows) U /= 2;
     out->kind = p.v2 ? Kind::TiledV2 : Kind::TiledScalar;
     out->vec = VEC;
@@ -567,7 +576,7 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
     const std::string T2dup = p.v2_dtype == THOR_B200_BF16 ? "__bfloat162bfloat162" : "__half2half2";
 
     os << "// rows = " << rows << ", cols = " << cols << ", packs per row = " << ppr << ", CTA = " << tx << " x " << ty << " threads, " << U << " rows per thread\n";
-    os << "extern \"C\" __global__ void __launch_bounds__(256) fused_kernel(" << kernelParams(st, false) << ") {\n";
+    os << "extern \"C\" __global__ void " << launchBounds(st) << " fused_kernel(" << kernelParams(st, false) << ") {\n";
     os << "    constexpr int VEC = " << VEC << ", U = " << U << ", TX = " << tx << ", TY = " << ty << ";\n";
     os << "    constexpr tb_u64 ROWS = " << rows << "ull, COLS = " << cols << "ull, PPR = " << ppr << "ull;\n";
     os << "    const tb_u32 tx = threadIdx.x % TX, ty = threadIdx.x / TX;\n";
@@ -640,7 +649,7 @@ void emitGeneric(const Plan& p, Emitted* out, std::ostringstream& os) {
         for (uint64_t d : c.dims) numel *= d;
         out->numel = numel;
     }
-    os << "extern \"C\" __global__ void __launch_bounds__(256) fused_kernel(" << kernelParams(st, !st.broadcast) << ") {\n";
+    os << "extern \"C\" __global__ void " << launchBounds(st) << " fused_kernel(" << kernelParams(st, !st.broadcast) << ") {\n";
     if (st.broadcast) os << "    constexpr tb_u64 numel = " << numel << "ull;\n";
     os << "    const tb_u64 i = (tb_u64)blockIdx.x * 256 + threadIdx.x;\n    if (i >= numel) return;\n";
     emitScalarLoads(st, os);
@@ -667,6 +676,13 @@ void emitGeneric(const Plan& p, Emitted* out, std::ostringstream& os) {
 }
 
 }  // namespace
+
+std::string scalarNodeExpression(const std::vector<thor_b200_expr_node>& nodes, const std::vector<thor_b200_expr_input>& inputs, size_t k) {
+    return scalarNodeExprImpl(nodes, inputs, k);
+}
+const char* cTypeName(int dtype) { return ctype(dtype); }
+std::string convertExpression(const std::string& e, int src, int dst) { return cvt(e, src, dst); }
+bool isFusedStageOp(uint16_t op) { return isKnownOp(op); }
 
 const char* kindName(Kind k) {
     switch (k) {

@@ -19,6 +19,9 @@ struct Stage {
     std::vector<uint64_t> dims;                 // [rank]
     std::vector<std::vector<int64_t>> strides;  // [n_inputs][rank] (tensor inputs only)
     bool fast_math = false;
+    int rows_per_thread = 0;   // tuning overrides, 0 = automatic
+    int min_ctas_per_sm = 0;
+    int packs_per_thread = 0;
 };
 
 enum class Kind { FlatV2, FlatScalar, TiledV2, TiledScalar, Generic };
@@ -45,5 +48,12 @@ std::string validate(const Stage& stage);
 std::string emit(const Stage& stage, bool force_generic, Emitted* out);
 
 const char* kindName(Kind k);
+
+// Building blocks shared with the row-program emitter.  A node's value lives in the variable "v<k>"
+// typed as its output dtype; tensor inputs are "x<slot>", scalars "s<slot>".
+std::string scalarNodeExpression(const std::vector<thor_b200_expr_node>& nodes, const std::vector<thor_b200_expr_input>& inputs, size_t k);
+const char* cTypeName(int dtype);
+std::string convertExpression(const std::string& e, int src, int dst);
+bool isFusedStageOp(uint16_t op);
 
 }  // namespace tb::expr

@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "expr_emit.h"
 #include "expr_prelude.h"
+#include "jit.h"
 
 namespace tb::expr {
 
@@ -103,21 +104,16 @@ int loadNvrtc(Nvrtc** out) {
     return THOR_B200_OK;
 }
 
-struct Module {
-    std::string cubin;
-    cudaLibrary_t library = nullptr;
-    cudaKernel_t kernel = nullptr;
-    std::mutex load_mutex;
-    ~Module() {
-        // Unloading at process exit races the CUDA runtime's own teardown; modules live for the
-        // life of the process like the reference's global compile cache.
-    }
-};
-
 std::mutex g_cache_mutex;
-std::unordered_map<std::string, std::shared_ptr<Module>> g_cache;  // key: fast-math flag + source
+std::unordered_map<std::string, std::shared_ptr<jit::Module>> g_cache;  // key: fast-math flag + source
 
-int compileSource(const std::string& source, bool fast_math, std::shared_ptr<Module>* out) {
+}  // namespace
+}  // namespace tb::expr
+
+namespace tb::jit {
+using namespace tb::expr;
+
+int compileSource(const std::string& source, bool fast_math, const char* kernel_name, std::shared_ptr<Module>* out) {
     const std::string key = (fast_math ? "F" : "P") + source;
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
@@ -130,9 +126,9 @@ int compileSource(const std::string& source, bool fast_math, std::shared_ptr<Mod
     Nvrtc* rt = nullptr;
     if (int st = loadNvrtc(&rt)) return st;
     nvrtcProgram prog = nullptr;
-    const char* header_src[] = {kPrelude};
-    const char* header_name[] = {"tb_prelude.cuh"};
-    nvrtcResult r = rt->createProgram(&prog, source.c_str(), "thor_b200_fused_stage.cu", 1, header_src, header_name);
+    const char* header_src[] = {kPrelude, kRowProgPrelude};
+    const char* header_name[] = {"tb_prelude.cuh", "tb_rowprog.cuh"};
+    nvrtcResult r = rt->createProgram(&prog, source.c_str(), "thor_b200_fused_stage.cu", 2, header_src, header_name);
     if (r != NVRTC_SUCCESS) return fail(THOR_B200_JIT_ERROR, "nvrtcCreateProgram: %s", rt->errorString(r));
     const std::string inc = "--include-path=" + rt->include_dir;
     std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-fmad=true", "-default-device", inc.c_str()};
@@ -148,6 +144,7 @@ int compileSource(const std::string& source, bool fast_math, std::shared_ptr<Mod
         return fail(THOR_B200_JIT_ERROR, "NVRTC compilation failed (%s): %s", rt->errorString(r), log.c_str());
     }
     auto mod = std::make_shared<Module>();
+    mod->kernel_name = kernel_name;
     size_t size = 0;
     r = rt->getCubinSize(prog, &size);
     if (r == NVRTC_SUCCESS && size) {
@@ -172,17 +169,19 @@ int ensureLoaded(Module& m) {
     cudaLibrary_t lib = nullptr;
     TB_CUDA(cudaLibraryLoadData(&lib, m.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
     cudaKernel_t k = nullptr;
-    TB_CUDA(cudaLibraryGetKernel(&k, lib, "fused_kernel"));
+    TB_CUDA(cudaLibraryGetKernel(&k, lib, m.kernel_name.c_str()));
     m.library = lib;
     m.kernel = k;
     return THOR_B200_OK;
 }
 
-}  // namespace
+}  // namespace tb::jit
+
+namespace tb::expr {
 
 struct Variant {
     Emitted em;
-    std::shared_ptr<Module> module;
+    std::shared_ptr<jit::Module> module;
 };
 
 }  // namespace tb::expr
@@ -205,8 +204,8 @@ namespace {
 int launchVariant(const thor_b200_expr& e, const Variant& v, const void* const* input_ptrs, const float* runtime_scalars, void* const* output_ptrs,
                   uint64_t numel, cudaStream_t stream) {
     const Stage& st = e.stage;
-    Module& m = *v.module;
-    if (int s = ensureLoaded(m)) return s;
+    jit::Module& m = *v.module;
+    if (int s = jit::ensureLoaded(m)) return s;
     // kernel parameters: inputs in slot order, outputs, then numel for flat kernels
     constexpr size_t kMaxArgs = 64;
     void* args[kMaxArgs];
@@ -287,6 +286,11 @@ int thor_b200_expr_compile(const thor_b200_expr_node* nodes, uint32_t n_nodes, c
     e->stage.outputs.assign(outputs, outputs + n_outputs);
     e->stage.fast_math = options && options->use_fast_math;
     e->compile_only = options && options->compile_only;
+    if (options) {
+        e->stage.rows_per_thread = options->rows_per_thread;
+        e->stage.min_ctas_per_sm = options->min_ctas_per_sm;
+        e->stage.packs_per_thread = options->packs_per_thread;
+    }
     if (broadcast) {
         TB_REQUIRE(broadcast->rank >= 1 && broadcast->rank <= THOR_B200_MAX_RANK, "expr_compile: broadcast rank %u out of range", broadcast->rank);
         TB_REQUIRE(broadcast->input_strides != nullptr || n_inputs == 0, "expr_compile: broadcast strides missing");
@@ -301,9 +305,9 @@ int thor_b200_expr_compile(const thor_b200_expr_node* nodes, uint32_t n_nodes, c
     const std::string why = emit(e->stage, false, &e->fast.em);
     if (!why.empty()) return fail(THOR_B200_INVALID_ARGUMENT, "expr_compile: %s", why.c_str());
     e->fast_is_generic = e->fast.em.kind == Kind::Generic;
-    if (int st = compileSource(e->fast.em.source, e->stage.fast_math, &e->fast.module)) return st;
+    if (int st = jit::compileSource(e->fast.em.source, e->stage.fast_math, "fused_kernel", &e->fast.module)) return st;
     if (!e->compile_only)
-        if (int st = ensureLoaded(*e->fast.module)) return st;
+        if (int st = jit::ensureLoaded(*e->fast.module)) return st;
     *out_expr = e.release();
     return THOR_B200_OK;
 }
@@ -335,7 +339,7 @@ int thor_b200_expr_launch(thor_b200_expr* e, const void* const* input_ptrs, cons
         if (!e->safe_ready) {
             const std::string why = emit(st, true, &e->safe.em);
             if (!why.empty()) return fail(THOR_B200_INVALID_ARGUMENT, "expr_launch: %s", why.c_str());
-            if (int s = compileSource(e->safe.em.source, st.fast_math, &e->safe.module)) return s;
+            if (int s = jit::compileSource(e->safe.em.source, st.fast_math, "fused_kernel", &e->safe.module)) return s;
             e->safe_ready = true;
         }
     }

@@ -101,4 +101,33 @@ __device__ __forceinline__ float tb_digammaf(float x) {
 }
 )TBPRELUDE";
 
+// Team-wide reductions of the row-program kernels ("tb_rowprog.cuh").
+static const char* const kRowProgPrelude = R"TBROWPROG(
+__device__ __forceinline__ float tb_add(float a, float b) { return a + b; }
+__device__ __forceinline__ float tb_mul(float a, float b) { return a * b; }
+// NaN-propagating min / max, the rule of the reduction seam.
+__device__ __forceinline__ float tb_nanmin(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
+__device__ __forceinline__ float tb_nanmax(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
+
+// Stage 1: xor butterfly inside each warp (every lane ends with the warp's value, bit-identical
+// across lanes because the operators are commutative); warp leaders of wide teams publish it.
+template <int TEAM, float (*OP)(float, float)>
+__device__ __forceinline__ float tb_team_reduce_stage1(float v, float* smem) {
+    constexpr int SPAN = TEAM < 32 ? TEAM : 32;
+#pragma unroll
+    for (int off = SPAN / 2; off > 0; off >>= 1) v = OP(v, __shfl_xor_sync(0xffffffffu, v, off, SPAN));
+    if (TEAM > 32 && (threadIdx.x & 31) == 0) smem[(threadIdx.x % TEAM) >> 5] = v;
+    return v;
+}
+// Stage 2 (after a __syncthreads): every thread folds the warp values in warp order.
+template <int TEAM, float (*OP)(float, float)>
+__device__ __forceinline__ float tb_team_reduce_stage2(float v, const float* smem) {
+    if (TEAM <= 32) return v;
+    float r = smem[0];
+#pragma unroll
+    for (int w = 1; w < TEAM / 32; ++w) r = OP(r, smem[w]);
+    return r;
+}
+)TBROWPROG";
+
 }  // namespace tb::expr

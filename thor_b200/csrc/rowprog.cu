@@ -1,0 +1,555 @@
+// Row programs: one single-pass kernel for "elementwise -> row reduction -> elementwise" chains.
+//
+// Kernel shape (generated source, NVRTC): a team of TEAM threads owns one row of `cols` elements
+// and keeps every FULL input of that row in registers as 16-byte packs (pack q of the row belongs
+// to thread q % TEAM).  Rounds alternate between
+//   (a) an element loop over the thread's packs that recomputes the needed part of the DAG from
+//       the registers and accumulates the arguments of the row reductions of this round in fp32,
+//   (b) one team-wide combine (shuffle tree + one shared-memory exchange) after which every
+//       thread holds the reduction results, and the ROW-class nodes that depend on them.
+// The last element loop evaluates the FULL outputs and stores them with 16-byte packs.  Each
+// input row is therefore read from HBM exactly once and each output row written exactly once.
+// With per-column operands (gamma, beta) or column reductions (dgamma, dbeta) the CTAs are
+// persistent: they walk rows r, r + grid, ..., keep the per-column operands in registers and
+// accumulate per-column fp32 partials, which a small fold kernel sums in CTA order.
+#include <algorithm>
+#include <memory>
+#include <sstream>
+
+#include "common.cuh"
+#include "expr_emit.h"
+#include "jit.h"
+
+namespace tb::rowprog {
+
+using tb::expr::cTypeName;
+using tb::expr::convertExpression;
+using tb::expr::scalarNodeExpression;
+
+namespace {
+
+enum Shape { FULL = THOR_B200_SHAPE_FULL, ROW = THOR_B200_SHAPE_ROW, COL = THOR_B200_SHAPE_COL, SCALAR = THOR_B200_SHAPE_SCALAR };
+
+bool isReduce(uint16_t op) { return (op >= THOR_B200_OP_REDUCE_SUM && op <= THOR_B200_OP_REDUCE_MAX) || (op >= THOR_B200_OP_REDUCE_AVG && op <= THOR_B200_OP_REDUCE_NORM2); }
+bool isLeaf(uint16_t op) { return op >= THOR_B200_OP_INPUT && op <= THOR_B200_OP_SCALAR_FP; }
+
+struct Program {
+    std::vector<thor_b200_expr_node> nodes;
+    std::vector<thor_b200_expr_input> inputs;
+    std::vector<int> input_shape;
+    std::vector<thor_b200_expr_output> outputs;
+    uint64_t rows = 0, cols = 0;
+    bool fast_math = false;
+    // analysis
+    std::vector<int> shape;   // per node
+    std::vector<bool> live;
+    std::vector<int> depth;   // number of row reductions below the node
+    std::vector<uint32_t> row_reduces, col_reduces;
+    // geometry
+    int vec = 4, team = 256, cta = 256, vpt = 1;
+    bool persistent = false;
+    uint32_t grid = 0;
+    std::string source;
+};
+
+const char* combineExpr(uint16_t op) {
+    switch (op) {
+        case THOR_B200_OP_REDUCE_PROD: return "tb_mul";
+        case THOR_B200_OP_REDUCE_MIN: return "tb_nanmin";
+        case THOR_B200_OP_REDUCE_MAX: return "tb_nanmax";
+        default: return "tb_add";
+    }
+}
+const char* identityExpr(uint16_t op) {
+    switch (op) {
+        case THOR_B200_OP_REDUCE_PROD: return "1.0f";
+        case THOR_B200_OP_REDUCE_MIN: return "__int_as_float(0x7f800000)";
+        case THOR_B200_OP_REDUCE_MAX: return "__int_as_float(0xff800000)";
+        default: return "0.0f";
+    }
+}
+std::string transformExpr(uint16_t op, const std::string& f) {
+    if (op == THOR_B200_OP_REDUCE_NORM1) return "fabsf(" + f + ")";
+    if (op == THOR_B200_OP_REDUCE_NORM2) return "(" + f + " * " + f + ")";
+    return f;
+}
+
+std::string analyse(Program& p) {
+    const size_t n = p.nodes.size();
+    p.shape.assign(n, SCALAR);
+    p.depth.assign(n, 0);
+    p.live.assign(n, false);
+    for (const auto& o : p.outputs) {
+        if (o.node >= n) return "output node out of range";
+        p.live[o.node] = true;
+    }
+    for (size_t k = n; k-- > 0;) {
+        if (!p.live[k]) continue;
+        for (uint32_t par : {p.nodes[k].lhs, p.nodes[k].rhs, p.nodes[k].aux})
+            if (par != THOR_B200_NO_NODE && !(isReduce(p.nodes[k].op) && par != p.nodes[k].lhs)) {
+                if (par >= k) return "nodes are not topologically ordered";
+                p.live[par] = true;
+            }
+    }
+    std::vector<int> consumers(n, 0);
+    for (size_t k = 0; k < n; ++k) {
+        if (!p.live[k]) continue;
+        const auto& nd = p.nodes[k];
+        if (isLeaf(nd.op)) {
+            if (nd.op == THOR_B200_OP_INPUT) {
+                if (nd.input_slot >= p.inputs.size() || p.inputs[nd.input_slot].kind != THOR_B200_INPUT_TENSOR) return "bad input slot";
+                p.shape[k] = p.input_shape[nd.input_slot];
+            } else if (nd.op != THOR_B200_OP_SCALAR_FP) {
+                if (nd.input_slot >= p.inputs.size()) return "bad input slot";
+            }
+            continue;
+        }
+        if (isReduce(nd.op)) {
+            const int ps = p.shape[nd.lhs];
+            consumers[nd.lhs]++;
+            if (nd.input_slot == 0) {
+                if (ps != FULL) return "a row reduction needs a [rows, cols] argument";
+                p.shape[k] = ROW;
+                p.depth[k] = p.depth[nd.lhs] + 1;
+                p.row_reduces.push_back(static_cast<uint32_t>(k));
+            } else if (nd.input_slot == 1) {
+                if (ps != FULL) return "a column reduction needs a [rows, cols] argument";
+                if (nd.op != THOR_B200_OP_REDUCE_SUM && nd.op != THOR_B200_OP_REDUCE_AVG) return "column reductions support sum and mean";
+                p.shape[k] = COL;
+                p.depth[k] = p.depth[nd.lhs];
+                p.col_reduces.push_back(static_cast<uint32_t>(k));
+            } else {
+                return "reduction axis selector must be 0 (columns) or 1 (rows)";
+            }
+            continue;
+        }
+        if (!tb::expr::isFusedStageOp(nd.op)) return "op is not supported in a row program";
+        int sh = SCALAR, d = 0;
+        for (uint32_t par : {nd.lhs, nd.rhs, nd.aux}) {
+            if (par == THOR_B200_NO_NODE) continue;
+            consumers[par]++;
+            const int ps = p.shape[par];
+            if (ps == SCALAR) {
+            } else if (sh == SCALAR) sh = ps;
+            else if (sh != ps) sh = FULL;
+            d = std::max(d, p.depth[par]);
+        }
+        p.shape[k] = sh;
+        p.depth[k] = d;
+    }
+    for (uint32_t k : p.col_reduces)
+        if (consumers[k] != 0) return "a column reduction may only be an output";
+    bool any_full = false;
+    for (const auto& o : p.outputs) {
+        const int sh = p.shape[o.node];
+        if (sh == SCALAR) return "scalar outputs are not produced by a row program";
+        if (sh == COL && !isReduce(p.nodes[o.node].op)) return "per-column outputs must be column reductions";
+        if (o.dtype != p.nodes[o.node].output_dtype) return "output dtype differs from its node's output dtype";
+        any_full = any_full || sh == FULL || sh == ROW || sh == COL;
+    }
+    if (p.row_reduces.empty() && p.col_reduces.empty()) return "no reduction: an ordinary fused stage is the right kernel";
+    return "";
+}
+
+// Statements "const T vK = <expr>;" for the given nodes (already in topological order).
+void emitStatements(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
+    for (uint32_t k : ids) os << indent << "const " << cTypeName(p.nodes[k].output_dtype) << " v" << k << " = " << scalarNodeExpression(p.nodes, p.inputs, k) << ";\n";
+}
+
+// FULL / COL-class ancestors of `targets` (inclusive) that an element loop has to evaluate.
+std::vector<uint32_t> elementClosure(const Program& p, const std::vector<uint32_t>& targets) {
+    std::vector<bool> need(p.nodes.size(), false);
+    std::vector<uint32_t> stack(targets.begin(), targets.end());
+    while (!stack.empty()) {
+        const uint32_t k = stack.back();
+        stack.pop_back();
+        if (need[k]) continue;
+        const int sh = p.shape[k];
+        if (sh == ROW || sh == SCALAR) continue;  // row-scope values: already computed, referenced by name
+        need[k] = true;
+        if (isLeaf(p.nodes[k].op) || isReduce(p.nodes[k].op)) continue;
+        for (uint32_t par : {p.nodes[k].lhs, p.nodes[k].rhs, p.nodes[k].aux})
+            if (par != THOR_B200_NO_NODE) stack.push_back(par);
+    }
+    std::vector<uint32_t> out;
+    for (uint32_t k = 0; k < p.nodes.size(); ++k)
+        if (need[k]) out.push_back(k);
+    return out;
+}
+
+std::string elemTypeOfInput(const Program& p, size_t slot) { return cTypeName(p.inputs[slot].dtype); }
+
+// Declarations of the element values x<slot> that `ids` read, for lane j of pack k.
+void emitElementInputs(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
+    std::vector<bool> done(p.inputs.size(), false);
+    for (uint32_t k : ids) {
+        const auto& nd = p.nodes[k];
+        if (nd.op != THOR_B200_OP_INPUT || done[nd.input_slot]) continue;
+        done[nd.input_slot] = true;
+        const size_t s = nd.input_slot;
+        const std::string T = elemTypeOfInput(p, s);
+        if (p.input_shape[s] == FULL) os << indent << "const " << T << " x" << s << " = reinterpret_cast<const " << T << "*>(&f" << s << "[k])[j];\n";
+        else os << indent << "const " << T << " x" << s << " = reinterpret_cast<const " << T << "*>(&c" << s << "[k])[j];\n";
+    }
+}
+
+// Per-pack loads of COL inputs for non-persistent programs (L1/L2 resident, re-read each round).
+void emitColumnPackLoads(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
+    if (p.persistent) return;
+    std::vector<bool> done(p.inputs.size(), false);
+    for (uint32_t k : ids) {
+        const auto& nd = p.nodes[k];
+        if (nd.op != THOR_B200_OP_INPUT || p.input_shape[nd.input_slot] != COL || done[nd.input_slot]) continue;
+        done[nd.input_slot] = true;
+        os << indent << "tb_load_keep(c" << nd.input_slot << "[k], in" << nd.input_slot << " + (tb_u64)q * VEC);\n";
+    }
+}
+
+std::string emit(Program& p) {
+    std::ostringstream os;
+    const int VEC = p.vec, TEAM = p.team, CTA = p.cta, VPT = p.vpt;
+    const int teams_per_cta = CTA / TEAM;
+    const uint64_t packs_per_row = p.cols / VEC;
+    int max_depth = 0;
+    for (uint32_t k : p.row_reduces) max_depth = std::max(max_depth, p.depth[k]);
+
+    os << "// generated by thor_b200: row program, " << p.nodes.size() << " nodes, rows = " << p.rows << ", cols = " << p.cols << ", team = " << TEAM
+       << " threads, " << VPT << " packs of " << VEC << " per thread" << (p.persistent ? ", persistent" : "") << "\n";
+    os << "#include \"tb_prelude.cuh\"\n#include \"tb_rowprog.cuh\"\n\n";
+    // kernel signature
+    os << "extern \"C\" __global__ void __launch_bounds__(" << CTA << ") row_kernel(";
+    bool first = true;
+    for (size_t s = 0; s < p.inputs.size(); ++s) {
+        os << (first ? "" : ", ");
+        first = false;
+        if (p.inputs[s].kind == THOR_B200_INPUT_RUNTIME_SCALAR_FP32) os << "const float s" << s;
+        else os << "const " << cTypeName(p.inputs[s].dtype) << "* __restrict__ in" << s;
+    }
+    for (size_t o = 0; o < p.outputs.size(); ++o) {
+        os << (first ? "" : ", ");
+        first = false;
+        os << cTypeName(p.outputs[o].dtype) << "* __restrict__ out" << o;
+    }
+    os << (first ? "" : ", ") << "float* __restrict__ ws) {\n";
+    os << "    constexpr int VEC = " << VEC << ", TEAM = " << TEAM << ", VPT = " << VPT << ", TEAMS = " << teams_per_cta << ";\n";
+    os << "    constexpr tb_u64 ROWS = " << p.rows << "ull, COLS = " << p.cols << "ull;\n";
+    os << "    constexpr tb_u32 PPR = " << packs_per_row << "u;\n";
+    os << "    __shared__ float red_smem[" << std::max<size_t>(1, p.row_reduces.size()) << "][TEAMS][TEAM > 32 ? TEAM / 32 : 1];\n";
+    os << "    const int t = threadIdx.x % TEAM, team_id = threadIdx.x / TEAM;\n";
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == SCALAR))
+            os << "    const " << cTypeName(p.inputs[s].dtype) << (p.inputs[s].kind == THOR_B200_INPUT_TENSOR ? " x" : " s") << s << " = in" << s << "[0];\n";
+    // per-column operands: registers for the whole kernel when persistent
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL) {
+            os << "    tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> c" << s << "[VPT];\n";
+            if (p.persistent) {
+                os << "#pragma unroll\n    for (int k = 0; k < VPT; ++k) {\n        const tb_u32 q = t + k * TEAM;\n        if (q < PPR) tb_load_keep(c" << s
+                   << "[k], in" << s << " + (tb_u64)q * VEC);\n    }\n";
+            }
+        }
+    // column-reduction accumulators
+    for (uint32_t k : p.col_reduces) {
+        os << "    float acc" << k << "[VPT][VEC];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC; ++j) acc" << k
+           << "[k][j] = 0.0f;\n";
+    }
+    // row loop
+    if (p.persistent) os << "    for (tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id; row < ROWS; row += (tb_u64)gridDim.x * TEAMS) {\n";
+    else os << "    {\n        const tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id;\n        const bool row_ok = row < ROWS;\n";
+    const std::string I = "        ";
+    const std::string guard = p.persistent ? "q < PPR" : "row_ok && q < PPR";
+    // load FULL inputs
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) os << I << "tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> f" << s << "[VPT];\n";
+    os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard << ") {\n";
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL)
+            os << I << "        tb_load_stream(f" << s << "[k], in" << s << " + row * COLS + (tb_u64)q * VEC);\n";
+    os << I << "    }\n" << I << "}\n";
+    // ROW inputs
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == ROW)
+            os << I << "const " << cTypeName(p.inputs[s].dtype) << " x" << s << " = " << (p.persistent ? "" : "row_ok ? ") << "in" << s << "[row]"
+               << (p.persistent ? "" : std::string(" : ") + cTypeName(p.inputs[s].dtype) + "()") << ";\n";
+
+    // row-scope nodes are emitted as soon as their depth is reached
+    std::vector<bool> emitted(p.nodes.size(), false);
+    auto emitRowScope = [&](int d) {
+        std::vector<uint32_t> ids;
+        for (uint32_t k = 0; k < p.nodes.size(); ++k) {
+            if (!p.live[k] || emitted[k] || isReduce(p.nodes[k].op)) continue;
+            if ((p.shape[k] == ROW || p.shape[k] == SCALAR) && p.depth[k] <= d) {
+                ids.push_back(k);
+                emitted[k] = true;
+            }
+        }
+        emitStatements(p, ids, I, os);
+    };
+    emitRowScope(0);
+    for (int d = 1; d <= max_depth; ++d) {
+        std::vector<uint32_t> round;
+        for (uint32_t k : p.row_reduces)
+            if (p.depth[k] == d) round.push_back(k);
+        if (round.empty()) continue;
+        std::vector<uint32_t> args;
+        for (uint32_t k : round) args.push_back(p.nodes[k].lhs);
+        const std::vector<uint32_t> closure = elementClosure(p, args);
+        os << I << "// round " << d << ": " << round.size() << " row reduction(s)\n";
+        for (uint32_t k : round) os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+        os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard << ") {\n";
+        emitColumnPackLoads(p, closure, I + "        ", os);
+        os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; ++j) {\n";
+        emitElementInputs(p, closure, I + "            ", os);
+        emitStatements(p, closure, I + "            ", os);
+        for (uint32_t k : round) {
+            const uint32_t a = p.nodes[k].lhs;
+            const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
+            os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+        }
+        os << I << "        }\n" << I << "    }\n" << I << "}\n";
+        // team combine: all reductions of the round share one shared-memory exchange
+        size_t slot = 0;
+        for (uint32_t k : round) {
+            const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
+            os << I << "r" << k << " = tb_team_reduce_stage1<TEAM, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][team_id]);\n";
+            ++slot;
+        }
+        os << I << "if (TEAM > 32) __syncthreads();\n";
+        for (uint32_t k : round) {
+            const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
+            const auto& nd = p.nodes[k];
+            os << I << "r" << k << " = tb_team_reduce_stage2<TEAM, " << combineExpr(nd.op) << ">(r" << k << ", red_smem[" << idx << "][team_id]);\n";
+            std::string fin = "r" + std::to_string(k);
+            if (nd.op == THOR_B200_OP_REDUCE_AVG) fin = "(" + fin + " / " + std::to_string(p.cols) + ".0f)";
+            if (nd.op == THOR_B200_OP_REDUCE_NORM2) fin = "sqrtf(" + fin + ")";
+            os << I << "const " << cTypeName(nd.output_dtype) << " v" << k << " = " << convertExpression(fin, THOR_B200_FP32, nd.output_dtype) << ";\n";
+            emitted[k] = true;
+        }
+        emitRowScope(d);
+    }
+    // final element loop: FULL outputs and column-reduction arguments
+    std::vector<uint32_t> finals;
+    for (const auto& o : p.outputs)
+        if (p.shape[o.node] == FULL) finals.push_back(o.node);
+    for (uint32_t k : p.col_reduces) finals.push_back(p.nodes[k].lhs);
+    if (!finals.empty()) {
+        const std::vector<uint32_t> closure = elementClosure(p, finals);
+        os << I << "// outputs\n#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard << ") {\n";
+        emitColumnPackLoads(p, closure, I + "        ", os);
+        for (size_t o = 0; o < p.outputs.size(); ++o)
+            if (p.shape[p.outputs[o].node] == FULL) os << I << "        tb_pack<VEC * " << dtypeSize(p.outputs[o].dtype) << "> w" << o << ";\n";
+        os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; ++j) {\n";
+        emitElementInputs(p, closure, I + "            ", os);
+        emitStatements(p, closure, I + "            ", os);
+        for (size_t o = 0; o < p.outputs.size(); ++o)
+            if (p.shape[p.outputs[o].node] == FULL)
+                os << I << "            reinterpret_cast<" << cTypeName(p.outputs[o].dtype) << "*>(&w" << o << ")[j] = v" << p.outputs[o].node << ";\n";
+        for (uint32_t k : p.col_reduces) {
+            const uint32_t a = p.nodes[k].lhs;
+            os << I << "            acc" << k << "[k][j] += " << convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32) << ";\n";
+        }
+        os << I << "        }\n";
+        for (size_t o = 0; o < p.outputs.size(); ++o)
+            if (p.shape[p.outputs[o].node] == FULL) os << I << "        tb_store_stream(out" << o << " + row * COLS + (tb_u64)q * VEC, w" << o << ");\n";
+        os << I << "    }\n" << I << "}\n";
+    }
+    // ROW outputs
+    for (size_t o = 0; o < p.outputs.size(); ++o)
+        if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0" << (p.persistent ? "" : " && row_ok") << ") out" << o << "[row] = v" << p.outputs[o].node << ";\n";
+    if (p.persistent && p.row_reduces.size() > 0) os << I << "if (TEAM > 32) __syncthreads();  // shared-memory slots are reused by the next row\n";
+    os << "    }\n";
+    // column partials: ws[c][cta*TEAMS + team][COLS]
+    size_t ci = 0;
+    for (uint32_t k : p.col_reduces) {
+        os << "    {\n        float* part = ws + ((tb_u64)" << ci << " * gridDim.x * TEAMS + (tb_u64)blockIdx.x * TEAMS + team_id) * COLS;\n";
+        os << "#pragma unroll\n        for (int k = 0; k < VPT; ++k) {\n            const tb_u32 q = t + k * TEAM;\n            if (q < PPR) {\n";
+        os << "#pragma unroll\n                for (int j = 0; j < VEC; j += 4) *reinterpret_cast<float4*>(part + (tb_u64)q * VEC + j) = make_float4(acc" << k << "[k][j], acc" << k
+           << "[k][j + 1], acc" << k << "[k][j + 2], acc" << k << "[k][j + 3]);\n";
+        os << "            }\n        }\n    }\n";
+        ++ci;
+    }
+    os << "}\n";
+    p.source = os.str();
+    return "";
+}
+
+// Folds column partials [parts][cols] in part order and stores in the output dtype.
+__global__ void __launch_bounds__(256) foldColumnPartials(const float* __restrict__ ws, uint32_t parts, uint64_t cols, void* out, int out_dtype, float divisor) {
+    const uint64_t c = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (c >= cols) return;
+    float v = 0.0f;
+    for (uint32_t s = 0; s < parts; ++s) v += ws[static_cast<uint64_t>(s) * cols + c];
+    if (divisor != 1.0f) v = v / divisor;
+    switch (out_dtype) {
+        case THOR_B200_FP32: static_cast<float*>(out)[c] = v; break;
+        case THOR_B200_FP16: static_cast<__half*>(out)[c] = __float2half_rn(v); break;
+        case THOR_B200_BF16: static_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(v); break;
+        case THOR_B200_FP8_E4M3: static_cast<__nv_fp8_storage_t*>(out)[c] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); break;
+        case THOR_B200_FP8_E5M2: static_cast<__nv_fp8_storage_t*>(out)[c] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2); break;
+        default: break;
+    }
+}
+
+}  // namespace
+}  // namespace tb::rowprog
+
+struct thor_b200_rowprog {
+    tb::rowprog::Program prog;
+    std::shared_ptr<tb::jit::Module> module;
+    size_t workspace_bytes = 1;
+    bool compile_only = false;
+};
+
+extern "C" {
+
+int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog** out_prog, size_t* workspace_bytes) {
+    using namespace tb;
+    using namespace tb::rowprog;
+    TB_REQUIRE(d != nullptr && out_prog != nullptr && workspace_bytes != nullptr, "rowprog_compile: null argument");
+    *out_prog = nullptr;
+    TB_REQUIRE(d->nodes != nullptr && d->n_nodes > 0 && d->outputs != nullptr && d->n_outputs > 0, "rowprog_compile: empty program");
+    TB_REQUIRE(d->rows > 0 && d->cols > 0, "rowprog_compile: zero-sized dimension");
+    TB_REQUIRE(d->n_inputs == 0 || (d->inputs != nullptr && d->input_shapes != nullptr), "rowprog_compile: inputs missing");
+    auto h = std::make_unique<thor_b200_rowprog>();
+    Program& p = h->prog;
+    p.nodes.assign(d->nodes, d->nodes + d->n_nodes);
+    p.inputs.assign(d->inputs, d->inputs + d->n_inputs);
+    p.input_shape.assign(d->input_shapes, d->input_shapes + d->n_inputs);
+    p.outputs.assign(d->outputs, d->outputs + d->n_outputs);
+    p.rows = d->rows;
+    p.cols = d->cols;
+    p.fast_math = d->options.use_fast_math != 0;
+    h->compile_only = d->options.compile_only != 0;
+    for (size_t s = 0; s < p.inputs.size(); ++s) {
+        TB_REQUIRE(p.inputs[s].kind >= 0 && p.inputs[s].kind <= 2, "rowprog_compile: input %zu has an unknown kind", s);
+        TB_REQUIRE(dtypeSize(p.inputs[s].dtype) != 0 && p.inputs[s].dtype != THOR_B200_FP64, "rowprog_compile: input %zu has an unsupported dtype", s);
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR) TB_REQUIRE(p.input_shape[s] >= 0 && p.input_shape[s] <= 3, "rowprog_compile: input %zu has an unknown shape class", s);
+    }
+    const std::string why = analyse(p);
+    if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
+
+    // geometry: pack width from the narrowest FULL / COL tensor, team size from the row length
+    size_t mn = 8, mx = 1;
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && (p.input_shape[s] == FULL || p.input_shape[s] == COL)) {
+            mn = std::min(mn, dtypeSize(p.inputs[s].dtype));
+            mx = std::max(mx, dtypeSize(p.inputs[s].dtype));
+        }
+    for (const auto& o : p.outputs)
+        if (p.shape[o.node] == FULL) {
+            mn = std::min(mn, dtypeSize(o.dtype));
+            mx = std::max(mx, dtypeSize(o.dtype));
+        }
+    if (mn > mx) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: no [rows, cols] tensor in the program");
+    int vec = static_cast<int>(16 / mn);
+    if (vec < 4) vec = 4;
+    while (vec > 4 && static_cast<size_t>(vec) * mx > 64) vec /= 2;
+    if (p.cols % vec != 0) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: cols (%llu) is not a multiple of the pack width %d", static_cast<unsigned long long>(p.cols), vec);
+    const uint64_t packs = p.cols / vec;
+    if (packs > 1024ull * 8) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: rows of %llu elements do not fit one CTA's registers", static_cast<unsigned long long>(p.cols));
+    int team = 32;
+    while (team < 1024 && packs > static_cast<uint64_t>(team) * 4) team *= 2;
+    if (team == 64) team = 128;
+    p.vec = vec;
+    p.team = team;
+    p.cta = team < 256 ? 256 : team;
+    p.vpt = static_cast<int>((packs + team - 1) / team);
+    bool has_col_input = false;
+    for (size_t s = 0; s < p.inputs.size(); ++s) has_col_input = has_col_input || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL);
+    p.persistent = has_col_input || !p.col_reduces.empty();
+    const uint64_t teams_per_cta = p.cta / p.team;
+    const uint64_t ctas_for_rows = (p.rows + teams_per_cta - 1) / teams_per_cta;
+    int sms = 148;
+    {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sms = v;
+        else (void)cudaGetLastError();
+    }
+    if (p.persistent) {
+        // column accumulators make every extra CTA cost a [cols] fp32 partial row: two CTAs per SM then
+        const uint64_t resident = p.col_reduces.empty() ? static_cast<uint64_t>(sms) * std::max(1, 1024 / p.cta) * 2 : static_cast<uint64_t>(sms) * 2;
+        p.grid = static_cast<uint32_t>(std::min<uint64_t>(ctas_for_rows, resident));
+    } else {
+        if (ctas_for_rows > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: too many rows for one grid");
+        p.grid = static_cast<uint32_t>(ctas_for_rows);
+    }
+    const std::string err = emit(p);
+    if (!err.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", err.c_str());
+    h->workspace_bytes = p.col_reduces.empty() ? 1 : p.col_reduces.size() * static_cast<size_t>(p.grid) * teams_per_cta * p.cols * sizeof(float);
+    if (int st = jit::compileSource(p.source, p.fast_math, "row_kernel", &h->module)) return st;
+    if (!h->compile_only)
+        if (int st = jit::ensureLoaded(*h->module)) return st;
+    *workspace_bytes = h->workspace_bytes;
+    *out_prog = h.release();
+    return THOR_B200_OK;
+}
+
+int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs, const float* runtime_scalars, void* const* output_ptrs, void* workspace,
+                             size_t workspace_bytes, void* stream_v) {
+    using namespace tb;
+    using namespace tb::rowprog;
+    TB_REQUIRE(h != nullptr, "rowprog_launch: null handle");
+    TB_REQUIRE(!h->compile_only, "rowprog_launch: handle was compiled with compile_only");
+    TB_REQUIRE(output_ptrs != nullptr, "rowprog_launch: output_ptrs is null");
+    const Program& p = h->prog;
+    TB_REQUIRE(workspace_bytes >= h->workspace_bytes, "rowprog_launch: workspace too small");
+    TB_REQUIRE(p.col_reduces.empty() || (workspace != nullptr && isAligned(workspace, 16)), "rowprog_launch: workspace must be a 16-byte aligned device pointer");
+    if (int st = jit::ensureLoaded(*h->module)) return st;
+    constexpr size_t kMaxArgs = 64;
+    TB_REQUIRE(p.inputs.size() + p.outputs.size() + 1 <= kMaxArgs, "rowprog_launch: too many kernel arguments");
+    void* args[kMaxArgs];
+    const void* ptr_store[kMaxArgs];
+    float scalar_store[kMaxArgs];
+    size_t n = 0;
+    for (size_t s = 0; s < p.inputs.size(); ++s) {
+        if (p.inputs[s].kind == THOR_B200_INPUT_RUNTIME_SCALAR_FP32) {
+            TB_REQUIRE(runtime_scalars != nullptr, "rowprog_launch: runtime_scalars is null");
+            scalar_store[n] = runtime_scalars[s];
+            args[n] = &scalar_store[n];
+        } else {
+            TB_REQUIRE(input_ptrs != nullptr && input_ptrs[s] != nullptr, "rowprog_launch: input %zu is null", s);
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && (p.input_shape[s] == FULL || p.input_shape[s] == COL))
+                TB_REQUIRE(isAligned(input_ptrs[s], 16), "rowprog_launch: input %zu must be 16-byte aligned", s);
+            ptr_store[n] = input_ptrs[s];
+            args[n] = &ptr_store[n];
+        }
+        ++n;
+    }
+    for (size_t o = 0; o < p.outputs.size(); ++o) {
+        TB_REQUIRE(output_ptrs[o] != nullptr, "rowprog_launch: output %zu is null", o);
+        // column-reduction outputs are written by the fold kernel; the row kernel gets the pointer but does not use it
+        if (p.shape[p.outputs[o].node] == FULL) TB_REQUIRE(isAligned(output_ptrs[o], 16), "rowprog_launch: output %zu must be 16-byte aligned", o);
+        ptr_store[n] = output_ptrs[o];
+        args[n] = &ptr_store[n];
+        ++n;
+    }
+    const void* ws_ptr = workspace;
+    args[n++] = &ws_ptr;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, 0, stream));
+    countLaunch();
+    if (!p.col_reduces.empty()) {
+        const uint32_t parts = p.grid * static_cast<uint32_t>(p.cta / p.team);
+        size_t ci = 0;
+        for (uint32_t k : p.col_reduces) {
+            size_t o = 0;
+            for (; o < p.outputs.size(); ++o)
+                if (p.outputs[o].node == k) break;
+            const float divisor = p.nodes[k].op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows) : 1.0f;
+            const float* part = static_cast<const float*>(workspace) + ci * static_cast<size_t>(parts) * p.cols;
+            foldColumnPartials<<<static_cast<unsigned>((p.cols + 255) / 256), 256, 0, stream>>>(part, parts, p.cols, output_ptrs[o], p.outputs[o].dtype, divisor);
+            TB_CUDA(cudaGetLastError());
+            ++ci;
+        }
+        countLaunch(p.col_reduces.size());
+    }
+    return THOR_B200_OK;
+}
+
+const char* thor_b200_rowprog_source(const thor_b200_rowprog* h) { return h ? h->prog.source.c_str() : ""; }
+
+uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) { return h ? 1u + static_cast<uint32_t>(h->prog.col_reduces.size()) : 0u; }
+
+void thor_b200_rowprog_destroy(thor_b200_rowprog* h) { delete h; }
+
+}  // extern "C"

@@ -153,6 +153,7 @@ struct PhysicalStage {
     size_t workspace_bytes = 0;
     // FusedRows
     std::function<void(void* stream)> custom_launch;
+    std::shared_ptr<std::vector<float>> shared_scalars;  // FusedRows: runtime scalars the launch closure reads
     uint64_t launches = 1;
 };
 
@@ -205,6 +206,7 @@ void StampedExecutionPlan::setRuntimeScalar(const std::string& name, float value
         for (size_t i = 0; i < s.scalar_names.size(); ++i)
             if (s.scalar_names[i] == name) {
                 s.scalars[i] = value;
+                if (s.shared_scalars) (*s.shared_scalars)[i] = value;
                 found = true;
             }
     if (!found) throw std::logic_error("StampedExecutionPlan has no runtime scalar named '" + name + "'");
@@ -413,13 +415,17 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
     // Optional physical fusion of row-reduction chains (softmax / LayerNorm class).
     std::vector<bool> covered(g.nodes.size(), false);  // nodes whose values a super-stage already produced or made unnecessary
     if (options_.fuse_row_reductions) {
-        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_};
+        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_, options_.use_fast_math};
         std::vector<RowFusionMatch> matches = matchRowFusions(ctx);
         for (RowFusionMatch& m : matches) {
             PhysicalStage st;
             st.kind = StageKind::FusedRows;
             st.physical_name = m.name;
+            st.source = m.source;
             st.launches = m.launches;
+            st.scalar_names = m.scalar_names;
+            st.shared_scalars = m.scalars;
+            st.scalars = *m.scalars;
             for (auto& [node, is_out] : m.produced) {
                 Tensor t = allocateFor(node, is_out);
                 node_tensor[node] = t;

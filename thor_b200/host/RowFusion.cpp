@@ -1,7 +1,220 @@
 #include "RowFusion.h"
 
+#include <algorithm>
+#include <map>
+#include <stdexcept>
+
+#include "thor_b200.h"
+
 namespace ThorB200 {
 
-std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext&) { return {}; }
+namespace {
+
+uint64_t numelOf(const std::vector<uint64_t>& d) {
+    uint64_t n = 1;
+    for (uint64_t v : d) n *= v;
+    return n;
+}
+
+struct ProgHandle {
+    thor_b200_rowprog* h = nullptr;
+    ~ProgHandle() { thor_b200_rowprog_destroy(h); }
+};
+
+}  // namespace
+
+std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
+    const PhysicalExpression& g = ctx.graph;
+    const size_t n = g.nodes.size();
+    std::vector<bool> needed(n, false);
+    for (const auto& o : ctx.outputs) needed[o.node_idx] = true;
+    for (size_t k = n; k-- > 0;) {
+        if (!needed[k]) continue;
+        for (uint32_t p : {g.nodes[k].lhs, g.nodes[k].rhs, g.nodes[k].aux})
+            if (p != UINT32_MAX) needed[p] = true;
+    }
+    // the [rows, cols] frame: the argument of the first reduction
+    std::vector<uint64_t> frame;
+    for (size_t k = 0; k < n && frame.empty(); ++k)
+        if (needed[k] && isReductionOp(g.nodes[k].op)) frame = ctx.shape[g.nodes[k].lhs];
+    if (frame.empty() || frame.size() < 1) return {};
+    const uint64_t cols = frame.back();
+    const uint64_t total = numelOf(frame);
+    if (cols < 2 || total == cols) {
+        // a 1-D tensor reduced over its only axis is a full reduction, not a row program
+        if (frame.size() < 2 || total == cols) return {};
+    }
+    const uint64_t rows = total / cols;
+
+    auto classify = [&](const std::vector<uint64_t>& d) -> int {
+        const uint64_t ne = numelOf(d);
+        if (ne == 1) return THOR_B200_SHAPE_SCALAR;
+        if (d.size() > frame.size()) return -1;
+        const size_t pad = frame.size() - d.size();
+        bool full = true, row = true, col = true;
+        for (size_t i = 0; i < frame.size(); ++i) {
+            const uint64_t v = i < pad ? 1 : d[i - pad];
+            const bool last = i + 1 == frame.size();
+            if (v != frame[i]) full = false;
+            if (last ? v != 1 : v != frame[i]) row = false;
+            if (last ? v != frame[i] : v != 1) col = false;
+        }
+        if (full) return THOR_B200_SHAPE_FULL;
+        if (row) return THOR_B200_SHAPE_ROW;
+        if (col) return THOR_B200_SHAPE_COL;
+        return -1;
+    };
+
+    std::vector<thor_b200_expr_node> nodes;
+    std::vector<thor_b200_expr_input> inputs;
+    std::vector<int32_t> input_shapes;
+    std::vector<std::string> scalar_names;
+    auto scalars = std::make_shared<std::vector<float>>();
+    std::vector<uint32_t> input_graph_slot;  // program slot -> graph input slot
+    std::map<uint32_t, uint32_t> remap;      // graph node -> program node
+    std::map<uint32_t, uint32_t> slot_of_graph_input;
+    for (uint32_t k = 0; k < n; ++k) {
+        if (!needed[k]) continue;
+        const ExprNode& nd = g.nodes[k];
+        if (isArgReductionOp(nd.op)) return {};
+        if (isViewOp(nd.op)) {
+            // squeeze / unsqueeze / reshape of a value whose class does not change is an alias
+            const int a = classify(ctx.shape[nd.lhs]), b = classify(ctx.shape[k]);
+            if (a < 0 || a != b) {
+                // [1, C] column sums squeezed to [C] keep class COL; anything else is not a row program
+                return {};
+            }
+            remap[k] = remap.at(nd.lhs);
+            continue;
+        }
+        thor_b200_expr_node cn{};
+        cn.lhs = cn.rhs = cn.aux = THOR_B200_NO_NODE;
+        cn.input_slot = THOR_B200_NO_NODE;
+        cn.output_dtype = static_cast<uint16_t>(*nd.output_dtype);
+        cn.compute_dtype = static_cast<uint16_t>(nd.compute_dtype.value_or(*nd.output_dtype));
+        if (nd.op == ExprOp::INPUT || nd.op == ExprOp::TENSOR_RUNTIME_SCALAR || nd.op == ExprOp::RUNTIME_SCALAR) {
+            uint32_t slot;
+            auto it = slot_of_graph_input.find(nd.input_slot);
+            if (it != slot_of_graph_input.end()) {
+                slot = it->second;
+            } else {
+                slot = static_cast<uint32_t>(inputs.size());
+                slot_of_graph_input[nd.input_slot] = slot;
+                input_graph_slot.push_back(nd.input_slot);
+                if (nd.op == ExprOp::RUNTIME_SCALAR) {
+                    inputs.push_back({THOR_B200_INPUT_RUNTIME_SCALAR_FP32, THOR_B200_FP32});
+                    input_shapes.push_back(THOR_B200_SHAPE_SCALAR);
+                    scalar_names.push_back(g.inputs[nd.input_slot].name);
+                    scalars->push_back(ctx.bound[nd.input_slot].scalar);
+                } else {
+                    const Tensor& t = ctx.bound[nd.input_slot].tensor;
+                    const int cls = nd.op == ExprOp::TENSOR_RUNTIME_SCALAR ? THOR_B200_SHAPE_SCALAR : classify(t.getDimensions());
+                    if (cls < 0) return {};
+                    inputs.push_back({nd.op == ExprOp::TENSOR_RUNTIME_SCALAR ? THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR : THOR_B200_INPUT_TENSOR,
+                                      static_cast<int>(t.getDataType())});
+                    input_shapes.push_back(cls);
+                    scalar_names.push_back("");
+                    scalars->push_back(0.0f);
+                }
+            }
+            cn.op = static_cast<uint16_t>(nd.op);
+            cn.input_slot = slot;
+            cn.input_dtype = static_cast<uint16_t>(inputs[slot].dtype);
+        } else if (nd.op == ExprOp::SCALAR_FP) {
+            cn.op = THOR_B200_OP_SCALAR_FP;
+            cn.scalar_fp = nd.scalar_fp;
+        } else if (isValueReductionOp(nd.op)) {
+            const auto& in_shape = ctx.shape[nd.lhs];
+            if (classify(in_shape) != THOR_B200_SHAPE_FULL) return {};
+            const size_t pad = frame.size() - in_shape.size();
+            if (pad != 0) return {};
+            std::vector<bool> reduced(in_shape.size(), nd.reduction_axes.empty());
+            for (uint64_t ax : nd.reduction_axes) reduced[ax] = true;
+            bool only_last = true, all_but_last = true;
+            for (size_t i = 0; i < in_shape.size(); ++i) {
+                if (in_shape[i] == 1) continue;
+                const bool last = i + 1 == in_shape.size();
+                if (last ? !reduced[i] : reduced[i]) only_last = false;
+                if (last ? reduced[i] : !reduced[i]) all_but_last = false;
+            }
+            if (!only_last && !all_but_last) return {};
+            cn.op = static_cast<uint16_t>(nd.op);
+            cn.lhs = remap.at(nd.lhs);
+            cn.input_slot = only_last ? 0u : 1u;
+        } else {
+            if (classify(ctx.shape[k]) < 0) return {};
+            cn.op = static_cast<uint16_t>(nd.op);
+            if (nd.lhs != UINT32_MAX) cn.lhs = remap.at(nd.lhs);
+            if (nd.rhs != UINT32_MAX) cn.rhs = remap.at(nd.rhs);
+            if (nd.aux != UINT32_MAX) cn.aux = remap.at(nd.aux);
+        }
+        remap[k] = static_cast<uint32_t>(nodes.size());
+        nodes.push_back(cn);
+    }
+    std::vector<thor_b200_expr_output> outs;
+    for (const auto& o : ctx.outputs) {
+        const ExprNode& on = g.nodes[o.node_idx];
+        if (isLeafOp(on.op)) return {};
+        outs.push_back({remap.at(o.node_idx), static_cast<int>(*on.output_dtype)});
+    }
+    // two outputs that alias one program node (e.g. a value and its squeezed view) are not handled here
+    for (size_t i = 0; i < outs.size(); ++i)
+        for (size_t j = i + 1; j < outs.size(); ++j)
+            if (outs[i].node == outs[j].node) return {};
+
+    thor_b200_rowprog_desc d{};
+    d.nodes = nodes.data();
+    d.n_nodes = static_cast<uint32_t>(nodes.size());
+    d.inputs = inputs.data();
+    d.input_shapes = input_shapes.data();
+    d.n_inputs = static_cast<uint32_t>(inputs.size());
+    d.outputs = outs.data();
+    d.n_outputs = static_cast<uint32_t>(outs.size());
+    d.rows = rows;
+    d.cols = cols;
+    d.options.use_fast_math = ctx.use_fast_math;
+    auto prog = std::make_shared<ProgHandle>();
+    size_t ws_bytes = 1;
+    const int status = thor_b200_rowprog_compile(&d, &prog->h, &ws_bytes);
+    if (status == THOR_B200_UNSUPPORTED) return {};
+    if (status != THOR_B200_OK) throw std::runtime_error(std::string("row program: ") + thor_b200_last_error());
+
+    RowFusionMatch m;
+    m.name = "row_program";
+    m.source = thor_b200_rowprog_source(prog->h);
+    m.launches = thor_b200_rowprog_launch_count(prog->h);
+    m.scalar_names = scalar_names;
+    m.scalars = scalars;
+    std::vector<uint32_t> out_nodes;
+    for (const auto& o : ctx.outputs) {
+        m.produced.push_back({o.node_idx, true});
+        out_nodes.push_back(o.node_idx);
+    }
+    for (uint32_t k = 0; k < n; ++k)
+        if (needed[k] && !isLeafOp(g.nodes[k].op)) m.absorbed.push_back(k);
+    const int device = ctx.device_num;
+    std::vector<Tensor> in_tensors;
+    for (uint32_t gs : input_graph_slot) in_tensors.push_back(ctx.bound[gs].tensor);
+    m.bind = [prog, ws_bytes, out_nodes, in_tensors, scalars, device](std::vector<Tensor>& node_tensor, std::vector<Tensor>& keep_alive,
+                                                                       uint64_t& intermediate_bytes) -> std::function<void(void*)> {
+        Tensor ws = Tensor::allocate(DataType::UINT8, {static_cast<uint64_t>(ws_bytes)}, device);
+        if (ws_bytes > 1) intermediate_bytes += ws_bytes;
+        std::vector<const void*> in_ptrs;
+        for (const Tensor& t : in_tensors) {
+            in_ptrs.push_back(t.isInitialized() ? t.getMemPtr() : nullptr);
+            if (t.isInitialized()) keep_alive.push_back(t);
+        }
+        std::vector<void*> out_ptrs;
+        for (uint32_t k : out_nodes) out_ptrs.push_back(node_tensor[k].getMemPtr());
+        keep_alive.push_back(ws);
+        return [prog, in_ptrs, out_ptrs, ws, ws_bytes, scalars](void* stream) {
+            const int st = thor_b200_rowprog_launch(prog->h, in_ptrs.data(), scalars->data(), out_ptrs.data(), ws.getMemPtr(), ws_bytes, stream);
+            if (st != THOR_B200_OK) throw std::runtime_error(std::string("row program launch: ") + thor_b200_last_error());
+        };
+    };
+    std::vector<RowFusionMatch> out;
+    out.push_back(std::move(m));
+    return out;
+}
 
 }  // namespace ThorB200
