@@ -402,7 +402,83 @@ def torch_cat(ts):
     return torch.cat([t.reshape(-1) for t in ts])
 
 
-WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c4": C4FullReduce}
+def _layernorm_expr(ex, eps=1e-5):
+    from thor_b200 import DataType
+
+    x, gamma, beta = ex.input("x"), ex.input("gamma"), ex.input("beta")
+    mean = x.reduce_mean([1])
+    xc = x - mean
+    var = (xc * xc).reduce_mean([1])
+    rstd = 1.0 / (var + eps).sqrt()
+    return (xc * rstd * gamma + beta).cast(DataType.bf16)
+
+
+class C5LayerNormFwd(Workload):
+    name = "c5_layernorm_forward_bf16"
+    description = "Expression-authored LayerNorm forward over bf16 [32768,8192] per GPU (mean/var row reductions fused with the elementwise terms)"
+    dtype = "bf16"
+    ROWS, COLS = 32768, 8192
+
+    def _inputs(self, gen):
+        import torch
+
+        R, C = self.ROWS, self.COLS
+        x = torch.randn(R, C, device="cuda", generator=gen).bfloat16()
+        gamma = (torch.rand(C, device="cuda", generator=gen) * 0.2 + 0.9).bfloat16()
+        beta = (torch.randn(C, device="cuda", generator=gen) * 0.02).bfloat16()
+        return x, gamma, beta
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        gen = torch.Generator(device="cuda").manual_seed(55 + self.dist.rank)
+        eq = ex.compile({"y": _layernorm_expr(ex)})
+        self.sets = []
+        for _ in range(2):
+            x, gamma, beta = self._inputs(gen)
+            y = torch.empty_like(x)
+            self.sets.append((eq.stamp({"x": x, "gamma": gamma, "beta": beta}, outputs={"y": y}), x, y))
+        self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
+        self.kernel_kind = self.sets[0][0].physical_stage_names()
+
+    def algorithmic_bytes(self): return 2 * self.ROWS * self.COLS * 2 + 2 * self.COLS * 2
+    def units(self): return self.ROWS * self.COLS
+    def step(self, i): self.sets[i % len(self.sets)][0].run()
+
+
+class C5LayerNormBwd(C5LayerNormFwd):
+    name = "c5_layernorm_backward_bf16"
+    description = "autodiff-generated LayerNorm backward (dx, dgamma, dbeta) over bf16 [32768,8192] per GPU; dgamma/dbeta allreduced when N > 1"
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
+        bwd = ex.compile({"y": _layernorm_expr(ex)}).compile_backward(["x", "gamma", "beta"])
+        self.sets = []
+        for _ in range(2):
+            x, gamma, beta = self._inputs(gen)
+            dy = (torch.randn(self.ROWS, self.COLS, device="cuda", generator=gen) * 1e-2).bfloat16()
+            plan = bwd.stamp({"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy})
+            self.sets.append((plan, x, dy, torch_cat([plan.output("gamma_grad"), plan.output("beta_grad")])))
+        self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
+        self.kernel_kind = self.sets[0][0].physical_stage_names()
+
+    def algorithmic_bytes(self): return 3 * self.ROWS * self.COLS * 2 + 3 * self.COLS * 2
+    def step(self, i):
+        plan = self.sets[i % len(self.sets)][0]
+        plan.run()
+        if self.dist.enabled:
+            packed = torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()])
+            self.dist.all_reduce(packed, "sum")
+
+
+WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
+             "c5_bwd": C5LayerNormBwd}
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -453,7 +529,8 @@ def run_workload(dist: Dist, cls, steps: int, warmup: int, sample_clocks: bool, 
     before = thor_b200.launch_count()
     sampler = ClockSampler(dist.local_rank if dist.enabled else 0) if (sample_clocks and dist.rank == 0) else None
     ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler)
-    launches = (thor_b200.launch_count() - before) * steps // (steps + warmup)
+    del before
+    launches = wl.launches_per_step * steps  # kernels of this library inside the timed region
     return wl, ms, wall, clocks, launches
 
 

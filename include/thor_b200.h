@@ -273,7 +273,11 @@ THOR_B200_API void thor_b200_argreduce_plan_destroy(thor_b200_argreduce_plan* pl
  *     value and yields a ROW value that later nodes may consume (softmax max / sum, mean, variance);
  *   - REDUCE_{SUM,AVG} with input_slot = 1 reduces along the rows of a FULL value and yields a COL value
  *     that must be an output (LayerNorm dgamma / dbeta): persistent CTAs keep per-column fp32
- *     partials in registers, write them to the workspace and a second kernel folds them in order.
+ *     partials in registers, write them to the workspace and a second kernel folds them in order;
+ *   - REDUCE_* with input_slot = 2 reduces over ALL rows * cols elements and must be an output; a program
+ *     made only of such reductions (e.g. sum, sum of squares and max of one tensor) reads its inputs
+ *     once for all of them: the single-pass replacement of several DeviceTransformReduce calls plus
+ *     the materialised elementwise stages in front of them.
  * One CTA (or one warp for short rows) owns a row, keeps it in registers, and every node keeps the
  * per-node dtype rule of the fused stages; reductions convert to fp32, accumulate in fp32 and
  * round once to the node's output dtype, like the reduction seam.

@@ -37,7 +37,7 @@ def test_softmax_row_program_matches_staged_and_oracle(rows, cols):
     for plan in (fused, staged):
         got = plan.output().cpu().numpy()
         np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-12)
-    assert fused.kernel_launches_per_run() == 1 and staged.kernel_launches_per_run() == 4
+    assert fused.kernel_launches_per_run() == 1 and staged.kernel_launches_per_run() >= 4
     assert fused.intermediate_bytes() <= 1 and staged.intermediate_bytes() >= rows * cols * 4
 
 
@@ -119,12 +119,14 @@ def test_layernorm_backward_from_autodiff(rows, cols):
     d = eo.ulp_distance(got, dxw, o.BF16)
     d = np.where(np.abs(got - dxw) <= 2e-8, 0.0, d)
     assert d.max() <= 1.0, d.max()
-    dg = fused.output("gamma_grad").float().cpu().numpy().astype(np.float64).reshape(-1)
-    db = fused.output("beta_grad").float().cpu().numpy().astype(np.float64).reshape(-1)
-    scale_g = np.abs(dg_w) + 1e-3 * np.sqrt(rows) * 1e-2
-    assert fused.output("gamma_grad").dtype == torch.float32
-    assert (np.abs(dg - dg_w) <= 1e-5 * scale_g + 2e-7 * rows * 1e-2).all()
-    assert (np.abs(db - db_w) <= 1e-5 * np.abs(db_w) + 2e-7 * rows * 1e-2).all()
+    # gradients are written in the dtype of their input (bf16 here): fp32 column sums within 1e-5, then one bf16 rounding
+    assert fused.output("gamma_grad").dtype == torch.bfloat16 and fused.output("beta_grad").dtype == torch.bfloat16
+    dg = o.to_float64(_bf16(fused.output("gamma_grad")).reshape(-1), o.BF16)
+    db = o.to_float64(_bf16(fused.output("beta_grad")).reshape(-1), o.BF16)
+    for got_c, want_c in ((dg, dg_w), (db, db_w)):
+        dd = eo.ulp_distance(got_c, eo.round_to(want_c, o.BF16), o.BF16)
+        dd = np.where(np.abs(got_c - want_c) <= 1e-5 * np.abs(want_c) + 2e-7 * rows * 1e-2 + 2.0 ** -9 * np.abs(want_c), 0.0, dd)
+        assert dd.max() <= 1.0, dd.max()
 
 
 def test_layernorm_backward_staged_plan_agrees():
@@ -167,3 +169,29 @@ def test_autodiff_unbroadcasts_with_reduce_sum():
     torch.cuda.synchronize()
     assert plan.output("w_grad").shape == (128,)
     assert torch.allclose(plan.output("w_grad"), (g * x).sum(0), rtol=1e-5, atol=1e-5)
+
+
+def test_full_reductions_of_one_tensor_share_one_pass():
+    """sum, (x*x).reduce_sum() and max of a bf16 vector (configuration 4 at a small size): one flat reduce
+    program instead of an elementwise stage and three DeviceTransformReduce passes.  The x*x node is a bf16
+    node, so the product is rounded to bf16 before the fp32 accumulation (cf. Lamb.cpp:106)."""
+    n = (1 << 22) + 13
+    x = (torch.randn(n, device="cuda") + 0.01).bfloat16()
+
+    def build():
+        xi = ex.input("x")
+        return {"sum": xi.reduce_sum(), "sumsq": (xi * xi).reduce_sum(), "max": xi.reduce_max()}
+
+    fused = ex.compile(build()).stamp({"x": x})
+    staged = ex.compile(build(), fuse_row_reductions=False).stamp({"x": x})
+    fused.run()
+    staged.run()
+    torch.cuda.synchronize()
+    assert fused.physical_stage_names() == ["row_program"]
+    assert staged.stage_kind_names() == ["FusedKernel", "Reduction", "Reduction", "Reduction"]
+    s, q, m = o.c4_stats(_bf16(x))
+    for plan in (fused, staged):
+        assert abs(float(plan.output("sum")) - s) <= 1e-5 * abs(s) + 2e-7 * n
+        assert abs(float(plan.output("sumsq")) - q) <= 1e-5 * abs(q)
+        assert float(plan.output("max")) == m
+    assert fused.intermediate_bytes() < (1 << 20) and staged.intermediate_bytes() >= 2 * n

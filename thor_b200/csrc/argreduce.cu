@@ -126,9 +126,17 @@ __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
             const uint64_t body0 = lo + head;
             const uint64_t n_packs = (hi - body0) / VEC;
             const uint64_t tail0 = body0 + n_packs * VEC;
+            // A thread visits its elements in increasing index order, so inside a thread a strict comparison keeps
+            // the earliest of equal values and the first NaN sticks; the full ordering rule is only needed when
+            // candidates of different threads meet.
+            float bv = 0.0f;
+            uint64_t bi = kNoIndex;
             auto consider = [&](uint64_t idx, float v) {
-                const Cand c{v, idx};
-                if (better<IS_MAX>(c, best)) best = c;
+                const bool take = bi == kNoIndex || (bv == bv && (v != v || (IS_MAX ? v > bv : v < bv)));
+                if (take) {
+                    bv = v;
+                    bi = idx;
+                }
             };
             for (uint64_t i = lo + t; i < body0; i += TEAM) consider(i, toFloat(p[i]));
             for (uint64_t q = t; q < n_packs; q += static_cast<uint64_t>(TEAM) * U) {
@@ -139,11 +147,21 @@ __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
 #pragma unroll
                 for (int u = 0; u < U; ++u)
                     if (q + static_cast<uint64_t>(u) * TEAM < n_packs) {
+                        // value-only scan of the pack; the index is materialised once per pack
+                        float pv = toFloat(reinterpret_cast<const T*>(&pk[u])[0]);
+                        int pj = 0;
 #pragma unroll
-                        for (int j = 0; j < VEC; ++j) consider(body0 + (q + static_cast<uint64_t>(u) * TEAM) * VEC + j, toFloat(reinterpret_cast<const T*>(&pk[u])[j]));
+                        for (int j = 1; j < VEC; ++j) {
+                            const float v = toFloat(reinterpret_cast<const T*>(&pk[u])[j]);
+                            const bool take = pv == pv && (v != v || (IS_MAX ? v > pv : v < pv));
+                            pv = take ? v : pv;
+                            pj = take ? j : pj;
+                        }
+                        consider(body0 + (q + static_cast<uint64_t>(u) * TEAM) * VEC + pj, pv);
                     }
             }
             for (uint64_t i = tail0 + t; i < hi; i += TEAM) consider(i, toFloat(p[i]));
+            best = Cand{bv, bi};
         }
     }
     best = teamBest<IS_MAX, TEAM>(best, sv, si);

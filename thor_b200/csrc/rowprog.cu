@@ -44,7 +44,7 @@ struct Program {
     std::vector<int> shape;   // per node
     std::vector<bool> live;
     std::vector<int> depth;   // number of row reductions below the node
-    std::vector<uint32_t> row_reduces, col_reduces;
+    std::vector<uint32_t> row_reduces, col_reduces, all_reduces;
     // geometry
     int vec = 4, team = 256, cta = 256, vpt = 1;
     bool persistent = false;
@@ -118,8 +118,13 @@ std::string analyse(Program& p) {
                 p.shape[k] = COL;
                 p.depth[k] = p.depth[nd.lhs];
                 p.col_reduces.push_back(static_cast<uint32_t>(k));
+            } else if (nd.input_slot == 2) {
+                if (ps != FULL) return "a full reduction needs a full-shaped argument";
+                p.shape[k] = SCALAR;
+                p.depth[k] = p.depth[nd.lhs];
+                p.all_reduces.push_back(static_cast<uint32_t>(k));
             } else {
-                return "reduction axis selector must be 0 (columns) or 1 (rows)";
+                return "reduction axis selector must be 0 (columns), 1 (rows) or 2 (all elements)";
             }
             continue;
         }
@@ -139,6 +144,19 @@ std::string analyse(Program& p) {
     }
     for (uint32_t k : p.col_reduces)
         if (consumers[k] != 0) return "a column reduction may only be an output";
+    if (!p.all_reduces.empty()) {
+        // flat reduce program: every output is a reduction over all elements of an elementwise expression
+        if (!p.row_reduces.empty() || !p.col_reduces.empty()) return "full reductions cannot be mixed with row or column reductions";
+        for (uint32_t k : p.all_reduces)
+            if (consumers[k] != 0) return "a full reduction may only be an output";
+        for (const auto& o : p.outputs) {
+            if (std::find(p.all_reduces.begin(), p.all_reduces.end(), o.node) == p.all_reduces.end()) return "every output of a flat reduce program must be a full reduction";
+            if (o.dtype != p.nodes[o.node].output_dtype) return "output dtype differs from its node's output dtype";
+        }
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] != FULL && p.input_shape[s] != SCALAR) return "flat reduce programs take full-shaped or one-element tensors";
+        return "";
+    }
     bool any_full = false;
     for (const auto& o : p.outputs) {
         const int sh = p.shape[o.node];
@@ -373,6 +391,131 @@ std::string emit(Program& p) {
     return "";
 }
 
+// Flat reduce program: rows * cols elements viewed as one vector.  CTA b streams packs
+// [b * CHUNK, (b + 1) * CHUNK) with 4 independent 16-byte loads in flight per thread and tensor,
+// evaluates the elementwise DAG per element, keeps one fp32 accumulator per requested reduction
+// and writes one partial per reduction; foldFullPartials then combines the partials in CTA order.
+std::string emitFlat(Program& p) {
+    std::ostringstream os;
+    const int VEC = p.vec;
+    const uint64_t numel = p.rows * p.cols;
+    os << "// generated by thor_b200: flat reduce program, " << p.nodes.size() << " nodes, " << numel << " elements, " << p.all_reduces.size() << " reduction(s)\n";
+    os << "#include \"tb_prelude.cuh\"\n#include \"tb_rowprog.cuh\"\n\n";
+    os << "extern \"C\" __global__ void __launch_bounds__(256) row_kernel(";
+    bool first = true;
+    for (size_t s = 0; s < p.inputs.size(); ++s) {
+        os << (first ? "" : ", ");
+        first = false;
+        if (p.inputs[s].kind == THOR_B200_INPUT_RUNTIME_SCALAR_FP32) os << "const float s" << s;
+        else os << "const " << cTypeName(p.inputs[s].dtype) << "* __restrict__ in" << s;
+    }
+    for (size_t o = 0; o < p.outputs.size(); ++o) {
+        os << (first ? "" : ", ");
+        first = false;
+        os << cTypeName(p.outputs[o].dtype) << "* __restrict__ out" << o;
+    }
+    os << (first ? "" : ", ") << "float* __restrict__ ws) {\n";
+    os << "    constexpr int VEC = " << VEC << ", U = 4, ITERS = " << p.vpt << ";\n";
+    os << "    constexpr tb_u64 NUMEL = " << numel << "ull, NPACKS = NUMEL / VEC, CHUNK = 256ull * U * ITERS;\n";
+    os << "    __shared__ float red_smem[" << p.all_reduces.size() << "][1][8];\n";
+    os << "    const int t = threadIdx.x;\n";
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == SCALAR))
+            os << "    const " << cTypeName(p.inputs[s].dtype) << (p.inputs[s].kind == THOR_B200_INPUT_TENSOR ? " x" : " s") << s << " = in" << s << "[0];\n";
+    // scalar-class nodes
+    std::vector<uint32_t> scalars_first;
+    for (uint32_t k = 0; k < p.nodes.size(); ++k)
+        if (p.live[k] && p.shape[k] == SCALAR && !isReduce(p.nodes[k].op)) scalars_first.push_back(k);
+    emitStatements(p, scalars_first, "    ", os);
+    for (uint32_t k : p.all_reduces) os << "    float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+    std::vector<uint32_t> args;
+    for (uint32_t k : p.all_reduces) args.push_back(p.nodes[k].lhs);
+    const std::vector<uint32_t> closure = elementClosure(p, args);
+    auto emitAccumulate = [&](const std::string& indent) {
+        emitStatements(p, closure, indent, os);
+        for (uint32_t k : p.all_reduces) {
+            const uint32_t a = p.nodes[k].lhs;
+            const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
+            os << indent << "r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+        }
+    };
+    os << "    const tb_u64 chunk0 = (tb_u64)blockIdx.x * CHUNK;\n";
+    os << "#pragma unroll 1\n    for (int it = 0; it < ITERS; ++it) {\n";
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) os << "        tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> f" << s << "[U];\n";
+    os << "#pragma unroll\n        for (int k = 0; k < U; ++k) {\n            const tb_u64 q = chunk0 + (tb_u64)(it * U + k) * 256 + t;\n            if (q < NPACKS) {\n";
+    for (size_t s = 0; s < p.inputs.size(); ++s)
+        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) os << "                tb_load_stream(f" << s << "[k], in" << s << " + q * VEC);\n";
+    os << "            }\n        }\n";
+    os << "#pragma unroll\n        for (int k = 0; k < U; ++k) {\n            const tb_u64 q = chunk0 + (tb_u64)(it * U + k) * 256 + t;\n            if (q < NPACKS) {\n";
+    os << "#pragma unroll\n                for (int j = 0; j < VEC; ++j) {\n";
+    emitElementInputs(p, closure, "                    ", os);
+    emitAccumulate("                    ");
+    os << "                }\n            }\n        }\n    }\n";
+    // ragged tail: NUMEL % VEC elements, one per thread of CTA 0
+    os << "    if (blockIdx.x == 0) {\n        const tb_u64 i = NPACKS * VEC + t;\n        if (i < NUMEL) {\n";
+    {
+        std::vector<bool> done(p.inputs.size(), false);
+        for (uint32_t k : closure) {
+            const auto& nd = p.nodes[k];
+            if (nd.op != THOR_B200_OP_INPUT || done[nd.input_slot] || p.input_shape[nd.input_slot] != FULL) continue;
+            done[nd.input_slot] = true;
+            os << "            const " << cTypeName(p.inputs[nd.input_slot].dtype) << " x" << nd.input_slot << " = in" << nd.input_slot << "[i];\n";
+        }
+    }
+    emitAccumulate("            ");
+    os << "        }\n    }\n";
+    size_t idx = 0;
+    for (uint32_t k : p.all_reduces) {
+        os << "    r" << k << " = tb_team_reduce_stage1<256, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][0]);\n";
+        ++idx;
+    }
+    os << "    __syncthreads();\n";
+    idx = 0;
+    for (uint32_t k : p.all_reduces) {
+        os << "    r" << k << " = tb_team_reduce_stage2<256, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][0]);\n";
+        os << "    if (t == 0) ws[(tb_u64)" << idx << " * gridDim.x + blockIdx.x] = r" << k << ";\n";
+        ++idx;
+    }
+    os << "}\n";
+    p.source = os.str();
+    return "";
+}
+
+// Folds the per-CTA partials of one full reduction: one CTA, thread t takes partials t, t + 1024, ...
+template <int OP>
+__device__ __forceinline__ float foldCombine(float a, float b) {
+    if (OP == 1) return a * b;
+    if (OP == 2) return a != a ? a : (b != b ? b : fminf(a, b));
+    if (OP == 3) return a != a ? a : (b != b ? b : fmaxf(a, b));
+    return a + b;
+}
+template <int OP>
+__global__ void __launch_bounds__(1024) foldFullPartials(const float* __restrict__ ws, uint32_t parts, void* out, int out_dtype, float divisor, int take_sqrt) {
+    __shared__ float sm[32];
+    const float identity = OP == 1 ? 1.0f : (OP == 2 ? __int_as_float(0x7f800000) : (OP == 3 ? __int_as_float(0xff800000) : 0.0f));
+    float v = identity;
+    for (uint32_t s = threadIdx.x; s < parts; s += 1024) v = foldCombine<OP>(v, ws[s]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = foldCombine<OP>(v, __shfl_xor_sync(0xffffffffu, v, off));
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float r = sm[0];
+        for (int w = 1; w < 32; ++w) r = foldCombine<OP>(r, sm[w]);
+        if (divisor != 1.0f) r = r / divisor;
+        if (take_sqrt) r = sqrtf(r);
+        switch (out_dtype) {
+            case THOR_B200_FP32: static_cast<float*>(out)[0] = r; break;
+            case THOR_B200_FP16: static_cast<__half*>(out)[0] = __float2half_rn(r); break;
+            case THOR_B200_BF16: static_cast<__nv_bfloat16*>(out)[0] = __float2bfloat16_rn(r); break;
+            case THOR_B200_FP8_E4M3: static_cast<__nv_fp8_storage_t*>(out)[0] = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3); break;
+            case THOR_B200_FP8_E5M2: static_cast<__nv_fp8_storage_t*>(out)[0] = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E5M2); break;
+            default: break;
+        }
+    }
+}
+
 // Folds column partials [parts][cols] in part order and stores in the output dtype.
 __global__ void __launch_bounds__(256) foldColumnPartials(const float* __restrict__ ws, uint32_t parts, uint64_t cols, void* out, int out_dtype, float divisor) {
     const uint64_t c = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -441,6 +584,28 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
             mx = std::max(mx, dtypeSize(o.dtype));
         }
     if (mn > mx) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: no [rows, cols] tensor in the program");
+    if (!p.all_reduces.empty()) {
+        // flat reduce program over rows * cols elements
+        p.vec = static_cast<int>(16 / mn);
+        p.team = p.cta = 256;
+        const uint64_t numel = p.rows * p.cols;
+        const uint64_t packs = numel / p.vec;
+        p.vpt = 4;  // iterations of 4 packs per thread: one CTA streams 256 * 16 packs (64 KiB of the narrowest tensor)
+        const uint64_t chunk = 256ull * 4 * p.vpt;
+        const uint64_t blocks = std::max<uint64_t>(1, (packs + chunk - 1) / chunk);
+        if (blocks > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: too many elements for one grid");
+        p.grid = static_cast<uint32_t>(blocks);
+        p.persistent = false;
+        const std::string ferr = emitFlat(p);
+        if (!ferr.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", ferr.c_str());
+        h->workspace_bytes = p.all_reduces.size() * static_cast<size_t>(p.grid) * sizeof(float);
+        if (int st = jit::compileSource(p.source, p.fast_math, "row_kernel", &h->module)) return st;
+        if (!h->compile_only)
+            if (int st = jit::ensureLoaded(*h->module)) return st;
+        *workspace_bytes = h->workspace_bytes;
+        *out_prog = h.release();
+        return THOR_B200_OK;
+    }
     int vec = static_cast<int>(16 / mn);
     if (vec < 4) vec = 4;
     while (vec > 4 && static_cast<size_t>(vec) * mx > 64) vec /= 2;
@@ -493,7 +658,8 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
     TB_REQUIRE(output_ptrs != nullptr, "rowprog_launch: output_ptrs is null");
     const Program& p = h->prog;
     TB_REQUIRE(workspace_bytes >= h->workspace_bytes, "rowprog_launch: workspace too small");
-    TB_REQUIRE(p.col_reduces.empty() || (workspace != nullptr && isAligned(workspace, 16)), "rowprog_launch: workspace must be a 16-byte aligned device pointer");
+    TB_REQUIRE((p.col_reduces.empty() && p.all_reduces.empty()) || (workspace != nullptr && isAligned(workspace, 16)),
+               "rowprog_launch: workspace must be a 16-byte aligned device pointer");
     if (int st = jit::ensureLoaded(*h->module)) return st;
     constexpr size_t kMaxArgs = 64;
     TB_REQUIRE(p.inputs.size() + p.outputs.size() + 1 <= kMaxArgs, "rowprog_launch: too many kernel arguments");
@@ -528,6 +694,25 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, 0, stream));
     countLaunch();
+    if (!p.all_reduces.empty()) {
+        size_t idx = 0;
+        for (uint32_t k : p.all_reduces) {
+            size_t o = 0;
+            for (; o < p.outputs.size(); ++o)
+                if (p.outputs[o].node == k) break;
+            const uint16_t op = p.nodes[k].op;
+            const float divisor = op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows * p.cols) : 1.0f;
+            const int take_sqrt = op == THOR_B200_OP_REDUCE_NORM2;
+            const float* part = static_cast<const float*>(workspace) + idx * static_cast<size_t>(p.grid);
+            if (op == THOR_B200_OP_REDUCE_PROD) foldFullPartials<1><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            else if (op == THOR_B200_OP_REDUCE_MIN) foldFullPartials<2><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            else if (op == THOR_B200_OP_REDUCE_MAX) foldFullPartials<3><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            else foldFullPartials<0><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            TB_CUDA(cudaGetLastError());
+            ++idx;
+        }
+        countLaunch(p.all_reduces.size());
+    }
     if (!p.col_reduces.empty()) {
         const uint32_t parts = p.grid * static_cast<uint32_t>(p.cta / p.team);
         size_t ci = 0;
@@ -548,7 +733,9 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
 
 const char* thor_b200_rowprog_source(const thor_b200_rowprog* h) { return h ? h->prog.source.c_str() : ""; }
 
-uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) { return h ? 1u + static_cast<uint32_t>(h->prog.col_reduces.size()) : 0u; }
+uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) {
+    return h ? 1u + static_cast<uint32_t>(h->prog.col_reduces.size() + h->prog.all_reduces.size()) : 0u;
+}
 
 void thor_b200_rowprog_destroy(thor_b200_rowprog* h) { delete h; }
 

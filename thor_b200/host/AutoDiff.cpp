@@ -63,7 +63,8 @@ struct Builder {
 }  // namespace
 
 Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::string>& wrt_names, const std::string& upstream_prefix,
-                             const std::unordered_map<std::string, std::vector<uint64_t>>& input_dims) {
+                             const std::unordered_map<std::string, std::vector<uint64_t>>& input_dims,
+                             const std::unordered_map<std::string, DataType>& input_dtypes) {
     if (!forward.expression()) throw std::logic_error("buildBackwardOutputs requires forward outputs");
     Builder b;
     b.fwd = std::make_shared<PhysicalExpression>(*forward.expression());
@@ -78,6 +79,17 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
         }
     }
     b.fwd_shape = inferNodeShapes(g, in_dims);
+    // resolved dtypes of the forward nodes (queried by the CAST rule); the cloned forward nodes stay unresolved
+    PhysicalOutputs resolved = forward.physicalOutputs();
+    resolved.expr = std::make_shared<PhysicalExpression>(g);
+    {
+        std::vector<DataType> dts(g.inputs.size(), DataType::FP32);
+        for (const NamedInput& ni : g.inputs) {
+            auto it = input_dtypes.find(ni.name);
+            if (it != input_dtypes.end()) dts[ni.slot] = it->second;
+        }
+        resolveOutputsDTypesInPlace(resolved, dts);
+    }
 
     // seed: upstream gradient inputs
     std::map<uint32_t, Expression> grad;
@@ -199,7 +211,7 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
             case ExprOp::CAST:
                 // straight-through: the gradient is converted back to the source dtype (AutoDiff.cpp, CAST rule)
                 if (wants(nd.lhs)) {
-                    const std::optional<DataType> src = g.nodes[nd.lhs].output_dtype;
+                    const std::optional<DataType> src = resolved.expr->nodes[nd.lhs].output_dtype;
                     accumulate(nd.lhs, src.has_value() ? G.cast(*src) : G);
                 }
                 break;
@@ -243,6 +255,12 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
             if (es != b.fwd_shape[k]) {
                 if (numelOf(es) == numelOf(b.fwd_shape[k])) e = e.reshape(b.fwd_shape[k]);
                 else throw std::logic_error("buildBackwardOutputs: gradient of '" + w + "' needs an explicit broadcast, which this build does not provide");
+            }
+            // terminal dtype = dtype of the forward input; a terminal reduction stores it directly
+            auto dt = input_dtypes.find(w);
+            if (dt != input_dtypes.end() && isFusionFloat(dt->second)) {
+                const ExprNode& term = e.graph()->nodes[e.nodeIndex()];
+                e = isValueReductionOp(term.op) ? e.withOutputDType(dt->second) : e.cast(dt->second);
             }
             named.emplace_back(w + "_grad", e);
             break;

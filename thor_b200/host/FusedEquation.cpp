@@ -308,9 +308,13 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
     if (deferred_backward_) {
         // shapes are known only now: build the backward DAG for these forward shapes
         std::unordered_map<std::string, std::vector<uint64_t>> dims;
+        std::unordered_map<std::string, DataType> dtypes;
         for (const auto& kv : inputs)
-            if (!kv.second.is_scalar) dims[kv.first] = kv.second.tensor.getDimensions();
-        outputs = buildBackwardOutputs(deferred_backward_->forward, deferred_backward_->wrt, deferred_backward_->upstream_prefix, dims);
+            if (!kv.second.is_scalar) {
+                dims[kv.first] = kv.second.tensor.getDimensions();
+                dtypes[kv.first] = kv.second.tensor.getDataType();
+            }
+        outputs = buildBackwardOutputs(deferred_backward_->forward, deferred_backward_->wrt, deferred_backward_->upstream_prefix, dims, dtypes);
     }
     PhysicalOutputs phys = outputs.physicalOutputs();
     // private copy: dtype resolution writes into the graph

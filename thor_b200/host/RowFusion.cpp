@@ -40,10 +40,6 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
     if (frame.empty() || frame.size() < 1) return {};
     const uint64_t cols = frame.back();
     const uint64_t total = numelOf(frame);
-    if (cols < 2 || total == cols) {
-        // a 1-D tensor reduced over its only axis is a full reduction, not a row program
-        if (frame.size() < 2 || total == cols) return {};
-    }
     const uint64_t rows = total / cols;
 
     auto classify = [&](const std::vector<uint64_t>& d) -> int {
@@ -130,17 +126,18 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
             if (pad != 0) return {};
             std::vector<bool> reduced(in_shape.size(), nd.reduction_axes.empty());
             for (uint64_t ax : nd.reduction_axes) reduced[ax] = true;
-            bool only_last = true, all_but_last = true;
+            bool only_last = true, all_but_last = true, all = true;
             for (size_t i = 0; i < in_shape.size(); ++i) {
                 if (in_shape[i] == 1) continue;
                 const bool last = i + 1 == in_shape.size();
                 if (last ? !reduced[i] : reduced[i]) only_last = false;
                 if (last ? reduced[i] : !reduced[i]) all_but_last = false;
+                if (!reduced[i]) all = false;
             }
-            if (!only_last && !all_but_last) return {};
+            if (!only_last && !all_but_last && !all) return {};
             cn.op = static_cast<uint16_t>(nd.op);
             cn.lhs = remap.at(nd.lhs);
-            cn.input_slot = only_last ? 0u : 1u;
+            cn.input_slot = all ? 2u : (only_last ? 0u : 1u);
         } else {
             if (classify(ctx.shape[k]) < 0) return {};
             cn.op = static_cast<uint16_t>(nd.op);
