@@ -66,14 +66,25 @@ __device__ __forceinline__ void storeResult(const ArgArgs& a, uint64_t out_idx, 
     if (a.value_out) storeValue(a.value_out, a.value_dtype, out_idx, c.v);
 }
 
-template <bool IS_MAX, int TEAM>
+// IDX32: every index of the reduction domain fits 32 bits (kNoIndex travels as 0xffffffff), which halves
+// the shuffle traffic of the combine.
+template <bool IDX32>
+__device__ __forceinline__ unsigned long long shflIndex(unsigned long long i, int off, int span) {
+    if (IDX32) {
+        const unsigned int lo = __shfl_down_sync(0xffffffffu, static_cast<unsigned int>(i), off, span);
+        return lo == 0xffffffffu ? kNoIndex : static_cast<unsigned long long>(lo);
+    }
+    return __shfl_down_sync(0xffffffffu, i, off, span);
+}
+
+template <bool IS_MAX, int TEAM, bool IDX32 = false>
 __device__ __forceinline__ Cand teamBest(Cand c, float* sv, unsigned long long* si) {
     constexpr int kSpan = TEAM < 32 ? TEAM : 32;
 #pragma unroll
     for (int off = kSpan / 2; off > 0; off >>= 1) {
         Cand o;
         o.v = __shfl_down_sync(0xffffffffu, c.v, off, kSpan);
-        o.i = __shfl_down_sync(0xffffffffu, c.i, off, kSpan);
+        o.i = shflIndex<IDX32>(c.i, off, kSpan);
         if (better<IS_MAX>(o, c)) c = o;
     }
     if constexpr (TEAM > 32) {
@@ -103,7 +114,7 @@ __device__ __forceinline__ Cand teamBest(Cand c, float* sv, unsigned long long* 
     return c;
 }
 
-template <class T, bool IS_MAX, int TEAM>
+template <class T, bool IS_MAX, int TEAM, bool IDX32>
 __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
     constexpr int VEC = 16 / sizeof(T);
     constexpr int U = 4;
@@ -164,7 +175,7 @@ __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
             best = Cand{bv, bi};
         }
     }
-    best = teamBest<IS_MAX, TEAM>(best, sv, si);
+    best = teamBest<IS_MAX, TEAM, IDX32>(best, sv, si);
     if (t == 0 && row < a.outer) {
         if (a.splits == 1) storeResult(a, row, best);
         else {
@@ -258,11 +269,16 @@ int launchArg(const thor_b200_argreduce_plan& p, const ArgArgs& a, cudaStream_t 
         const uint64_t teams = kThreads / p.team;
         const uint64_t blocks = ((a.outer + teams - 1) / teams) * a.splits;
         if (blocks > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "argreduce: grid too large");
+        const bool idx32 = a.reduction < 0xffffffffull;
+#define TB_ARG_ROWS(TEAMV)                                                                                              \
+    if (idx32) argRowsKernel<T, IS_MAX, TEAMV, true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a);        \
+    else argRowsKernel<T, IS_MAX, TEAMV, false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a);
         switch (p.team) {
-            case 8: argRowsKernel<T, IS_MAX, 8><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a); break;
-            case 32: argRowsKernel<T, IS_MAX, 32><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a); break;
-            default: argRowsKernel<T, IS_MAX, 256><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a); break;
+            case 8: TB_ARG_ROWS(8) break;
+            case 32: TB_ARG_ROWS(32) break;
+            default: TB_ARG_ROWS(256) break;
         }
+#undef TB_ARG_ROWS
         countLaunch();
         TB_CUDA(cudaGetLastError());
         if (a.splits > 1) {
@@ -327,7 +343,9 @@ int thor_b200_argreduce_plan_create(const thor_b200_argreduce_desc* d, thor_b200
     if (d->inner == 1) {
         p->rows = true;
         const uint64_t packs = (d->reduction + vec - 1) / vec;
-        p->team = packs <= 16 ? 8 : (packs <= 512 ? 32 : 256);
+        // one warp per row up to 2048 packs: the (value, index) combine then needs no shared memory and no
+        // barrier, which matters because it costs far more than a plain sum
+        p->team = packs <= 16 ? 8 : (packs <= 2048 && d->outer >= static_cast<uint64_t>(16 * sms) ? 32 : (packs <= 512 ? 32 : 256));
         const uint64_t ctas = (d->outer + (kThreads / p->team) - 1) / (kThreads / p->team);
         if (p->team == 256 && ctas < static_cast<uint64_t>(2 * sms)) {
             uint64_t s = (packs + 4095) / 4096;

@@ -13,6 +13,7 @@
 // persistent: they walk rows r, r + grid, ..., keep the per-column operands in registers and
 // accumulate per-column fp32 partials, which a small fold kernel sums in CTA order.
 #include <algorithm>
+#include <cstdlib>
 #include <memory>
 #include <sstream>
 
@@ -48,6 +49,8 @@ struct Program {
     // geometry
     int vec = 4, team = 256, cta = 256, vpt = 1;
     bool persistent = false;
+    bool prefetch = false;  // persistent programs: load row r + stride while row r is being computed
+    int min_ctas = 0;       // second __launch_bounds__ argument, 0 = none
     uint32_t grid = 0;
     std::string source;
 };
@@ -235,7 +238,7 @@ std::string emit(Program& p) {
        << " threads, " << VPT << " packs of " << VEC << " per thread" << (p.persistent ? ", persistent" : "") << "\n";
     os << "#include \"tb_prelude.cuh\"\n#include \"tb_rowprog.cuh\"\n\n";
     // kernel signature
-    os << "extern \"C\" __global__ void __launch_bounds__(" << CTA << ") row_kernel(";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << CTA << (p.min_ctas > 0 ? ", " + std::to_string(p.min_ctas) : std::string()) << ") row_kernel(";
     bool first = true;
     for (size_t s = 0; s < p.inputs.size(); ++s) {
         os << (first ? "" : ", ");
@@ -272,18 +275,37 @@ std::string emit(Program& p) {
            << "[k][j] = 0.0f;\n";
     }
     // row loop
-    if (p.persistent) os << "    for (tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id; row < ROWS; row += (tb_u64)gridDim.x * TEAMS) {\n";
-    else os << "    {\n        const tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id;\n        const bool row_ok = row < ROWS;\n";
     const std::string I = "        ";
+    auto declareFull = [&](const std::string& prefix, const std::string& indent) {
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL)
+                os << indent << "tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> " << prefix << s << "[VPT];\n";
+    };
+    auto loadFull = [&](const std::string& prefix, const std::string& row, const std::string& cond, const std::string& indent) {
+        os << "#pragma unroll\n" << indent << "for (int k = 0; k < VPT; ++k) {\n" << indent << "    const tb_u32 q = t + k * TEAM;\n" << indent << "    if (" << cond << ") {\n";
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL)
+                os << indent << "        tb_load_stream(" << prefix << s << "[k], in" << s << " + (" << row << ") * COLS + (tb_u64)q * VEC);\n";
+        os << indent << "    }\n" << indent << "}\n";
+    };
     const std::string guard = p.persistent ? "q < PPR" : "row_ok && q < PPR";
-    // load FULL inputs
-    for (size_t s = 0; s < p.inputs.size(); ++s)
-        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) os << I << "tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> f" << s << "[VPT];\n";
-    os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard << ") {\n";
-    for (size_t s = 0; s < p.inputs.size(); ++s)
-        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL)
-            os << I << "        tb_load_stream(f" << s << "[k], in" << s << " + row * COLS + (tb_u64)q * VEC);\n";
-    os << I << "    }\n" << I << "}\n";
+    if (p.persistent && p.prefetch) {
+        os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
+        declareFull("f", "    ");
+        declareFull("n", "    ");
+        loadFull("f", "row_first", "row_first < ROWS && q < PPR", "    ");
+        os << "    for (tb_u64 row = row_first; row < ROWS; row += row_stride) {\n";
+        os << I << "// the next row of this team is requested before the current one is touched\n";
+        loadFull("n", "row + row_stride", "row + row_stride < ROWS && q < PPR", I);
+    } else if (p.persistent) {
+        os << "    for (tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id; row < ROWS; row += (tb_u64)gridDim.x * TEAMS) {\n";
+        declareFull("f", I);
+        loadFull("f", "row", guard, I);
+    } else {
+        os << "    {\n        const tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id;\n        const bool row_ok = row < ROWS;\n";
+        declareFull("f", I);
+        loadFull("f", "row", guard, I);
+    }
     // ROW inputs
     for (size_t s = 0; s < p.inputs.size(); ++s)
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == ROW)
@@ -313,7 +335,11 @@ std::string emit(Program& p) {
         for (uint32_t k : round) args.push_back(p.nodes[k].lhs);
         const std::vector<uint32_t> closure = elementClosure(p, args);
         os << I << "// round " << d << ": " << round.size() << " row reduction(s)\n";
-        for (uint32_t k : round) os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+        auto isMinMax = [&](uint32_t k) { return p.nodes[k].op == THOR_B200_OP_REDUCE_MIN || p.nodes[k].op == THOR_B200_OP_REDUCE_MAX; };
+        for (uint32_t k : round) {
+            os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+            if (isMinMax(k)) os << I << "bool nan" << k << " = false;  // min / max: fminf / fmaxf plus a sticky NaN predicate per element\n";
+        }
         os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard << ") {\n";
         emitColumnPackLoads(p, closure, I + "        ", os);
         os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; ++j) {\n";
@@ -322,12 +348,17 @@ std::string emit(Program& p) {
         for (uint32_t k : round) {
             const uint32_t a = p.nodes[k].lhs;
             const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
-            os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+            if (isMinMax(k))
+                os << I << "            { const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
+                   << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
+            else
+                os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
         }
         os << I << "        }\n" << I << "    }\n" << I << "}\n";
         // team combine: all reductions of the round share one shared-memory exchange
         size_t slot = 0;
         for (uint32_t k : round) {
+            if (isMinMax(k)) os << I << "if (nan" << k << ") r" << k << " = __int_as_float(0x7fffffff);\n";
             const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
             os << I << "r" << k << " = tb_team_reduce_stage1<TEAM, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][team_id]);\n";
             ++slot;
@@ -375,6 +406,12 @@ std::string emit(Program& p) {
     for (size_t o = 0; o < p.outputs.size(); ++o)
         if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0" << (p.persistent ? "" : " && row_ok") << ") out" << o << "[row] = v" << p.outputs[o].node << ";\n";
     if (p.persistent && p.row_reduces.size() > 0) os << I << "if (TEAM > 32) __syncthreads();  // shared-memory slots are reused by the next row\n";
+    if (p.persistent && p.prefetch) {
+        os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n";
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) os << I << "    f" << s << "[k] = n" << s << "[k];\n";
+        os << I << "}\n";
+    }
     os << "    }\n";
     // column partials: ws[c][cta*TEAMS + team][COLS]
     size_t ci = 0;
@@ -427,7 +464,13 @@ std::string emitFlat(Program& p) {
     for (uint32_t k = 0; k < p.nodes.size(); ++k)
         if (p.live[k] && p.shape[k] == SCALAR && !isReduce(p.nodes[k].op)) scalars_first.push_back(k);
     emitStatements(p, scalars_first, "    ", os);
-    for (uint32_t k : p.all_reduces) os << "    float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+    auto isMinMax = [&](uint32_t k) { return p.nodes[k].op == THOR_B200_OP_REDUCE_MIN || p.nodes[k].op == THOR_B200_OP_REDUCE_MAX; };
+    for (uint32_t k : p.all_reduces) {
+        os << "    float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+        // min / max: the per-element step is fminf / fmaxf plus a sticky "saw a NaN" predicate (2 instructions);
+        // the NaN-propagating rule is restored once per thread before the CTA-wide combine
+        if (isMinMax(k)) os << "    bool nan" << k << " = false;\n";
+    }
     std::vector<uint32_t> args;
     for (uint32_t k : p.all_reduces) args.push_back(p.nodes[k].lhs);
     const std::vector<uint32_t> closure = elementClosure(p, args);
@@ -436,7 +479,12 @@ std::string emitFlat(Program& p) {
         for (uint32_t k : p.all_reduces) {
             const uint32_t a = p.nodes[k].lhs;
             const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
-            os << indent << "r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+            if (isMinMax(k)) {
+                os << indent << "{ const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
+                   << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
+            } else {
+                os << indent << "r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+            }
         }
     };
     os << "    const tb_u64 chunk0 = (tb_u64)blockIdx.x * CHUNK;\n";
@@ -467,6 +515,7 @@ std::string emitFlat(Program& p) {
     os << "        }\n    }\n";
     size_t idx = 0;
     for (uint32_t k : p.all_reduces) {
+        if (isMinMax(k)) os << "    if (nan" << k << ") r" << k << " = __int_as_float(0x7fffffff);\n";
         os << "    r" << k << " = tb_team_reduce_stage1<256, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][0]);\n";
         ++idx;
     }
@@ -612,9 +661,20 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     if (p.cols % vec != 0) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: cols (%llu) is not a multiple of the pack width %d", static_cast<unsigned long long>(p.cols), vec);
     const uint64_t packs = p.cols / vec;
     if (packs > 1024ull * 8) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: rows of %llu elements do not fit one CTA's registers", static_cast<unsigned long long>(p.cols));
+    // Packs per thread: up to 4.
+    const auto envInt = [](const char* name, int fallback) {
+        const char* v = getenv(name);
+        return v && *v ? atoi(v) : fallback;
+    };
+    const int vpt_target = 4;  // measured: 4 packs per thread beat 2 even with column accumulators in registers
     int team = 32;
-    while (team < 1024 && packs > static_cast<uint64_t>(team) * 4) team *= 2;
+    while (team < 1024 && packs > static_cast<uint64_t>(team) * vpt_target) team *= 2;
     if (team == 64) team = 128;
+    // tuning overrides for experiments: THOR_B200_ROWPROG_TEAM / _PREFETCH / _CTAS_PER_SM
+    {
+        const int forced = envInt("THOR_B200_ROWPROG_TEAM", 0);
+        if ((forced == 32 || forced == 128 || forced == 256 || forced == 512 || forced == 1024) && packs <= static_cast<uint64_t>(forced) * 8) team = forced;
+    }
     p.vec = vec;
     p.team = team;
     p.cta = team < 256 ? 256 : team;
@@ -622,6 +682,8 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     bool has_col_input = false;
     for (size_t s = 0; s < p.inputs.size(); ++s) has_col_input = has_col_input || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL);
     p.persistent = has_col_input || !p.col_reduces.empty();
+    p.prefetch = p.persistent && envInt("THOR_B200_ROWPROG_PREFETCH", 1) != 0;
+    p.min_ctas = envInt("THOR_B200_ROWPROG_MIN_CTAS", d->options.min_ctas_per_sm);
     const uint64_t teams_per_cta = p.cta / p.team;
     const uint64_t ctas_for_rows = (p.rows + teams_per_cta - 1) / teams_per_cta;
     int sms = 148;
@@ -631,8 +693,11 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         else (void)cudaGetLastError();
     }
     if (p.persistent) {
-        // column accumulators make every extra CTA cost a [cols] fp32 partial row: two CTAs per SM then
-        const uint64_t resident = p.col_reduces.empty() ? static_cast<uint64_t>(sms) * std::max(1, 1024 / p.cta) * 2 : static_cast<uint64_t>(sms) * 2;
+        // every extra CTA of a program with column reductions costs a [cols] fp32 partial row
+        // measured on B200 (LayerNorm [32768, 8192] bf16): 2 CTAs per SM for the forward program, 1 for the
+        // backward program whose per-column accumulators take most of the register file
+        uint64_t resident = p.col_reduces.empty() ? static_cast<uint64_t>(sms) * 2 : static_cast<uint64_t>(sms);
+        if (const int per_sm = envInt("THOR_B200_ROWPROG_CTAS_PER_SM", 0)) resident = static_cast<uint64_t>(sms) * per_sm;
         p.grid = static_cast<uint32_t>(std::min<uint64_t>(ctas_for_rows, resident));
     } else {
         if (ctas_for_rows > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: too many rows for one grid");
