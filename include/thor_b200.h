@@ -311,6 +311,27 @@ THOR_B200_API const char* thor_b200_rowprog_source(const thor_b200_rowprog* prog
 THOR_B200_API uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* prog);
 THOR_B200_API void thor_b200_rowprog_destroy(thor_b200_rowprog* prog);
 
+/* ---------------------------------------------------------------------------------------------
+ * Full reduction for callers that cannot allocate.  It has no counterpart in the reference, whose
+ * reductions always stamp a workspace first (CubReduction::stampValidated).
+ *
+ * Reduces the n elements of `input` (one dense vector) to a single value in `output`, with the same
+ * arithmetic as thor_b200_reduce_launch for outer = inner = 1.  The scratch the two-phase reduction
+ * needs is a fixed 256 KiB array inside the library instead of a caller workspace, so the call
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.  It exists for callers
+ * that have no point at which they could allocate: a step that is being captured into a CUDA graph,
+ * a process that distributed all of its device memory at start-up, a latency-critical loop that must
+ * not hit cudaMalloc's device-wide synchronisation.
+ *
+ * Limit: at most 65536 partials, i.e. n <= 65536 * 4096 * (16 / element size) elements (2^30 for fp32,
+ * 2^31 for fp16 / bf16, 2^32 for fp8); larger inputs are rejected with THOR_B200_INVALID_ARGUMENT.
+ * The first call on each device looks up the array's device address; make that first call outside
+ * of any stream capture.  All calls on a device share the one array: two calls whose kernels can
+ * overlap on the GPU (different streams, no dependency) race on it and must be ordered by the caller.
+ * ------------------------------------------------------------------------------------------- */
+THOR_B200_API int thor_b200_reduce_full_noalloc(int op, const void* input, int input_dtype, uint64_t n, void* output, int output_dtype,
+                                                float output_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

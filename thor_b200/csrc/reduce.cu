@@ -16,6 +16,7 @@
 
 #include <cfloat>
 #include <memory>
+#include <mutex>
 
 namespace tb {
 
@@ -466,3 +467,89 @@ const char* thor_b200_reduce_plan_kind(const thor_b200_reduce_plan* p) { return 
 void thor_b200_reduce_plan_destroy(thor_b200_reduce_plan* p) { delete p; }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Full reduction without any allocation by anybody.
+//
+// thor_b200_reduce_launch needs a workspace that somebody allocated beforehand.  Some callers have no
+// such moment: code that is being recorded into a CUDA graph (cudaMalloc is illegal while a stream
+// is capturing), code that runs under a fixed device-memory budget where every byte was handed out
+// at start-up, and code on a latency-critical path where cudaMalloc's implicit device
+// synchronisation is not acceptable.  For them the per-CTA partials of the two-phase full reduction
+// live in the fixed array below, which is part of the library image: every GPU that loads the
+// library carries these 256 KiB until the process exits.
+// ---------------------------------------------------------------------------------------------------
+namespace tb {
+namespace {
+
+constexpr uint32_t kNoAllocMaxPartials = 65536;  // 256 KiB of fp32 partials
+static __device__ __align__(256) float g_noalloc_partials[kNoAllocMaxPartials];
+
+// Device address of g_noalloc_partials per device ordinal.  In host code the array's name is only a
+// handle for the runtime, never a pointer a kernel could use, so the address is looked up once per
+// device with cudaGetSymbolAddress while that device is current.
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[64] = {};
+
+int noAllocScratch(float** out) {
+    int dev = -1;
+    TB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(THOR_B200_CUDA_ERROR, "reduce_full_noalloc: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        TB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_partials));
+        g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return THOR_B200_OK;
+}
+
+}  // namespace
+}  // namespace tb
+
+extern "C" int thor_b200_reduce_full_noalloc(int op, const void* input, int input_dtype, uint64_t n, void* output, int output_dtype, float output_scale,
+                                             void* stream_v) {
+    using namespace tb;
+    TB_REQUIRE(op >= THOR_B200_REDUCE_SUM && op <= THOR_B200_REDUCE_L2NORM, "reduce_full_noalloc: unknown op %d", op);
+    TB_REQUIRE(isReduceFloat(input_dtype), "reduce_full_noalloc: unsupported input dtype %s", dtypeName(input_dtype));
+    TB_REQUIRE(isReduceFloat(output_dtype), "reduce_full_noalloc: unsupported output dtype %s", dtypeName(output_dtype));
+    TB_REQUIRE(input != nullptr && output != nullptr, "reduce_full_noalloc: null tensor pointer");
+    TB_REQUIRE(n > 0, "reduce_full_noalloc: zero-sized dimension");
+    TB_REQUIRE(output_scale == output_scale && output_scale - output_scale == 0.0f, "reduce_full_noalloc: output_scale must be finite");
+    // same cut as the planned path: one CTA per 4096 sixteen-byte packs
+    const uint64_t vec = 16 / dtypeSize(input_dtype);
+    const uint64_t packs = (n + vec - 1) / vec;
+    const uint64_t splits = (packs + 4095) / 4096;
+    const uint64_t max_elements = static_cast<uint64_t>(kNoAllocMaxPartials) * 4096 * vec;
+    if (splits > kNoAllocMaxPartials)
+        return fail(THOR_B200_INVALID_ARGUMENT,
+                    "reduce_full_noalloc: %llu elements of %s exceed the fixed scratch of %u partials (limit %llu elements); use thor_b200_reduce_launch with a workspace",
+                    static_cast<unsigned long long>(n), dtypeName(input_dtype), kNoAllocMaxPartials, static_cast<unsigned long long>(max_elements));
+    float* scratch = nullptr;
+    if (int st = noAllocScratch(&scratch)) return st;
+    thor_b200_reduce_plan plan{};
+    plan.desc.op = op;
+    plan.desc.input_dtype = input_dtype;
+    plan.desc.output_dtype = output_dtype;
+    plan.desc.outer = 1;
+    plan.desc.reduction = n;
+    plan.desc.inner = 1;
+    plan.family = Family::Rows;
+    plan.team = 256;
+    plan.splits = static_cast<uint32_t>(splits);
+    const float divisor = op == THOR_B200_REDUCE_MEAN ? static_cast<float>(n) : 1.0f;
+    // Every partial the fold kernel reads is written by the first kernel of this same call, so nothing
+    // in the array has to start at zero and stale values of earlier calls are never observed.
+    const RowsArgs ra{input, output, scratch, 1, n, 1, plan.splits, op, output_dtype, divisor, output_scale};
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    switch (input_dtype) {
+        case THOR_B200_FP32: return launchOp<float>(plan, &ra, nullptr, stream);
+        case THOR_B200_FP16: return launchOp<__half>(plan, &ra, nullptr, stream);
+        case THOR_B200_BF16: return launchOp<__nv_bfloat16>(plan, &ra, nullptr, stream);
+        case THOR_B200_FP8_E4M3: return launchOp<__nv_fp8_e4m3>(plan, &ra, nullptr, stream);
+        case THOR_B200_FP8_E5M2: return launchOp<__nv_fp8_e5m2>(plan, &ra, nullptr, stream);
+        default: break;
+    }
+    return fail(THOR_B200_INVALID_ARGUMENT, "reduce_full_noalloc: unsupported input dtype");
+}
