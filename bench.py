@@ -614,7 +614,9 @@ def main():
 
 
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.
-TRAFFIC_BYTES = {}
+# c2: 134.25 MB read + 27.91 MB written at half size (4096 rows), scaled x2 to the full launch; the written bytes
+# undercount the 134 MB output because most of it is still dirty in the 126 MB L2 when the kernel ends.
+TRAFFIC_BYTES = {"c2_fused_relu_axb_sigmoid": 324320256}
 
 if __name__ == "__main__":
     main()
