@@ -150,7 +150,7 @@ class Dist:
             self.dist.destroy_process_group()
 
 
-def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler | None = None):
+def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler | None = None, sample: bool = False):
     """W untimed + K timed calls of step(i); returns (device ms per step as max over ranks, wall ms per step)."""
     import torch
 
@@ -167,20 +167,21 @@ def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler 
     e1.record()
     dist.barrier()
     wall = (time.perf_counter() - t0) * 1e3 / steps
-    clocks = None
-    if sampler:
-        # nvidia-smi cannot sample faster than every few ms: when the timed region was shorter than that, keep the
-        # identical load running (untimed) until a handful of samples under load exist
-        extended = 0
-        t_ext = time.perf_counter()
-        while not dist.enabled and sampler.sample_count() < 5 and time.perf_counter() - t_ext < 2.0:
-            for i in range(steps):
-                step(warmup + steps + extended + i)
-            extended += steps
-            torch.cuda.synchronize()
-        clocks = sampler.stop()
-        clocks["untimed_extension_steps"] = extended
     ms = dist.max(e0.elapsed_time(e1) / steps)
+    clocks = None
+    if sample:
+        # nvidia-smi cannot sample faster than every ~20 ms: when the timed region was shorter than 400 ms every rank
+        # keeps the identical load running (untimed; the count derives from the rank-maximum time, so all ranks agree
+        # and collectives stay matched) until a handful of samples under load exist
+        extended = 0
+        if steps * ms < 400.0:
+            extended = int(400.0 / max(ms, 1e-3)) + 1
+            for i in range(extended):
+                step(warmup + steps + i)
+            dist.barrier()
+        if sampler:
+            clocks = sampler.stop()
+            clocks["untimed_extension_steps"] = extended
     return ms, wall, clocks
 
 
@@ -391,9 +392,9 @@ class C4FullReduce(Workload):
         self.plan.run()
         if self.dist.enabled:
             # per-GPU fp32 partials -> one allreduce each (sum for the additive statistics, max for the maximum)
-            packed = torch_cat(self.outs[:2])
-            self.dist.all_reduce(packed, "sum")
-            self.dist.all_reduce(self.outs[2], "max")
+            from thor_b200.sharding import combine_partials
+
+            combine_partials(sums=torch_cat(self.outs[:2]), maxima=self.outs[2])
 
 
 def torch_cat(ts):
@@ -473,8 +474,9 @@ class C5LayerNormBwd(C5LayerNormFwd):
         plan = self.sets[i % len(self.sets)][0]
         plan.run()
         if self.dist.enabled:
-            packed = torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()])
-            self.dist.all_reduce(packed, "sum")
+            from thor_b200.sharding import combine_partials
+
+            combine_partials(sums=torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()]))
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
@@ -528,7 +530,7 @@ def run_workload(dist: Dist, cls, steps: int, warmup: int, sample_clocks: bool, 
     wl.setup()
     before = thor_b200.launch_count()
     sampler = ClockSampler(dist.local_rank if dist.enabled else 0) if (sample_clocks and dist.rank == 0) else None
-    ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler)
+    ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler, sample_clocks)
     del before
     launches = wl.launches_per_step * steps  # kernels of this library inside the timed region
     return wl, ms, wall, clocks, launches

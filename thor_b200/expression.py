@@ -260,10 +260,13 @@ class Expression:
 
     # ---- compilation ------------------------------------------------------------------------------
     @staticmethod
-    def compile(expr: Union["Expression", Mapping[str, "Expression"]], device_num: int = 0, use_fast_math: bool = False,
+    def compile(expr: Union["Expression", Mapping[str, "Expression"]], device_num: Optional[int] = None, use_fast_math: bool = False,
                 fuse_row_reductions: bool = True) -> "FusedEquation":
-        """FusedEquation::compile: one Expression (output named "output") or a dict of named outputs."""
+        """FusedEquation::compile: one Expression (output named "output") or a dict of named outputs.
+        device_num defaults to the current CUDA device of the calling process."""
         named = {"output": expr} if isinstance(expr, Expression) else dict(expr)
+        if device_num is None:
+            device_num = torch.cuda.current_device() if torch.cuda.is_available() else 0
         return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions)
 
 

@@ -1,0 +1,46 @@
+"""Leading-dimension sharding across the GPUs of one box and the one collective the path needs.
+
+Elementwise stages, casts, row reductions and row programs need no communication: every rank runs
+the same kernels on its own contiguous block of rows.  Only values reduced over the sharded
+dimension (full reductions, LayerNorm dgamma / dbeta column sums) are combined, with one allreduce
+of the per-rank fp32 partials.  The reference has no multi-GPU path; this is new glue over
+``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n: int, rank: int, world: int, multiple: int = 8) -> Tuple[int, int]:
+    """Contiguous [start, stop) of `n` rows / elements for `rank`; every boundary but the last is a
+    multiple of `multiple` (16-byte packs stay aligned), sizes differ by at most `multiple`."""
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    blocks = -(-n // multiple)
+    per, extra = divmod(blocks, world)
+    start_block = rank * per + min(rank, extra)
+    stop_block = start_block + per + (1 if rank < extra else 0)
+    return min(n, start_block * multiple), min(n, stop_block * multiple)
+
+
+def combine_partials(sums: Optional[torch.Tensor] = None, maxima: Optional[torch.Tensor] = None, minima: Optional[torch.Tensor] = None,
+                     group=None) -> None:
+    """In-place allreduce of per-rank fp32 partials: `sums` with SUM (sum, sum of squares, dgamma, dbeta ...),
+    `maxima` with MAX, `minima` with MIN.  No-op without an initialised process group."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    if sums is not None:
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+    if maxima is not None:
+        dist.all_reduce(maxima, op=dist.ReduceOp.MAX, group=group)
+    if minima is not None:
+        dist.all_reduce(minima, op=dist.ReduceOp.MIN, group=group)
+
+
+def finalize_mean(total: torch.Tensor, global_count: int) -> torch.Tensor:
+    """Mean of a sharded reduction: divide the allreduced fp32 sum by the global element count (fp32 division,
+    like the reduction seam's finaliser)."""
+    return total / torch.tensor(float(global_count), dtype=torch.float32, device=total.device)
