@@ -20,7 +20,7 @@ def test_shard_ranges_cover_and_align():
             for (a0, a1), (b0, b1) in zip(ranges, ranges[1:]):
                 assert a1 == b0 and (a1 % 8 == 0 or a1 == n)
             sizes = [b - a for a, b in ranges]
-            assert max(sizes) - min(sizes) <= 8
+            assert max(sizes) - min(sizes) < 16  # one block of 8 plus the ragged last block
 
 
 def _free_port():
