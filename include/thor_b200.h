@@ -187,6 +187,12 @@ THOR_B200_API const char* thor_b200_expr_source(const thor_b200_expr* expr);
 /* "flat_v2", "flat_scalar", "bcast_tiled_v2", "bcast_tiled_scalar" or "bcast_generic": which kernel shape was chosen. */
 THOR_B200_API const char* thor_b200_expr_launch_kind(const thor_b200_expr* expr);
 THOR_B200_API void thor_b200_expr_destroy(thor_b200_expr* expr);
+/* 16-bit stages evaluate exp and division with leaner routines than cuda_fp16.hpp's h2exp / __h2div, the
+ * intrinsics the reference emits (CudaSourceEmitter.cpp:4376-4377).  This self-check runs both over every fp16
+ * input (exp) and every ordered input pair in both lanes (division) and writes four counters to device
+ * memory: [0] exp mismatches, [1] mismatches of the variant used for arguments known to be <= 0, [2] division
+ * mismatches, [3] division pairs checked (2^32).  Bit parity with the reference requires [0..2] == 0. */
+THOR_B200_API int thor_b200_selfcheck_pair_math(unsigned long long* device_counters, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Device memory for stamped plans.  Replaces the allocation half of ThorImplementation::Tensor

@@ -202,3 +202,20 @@ def test_run_rejects_multi_stage_expressions():
     eq = ex.compile(ex.input("x") - ex.input("x").reduce_max([1]))
     with pytest.raises(ThorB200InvalidArgument):
         eq.run({"x": x}, torch.empty_like(x))
+
+
+def test_lean_pair_math_is_bit_identical_to_the_toolkit_intrinsics():
+    """tb_h2exp / tb_h2exp_nonpos / tb_h2div against h2exp / __h2div: all 65536 inputs, all 2^32 pairs, both lanes."""
+    import ctypes as C
+
+    import torch
+
+    from thor_b200 import _native
+
+    counters = torch.full((4,), -1, dtype=torch.int64, device="cuda")
+    _native.lib.thor_b200_selfcheck_pair_math.argtypes = [C.c_void_p, C.c_void_p]
+    _native.check(_native.lib.thor_b200_selfcheck_pair_math(counters.data_ptr(), _native.stream_handle()))
+    torch.cuda.synchronize()
+    exp_bad, expn_bad, div_bad, checked = counters.tolist()
+    assert checked == 1 << 32
+    assert (exp_bad, expn_bad, div_bad) == (0, 0, 0)

@@ -18,6 +18,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <sstream>
 
 #include "common.cuh"
@@ -156,8 +157,38 @@ struct Plan {
     std::vector<bool> live;
     bool v2 = false;
     int v2_dtype = 0;
+    // value-range facts used to pick cheaper bit-identical routines: "<= 0 or NaN" / ">= 0 or NaN"
+    std::vector<bool> nonpos, nonneg;
+    bool lean_pair_math = true;
     explicit Plan(const Stage& s) : st(s) {}
 };
+
+void analyseSigns(Plan& p) {
+    const auto& n = p.st.nodes;
+    p.nonpos.assign(n.size(), false);
+    p.nonneg.assign(n.size(), false);
+    for (size_t k = 0; k < n.size(); ++k) {
+        if (!p.live[k]) continue;
+        const auto& nd = n[k];
+        auto np = [&](uint32_t i) { return i != THOR_B200_NO_NODE && p.nonpos[i]; };
+        auto nn = [&](uint32_t i) { return i != THOR_B200_NO_NODE && p.nonneg[i]; };
+        switch (nd.op) {
+            case THOR_B200_OP_SCALAR_FP: p.nonneg[k] = nd.scalar_fp >= 0.0; p.nonpos[k] = nd.scalar_fp <= 0.0; break;
+            case THOR_B200_OP_ABS: case THOR_B200_OP_EXP: case THOR_B200_OP_EXP2: case THOR_B200_OP_EXP10: case THOR_B200_OP_SQRT: case THOR_B200_OP_COSH:
+                p.nonneg[k] = true; break;
+            case THOR_B200_OP_NEG: p.nonneg[k] = np(nd.lhs); p.nonpos[k] = nn(nd.lhs); break;
+            case THOR_B200_OP_CAST: p.nonneg[k] = nn(nd.lhs); p.nonpos[k] = np(nd.lhs); break;
+            case THOR_B200_OP_MAX: p.nonneg[k] = nn(nd.lhs) || nn(nd.rhs); p.nonpos[k] = np(nd.lhs) && np(nd.rhs); break;
+            case THOR_B200_OP_MIN: p.nonpos[k] = np(nd.lhs) || np(nd.rhs); p.nonneg[k] = nn(nd.lhs) && nn(nd.rhs); break;
+            case THOR_B200_OP_MUL: case THOR_B200_OP_DIV:
+                p.nonneg[k] = (nn(nd.lhs) && nn(nd.rhs)) || (np(nd.lhs) && np(nd.rhs));
+                p.nonpos[k] = (nn(nd.lhs) && np(nd.rhs)) || (np(nd.lhs) && nn(nd.rhs));
+                break;
+            case THOR_B200_OP_ADD: p.nonneg[k] = nn(nd.lhs) && nn(nd.rhs); p.nonpos[k] = np(nd.lhs) && np(nd.rhs); break;
+            default: break;
+        }
+    }
+}
 
 void markLive(Plan& p) {
     const auto& n = p.st.nodes;
@@ -283,10 +314,12 @@ std::string v2NodeExpr(const Plan& p, size_t k) {
         case THOR_B200_OP_ADD: return "__hadd2(" + a + ", " + b + ")";
         case THOR_B200_OP_SUB: return "__hsub2(" + a + ", " + b + ")";
         case THOR_B200_OP_MUL: return "__hmul2(" + a + ", " + b + ")";
-        case THOR_B200_OP_DIV: return "__h2div(" + a + ", " + b + ")";
+        case THOR_B200_OP_DIV: return (!bf && p.lean_pair_math ? "tb_h2div(" : "__h2div(") + a + ", " + b + ")";
         case THOR_B200_OP_NEG: return "__hneg2(" + a + ")";
         case THOR_B200_OP_ABS: return "__hmax2(" + a + ", __hneg2(" + a + "))";
-        case THOR_B200_OP_EXP: return "h2exp(" + a + ")";
+        case THOR_B200_OP_EXP:
+            if (!bf && p.lean_pair_math) return std::string(p.nonpos[nd.lhs] ? "tb_h2exp_nonpos(" : "tb_h2exp(") + a + ")";
+            return "h2exp(" + a + ")";
         case THOR_B200_OP_EXP2: return "h2exp2(" + a + ")";
         case THOR_B200_OP_EXP10: return "h2exp10(" + a + ")";
         case THOR_B200_OP_LN: return "h2log(" + a + ")";
@@ -742,6 +775,8 @@ std::string emit(const Stage& st, bool force_generic, Emitted* out) {
     Plan p(st);
     markLive(p);
     decideV2(p);
+    analyseSigns(p);
+    if (const char* e = getenv("THOR_B200_LEAN_PAIR_MATH")) p.lean_pair_math = atoi(e) != 0;
     std::ostringstream os;
     os << "// generated by thor_b200: fused stage, " << st.nodes.size() << " nodes, " << st.inputs.size() << " inputs, " << st.outputs.size() << " outputs\n";
     os << "#include \"tb_prelude.cuh\"\n\n";

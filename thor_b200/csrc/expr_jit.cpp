@@ -346,6 +346,50 @@ int thor_b200_expr_launch(thor_b200_expr* e, const void* const* input_ptrs, cons
     return launchVariant(*e, e->safe, input_ptrs, runtime_scalars, output_ptrs, numel, stream);
 }
 
+// Exhaustive comparison of the lean pair routines of the device prelude with the toolkit's routines.
+static const char* const kSelfCheckSource = R"TBCHECK(
+#include "tb_prelude.cuh"
+__device__ __forceinline__ unsigned int tb_half2bits(const __half2 v) { return *reinterpret_cast<const unsigned int*>(&v); }
+extern "C" __global__ void __launch_bounds__(256) selfcheck_kernel(unsigned long long* counters) {
+    const unsigned int a16 = blockIdx.x;  // 65536 blocks: one per fp16 bit pattern
+    unsigned long long bad_exp = 0, bad_expn = 0, bad_div = 0, checks = 0;
+    // division: lane x computes a / b, lane y computes b / a, for every b: all 2^32 ordered pairs in both lanes
+    for (unsigned int b16 = threadIdx.x; b16 < 65536u; b16 += blockDim.x) {
+        const __half2 A = tb_bits2half2(a16 | (b16 << 16)), B = tb_bits2half2(b16 | (a16 << 16));
+        bad_div += tb_half2bits(__h2div(A, B)) != tb_half2bits(tb_h2div(A, B));
+        ++checks;
+    }
+    if (threadIdx.x == 0) {
+        // exp: every pattern in lane x, its complement in lane y
+        const __half2 X = tb_bits2half2(a16 | ((65535u - a16) << 16));
+        bad_exp += tb_half2bits(h2exp(X)) != tb_half2bits(tb_h2exp(X));
+        // exp of arguments that are <= 0 or NaN: every pattern with the sign bit set in lane x; +0 and the
+        // positive NaN patterns in lane y
+        const unsigned int y = (a16 & 0x3FFu) ? (0x7C00u | (a16 & 0x3FFu)) : 0u;
+        const __half2 N = tb_bits2half2((a16 | 0x8000u) | (y << 16));
+        bad_expn += tb_half2bits(h2exp(N)) != tb_half2bits(tb_h2exp_nonpos(N));
+    }
+    atomicAdd(&counters[0], bad_exp);
+    atomicAdd(&counters[1], bad_expn);
+    atomicAdd(&counters[2], bad_div);
+    atomicAdd(&counters[3], checks);
+}
+)TBCHECK";
+
+int thor_b200_selfcheck_pair_math(unsigned long long* device_counters, void* stream_v) {
+    using namespace tb;
+    TB_REQUIRE(device_counters != nullptr, "selfcheck_pair_math: device_counters is null");
+    std::shared_ptr<jit::Module> mod;
+    if (int st = jit::compileSource(kSelfCheckSource, false, "selfcheck_kernel", &mod)) return st;
+    if (int st = jit::ensureLoaded(*mod)) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    TB_CUDA(cudaMemsetAsync(device_counters, 0, 4 * sizeof(unsigned long long), stream));
+    void* args[] = {&device_counters};
+    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(mod->kernel), dim3(65536), dim3(256), args, 0, stream));
+    countLaunch();
+    return THOR_B200_OK;
+}
+
 const char* thor_b200_expr_source(const thor_b200_expr* e) { return e ? e->fast.em.source.c_str() : ""; }
 
 const char* thor_b200_expr_launch_kind(const thor_b200_expr* e) { return e ? tb::expr::kindName(e->fast.em.kind) : ""; }

@@ -68,6 +68,55 @@ __device__ __forceinline__ void tb_store_stream(void* dst, const tb_pack<BYTES>&
     }
 }
 
+// ---- lean pair math -------------------------------------------------------------------------------
+// Bit-identical replacements for two cuda_fp16.hpp pair routines that dominate the instruction count
+// of 16-bit stages (h2exp, __h2div).  Same arithmetic per lane (fp32 multiply by log2(e),
+// ex2.approx.ftz.f32, one round-to-nearest conversion, the same special-input corrections; fp32
+// reciprocal-multiply with the same refinement for tiny quotients), but packed conversions and a
+// packed test for the rare refinement.  thor_b200_selfcheck_pair_math compares them with the toolkit
+// routines over every input (exp) and every input pair (div).
+__device__ __forceinline__ __half2 tb_bits2half2(unsigned int v) {
+    __half2 r;
+    *reinterpret_cast<unsigned int*>(&r) = v;
+    return r;
+}
+__device__ __forceinline__ __half2 tb_h2exp_core(const __half2 a) {
+    const float2 f = __half22float2(a);
+    float lo, hi;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(lo) : "f"(__fmaf_rn(f.x, __int_as_float(0x3fb8aa3b), __int_as_float(0x80000000))));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(hi) : "f"(__fmaf_rn(f.y, __int_as_float(0x3fb8aa3b), __int_as_float(0x80000000))));
+    return __floats2half2_rn(lo, hi);
+}
+__device__ __forceinline__ __half2 tb_h2exp_fix(const __half2 a, const __half2 r, unsigned int special, unsigned int ulp) {
+    return __hfma2(__heq2(a, tb_bits2half2(special)), tb_bits2half2(ulp), r);
+}
+__device__ __forceinline__ __half2 tb_h2exp(const __half2 a) {
+    __half2 r = tb_h2exp_core(a);
+    r = tb_h2exp_fix(a, r, 0x1F791F79u, 0x94009400u);
+    r = tb_h2exp_fix(a, r, 0x25CF25CFu, 0x94009400u);
+    r = tb_h2exp_fix(a, r, 0xC13BC13Bu, 0x04000400u);
+    r = tb_h2exp_fix(a, r, 0xC1EFC1EFu, 0x02000200u);
+    return r;
+}
+// Argument known to be <= 0 (or NaN): the two corrections for positive inputs can never fire.
+__device__ __forceinline__ __half2 tb_h2exp_nonpos(const __half2 a) {
+    __half2 r = tb_h2exp_core(a);
+    r = tb_h2exp_fix(a, r, 0xC13BC13Bu, 0x04000400u);
+    r = tb_h2exp_fix(a, r, 0xC1EFC1EFu, 0x02000200u);
+    return r;
+}
+__device__ __forceinline__ __half2 tb_h2div(const __half2 a, const __half2 b) {
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    float rx, ry;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rx) : "f"(fb.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ry) : "f"(fb.y));
+    const __half2 v = __floats2half2_rn(rx * fa.x, ry * fa.y);
+    // the toolkit routine refines a lane whose quotient q satisfies 0 < |q| < 0x008F (as fp16 bits)
+    const unsigned int bits = *reinterpret_cast<const unsigned int*>(&v) & 0x7fff7fffu;
+    if (((bits & 0xffffu) - 1u) < 0x8Eu || ((bits >> 16) - 1u) < 0x8Eu) return __h2div(a, b);
+    return v;
+}
+
 // fp8 e4m3 stores saturate to the largest finite value (+-448).
 __device__ __forceinline__ __nv_fp8_e4m3 tb_to_e4m3(float v) {
     __nv_fp8_e4m3 r;
@@ -108,6 +157,15 @@ __device__ __forceinline__ float tb_mul(float a, float b) { return a * b; }
 // NaN-propagating min / max, the rule of the reduction seam.
 __device__ __forceinline__ float tb_nanmin(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 __device__ __forceinline__ float tb_nanmax(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
+
+// 16-byte asynchronous global -> shared copy (LDGSTS, bypasses registers and L1) and its group fences.
+__device__ __forceinline__ void tb_cp_async16(void* smem, const void* gmem) {
+    const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void tb_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tb_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Stage 1: xor butterfly inside each warp (every lane ends with the warp's value, bit-identical
 // across lanes because the operators are commutative); warp leaders of wide teams publish it.

@@ -51,6 +51,8 @@ struct Program {
     bool persistent = false;
     bool prefetch = false;  // persistent programs: load row r + stride while row r is being computed
     int min_ctas = 0;       // second __launch_bounds__ argument, 0 = none
+    bool stage_smem = false;  // persistent programs: rows are staged in shared memory with cp.async (double buffer)
+    size_t smem_bytes = 0;
     uint32_t grid = 0;
     std::string source;
 };
@@ -172,6 +174,117 @@ std::string analyse(Program& p) {
     return "";
 }
 
+
+// ---- linear hoisting of row sums -----------------------------------------------------------------
+// sum_j (c * f_j) = c * sum_j f_j when c is constant along the row.  Reverse-mode graphs are full of
+// such sums (every un-broadcast of a gradient that was scaled by a per-row statistic), and each
+// one that depends on an earlier row statistic costs a whole extra pass over the row in registers.
+// The rewrite expresses a SUM / AVG row reduction of a linear combination as the same combination of
+// reductions of its row-varying factors, which usually have a smaller depth.  Only fp32 nodes are
+// rewritten (in 16-bit graphs the per-element rounding of the products is part of the result), and
+// only when the reduction's depth drops.  The value changes by fp32 re-association only.
+struct LinearTerm {
+    std::vector<std::pair<uint32_t, bool>> coeffs;  // row-constant factors (node, is divisor)
+    uint32_t atom;                                  // row-varying factor
+    bool negative;
+};
+
+bool isF32Node(const thor_b200_expr_node& n) { return n.output_dtype == THOR_B200_FP32 && n.compute_dtype == THOR_B200_FP32; }
+
+void decomposeLinear(const Program& p, uint32_t k, std::vector<std::pair<uint32_t, bool>> coeffs, bool negative, std::vector<LinearTerm>& out) {
+    const auto& nd = p.nodes[k];
+    auto rowConst = [&](uint32_t i) { return p.shape[i] == ROW || p.shape[i] == SCALAR; };
+    if (p.shape[k] == FULL && isF32Node(nd)) {
+        if (nd.op == THOR_B200_OP_NEG) return decomposeLinear(p, nd.lhs, coeffs, !negative, out);
+        if ((nd.op == THOR_B200_OP_ADD || nd.op == THOR_B200_OP_SUB) && !rowConst(nd.lhs) && !rowConst(nd.rhs)) {
+            decomposeLinear(p, nd.lhs, coeffs, negative, out);
+            decomposeLinear(p, nd.rhs, coeffs, nd.op == THOR_B200_OP_SUB ? !negative : negative, out);
+            return;
+        }
+        if (nd.op == THOR_B200_OP_MUL && (rowConst(nd.lhs) != rowConst(nd.rhs))) {
+            const uint32_t c = rowConst(nd.lhs) ? nd.lhs : nd.rhs, f = rowConst(nd.lhs) ? nd.rhs : nd.lhs;
+            coeffs.push_back({c, false});
+            return decomposeLinear(p, f, coeffs, negative, out);
+        }
+        if (nd.op == THOR_B200_OP_DIV && rowConst(nd.rhs) && !rowConst(nd.lhs)) {
+            coeffs.push_back({nd.rhs, true});
+            return decomposeLinear(p, nd.lhs, coeffs, negative, out);
+        }
+    }
+    out.push_back({coeffs, k, negative});
+}
+
+// Returns true when the program was rewritten (the caller re-runs analyse()).
+bool hoistLinearRowSums(Program& p) {
+    bool changed = false;
+    std::vector<thor_b200_expr_node> out_nodes;
+    std::vector<uint32_t> remap(p.nodes.size(), THOR_B200_NO_NODE);
+    auto push = [&](thor_b200_expr_node n) {
+        out_nodes.push_back(n);
+        return static_cast<uint32_t>(out_nodes.size() - 1);
+    };
+    auto f32 = [&](uint16_t op, uint32_t lhs, uint32_t rhs) {
+        thor_b200_expr_node n{};
+        n.op = op;
+        n.output_dtype = n.compute_dtype = THOR_B200_FP32;
+        n.lhs = lhs;
+        n.rhs = rhs;
+        n.aux = THOR_B200_NO_NODE;
+        n.input_slot = THOR_B200_NO_NODE;
+        return n;
+    };
+    for (uint32_t k = 0; k < p.nodes.size(); ++k) {
+        thor_b200_expr_node nd = p.nodes[k];
+        const bool candidate = p.live[k] && isReduce(nd.op) && nd.input_slot == 0 && (nd.op == THOR_B200_OP_REDUCE_SUM || nd.op == THOR_B200_OP_REDUCE_AVG) &&
+                               nd.output_dtype == THOR_B200_FP32;
+        std::vector<LinearTerm> terms;
+        if (candidate) decomposeLinear(p, nd.lhs, {}, false, terms);
+        int new_depth = 0;
+        bool any_coeff = false;
+        for (const auto& t : terms) {
+            new_depth = std::max(new_depth, p.depth[t.atom] + 1);
+            for (const auto& c : t.coeffs) {
+                new_depth = std::max(new_depth, p.depth[c.first]);
+                any_coeff = true;
+            }
+        }
+        if (candidate && any_coeff && new_depth < p.depth[k]) {
+            // value = sum over terms of (+-) reduce(atom) * c1 * c2 / d1 ...
+            uint32_t total = THOR_B200_NO_NODE;
+            std::vector<std::pair<uint32_t, uint32_t>> reduced;  // atom (new index) -> reduce node
+            for (const auto& t : terms) {
+                const uint32_t atom = remap[t.atom];
+                uint32_t r = THOR_B200_NO_NODE;
+                for (const auto& pr : reduced)
+                    if (pr.first == atom) r = pr.second;
+                if (r == THOR_B200_NO_NODE) {
+                    thor_b200_expr_node rn = f32(nd.op, atom, THOR_B200_NO_NODE);
+                    rn.input_slot = 0;
+                    r = push(rn);
+                    reduced.push_back({atom, r});
+                }
+                uint32_t v = r;
+                for (const auto& c : t.coeffs) v = push(f32(c.second ? THOR_B200_OP_DIV : THOR_B200_OP_MUL, v, remap[c.first]));
+                if (total == THOR_B200_NO_NODE) total = t.negative ? push(f32(THOR_B200_OP_NEG, v, THOR_B200_NO_NODE)) : v;
+                else total = push(f32(t.negative ? THOR_B200_OP_SUB : THOR_B200_OP_ADD, total, v));
+            }
+            remap[k] = total;
+            changed = true;
+            continue;
+        }
+        for (uint32_t* par : {&nd.lhs, &nd.rhs, &nd.aux})
+            if (*par != THOR_B200_NO_NODE && !(isReduce(nd.op) && par != &nd.lhs)) *par = remap[*par] != THOR_B200_NO_NODE ? remap[*par] : *par;
+        remap[k] = push(nd);
+    }
+    if (!changed) return false;
+    for (auto& o : p.outputs) o.node = remap[o.node];
+    p.nodes = out_nodes;
+    p.row_reduces.clear();
+    p.col_reduces.clear();
+    p.all_reduces.clear();
+    return true;
+}
+
 // Statements "const T vK = <expr>;" for the given nodes (already in topological order).
 void emitStatements(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
     for (uint32_t k : ids) os << indent << "const " << cTypeName(p.nodes[k].output_dtype) << " v" << k << " = " << scalarNodeExpression(p.nodes, p.inputs, k) << ";\n";
@@ -202,6 +315,7 @@ std::string elemTypeOfInput(const Program& p, size_t slot) { return cTypeName(p.
 
 // Declarations of the element values x<slot> that `ids` read, for lane j of pack k.
 void emitElementInputs(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
+    const bool staged = p.persistent && p.stage_smem;
     std::vector<bool> done(p.inputs.size(), false);
     for (uint32_t k : ids) {
         const auto& nd = p.nodes[k];
@@ -209,13 +323,30 @@ void emitElementInputs(const Program& p, const std::vector<uint32_t>& ids, const
         done[nd.input_slot] = true;
         const size_t s = nd.input_slot;
         const std::string T = elemTypeOfInput(p, s);
-        if (p.input_shape[s] == FULL) os << indent << "const " << T << " x" << s << " = reinterpret_cast<const " << T << "*>(&f" << s << "[k])[j];\n";
+        if (p.input_shape[s] == FULL)
+            os << indent << "const " << T << " x" << s << " = reinterpret_cast<const " << T << "*>(&" << (staged ? "g" + std::to_string(s) : "f" + std::to_string(s) + "[k]")
+               << ")[j];\n";
         else os << indent << "const " << T << " x" << s << " = reinterpret_cast<const " << T << "*>(&c" << s << "[k])[j];\n";
     }
 }
 
 // Per-pack loads of COL inputs for non-persistent programs (L1/L2 resident, re-read each round).
 void emitColumnPackLoads(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
+    if (p.persistent && p.stage_smem) {
+        // this thread's pack k of the current row, from its private slot of the staging buffer
+        std::vector<bool> done(p.inputs.size(), false);
+        size_t fi = 0;
+        std::vector<size_t> full_index(p.inputs.size(), 0);
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) full_index[s] = fi++;
+        for (uint32_t k : ids) {
+            const auto& nd = p.nodes[k];
+            if (nd.op != THOR_B200_OP_INPUT || p.input_shape[nd.input_slot] != FULL || done[nd.input_slot]) continue;
+            done[nd.input_slot] = true;
+            os << indent << "const uint4 g" << nd.input_slot << " = tb_stage[((" << full_index[nd.input_slot] << " * 2 + buf) * VPT + k) * " << p.cta << " + threadIdx.x];\n";
+        }
+        return;
+    }
     if (p.persistent) return;
     std::vector<bool> done(p.inputs.size(), false);
     for (uint32_t k : ids) {
@@ -289,7 +420,28 @@ std::string emit(Program& p) {
         os << indent << "    }\n" << indent << "}\n";
     };
     const std::string guard = p.persistent ? "q < PPR" : "row_ok && q < PPR";
-    if (p.persistent && p.prefetch) {
+    if (p.persistent && p.stage_smem) {
+        os << "    extern __shared__ uint4 tb_stage[];  // [full input][2 buffers][VPT][CTA threads] 16-byte packs, slot private to its thread\n";
+        os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
+        auto issue = [&](const std::string& row, const std::string& bufexpr, const std::string& indent) {
+            os << indent << "if (" << row << " < ROWS) {\n#pragma unroll\n" << indent << "    for (int k = 0; k < VPT; ++k) {\n" << indent << "        const tb_u32 q = t + k * TEAM;\n"
+               << indent << "        if (q < PPR) {\n";
+            size_t fi = 0;
+            for (size_t s = 0; s < p.inputs.size(); ++s)
+                if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
+                    os << indent << "            tb_cp_async16(&tb_stage[((" << fi << " * 2 + " << bufexpr << ") * VPT + k) * " << p.cta << " + threadIdx.x], in" << s << " + (" << row
+                       << ") * COLS + (tb_u64)q * VEC);\n";
+                    ++fi;
+                }
+            os << indent << "        }\n" << indent << "    }\n" << indent << "}\n" << indent << "tb_cp_async_commit();\n";
+        };
+        os << "    int buf = 0;\n";
+        issue("row_first", "0", "    ");
+        os << "    for (tb_u64 row = row_first; row < ROWS; row += row_stride) {\n";
+        os << I << "// the copy of this team's next row runs while the current row is computed\n";
+        issue("row + row_stride", "(buf ^ 1)", I);
+        os << I << "tb_cp_async_wait<1>();\n";
+    } else if (p.persistent && p.prefetch) {
         os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
         declareFull("f", "    ");
         declareFull("n", "    ");
@@ -406,7 +558,9 @@ std::string emit(Program& p) {
     for (size_t o = 0; o < p.outputs.size(); ++o)
         if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0" << (p.persistent ? "" : " && row_ok") << ") out" << o << "[row] = v" << p.outputs[o].node << ";\n";
     if (p.persistent && p.row_reduces.size() > 0) os << I << "if (TEAM > 32) __syncthreads();  // shared-memory slots are reused by the next row\n";
-    if (p.persistent && p.prefetch) {
+    if (p.persistent && p.stage_smem) {
+        os << I << "buf ^= 1;\n";
+    } else if (p.persistent && p.prefetch) {
         os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n";
         for (size_t s = 0; s < p.inputs.size(); ++s)
             if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) os << I << "    f" << s << "[k] = n" << s << "[k];\n";
@@ -590,6 +744,7 @@ struct thor_b200_rowprog {
     std::shared_ptr<tb::jit::Module> module;
     size_t workspace_bytes = 1;
     bool compile_only = false;
+    bool smem_opted_in[64] = {};
 };
 
 extern "C" {
@@ -617,8 +772,14 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         TB_REQUIRE(dtypeSize(p.inputs[s].dtype) != 0 && p.inputs[s].dtype != THOR_B200_FP64, "rowprog_compile: input %zu has an unsupported dtype", s);
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR) TB_REQUIRE(p.input_shape[s] >= 0 && p.input_shape[s] <= 3, "rowprog_compile: input %zu has an unknown shape class", s);
     }
-    const std::string why = analyse(p);
+    std::string why = analyse(p);
     if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
+    if (getenv("THOR_B200_ROWPROG_HOIST") == nullptr || atoi(getenv("THOR_B200_ROWPROG_HOIST")) != 0) {
+        for (int pass = 0; pass < 4 && hoistLinearRowSums(p); ++pass) {
+            why = analyse(p);
+            if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
+        }
+    }
 
     // geometry: pack width from the narrowest FULL / COL tensor, team size from the row length
     size_t mn = 8, mx = 1;
@@ -684,6 +845,22 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     p.persistent = has_col_input || !p.col_reduces.empty();
     p.prefetch = p.persistent && envInt("THOR_B200_ROWPROG_PREFETCH", 1) != 0;
     p.min_ctas = envInt("THOR_B200_ROWPROG_MIN_CTAS", d->options.min_ctas_per_sm);
+    {
+        // Staging rows in shared memory (cp.async, thread-private slots) frees the registers of both row buffers.
+        bool packs16 = true;
+        size_t n_full = 0;
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
+                ++n_full;
+                packs16 = packs16 && dtypeSize(p.inputs[s].dtype) * p.vec == 16;
+            }
+        const size_t bytes = n_full * 2 * static_cast<size_t>(p.vpt) * p.cta * 16;
+        // measured on B200 (LayerNorm backward [32768, 8192] bf16): 435 us staged against 348 us with the register double buffer,
+        // so staging is opt-in
+        const bool wanted = envInt("THOR_B200_ROWPROG_STAGE", 0) != 0;
+        p.stage_smem = p.persistent && wanted && packs16 && n_full > 0 && bytes <= 200 * 1024;
+        p.smem_bytes = p.stage_smem ? bytes : 0;
+    }
     const uint64_t teams_per_cta = p.cta / p.team;
     const uint64_t ctas_for_rows = (p.rows + teams_per_cta - 1) / teams_per_cta;
     int sms = 148;
@@ -757,7 +934,15 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
     const void* ws_ptr = workspace;
     args[n++] = &ws_ptr;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, 0, stream));
+    if (p.smem_bytes > 48 * 1024) {
+        int dev = 0;
+        TB_CUDA(cudaGetDevice(&dev));
+        if (!h->smem_opted_in[dev & 63]) {
+            TB_CUDA(cudaKernelSetAttributeForDevice(h->module->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem_bytes), dev));
+            h->smem_opted_in[dev & 63] = true;
+        }
+    }
+    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, p.smem_bytes, stream));
     countLaunch();
     if (!p.all_reduces.empty()) {
         size_t idx = 0;
