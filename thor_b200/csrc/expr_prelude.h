@@ -164,6 +164,13 @@ __device__ __forceinline__ void tb_cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void tb_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// two-lane value of a type without a native pair type; tb_both broadcasts a float to both lanes of a float2
+template <class T>
+struct tb_pr {
+    T x, y;
+};
+__device__ __forceinline__ float2 tb_both(float v) { return make_float2(v, v); }
+__device__ __forceinline__ void tb_prefetch_l2(const void* gmem) { asm volatile("prefetch.global.L2 [%0];" ::"l"(gmem)); }
 template <int N>
 __device__ __forceinline__ void tb_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 

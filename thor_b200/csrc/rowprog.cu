@@ -50,7 +50,9 @@ struct Program {
     int vec = 4, team = 256, cta = 256, vpt = 1;
     bool persistent = false;
     bool prefetch = false;  // persistent programs: load row r + stride while row r is being computed
+    bool prefetch_l2 = false;  // persistent programs: only pull row r + stride into L2 (costs no registers)
     int min_ctas = 0;       // second __launch_bounds__ argument, 0 = none
+    bool pairs = false;     // element loops handle two neighbouring elements per step; fp32 + - * map onto the packed f32x2 instructions
     bool stage_smem = false;  // persistent programs: rows are staged in shared memory with cp.async (double buffer)
     size_t smem_bytes = 0;
     uint32_t grid = 0;
@@ -290,6 +292,106 @@ void emitStatements(const Program& p, const std::vector<uint32_t>& ids, const st
     for (uint32_t k : ids) os << indent << "const " << cTypeName(p.nodes[k].output_dtype) << " v" << k << " = " << scalarNodeExpression(p.nodes, p.inputs, k) << ";\n";
 }
 
+// ---- pair mode ---------------------------------------------------------------------------------
+// Element loops of a pair-mode program advance two elements per step.  Every element-level node k
+// is a two-lane value pK (float2, __half2, __nv_bfloat162 or tb_pr<T>); row-scope values keep their
+// scalar names vK.  fp32 additions, subtractions and multiplications become one packed f32x2
+// instruction per pair (a multiply feeding an add becomes a packed fma), 16-bit float conversions
+// use the two-lane conversion instructions, and every other op is evaluated lane by lane from the
+// scalar expression, so the value of each lane is the one the scalar body would compute up to the
+// placement of fused multiply-adds.
+std::string pairType(int d) {
+    if (d == THOR_B200_FP32) return "float2";
+    if (d == THOR_B200_FP16) return "__half2";
+    if (d == THOR_B200_BF16) return "__nv_bfloat162";
+    return std::string("tb_pr<") + cTypeName(d) + ">";
+}
+std::string makePair(int d, const std::string& x, const std::string& y) {
+    if (d == THOR_B200_FP32) return "make_float2(" + x + ", " + y + ")";
+    if (d == THOR_B200_FP16) return "__halves2half2(" + x + ", " + y + ")";
+    if (d == THOR_B200_BF16) return "__halves2bfloat162(" + x + ", " + y + ")";
+    return pairType(d) + "{" + x + ", " + y + "}";
+}
+// `e` must be a plain name: it may be evaluated once per lane.
+std::string convertPair(const std::string& e, int src, int dst) {
+    if (src == dst) return e;
+    if (dst == THOR_B200_FP32 && src == THOR_B200_BF16) return "__bfloat1622float2(" + e + ")";
+    if (dst == THOR_B200_FP32 && src == THOR_B200_FP16) return "__half22float2(" + e + ")";
+    if (src == THOR_B200_FP32 && dst == THOR_B200_BF16) return "__float22bfloat162_rn(" + e + ")";
+    if (src == THOR_B200_FP32 && dst == THOR_B200_FP16) return "__float22half2_rn(" + e + ")";
+    return makePair(dst, convertExpression(e + ".x", src, dst), convertExpression(e + ".y", src, dst));
+}
+bool elementLevel(const Program& p, uint32_t k) { return p.shape[k] == FULL || p.shape[k] == COL; }
+
+// float2 view of node `idx` for a packed fp32 instruction.
+std::string pairAsFloat2(const Program& p, uint32_t idx) {
+    const int d = p.nodes[idx].output_dtype;
+    if (elementLevel(p, idx)) return convertPair("p" + std::to_string(idx), d, THOR_B200_FP32);
+    return "tb_both(" + convertExpression("v" + std::to_string(idx), d, THOR_B200_FP32) + ")";
+}
+bool packedMul(const Program& p, uint32_t idx) {
+    if (idx == THOR_B200_NO_NODE || !elementLevel(p, idx)) return false;
+    const auto& m = p.nodes[idx];
+    return m.op == THOR_B200_OP_MUL && m.compute_dtype == THOR_B200_FP32 && m.output_dtype == THOR_B200_FP32;
+}
+// fp32 value of node `idx` plus `addend` (a float2 expression), with the multiply folded into an fma when `idx` is one.
+std::string pairPlus(const Program& p, uint32_t idx, const std::string& addend) {
+    if (packedMul(p, idx)) return "__ffma2_rn(" + pairAsFloat2(p, p.nodes[idx].lhs) + ", " + pairAsFloat2(p, p.nodes[idx].rhs) + ", " + addend + ")";
+    return "__fadd2_rn(" + pairAsFloat2(p, idx) + ", " + addend + ")";
+}
+
+void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
+    for (uint32_t k : ids) {
+        const auto& nd = p.nodes[k];
+        const int O = nd.output_dtype;
+        const std::string name = "p" + std::to_string(k);
+        std::string packed;  // float2 expression when the node has a packed form
+        if (nd.op == THOR_B200_OP_INPUT) {
+            os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("px" + std::to_string(nd.input_slot), p.inputs[nd.input_slot].dtype, O) << ";\n";
+            continue;
+        }
+        if (nd.op == THOR_B200_OP_CAST && elementLevel(p, nd.lhs)) {
+            os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("p" + std::to_string(nd.lhs), p.nodes[nd.lhs].output_dtype, O) << ";\n";
+            continue;
+        }
+        if (nd.compute_dtype == THOR_B200_FP32) {
+            if (nd.op == THOR_B200_OP_ADD) {
+                if (packedMul(p, nd.lhs)) packed = pairPlus(p, nd.lhs, pairAsFloat2(p, nd.rhs));
+                else packed = pairPlus(p, nd.rhs, pairAsFloat2(p, nd.lhs));
+            } else if (nd.op == THOR_B200_OP_SUB && !elementLevel(p, nd.rhs)) {
+                // the negated row value is loop invariant
+                packed = "__fadd2_rn(" + pairAsFloat2(p, nd.lhs) + ", tb_both(-" + convertExpression("v" + std::to_string(nd.rhs), p.nodes[nd.rhs].output_dtype, THOR_B200_FP32) + "))";
+            } else if (nd.op == THOR_B200_OP_SUB) {
+                packed = "__ffma2_rn(" + pairAsFloat2(p, nd.rhs) + ", tb_both(-1.0f), " + pairAsFloat2(p, nd.lhs) + ")";  // a - b, exact
+            } else if (nd.op == THOR_B200_OP_MUL) {
+                packed = "__fmul2_rn(" + pairAsFloat2(p, nd.lhs) + ", " + pairAsFloat2(p, nd.rhs) + ")";
+            }
+        }
+        if (!packed.empty()) {
+            if (O == THOR_B200_FP32) {
+                os << indent << "const float2 " << name << " = " << packed << ";\n";
+            } else {
+                os << indent << "const float2 t" << k << " = " << packed << ";\n";
+                os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("t" + std::to_string(k), THOR_B200_FP32, O) << ";\n";
+            }
+            continue;
+        }
+        // lane by lane from the scalar expression
+        const std::string expr = scalarNodeExpression(p.nodes, p.inputs, k);
+        os << indent << pairType(O) << " " << name << ";\n";
+        for (const char* lane : {".x", ".y"}) {
+            os << indent << "{ ";
+            std::vector<uint32_t> seen;
+            for (uint32_t par : {nd.lhs, nd.rhs, nd.aux}) {
+                if (par == THOR_B200_NO_NODE || !elementLevel(p, par) || std::find(seen.begin(), seen.end(), par) != seen.end()) continue;
+                seen.push_back(par);
+                os << "const " << cTypeName(p.nodes[par].output_dtype) << " v" << par << " = p" << par << lane << "; ";
+            }
+            os << name << lane << " = " << expr << "; }\n";
+        }
+    }
+}
+
 // FULL / COL-class ancestors of `targets` (inclusive) that an element loop has to evaluate.
 std::vector<uint32_t> elementClosure(const Program& p, const std::vector<uint32_t>& targets) {
     std::vector<bool> need(p.nodes.size(), false);
@@ -323,6 +425,12 @@ void emitElementInputs(const Program& p, const std::vector<uint32_t>& ids, const
         done[nd.input_slot] = true;
         const size_t s = nd.input_slot;
         const std::string T = elemTypeOfInput(p, s);
+        if (p.pairs) {
+            const std::string PT = pairType(p.inputs[s].dtype);
+            const std::string src = p.input_shape[s] == FULL ? (staged ? "g" + std::to_string(s) : "f" + std::to_string(s) + "[k]") : "c" + std::to_string(s) + "[k]";
+            os << indent << "const " << PT << " px" << s << " = reinterpret_cast<const " << PT << "*>(&" << src << ")[j >> 1];\n";
+            continue;
+        }
         if (p.input_shape[s] == FULL)
             os << indent << "const " << T << " x" << s << " = reinterpret_cast<const " << T << "*>(&" << (staged ? "g" + std::to_string(s) : "f" + std::to_string(s) + "[k]")
                << ")[j];\n";
@@ -402,8 +510,12 @@ std::string emit(Program& p) {
         }
     // column-reduction accumulators
     for (uint32_t k : p.col_reduces) {
-        os << "    float acc" << k << "[VPT][VEC];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC; ++j) acc" << k
-           << "[k][j] = 0.0f;\n";
+        if (p.pairs)
+            os << "    float2 acc" << k << "[VPT][VEC / 2];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC / 2; ++j) acc" << k
+               << "[k][j] = make_float2(0.0f, 0.0f);\n";
+        else
+            os << "    float acc" << k << "[VPT][VEC];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC; ++j) acc" << k
+               << "[k][j] = 0.0f;\n";
     }
     // row loop
     const std::string I = "        ";
@@ -453,6 +565,14 @@ std::string emit(Program& p) {
         os << "    for (tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id; row < ROWS; row += (tb_u64)gridDim.x * TEAMS) {\n";
         declareFull("f", I);
         loadFull("f", "row", guard, I);
+        if (p.prefetch_l2) {
+            os << I << "{\n" << I << "    const tb_u64 next = row + (tb_u64)gridDim.x * TEAMS;\n" << I << "    if (next < ROWS) {\n#pragma unroll\n" << I
+               << "        for (int k = 0; k < VPT; ++k) {\n" << I << "            const tb_u32 q = t + k * TEAM;\n" << I << "            if (q < PPR) {\n";
+            for (size_t s2 = 0; s2 < p.inputs.size(); ++s2)
+                if (p.inputs[s2].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s2] == FULL)
+                    os << I << "                tb_prefetch_l2(in" << s2 << " + next * COLS + (tb_u64)q * VEC);\n";
+            os << I << "            }\n" << I << "        }\n" << I << "    }\n" << I << "}\n";
+        }
     } else {
         os << "    {\n        const tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id;\n        const bool row_ok = row < ROWS;\n";
         declareFull("f", I);
@@ -489,24 +609,52 @@ std::string emit(Program& p) {
         os << I << "// round " << d << ": " << round.size() << " row reduction(s)\n";
         auto isMinMax = [&](uint32_t k) { return p.nodes[k].op == THOR_B200_OP_REDUCE_MIN || p.nodes[k].op == THOR_B200_OP_REDUCE_MAX; };
         for (uint32_t k : round) {
-            os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
+            if (p.pairs) os << I << "float2 q" << k << " = tb_both(" << identityExpr(p.nodes[k].op) << ");  // one partial per lane\n";
+            else os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
             if (isMinMax(k)) os << I << "bool nan" << k << " = false;  // min / max: fminf / fmaxf plus a sticky NaN predicate per element\n";
         }
         os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard << ") {\n";
         emitColumnPackLoads(p, closure, I + "        ", os);
-        os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; ++j) {\n";
+        os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; " << (p.pairs ? "j += 2" : "++j") << ") {\n";
         emitElementInputs(p, closure, I + "            ", os);
-        emitStatements(p, closure, I + "            ", os);
-        for (uint32_t k : round) {
-            const uint32_t a = p.nodes[k].lhs;
-            const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
-            if (isMinMax(k))
-                os << I << "            { const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
-                   << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
-            else
-                os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+        if (p.pairs) {
+            emitPairStatements(p, closure, I + "            ", os);
+            for (uint32_t k : round) {
+                const uint32_t a = p.nodes[k].lhs;
+                const uint16_t op = p.nodes[k].op;
+                const std::string acc = "q" + std::to_string(k);
+                if (op == THOR_B200_OP_REDUCE_SUM || op == THOR_B200_OP_REDUCE_AVG) {
+                    os << I << "            " << acc << " = " << pairPlus(p, a, acc) << ";\n";
+                } else if (op == THOR_B200_OP_REDUCE_NORM2) {
+                    os << I << "            { const float2 a" << k << " = " << pairAsFloat2(p, a) << "; " << acc << " = __ffma2_rn(a" << k << ", a" << k << ", " << acc << "); }\n";
+                } else if (isMinMax(k)) {
+                    const char* fn = op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf";
+                    os << I << "            { const float2 a" << k << " = " << pairAsFloat2(p, a) << "; nan" << k << " = nan" << k << " || (a" << k << ".x != a" << k << ".x) || (a" << k
+                       << ".y != a" << k << ".y); " << acc << ".x = " << fn << "(" << acc << ".x, a" << k << ".x); " << acc << ".y = " << fn << "(" << acc << ".y, a" << k << ".y); }\n";
+                } else {
+                    os << I << "            { const float2 a" << k << " = " << pairAsFloat2(p, a) << "; " << acc << ".x = " << combineExpr(op) << "(" << acc << ".x, "
+                       << transformExpr(op, "a" + std::to_string(k) + ".x") << "); " << acc << ".y = " << combineExpr(op) << "(" << acc << ".y, "
+                       << transformExpr(op, "a" + std::to_string(k) + ".y") << "); }\n";
+                }
+            }
+        } else {
+            emitStatements(p, closure, I + "            ", os);
+            for (uint32_t k : round) {
+                const uint32_t a = p.nodes[k].lhs;
+                const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
+                if (isMinMax(k))
+                    os << I << "            { const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
+                       << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
+                else
+                    os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
+            }
         }
         os << I << "        }\n" << I << "    }\n" << I << "}\n";
+        if (p.pairs)
+            for (uint32_t k : round) {
+                const bool mm = isMinMax(k);
+                os << I << "float r" << k << " = " << (mm ? (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") : combineExpr(p.nodes[k].op)) << "(q" << k << ".x, q" << k << ".y);\n";
+            }
         // team combine: all reductions of the round share one shared-memory exchange
         size_t slot = 0;
         for (uint32_t k : round) {
@@ -539,15 +687,23 @@ std::string emit(Program& p) {
         emitColumnPackLoads(p, closure, I + "        ", os);
         for (size_t o = 0; o < p.outputs.size(); ++o)
             if (p.shape[p.outputs[o].node] == FULL) os << I << "        tb_pack<VEC * " << dtypeSize(p.outputs[o].dtype) << "> w" << o << ";\n";
-        os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; ++j) {\n";
+        os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; " << (p.pairs ? "j += 2" : "++j") << ") {\n";
         emitElementInputs(p, closure, I + "            ", os);
-        emitStatements(p, closure, I + "            ", os);
-        for (size_t o = 0; o < p.outputs.size(); ++o)
-            if (p.shape[p.outputs[o].node] == FULL)
-                os << I << "            reinterpret_cast<" << cTypeName(p.outputs[o].dtype) << "*>(&w" << o << ")[j] = v" << p.outputs[o].node << ";\n";
-        for (uint32_t k : p.col_reduces) {
-            const uint32_t a = p.nodes[k].lhs;
-            os << I << "            acc" << k << "[k][j] += " << convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32) << ";\n";
+        if (p.pairs) {
+            emitPairStatements(p, closure, I + "            ", os);
+            for (size_t o = 0; o < p.outputs.size(); ++o)
+                if (p.shape[p.outputs[o].node] == FULL)
+                    os << I << "            reinterpret_cast<" << pairType(p.outputs[o].dtype) << "*>(&w" << o << ")[j >> 1] = p" << p.outputs[o].node << ";\n";
+            for (uint32_t k : p.col_reduces) os << I << "            acc" << k << "[k][j >> 1] = " << pairPlus(p, p.nodes[k].lhs, "acc" + std::to_string(k) + "[k][j >> 1]") << ";\n";
+        } else {
+            emitStatements(p, closure, I + "            ", os);
+            for (size_t o = 0; o < p.outputs.size(); ++o)
+                if (p.shape[p.outputs[o].node] == FULL)
+                    os << I << "            reinterpret_cast<" << cTypeName(p.outputs[o].dtype) << "*>(&w" << o << ")[j] = v" << p.outputs[o].node << ";\n";
+            for (uint32_t k : p.col_reduces) {
+                const uint32_t a = p.nodes[k].lhs;
+                os << I << "            acc" << k << "[k][j] += " << convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32) << ";\n";
+            }
         }
         os << I << "        }\n";
         for (size_t o = 0; o < p.outputs.size(); ++o)
@@ -572,8 +728,12 @@ std::string emit(Program& p) {
     for (uint32_t k : p.col_reduces) {
         os << "    {\n        float* part = ws + ((tb_u64)" << ci << " * gridDim.x * TEAMS + (tb_u64)blockIdx.x * TEAMS + team_id) * COLS;\n";
         os << "#pragma unroll\n        for (int k = 0; k < VPT; ++k) {\n            const tb_u32 q = t + k * TEAM;\n            if (q < PPR) {\n";
-        os << "#pragma unroll\n                for (int j = 0; j < VEC; j += 4) *reinterpret_cast<float4*>(part + (tb_u64)q * VEC + j) = make_float4(acc" << k << "[k][j], acc" << k
-           << "[k][j + 1], acc" << k << "[k][j + 2], acc" << k << "[k][j + 3]);\n";
+        if (p.pairs)
+            os << "#pragma unroll\n                for (int j = 0; j < VEC; j += 4) *reinterpret_cast<float4*>(part + (tb_u64)q * VEC + j) = make_float4(acc" << k << "[k][j >> 1].x, acc"
+               << k << "[k][j >> 1].y, acc" << k << "[k][(j >> 1) + 1].x, acc" << k << "[k][(j >> 1) + 1].y);\n";
+        else
+            os << "#pragma unroll\n                for (int j = 0; j < VEC; j += 4) *reinterpret_cast<float4*>(part + (tb_u64)q * VEC + j) = make_float4(acc" << k << "[k][j], acc" << k
+               << "[k][j + 1], acc" << k << "[k][j + 2], acc" << k << "[k][j + 3]);\n";
         os << "            }\n        }\n    }\n";
         ++ci;
     }
@@ -843,8 +1003,11 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     bool has_col_input = false;
     for (size_t s = 0; s < p.inputs.size(); ++s) has_col_input = has_col_input || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL);
     p.persistent = has_col_input || !p.col_reduces.empty();
-    p.prefetch = p.persistent && envInt("THOR_B200_ROWPROG_PREFETCH", 1) != 0;
+    const int prefetch_mode = envInt("THOR_B200_ROWPROG_PREFETCH", 1);  // 0 none, 1 registers, 2 L2 only
+    p.prefetch = p.persistent && prefetch_mode == 1;
+    p.prefetch_l2 = p.persistent && prefetch_mode == 2;
     p.min_ctas = envInt("THOR_B200_ROWPROG_MIN_CTAS", d->options.min_ctas_per_sm);
+    p.pairs = envInt("THOR_B200_ROWPROG_PAIRS", 1) != 0;
     {
         // Staging rows in shared memory (cp.async, thread-private slots) frees the registers of both row buffers.
         bool packs16 = true;

@@ -291,9 +291,10 @@ def _bind_tensor(name: str, t: torch.Tensor, dtype: Optional[DataType] = None) -
 class StampedExecutionPlan:
     """A stamped plan: run() launches every stage; nothing is allocated or compiled at run time."""
 
-    def __init__(self, handle, keep):
+    def __init__(self, handle, keep, plan_only: bool = False):
         self._h = handle
         self._keep = keep  # torch tensors whose memory the plan points at
+        self._plan_only = plan_only
 
     def __del__(self):
         try:
@@ -316,6 +317,12 @@ class StampedExecutionPlan:
     def physical_stage_names(self): return self._strings(1)
     def stage_sources(self): return self._strings(2)
     def output_names(self): return self._strings(3)
+    def output_spec(self, name: str = "output"):
+        """(shape, DataType) of the named output."""
+        b = _Binding()
+        _check(_host.thb_plan_output(self._h, name.encode(), C.byref(b)))
+        return [int(b.dims[i]) for i in range(b.rank)], DataType(b.dtype)
+
     def intermediate_bytes(self) -> int: return int(_host.thb_plan_intermediate_bytes(self._h))
     def kernel_launches_per_run(self) -> int: return int(_host.thb_plan_launches(self._h))
 
@@ -323,6 +330,8 @@ class StampedExecutionPlan:
         """The named output as a torch tensor aliasing the plan's memory (valid while the plan lives)."""
         b = _Binding()
         _check(_host.thb_plan_output(self._h, name.encode(), C.byref(b)))
+        if self._plan_only:
+            raise _native.ThorB200Error("plan-only plans own no memory")
         for t in self._keep:
             if t.data_ptr() == b.ptr:
                 return t
@@ -396,6 +405,32 @@ class FusedEquation:
         with torch.cuda.device(self.device_num):
             _check(_host.thb_stamp(self._h, in_arr, len(ins), out_arr, len(outs), _native.stream_handle(stream), C.byref(plan)))
         return StampedExecutionPlan(plan, keep)
+
+    def plan(self, inputs: Mapping[str, Union[tuple, float]]) -> StampedExecutionPlan:
+        """Stamps without a GPU: `inputs` maps each tensor name to (shape, DataType) and each runtime
+        scalar to a float.  The returned plan lists its stages, kernel shapes, emitted sources and
+        intermediate bytes exactly as a real stamp on those shapes would; run() and output() refuse."""
+        ins = []
+        for name, v in inputs.items():
+            b = _Binding()
+            b.name = name.encode()
+            if isinstance(v, (int, float)):
+                b.is_scalar = 1
+                b.scalar = float(v)
+            else:
+                shape, dtype = v
+                if len(shape) > 8:
+                    raise _native.ThorB200InvalidArgument(f"'{name}': rank above 8")
+                b.dtype = int(dtype)
+                b.rank = len(shape)
+                for i, d in enumerate(shape):
+                    b.dims[i] = int(d)
+                b.is_scalar = 0
+            ins.append(b)
+        in_arr = (_Binding * max(1, len(ins)))(*ins)
+        plan = C.c_void_p()
+        _check(_host.thb_stamp_plan_only(self._h, in_arr, len(ins), C.byref(plan)))
+        return StampedExecutionPlan(plan, [], plan_only=True)
 
     def run(self, inputs: Mapping[str, Union[torch.Tensor, float]], output: Union[torch.Tensor, Mapping[str, torch.Tensor]],
             stream: Optional[torch.cuda.Stream] = None) -> None:

@@ -164,12 +164,14 @@ struct StampedExecutionPlan::Impl {
     std::map<std::string, Tensor> outputs;
     std::vector<Tensor> keep_alive;
     uint64_t intermediate_bytes = 0;
+    bool plan_only = false;  // stamped with placeholder memory: describes the plan, cannot run
 };
 
 void StampedExecutionPlan::run() { runOn(impl_->stream); }
 
 void StampedExecutionPlan::runOn(const Stream& stream) {
     if (!impl_) throw std::logic_error("StampedExecutionPlan is empty");
+    if (impl_->plan_only) throw std::logic_error("StampedExecutionPlan was stamped in plan-only mode and cannot run");
     for (PhysicalStage& s : impl_->stages) {
         switch (s.kind) {
             case StageKind::FusedKernel:
@@ -352,6 +354,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
     Planner plan(g, phys.outputs, shape);
     auto impl = std::make_shared<StampedExecutionPlan::Impl>();
     impl->stream = stream;
+    impl->plan_only = Tensor::planOnly();
 
     // tensor that holds each materialised node (inputs, boundary outputs, materialised elementwise nodes)
     std::vector<Tensor> node_tensor(g.nodes.size());
@@ -667,6 +670,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
         }
         thor_b200_expr_options opt{};
         opt.use_fast_math = options_.use_fast_math;
+        opt.compile_only = Tensor::planOnly() ? 1 : 0;
         PhysicalStage st;
         st.kind = StageKind::FusedKernel;
         st.expr = std::make_shared<ExprHandle>();

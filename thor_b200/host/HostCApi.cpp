@@ -225,6 +225,23 @@ THB_API int thb_stamp(FusedEquation* eq, const thb_binding* inputs, uint32_t n_i
         *out = p;
     });
 }
+// Same as thb_stamp, but nothing touches a GPU: bindings carry shapes and dtypes only (their ptr is
+// ignored), outputs and intermediates get placeholder addresses and kernels are compiled, not loaded.
+THB_API int thb_stamp_plan_only(FusedEquation* eq, const thb_binding* inputs, uint32_t n_inputs, Plan** out) {
+    std::vector<thb_binding> in(inputs, inputs + n_inputs);
+    uint64_t placeholder = 0x200000000000ull;
+    for (auto& b : in) {
+        if (b.is_scalar) continue;
+        uint64_t bytes = dataTypeSize(static_cast<DataType>(b.dtype));
+        for (uint32_t i = 0; i < b.rank; ++i) bytes *= b.dims[i];
+        b.ptr = reinterpret_cast<void*>(placeholder);
+        placeholder += (bytes + 511) / 256 * 256;
+    }
+    Tensor::setPlanOnly(true);
+    const int status = thb_stamp(eq, in.data(), n_inputs, nullptr, 0, nullptr, out);
+    Tensor::setPlanOnly(false);
+    return status;
+}
 THB_API void thb_plan_free(Plan* p) { delete p; }
 THB_API int thb_plan_run(Plan* p, void* stream) {
     return guarded([&] {

@@ -170,6 +170,7 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
     d.rows = rows;
     d.cols = cols;
     d.options.use_fast_math = ctx.use_fast_math;
+    d.options.compile_only = Tensor::planOnly() ? 1 : 0;
     auto prog = std::make_shared<ProgHandle>();
     size_t ws_bytes = 1;
     const int status = thor_b200_rowprog_compile(&d, &prog->h, &ws_bytes);

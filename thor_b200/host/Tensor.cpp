@@ -16,11 +16,24 @@ Tensor Tensor::wrap(void* device_ptr, DataType dtype, std::vector<uint64_t> dims
     return t;
 }
 
+namespace {
+thread_local bool g_plan_only = false;
+thread_local uint64_t g_placeholder = 0x100000000000ull;  // never dereferenced
+}  // namespace
+
+void Tensor::setPlanOnly(bool on) { g_plan_only = on; }
+bool Tensor::planOnly() { return g_plan_only; }
+
 Tensor Tensor::allocate(DataType dtype, std::vector<uint64_t> dims, int gpu_num) {
     Tensor t;
     t.dtype_ = dtype;
     t.dims_ = std::move(dims);
     t.gpu_num_ = gpu_num;
+    if (g_plan_only) {
+        t.ptr_ = reinterpret_cast<void*>(g_placeholder);
+        g_placeholder += (t.getArraySizeInBytes() + 511) / 256 * 256;
+        return t;
+    }
     void* p = nullptr;
     // the caller has made gpu_num current (the reference wraps allocation in ScopedGpu)
     if (thor_b200_device_alloc(t.getArraySizeInBytes(), &p) != THOR_B200_OK)

@@ -28,6 +28,13 @@ class Tensor {
     // Allocates dense device memory on gpu_num (used at stamp time for intermediates and outputs).
     static Tensor allocate(DataType dtype, std::vector<uint64_t> dims, int gpu_num = 0);
 
+    // Plan-only mode (thread local): allocate() hands out distinct placeholder addresses instead of
+    // device memory and every kernel is compiled without being loaded, so that a plan (stages,
+    // kernel shapes, emitted sources, intermediate bytes) can be produced on a machine without a
+    // GPU.  A plan stamped in this mode refuses to run.
+    static void setPlanOnly(bool on);
+    static bool planOnly();
+
     bool isInitialized() const { return ptr_ != nullptr; }
     void* getMemPtr() const { return ptr_; }
     DataType getDataType() const { return dtype_; }
