@@ -116,6 +116,8 @@ __device__ __forceinline__ Cand teamBest(Cand c, float* sv, unsigned long long* 
 
 template <class T, bool IS_MAX, int TEAM, bool IDX32>
 __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     constexpr int VEC = 16 / sizeof(T);
     constexpr int U = 4;
     constexpr int kTeamsPerCta = kThreads / TEAM;
@@ -187,6 +189,8 @@ __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
 
 template <bool IS_MAX>
 __global__ void __launch_bounds__(kThreads) argRowsFoldKernel(ArgArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     __shared__ float sv[32];
     __shared__ unsigned long long si[32];
     const uint64_t row = blockIdx.x;
@@ -202,6 +206,8 @@ __global__ void __launch_bounds__(kThreads) argRowsFoldKernel(ArgArgs a) {
 // grid = (inner tiles, outer); block = TX x TY; thread (tx, ty) owns pack tx and rows ty, ty+TY, ...
 template <class T, bool IS_MAX, int VEC, int TX>
 __global__ void __launch_bounds__(kThreads) argColsKernel(ArgArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     constexpr int TY = kThreads / TX;
     constexpr int U = 4;
     __shared__ float sv[TY][TX * VEC + 1];
@@ -271,8 +277,8 @@ int launchArg(const thor_b200_argreduce_plan& p, const ArgArgs& a, cudaStream_t 
         if (blocks > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "argreduce: grid too large");
         const bool idx32 = a.reduction < 0xffffffffull;
 #define TB_ARG_ROWS(TEAMV)                                                                                              \
-    if (idx32) argRowsKernel<T, IS_MAX, TEAMV, true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a);        \
-    else argRowsKernel<T, IS_MAX, TEAMV, false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a);
+    if (idx32) (void)launchDependent(argRowsKernel<T, IS_MAX, TEAMV, true>, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, stream, a);        \
+    else (void)launchDependent(argRowsKernel<T, IS_MAX, TEAMV, false>, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, stream, a);
         switch (p.team) {
             case 8: TB_ARG_ROWS(8) break;
             case 32: TB_ARG_ROWS(32) break;
@@ -282,7 +288,7 @@ int launchArg(const thor_b200_argreduce_plan& p, const ArgArgs& a, cudaStream_t 
         countLaunch();
         TB_CUDA(cudaGetLastError());
         if (a.splits > 1) {
-            argRowsFoldKernel<IS_MAX><<<static_cast<unsigned>(a.outer), kThreads, 0, stream>>>(a);
+            (void)launchDependent(argRowsFoldKernel<IS_MAX>, dim3(static_cast<unsigned>(a.outer)), dim3(kThreads), 0, stream, a);
             countLaunch();
             TB_CUDA(cudaGetLastError());
         }
@@ -295,15 +301,15 @@ int launchArg(const thor_b200_argreduce_plan& p, const ArgArgs& a, cudaStream_t 
     if (a.reduction > 0xfffffffeull) return fail(THOR_B200_UNSUPPORTED, "argreduce: reduction axis of the tiled path is limited to 2^32 - 2 elements");
     dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(a.outer));
     if (p.cols_vec == 1) {
-        argColsKernel<T, IS_MAX, 1, 32><<<grid, kThreads, 0, stream>>>(a);
+        (void)launchDependent(argColsKernel<T, IS_MAX, 1, 32>, dim3(grid), dim3(kThreads), 0, stream, a);
     } else {
         switch (p.cols_tx) {
-            case 1: argColsKernel<T, IS_MAX, VEC, 1><<<grid, kThreads, 0, stream>>>(a); break;
-            case 2: argColsKernel<T, IS_MAX, VEC, 2><<<grid, kThreads, 0, stream>>>(a); break;
-            case 4: argColsKernel<T, IS_MAX, VEC, 4><<<grid, kThreads, 0, stream>>>(a); break;
-            case 8: argColsKernel<T, IS_MAX, VEC, 8><<<grid, kThreads, 0, stream>>>(a); break;
-            case 16: argColsKernel<T, IS_MAX, VEC, 16><<<grid, kThreads, 0, stream>>>(a); break;
-            default: argColsKernel<T, IS_MAX, VEC, 32><<<grid, kThreads, 0, stream>>>(a); break;
+            case 1: (void)launchDependent(argColsKernel<T, IS_MAX, VEC, 1>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 2: (void)launchDependent(argColsKernel<T, IS_MAX, VEC, 2>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 4: (void)launchDependent(argColsKernel<T, IS_MAX, VEC, 4>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 8: (void)launchDependent(argColsKernel<T, IS_MAX, VEC, 8>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 16: (void)launchDependent(argColsKernel<T, IS_MAX, VEC, 16>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            default: (void)launchDependent(argColsKernel<T, IS_MAX, VEC, 32>, dim3(grid), dim3(kThreads), 0, stream, a); break;
         }
     }
     countLaunch();

@@ -1,6 +1,8 @@
 // Status plumbing of the C ABI: thread-local error text, launch counter, per-device properties.
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <mutex>
 
 namespace tb {
@@ -24,6 +26,14 @@ void clearError() { lastErrorSlot().clear(); }
 
 static std::atomic<uint64_t> g_launches{0};
 void countLaunch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+bool dependentLaunchEnabled() {
+    static const bool on = [] {
+        const char* v = getenv("THOR_B200_DEPENDENT_LAUNCH");
+        return !(v && *v && atoi(v) == 0);
+    }();
+    return on;
+}
 
 int currentDeviceInfo(const DeviceInfo** out) {
     static DeviceInfo table[64];

@@ -56,6 +56,8 @@ struct CastGeom {
 
 template <class F, class T, int P, int U, bool WIDE>
 __global__ void __launch_bounds__(256) castPackedKernel(const F* __restrict__ src, T* __restrict__ dst, int64_t n_packs, int64_t n) {
+    gridDependencyWait();
+    gridLaunchDependents();
     // One CTA owns a contiguous run of 256 * U packs; thread t takes packs t, t + 256, ...
     const int64_t base = static_cast<int64_t>(blockIdx.x) * (256 * U) + threadIdx.x;
     Pack<P * sizeof(F)> in[U];
@@ -86,6 +88,8 @@ __global__ void __launch_bounds__(256) castPackedKernel(const F* __restrict__ sr
 // Fallback for pointers that are not aligned to the pack width (foreign sub-views).
 template <class F, class T>
 __global__ void __launch_bounds__(256) castScalarKernel(const F* __restrict__ src, T* __restrict__ dst, int64_t n) {
+    gridDependencyWait();
+    gridLaunchDependents();
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = Cvt<F, T>::run(src[i]);
 }
@@ -94,6 +98,8 @@ __global__ void __launch_bounds__(256) castScalarKernel(const F* __restrict__ sr
 // writes it, so the packed kernel is safe; this variant only drops __restrict__.
 template <class F, class T, int P>
 __global__ void __launch_bounds__(256) castInPlaceSameSizeKernel(void* buf, int64_t n_packs, int64_t n) {
+    gridDependencyWait();
+    gridLaunchDependents();
     static_assert(sizeof(F) == sizeof(T), "same-size in-place only");
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < n_packs; p += stride) {
@@ -130,7 +136,7 @@ int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream) {
             const int64_t n_packs = n / P;
             int64_t blocks = (n_packs + 255) / 256;
             blocks = blocks < 1 ? 1 : (blocks > resident ? resident : blocks);
-            castInPlaceSameSizeKernel<F, T, P><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dst_v, n_packs, n);
+            (void)launchDependent(castInPlaceSameSizeKernel<F, T, P>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, dst_v, n_packs, n);
             countLaunch();
             TB_CUDA(cudaGetLastError());
             return THOR_B200_OK;
@@ -147,13 +153,13 @@ int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream) {
         blocks = blocks < 1 ? 1 : blocks;
         if (blocks > 0x7FFFFFFF) return fail(THOR_B200_UNSUPPORTED, "cast: %lld elements exceed the launch grid", static_cast<long long>(n));
         if ((P * sizeof(F)) % 32 == 0 && isAligned(src_v, 32))
-            castPackedKernel<F, T, P, U, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, n_packs, n);
+            TB_CUDA(launchDependent(castPackedKernel<F, T, P, U, true>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, src, dst, n_packs, n));
         else
-            castPackedKernel<F, T, P, U, false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, n_packs, n);
+            TB_CUDA(launchDependent(castPackedKernel<F, T, P, U, false>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, src, dst, n_packs, n));
     } else {
         int64_t blocks = (n + 255) / 256;
         blocks = blocks < 1 ? 1 : (blocks > resident ? resident : blocks);
-        castScalarKernel<F, T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, n);
+        (void)launchDependent(castScalarKernel<F, T>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, src, dst, n);
     }
     countLaunch();
     TB_CUDA(cudaGetLastError());

@@ -40,6 +40,49 @@ void countLaunch(uint64_t n = 1);
                               cudaGetErrorString(_e), __FILE__, __LINE__);                     \
     } while (0)
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Every streaming kernel of the library is launched with stream serialization relaxed: its CTAs may
+// be placed on SMs while the tail of the previous kernel of the stream is still draining, which hides
+// most of the launch latency between back-to-back kernels.  The kernel's first statement is
+// gridDependencyWait(): it returns only once the previous kernel has completed and its writes are
+// visible, so stream-order semantics are unchanged (a predecessor that never signals counts as
+// signalling when it exits).  gridLaunchDependents() right after lets the next kernel do the same.
+#ifdef __CUDACC__
+__device__ __forceinline__ void gridDependencyWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gridLaunchDependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+bool dependentLaunchEnabled();  // THOR_B200_DEPENDENT_LAUNCH=0 turns the launch attribute off
+
+template <class... KArgs, class... Args>
+cudaError_t launchDependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependentLaunchEnabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Same for a kernel handle with an argument-pointer array (generated kernels).
+inline cudaError_t launchDependentC(const void* kernel, dim3 grid, dim3 block, void** args, size_t smem, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependentLaunchEnabled() ? 1 : 0;
+    return cudaLaunchKernelExC(&cfg, kernel, args);
+}
+
 // Device properties that launch geometry needs, cached per device.
 struct DeviceInfo {
     int sm_count = 0;

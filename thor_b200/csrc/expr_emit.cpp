@@ -453,6 +453,7 @@ void emitFlat(const Plan& p, Emitted* out, std::ostringstream& os) {
     out->unroll = U;
     out->threads = 256;
     os << "extern \"C\" __global__ void " << launchBounds(st) << " fused_kernel(" << kernelParams(st, true) << ") {\n";
+    os << "    tb_grid_wait();\n";
     os << "    constexpr int VEC = " << VEC << ", U = " << U << ";\n";
     os << "    const tb_u64 n_packs = numel / VEC;\n";
     os << "    const tb_u64 base = (tb_u64)blockIdx.x * (256 * U) + threadIdx.x;\n";
@@ -610,6 +611,7 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
 
     os << "// rows = " << rows << ", cols = " << cols << ", packs per row = " << ppr << ", CTA = " << tx << " x " << ty << " threads, " << U << " rows per thread\n";
     os << "extern \"C\" __global__ void " << launchBounds(st) << " fused_kernel(" << kernelParams(st, false) << ") {\n";
+    os << "    tb_grid_wait();\n";
     os << "    constexpr int VEC = " << VEC << ", U = " << U << ", TX = " << tx << ", TY = " << ty << ";\n";
     os << "    constexpr tb_u64 ROWS = " << rows << "ull, COLS = " << cols << "ull, PPR = " << ppr << "ull;\n";
     os << "    const tb_u32 tx = threadIdx.x % TX, ty = threadIdx.x / TX;\n";
@@ -683,6 +685,7 @@ void emitGeneric(const Plan& p, Emitted* out, std::ostringstream& os) {
         out->numel = numel;
     }
     os << "extern \"C\" __global__ void " << launchBounds(st) << " fused_kernel(" << kernelParams(st, !st.broadcast) << ") {\n";
+    os << "    tb_grid_wait();\n";
     if (st.broadcast) os << "    constexpr tb_u64 numel = " << numel << "ull;\n";
     os << "    const tb_u64 i = (tb_u64)blockIdx.x * 256 + threadIdx.x;\n    if (i >= numel) return;\n";
     emitScalarLoads(st, os);

@@ -258,7 +258,7 @@ int launchVariant(const thor_b200_expr& e, const Variant& v, const void* const* 
             grid.x = static_cast<unsigned>(blocks == 0 ? 1 : blocks);
         } break;
     }
-    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(m.kernel), grid, block, args, 0, stream));
+    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(m.kernel), grid, block, args, 0, stream));
     countLaunch();
     return THOR_B200_OK;
 }

@@ -13,6 +13,13 @@ static const char* const kPrelude = R"TBPRELUDE(
 typedef unsigned long long tb_u64;
 typedef unsigned int tb_u32;
 
+// First statements of every generated kernel: wait until the previous kernel of the stream has completed
+// and its writes are visible (the kernel is launched with stream serialization relaxed, so its CTAs may
+// already sit on the SMs while that kernel drains), then let the next kernel be placed the same way.
+__device__ __forceinline__ void tb_grid_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 template <int BYTES>
 struct __align__(BYTES >= 16 ? 16 : BYTES) tb_pack {
     unsigned char b[BYTES];

@@ -111,6 +111,8 @@ struct RowsArgs {
 // One team per (row, split).  blockIdx.x = row_group * splits + split.
 template <class T, int OP, int TEAM>
 __global__ void __launch_bounds__(kThreads) rowsKernel(RowsArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     using Tr = OpTraits<OP>;
     constexpr int VEC = 16 / sizeof(T);
     constexpr int U = 4;
@@ -166,6 +168,8 @@ __global__ void __launch_bounds__(kThreads) rowsKernel(RowsArgs a) {
 // Folds the per-split partials of each row: one CTA per row, thread t takes partials t, t+256, ...
 template <int OP>
 __global__ void __launch_bounds__(kThreads) rowsFoldKernel(RowsArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     using Tr = OpTraits<OP>;
     __shared__ float smem[32];
     const uint64_t row = blockIdx.x;
@@ -190,6 +194,8 @@ struct ColsArgs {
 // tile and rows ty, ty + TY, ... of the split.
 template <class T, int OP, int VEC, int TX>
 __global__ void __launch_bounds__(kThreads) colsKernel(ColsArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     using Tr = OpTraits<OP>;
     constexpr int TY = kThreads / TX;
     constexpr int U = 4;
@@ -235,6 +241,8 @@ __global__ void __launch_bounds__(kThreads) colsKernel(ColsArgs a) {
 
 template <int OP>
 __global__ void __launch_bounds__(kThreads) colsFoldKernel(ColsArgs a) {
+    gridDependencyWait();
+    gridLaunchDependents();
     using Tr = OpTraits<OP>;
     const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
     if (idx >= a.outer * a.inner) return;
@@ -273,14 +281,14 @@ int launchRowsT(const thor_b200_reduce_plan& p, const RowsArgs& a, cudaStream_t 
     const uint64_t blocks = groups * a.splits;
     if (blocks > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "reduce: grid too large");
     switch (p.team) {
-        case 8: rowsKernel<T, OP, 8><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a); break;
-        case 32: rowsKernel<T, OP, 32><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a); break;
-        default: rowsKernel<T, OP, 256><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a); break;
+        case 8: (void)launchDependent(rowsKernel<T, OP, 8>, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, stream, a); break;
+        case 32: (void)launchDependent(rowsKernel<T, OP, 32>, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, stream, a); break;
+        default: (void)launchDependent(rowsKernel<T, OP, 256>, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, stream, a); break;
     }
     countLaunch();
     TB_CUDA(cudaGetLastError());
     if (a.splits > 1) {
-        rowsFoldKernel<OP><<<static_cast<unsigned>(a.outer), kThreads, 0, stream>>>(a);
+        (void)launchDependent(rowsFoldKernel<OP>, dim3(static_cast<unsigned>(a.outer)), dim3(kThreads), 0, stream, a);
         countLaunch();
         TB_CUDA(cudaGetLastError());
     }
@@ -295,22 +303,22 @@ int launchColsT(const thor_b200_reduce_plan& p, const ColsArgs& a, cudaStream_t 
     if (tiles > 0x7FFFFFFFull || a.splits > 65535u || a.outer > 65535ull) return fail(THOR_B200_UNSUPPORTED, "reduce: grid too large");
     dim3 grid(static_cast<unsigned>(tiles), a.splits, static_cast<unsigned>(a.outer));
     if (p.cols_vec == 1) {
-        colsKernel<T, OP, 1, 32><<<grid, kThreads, 0, stream>>>(a);
+        (void)launchDependent(colsKernel<T, OP, 1, 32>, dim3(grid), dim3(kThreads), 0, stream, a);
     } else {
         switch (p.cols_tx) {
-            case 1: colsKernel<T, OP, VEC, 1><<<grid, kThreads, 0, stream>>>(a); break;
-            case 2: colsKernel<T, OP, VEC, 2><<<grid, kThreads, 0, stream>>>(a); break;
-            case 4: colsKernel<T, OP, VEC, 4><<<grid, kThreads, 0, stream>>>(a); break;
-            case 8: colsKernel<T, OP, VEC, 8><<<grid, kThreads, 0, stream>>>(a); break;
-            case 16: colsKernel<T, OP, VEC, 16><<<grid, kThreads, 0, stream>>>(a); break;
-            default: colsKernel<T, OP, VEC, 32><<<grid, kThreads, 0, stream>>>(a); break;
+            case 1: (void)launchDependent(colsKernel<T, OP, VEC, 1>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 2: (void)launchDependent(colsKernel<T, OP, VEC, 2>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 4: (void)launchDependent(colsKernel<T, OP, VEC, 4>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 8: (void)launchDependent(colsKernel<T, OP, VEC, 8>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            case 16: (void)launchDependent(colsKernel<T, OP, VEC, 16>, dim3(grid), dim3(kThreads), 0, stream, a); break;
+            default: (void)launchDependent(colsKernel<T, OP, VEC, 32>, dim3(grid), dim3(kThreads), 0, stream, a); break;
         }
     }
     countLaunch();
     TB_CUDA(cudaGetLastError());
     if (a.splits > 1) {
         const uint64_t n = a.outer * a.inner;
-        colsFoldKernel<OP><<<static_cast<unsigned>((n + kThreads - 1) / kThreads), kThreads, 0, stream>>>(a);
+        (void)launchDependent(colsFoldKernel<OP>, dim3(static_cast<unsigned>((n + kThreads - 1) / kThreads)), dim3(kThreads), 0, stream, a);
         countLaunch();
         TB_CUDA(cudaGetLastError());
     }

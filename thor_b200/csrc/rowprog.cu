@@ -490,11 +490,15 @@ std::string emit(Program& p) {
         first = false;
         os << cTypeName(p.outputs[o].dtype) << "* __restrict__ out" << o;
     }
-    os << (first ? "" : ", ") << "float* __restrict__ ws) {\n";
+    os << (first ? "" : ", ") << "float* __restrict__ ws) {\n    tb_grid_wait();\n";
     os << "    constexpr int VEC = " << VEC << ", TEAM = " << TEAM << ", VPT = " << VPT << ", TEAMS = " << teams_per_cta << ";\n";
     os << "    constexpr tb_u64 ROWS = " << p.rows << "ull, COLS = " << p.cols << "ull;\n";
     os << "    constexpr tb_u32 PPR = " << packs_per_row << "u;\n";
-    os << "    __shared__ float red_smem[" << std::max<size_t>(1, p.row_reduces.size()) << "][TEAMS][TEAM > 32 ? TEAM / 32 : 1];\n";
+    // persistent programs alternate between two sets of exchange slots from row to row, so that a row's
+    // slots are not rewritten before every thread has passed a barrier of the row in between
+    os << "    __shared__ float red_smem_all[" << (p.persistent ? 2 : 1) << "][" << std::max<size_t>(1, p.row_reduces.size()) << "][TEAMS][TEAM > 32 ? TEAM / 32 : 1];\n";
+    if (p.persistent) os << "    int red_set = 0;\n";
+    else os << "    float (*red_smem)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_smem_all[0];\n";
     os << "    const int t = threadIdx.x % TEAM, team_id = threadIdx.x / TEAM;\n";
     for (size_t s = 0; s < p.inputs.size(); ++s)
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == SCALAR))
@@ -531,7 +535,7 @@ std::string emit(Program& p) {
                 os << indent << "        tb_load_stream(" << prefix << s << "[k], in" << s << " + (" << row << ") * COLS + (tb_u64)q * VEC);\n";
         os << indent << "    }\n" << indent << "}\n";
     };
-    const std::string guard = p.persistent ? "q < PPR" : "row_ok && q < PPR";
+    const std::string guard = "row_ok && q < PPR";
     if (p.persistent && p.stage_smem) {
         os << "    extern __shared__ uint4 tb_stage[];  // [full input][2 buffers][VPT][CTA threads] 16-byte packs, slot private to its thread\n";
         os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
@@ -549,7 +553,8 @@ std::string emit(Program& p) {
         };
         os << "    int buf = 0;\n";
         issue("row_first", "0", "    ");
-        os << "    for (tb_u64 row = row_first; row < ROWS; row += row_stride) {\n";
+        os << "    for (tb_u64 row0 = (tb_u64)blockIdx.x * TEAMS; row0 < ROWS; row0 += row_stride) {  // same trip count for every team of the CTA\n";
+        os << I << "const tb_u64 row = row0 + team_id;\n" << I << "const bool row_ok = " << (teams_per_cta == 1 ? "true" : "row < ROWS") << ";\n";
         os << I << "// the copy of this team's next row runs while the current row is computed\n";
         issue("row + row_stride", "(buf ^ 1)", I);
         os << I << "tb_cp_async_wait<1>();\n";
@@ -558,11 +563,13 @@ std::string emit(Program& p) {
         declareFull("f", "    ");
         declareFull("n", "    ");
         loadFull("f", "row_first", "row_first < ROWS && q < PPR", "    ");
-        os << "    for (tb_u64 row = row_first; row < ROWS; row += row_stride) {\n";
+        os << "    for (tb_u64 row0 = (tb_u64)blockIdx.x * TEAMS; row0 < ROWS; row0 += row_stride) {  // same trip count for every team of the CTA\n";
+        os << I << "const tb_u64 row = row0 + team_id;\n" << I << "const bool row_ok = " << (teams_per_cta == 1 ? "true" : "row < ROWS") << ";\n";
         os << I << "// the next row of this team is requested before the current one is touched\n";
         loadFull("n", "row + row_stride", "row + row_stride < ROWS && q < PPR", I);
     } else if (p.persistent) {
-        os << "    for (tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id; row < ROWS; row += (tb_u64)gridDim.x * TEAMS) {\n";
+        os << "    for (tb_u64 row0 = (tb_u64)blockIdx.x * TEAMS; row0 < ROWS; row0 += (tb_u64)gridDim.x * TEAMS) {  // same trip count for every team of the CTA\n";
+        os << I << "const tb_u64 row = row0 + team_id;\n" << I << "const bool row_ok = " << (teams_per_cta == 1 ? "true" : "row < ROWS") << ";\n";
         declareFull("f", I);
         loadFull("f", "row", guard, I);
         if (p.prefetch_l2) {
@@ -578,11 +585,11 @@ std::string emit(Program& p) {
         declareFull("f", I);
         loadFull("f", "row", guard, I);
     }
+    if (p.persistent) os << I << "float (*red_smem)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_smem_all[red_set];\n";
     // ROW inputs
     for (size_t s = 0; s < p.inputs.size(); ++s)
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == ROW)
-            os << I << "const " << cTypeName(p.inputs[s].dtype) << " x" << s << " = " << (p.persistent ? "" : "row_ok ? ") << "in" << s << "[row]"
-               << (p.persistent ? "" : std::string(" : ") + cTypeName(p.inputs[s].dtype) + "()") << ";\n";
+            os << I << "const " << cTypeName(p.inputs[s].dtype) << " x" << s << " = row_ok ? in" << s << "[row] : " << cTypeName(p.inputs[s].dtype) << "();\n";
 
     // row-scope nodes are emitted as soon as their depth is reached
     std::vector<bool> emitted(p.nodes.size(), false);
@@ -712,8 +719,8 @@ std::string emit(Program& p) {
     }
     // ROW outputs
     for (size_t o = 0; o < p.outputs.size(); ++o)
-        if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0" << (p.persistent ? "" : " && row_ok") << ") out" << o << "[row] = v" << p.outputs[o].node << ";\n";
-    if (p.persistent && p.row_reduces.size() > 0) os << I << "if (TEAM > 32) __syncthreads();  // shared-memory slots are reused by the next row\n";
+        if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0 && row_ok) out" << o << "[row] = v" << p.outputs[o].node << ";\n";
+    if (p.persistent) os << I << "red_set ^= 1;\n";
     if (p.persistent && p.stage_smem) {
         os << I << "buf ^= 1;\n";
     } else if (p.persistent && p.prefetch) {
@@ -765,7 +772,7 @@ std::string emitFlat(Program& p) {
         first = false;
         os << cTypeName(p.outputs[o].dtype) << "* __restrict__ out" << o;
     }
-    os << (first ? "" : ", ") << "float* __restrict__ ws) {\n";
+    os << (first ? "" : ", ") << "float* __restrict__ ws) {\n    tb_grid_wait();\n";
     os << "    constexpr int VEC = " << VEC << ", U = 4, ITERS = " << p.vpt << ";\n";
     os << "    constexpr tb_u64 NUMEL = " << numel << "ull, NPACKS = NUMEL / VEC, CHUNK = 256ull * U * ITERS;\n";
     os << "    __shared__ float red_smem[" << p.all_reduces.size() << "][1][8];\n";
@@ -855,6 +862,8 @@ __device__ __forceinline__ float foldCombine(float a, float b) {
 }
 template <int OP>
 __global__ void __launch_bounds__(1024) foldFullPartials(const float* __restrict__ ws, uint32_t parts, void* out, int out_dtype, float divisor, int take_sqrt) {
+    gridDependencyWait();
+    gridLaunchDependents();
     __shared__ float sm[32];
     const float identity = OP == 1 ? 1.0f : (OP == 2 ? __int_as_float(0x7f800000) : (OP == 3 ? __int_as_float(0xff800000) : 0.0f));
     float v = identity;
@@ -881,6 +890,8 @@ __global__ void __launch_bounds__(1024) foldFullPartials(const float* __restrict
 
 // Folds column partials [parts][cols] in part order and stores in the output dtype.
 __global__ void __launch_bounds__(256) foldColumnPartials(const float* __restrict__ ws, uint32_t parts, uint64_t cols, void* out, int out_dtype, float divisor) {
+    gridDependencyWait();
+    gridLaunchDependents();
     const uint64_t c = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (c >= cols) return;
     float v = 0.0f;
@@ -1105,7 +1116,7 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
             h->smem_opted_in[dev & 63] = true;
         }
     }
-    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, p.smem_bytes, stream));
+    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, p.smem_bytes, stream));
     countLaunch();
     if (!p.all_reduces.empty()) {
         size_t idx = 0;
@@ -1117,10 +1128,10 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
             const float divisor = op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows * p.cols) : 1.0f;
             const int take_sqrt = op == THOR_B200_OP_REDUCE_NORM2;
             const float* part = static_cast<const float*>(workspace) + idx * static_cast<size_t>(p.grid);
-            if (op == THOR_B200_OP_REDUCE_PROD) foldFullPartials<1><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            else if (op == THOR_B200_OP_REDUCE_MIN) foldFullPartials<2><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            else if (op == THOR_B200_OP_REDUCE_MAX) foldFullPartials<3><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            else foldFullPartials<0><<<1, 1024, 0, stream>>>(part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            if (op == THOR_B200_OP_REDUCE_PROD) (void)launchDependent(foldFullPartials<1>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            else if (op == THOR_B200_OP_REDUCE_MIN) (void)launchDependent(foldFullPartials<2>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            else if (op == THOR_B200_OP_REDUCE_MAX) (void)launchDependent(foldFullPartials<3>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
+            else (void)launchDependent(foldFullPartials<0>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
             TB_CUDA(cudaGetLastError());
             ++idx;
         }
@@ -1135,7 +1146,7 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
                 if (p.outputs[o].node == k) break;
             const float divisor = p.nodes[k].op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows) : 1.0f;
             const float* part = static_cast<const float*>(workspace) + ci * static_cast<size_t>(parts) * p.cols;
-            foldColumnPartials<<<static_cast<unsigned>((p.cols + 255) / 256), 256, 0, stream>>>(part, parts, p.cols, output_ptrs[o], p.outputs[o].dtype, divisor);
+            (void)launchDependent(foldColumnPartials, dim3(static_cast<unsigned>((p.cols + 255) / 256)), dim3(256), 0, stream, part, parts, p.cols, output_ptrs[o], p.outputs[o].dtype, divisor);
             TB_CUDA(cudaGetLastError());
             ++ci;
         }
