@@ -1,0 +1,115 @@
+"""Host planner, dtype resolution and kernel generation without a GPU.
+
+`FusedEquation.plan` stamps against shapes and dtypes only: stages are planned, every kernel is
+generated and compiled for sm_100a (NVRTC needs no device), nothing is loaded or launched.  The
+stage lists asserted here are the ones the reference's planner reports for the same expressions
+(EquationCompiler::splitAtReductionBoundaries, EquationCompiler.cpp:7881; stage kinds in
+EquationCompiler.h:27)."""
+import pytest
+
+from thor_b200 import DataType as DT
+from thor_b200 import _native
+from thor_b200.expression import Expression as ex
+
+
+def _c2():
+    a, x, b, z = ex.input("a"), ex.input("x"), ex.input("b"), ex.input("z")
+    return (a * x + b).relu() * z.sigmoid()
+
+
+def _softmax():
+    x = ex.input("x")
+    e = (x - x.reduce_max([1])).exp()
+    return e / e.reduce_sum([1])
+
+
+def _layernorm(eps=1e-5):
+    x, gamma, beta = ex.input("x"), ex.input("gamma"), ex.input("beta")
+    xc = x - x.reduce_mean([1])
+    rstd = 1.0 / ((xc * xc).reduce_mean([1]) + eps).sqrt()
+    return (xc * rstd * gamma + beta).cast(DT.bf16)
+
+
+def test_broadcast_fused_expression_is_one_tiled_half2_stage():
+    plan = ex.compile(_c2()).plan({"a": ((8192,), DT.fp16), "x": ((8192, 8192), DT.fp16), "b": ((8192,), DT.fp16), "z": ((8192, 8192), DT.fp16)})
+    assert plan.stage_kind_names() == ["FusedKernel"]
+    assert plan.physical_stage_names() == ["bcast_tiled_v2"]
+    assert plan.kernel_launches_per_run() == 1 and plan.intermediate_bytes() == 0
+    assert plan.output_spec() == ([8192, 8192], DT.fp16)
+    src = plan.stage_sources()[0]
+    assert "__half2" in src and "griddepcontrol" not in src and "tb_grid_wait();" in src
+
+
+def test_flat_expression_without_broadcast_is_a_flat_stage():
+    x, y = ex.input("x"), ex.input("y")
+    plan = ex.compile((x * y + 1.0).tanh()).plan({"x": ((1 << 20,), DT.fp32), "y": ((1 << 20,), DT.fp32)})
+    assert plan.physical_stage_names() == ["flat_scalar"]
+    assert plan.output_spec() == ([1 << 20], DT.fp32)
+
+
+def test_mixed_fp16_bf16_promotes_to_fp32_and_scalars_do_not_promote():
+    x, y = ex.input("x"), ex.input("y")
+    plan = ex.compile({"sum": x + y, "scaled": x * 3.0}).plan({"x": ((64, 64), DT.fp16), "y": ((64, 64), DT.bf16)})
+    assert plan.output_spec("sum")[1] == DT.fp32
+    assert plan.output_spec("scaled")[1] == DT.fp16
+
+
+def test_softmax_is_one_row_program_or_four_stages():
+    shapes = {"x": ((65536, 4096), DT.fp32)}
+    fused = ex.compile(_softmax()).plan(shapes)
+    staged = ex.compile(_softmax(), fuse_row_reductions=False).plan(shapes)
+    assert fused.stage_kind_names() == staged.stage_kind_names() == ["Reduction", "FusedKernel", "Reduction", "FusedKernel"]
+    assert fused.physical_stage_names() == ["row_program"] and fused.kernel_launches_per_run() == 1
+    assert fused.intermediate_bytes() <= 1
+    assert len(staged.physical_stage_names()) == 4 and staged.physical_stage_names()[0].startswith("rows_")
+    assert staged.intermediate_bytes() >= 65536 * 4096 * 4
+    assert fused.output_spec() == staged.output_spec() == ([65536, 4096], DT.fp32)
+
+
+def test_argmax_stage_yields_uint32_indices():
+    plan = ex.compile(ex.input("x").argmax([1], squeeze_axes=[1])).plan({"x": ((1024, 4096), DT.fp32)})
+    assert plan.stage_kind_names() == ["ArgMinMax"]
+    assert plan.output_spec() == ([1024], DT.uint32)
+
+
+def test_layernorm_forward_and_backward_plans():
+    shapes = {"x": ((32768, 8192), DT.bf16), "gamma": ((8192,), DT.bf16), "beta": ((8192,), DT.bf16)}
+    fwd_eq = ex.compile({"y": _layernorm()})
+    fwd = fwd_eq.plan(shapes)
+    assert fwd.physical_stage_names() == ["row_program"] and fwd.kernel_launches_per_run() == 1
+    assert fwd.output_spec("y") == ([32768, 8192], DT.bf16)
+    bwd = fwd_eq.compile_backward(["x", "gamma", "beta"]).plan({**shapes, "__grad_output": ((32768, 8192), DT.bf16)})
+    assert sorted(bwd.output_names()) == ["beta_grad", "gamma_grad", "x_grad"]
+    # one row kernel plus one fold per column reduction; gradients come back in the dtype of their input
+    assert bwd.physical_stage_names() == ["row_program"] and bwd.kernel_launches_per_run() == 3
+    assert bwd.output_spec("x_grad") == ([32768, 8192], DT.bf16)
+    assert bwd.output_spec("gamma_grad") == ([8192], DT.bf16)
+    src = bwd.stage_sources()[0]
+    assert "__ffma2_rn" in src, "fp32 element math of row programs uses the packed f32x2 instructions"
+    # partial column sums: one fp32 row of [cols] per CTA and column reduction
+    assert bwd.intermediate_bytes() == 2 * 148 * 8192 * 4
+
+
+def test_three_full_reductions_share_one_pass():
+    x = ex.input("x")
+    plan = ex.compile({"sum": x.reduce_sum(), "sumsq": (x * x).reduce_sum(), "max": x.reduce_max()}).plan({"x": ((1 << 24,), DT.bf16)})
+    assert plan.physical_stage_names() == ["row_program"]
+    assert plan.kernel_launches_per_run() == 4  # one streaming pass + one single-CTA fold per statistic
+    for name in ("sum", "sumsq", "max"):
+        assert plan.output_spec(name)[1] == DT.fp32
+
+
+def test_plan_only_plans_refuse_to_run_and_own_no_memory():
+    plan = ex.compile(_softmax()).plan({"x": ((64, 128), DT.fp32)})
+    with pytest.raises((_native.ThorB200Error, _native.ThorB200InvalidArgument)):
+        plan.run()
+    with pytest.raises((_native.ThorB200Error, _native.ThorB200InvalidArgument)):
+        plan.output()
+
+
+def test_shape_errors_surface_at_plan_time():
+    x, y = ex.input("x"), ex.input("y")
+    with pytest.raises((_native.ThorB200Error, _native.ThorB200InvalidArgument)):
+        ex.compile(x + y).plan({"x": ((64, 3), DT.fp32), "y": ((64, 4), DT.fp32)})
+    with pytest.raises((_native.ThorB200Error, _native.ThorB200InvalidArgument)):
+        ex.compile(x + y).plan({"x": ((64, 3), DT.fp32)})
