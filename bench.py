@@ -615,10 +615,19 @@ def main():
     dist.close()
 
 
-# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/.
-# c2: 134.25 MB read + 27.91 MB written at half size (4096 rows), scaled x2 to the full launch; the written bytes
-# undercount the 134 MB output because most of it is still dirty in the 126 MB L2 when the kernel ends.
-TRAFFIC_BYTES = {"c2_fused_relu_axb_sigmoid": 324320256}
+# DRAM bytes of the dominant kernel per launch, measured with ncu on a reduced case of the same kernel (one
+# captured launch, summaries under profiles/) and scaled to the full launch by the elements processed: traffic
+# grows in proportion (every input byte is read once).  Written bytes undercount outputs that are still dirty
+# in the 126 MB L2 when a small case ends, so values below the algorithmic bytes mean "no re-reads", not less work.
+TRAFFIC_BYTES = {
+    "c1_cast_fp32_fp16": 72_500_000,                 # full size captured; most of the 33.5 MB output is still in L2 at kernel end
+    "c2_fused_relu_axb_sigmoid": 2 * 162_100_000,    # 4096 of 8192 rows captured
+    "c3_softmax_rows_fp32": 8 * 217_200_000,         # 8192 of 65536 rows captured
+    "c3_row_argmax_fp32": 8 * 138_300_000,
+    "c4_full_reductions_bf16": 16 * 273_800_000,     # 2^27 of 2^31 elements captured
+    "c5_layernorm_forward_bf16": 8 * 84_400_000,     # 4096 of 32768 rows captured
+    "c5_layernorm_backward_bf16": 8 * 169_300_000,
+}
 
 if __name__ == "__main__":
     main()
