@@ -74,7 +74,9 @@ THOR_B200_API uint64_t thor_b200_launch_count(void);
  * TypeConverter.h:61-66; launcher TypeConverterKernels.cu:1340-1433).
  * Converts n elements from src (src_dtype) to dst (dst_dtype) with the C++ static_cast rule of
  * the CUDA element types (fp8-e4m3 destinations saturate to +-448).  Both pointers are device
- * memory of the stream's device.  src == dst requests an in-place conversion; otherwise the two
+ * memory of the stream's device.  src == dst requests an in-place conversion (element i of the
+ * source view becomes element i of the destination view; between different element sizes the
+ * buffer must hold the larger view, TypeConverterKernels.cu:846-904); otherwise the two
  * ranges must not overlap.  n == 0 is a no-op.  src_dtype == dst_dtype is a caller bug and is
  * rejected, as in the reference.  Reads and writes exactly n elements: no tail padding needed.
  * ------------------------------------------------------------------------------------------- */

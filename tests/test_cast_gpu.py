@@ -109,6 +109,35 @@ def test_in_place_same_size():
     assert np.array_equal(d.cpu().numpy().view(np.float32), x.astype(np.float32))
 
 
+_NP = {DataType.fp32: np.float32, DataType.fp16: np.float16, DataType.int32: np.int32, DataType.int64: np.int64, DataType.uint8: np.uint8,
+       DataType.int16: np.int16, DataType.fp64: np.float64}
+
+
+@pytest.mark.parametrize("src,dst", [(DataType.fp32, DataType.fp16), (DataType.fp16, DataType.fp32), (DataType.int64, DataType.uint8),
+                                     (DataType.uint8, DataType.int64), (DataType.fp32, DataType.int16), (DataType.int16, DataType.fp64)])
+@pytest.mark.parametrize("n", [1, 255, 8192, 8193, 20000, (1 << 20) + 77, (1 << 24)])
+def test_in_place_between_element_sizes_matches_out_of_place(src, dst, n):
+    """Element i of the source view becomes element i of the destination view in the same buffer
+    (TypeConverterKernels.cu:846-904); compared bit for bit with the out-of-place conversion."""
+    rng = np.random.default_rng(n + int(src) * 31 + int(dst))
+    if src in (DataType.fp32, DataType.fp16):
+        x = (rng.standard_normal(n) * 50).astype(_NP[src])
+    else:
+        x = rng.integers(0, 100, n).astype(_NP[src])
+    ssz, dsz = x.itemsize, np.dtype(_NP[dst]).itemsize
+    buf = torch.zeros(n * max(ssz, dsz) + 64, dtype=torch.uint8, device="cuda")
+    buf[: n * ssz] = torch.from_numpy(x.view(np.uint8)).cuda()
+    buf[n * max(ssz, dsz):] = 0xAB  # guard bytes after the larger view
+    want = torch.empty(n * dsz, dtype=torch.uint8, device="cuda")
+    src_copy = buf[: n * ssz].clone()
+    TypeConverter.convert_type_raw(src_copy.data_ptr(), want.data_ptr(), src, dst, n)
+    TypeConverter.convert_type_raw(buf.data_ptr(), buf.data_ptr(), src, dst, n)
+    torch.cuda.synchronize()
+    assert torch.equal(buf[: n * dsz], want)
+    assert bool((buf[n * max(ssz, dsz):] == 0xAB).all())
+    assert np.array_equal(want.cpu().numpy().view(_NP[dst]), o.cast(x, src, dst))
+
+
 def test_unaligned_views_use_the_scalar_path():
     x = cast_input(5000, seed=11)
     d = torch.from_numpy(x).cuda()

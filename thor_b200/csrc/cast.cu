@@ -119,6 +119,73 @@ __global__ void __launch_bounds__(256) castInPlaceSameSizeKernel(void* buf, int6
     }
 }
 
+// Same-address conversion between element sizes, first block of elements: one CTA reads its (at
+// most kHeadElements) values into registers, meets at a barrier, then writes them; reads and writes
+// of this block overlap each other but nothing else.
+constexpr int kHeadElements = 8192;
+template <class F, class T>
+__global__ void __launch_bounds__(256) castInPlaceHeadKernel(void* buf, int count) {
+    gridDependencyWait();
+    gridLaunchDependents();
+    constexpr int PER = kHeadElements / 256;
+    F held[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + i * 256;
+        if (e < count) held[i] = reinterpret_cast<const F*>(buf)[e];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + i * 256;
+        if (e < count) reinterpret_cast<T*>(buf)[e] = Cvt<F, T>::run(held[i]);
+    }
+}
+
+template <class F, class T>
+int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream);
+
+// Same-address conversion between element sizes (element i of the source view becomes element i of
+// the destination view; TypeConverterKernels.cu:846-904 has the reference's semantics).  The range
+// is cut into stream-ordered passes whose writes land only on bytes that no later pass reads:
+//   narrowing: [0, head) by the head kernel, then [s, e) with e * sizeof(T) <= s * sizeof(F), upwards;
+//   widening:  [s, n) with s * sizeof(T) >= n * sizeof(F), then downwards, the head block last.
+// Each pass is the ordinary out-of-place kernel on disjoint byte ranges; pass boundaries are
+// multiples of 2048 elements so 16-byte packs stay aligned.  The number of launches grows with
+// log(n / head) to the base of the size ratio (12 for 2^24 fp32 -> fp16).
+template <class F, class T>
+int launchInPlaceResize(void* buf, int64_t n, cudaStream_t stream) {
+    constexpr int64_t S = sizeof(F), D = sizeof(T), kAlign = 2048;
+    F* src = static_cast<F*>(buf);
+    T* dst = static_cast<T*>(buf);
+    auto head = [&](int64_t count) -> int {
+        TB_CUDA(launchDependent(castInPlaceHeadKernel<F, T>, dim3(1), dim3(256), 0, stream, buf, static_cast<int>(count)));
+        countLaunch();
+        return THOR_B200_OK;
+    };
+    if constexpr (sizeof(F) > sizeof(T)) {
+        int64_t s = n < kHeadElements ? n : kHeadElements;
+        if (int st = head(s)) return st;
+        while (s < n) {
+            int64_t e = s * S / D;
+            e = e / kAlign * kAlign;
+            if (e > n) e = n;
+            if (int st = launchCast<F, T>(src + s, dst + s, e - s, stream)) return st;
+            s = e;
+        }
+    } else {
+        int64_t e = n;
+        while (e > kHeadElements) {
+            int64_t s = (e * S + D - 1) / D;
+            s = (s + kAlign - 1) / kAlign * kAlign;  // s < e because e > kHeadElements >= 2 * kAlign and S <= D / 2
+            if (int st = launchCast<F, T>(src + s, dst + s, e - s, stream)) return st;
+            e = s;
+        }
+        if (int st = head(e)) return st;
+    }
+    return THOR_B200_OK;
+}
+
 template <class F, class T>
 int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream) {
     using G = CastGeom<F, T>;
@@ -141,8 +208,7 @@ int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream) {
             TB_CUDA(cudaGetLastError());
             return THOR_B200_OK;
         } else {
-            return fail(THOR_B200_UNSUPPORTED, "in-place cast between element sizes %zu and %zu is not provided by this build",
-                        sizeof(F), sizeof(T));
+            return launchInPlaceResize<F, T>(dst_v, n, stream);
         }
     }
 
