@@ -66,6 +66,27 @@ def test_softmax_is_one_row_program_or_four_stages():
     assert fused.output_spec() == staged.output_spec() == ([65536, 4096], DT.fp32)
 
 
+def test_softmax_op_keeps_the_operand_dtype_and_is_one_row_program():
+    for dt in (DT.fp32, DT.bf16, DT.fp16):
+        plan = ex.compile(ex.input("x").softmax()).plan({"x": ((4096, 4096), dt)})
+        assert plan.physical_stage_names() == ["row_program"] and plan.kernel_launches_per_run() == 1
+        assert plan.output_spec() == ([4096, 4096], dt)
+    # instance mode: every axis but the first, whatever the rank
+    plan = ex.compile(ex.input("x").log_softmax(0)).plan({"x": ((64, 8, 16, 4), DT.fp32)})
+    assert plan.physical_stage_names() == ["row_program"]
+    # backward of the op: the row maximum carries no gradient, so no min/max-backward stage appears
+    bwd = ex.compile(ex.input("x").softmax()).compile_backward(["x"]).plan({"x": ((512, 1024), DT.bf16), "__grad_output": ((512, 1024), DT.bf16)})
+    assert bwd.physical_stage_names() == ["row_program"] and bwd.output_spec("x_grad") == ([512, 1024], DT.bf16)
+
+
+def test_row_programs_cover_reductions_over_a_trailing_block_of_axes():
+    x = ex.input("x")
+    xc = x - x.reduce_mean([1, 2])
+    plan = ex.compile(xc / ((xc * xc).reduce_mean([1, 2]) + 1e-5).sqrt()).plan({"x": ((128, 32, 64), DT.bf16)})
+    assert plan.physical_stage_names() == ["row_program"]
+    assert plan.output_spec() == ([128, 32, 64], DT.fp32)
+
+
 def test_argmax_stage_yields_uint32_indices():
     plan = ex.compile(ex.input("x").argmax([1], squeeze_axes=[1])).plan({"x": ((1024, 4096), DT.fp32)})
     assert plan.stage_kind_names() == ["ArgMinMax"]

@@ -226,6 +226,18 @@ class Expression:
     def hard_tanh(self, lo: float = -1.0, hi: float = 1.0): return self._composite("hard_tanh", lo, hi)
     def clamp(self, lo: float, hi: float): return self._composite("clamp", lo, hi)
 
+    # cudnnSoftmaxAlgorithm_t / cudnnSoftmaxMode_t values of the reference's softmax op
+    SOFTMAX_FAST, SOFTMAX_ACCURATE, SOFTMAX_LOG = 0, 1, 2
+    SOFTMAX_MODE_INSTANCE, SOFTMAX_MODE_CHANNEL = 0, 1
+
+    def softmax(self, algorithm: int = 1, mode: int = 1) -> "Expression":
+        """Softmax over axis 1 (channel mode) or over every axis but the first (instance mode), computed in
+        fp32 and stored in the operand's dtype; runs as one row program."""
+        return self._composite("softmax", float(algorithm), float(mode))
+
+    def log_softmax(self, mode: int = 1) -> "Expression":
+        return self._composite("log_softmax", 2.0, float(mode))
+
     # ---- shapes and reductions --------------------------------------------------------------------
     def _shape_op(self, op: int, values: Sequence[int]) -> "Expression":
         arr = (C.c_uint64 * max(1, len(values)))(*values)

@@ -113,6 +113,7 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
             reaches[k] = std::find(wrt_names.begin(), wrt_names.end(), g.inputs[nd.input_slot].name) != wrt_names.end();
             continue;
         }
+        if (nd.stop_gradient) continue;
         for (uint32_t p : {nd.lhs, nd.rhs, nd.aux})
             if (p != UINT32_MAX && reaches[p]) reaches[k] = true;
     }
@@ -223,8 +224,7 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
                 // unsqueeze the gradient back to keep-dims form; elementwise consumers broadcast it
                 const std::vector<uint64_t>& in_shape = b.fwd_shape[nd.lhs];
                 std::vector<uint64_t> keep(in_shape);
-                std::vector<bool> reduced(in_shape.size(), nd.reduction_axes.empty());
-                for (uint64_t ax : nd.reduction_axes) reduced[ax] = true;
+                const std::vector<bool> reduced = reducedAxesMask(nd, in_shape.size());
                 uint64_t count = 1;
                 for (size_t i = 0; i < in_shape.size(); ++i)
                     if (reduced[i]) {

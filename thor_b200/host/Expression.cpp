@@ -32,7 +32,7 @@ bool sameNode(const ExprNode& a, const ExprNode& b) {
     return a.op == b.op && a.lhs == b.lhs && a.rhs == b.rhs && a.aux == b.aux && a.input_slot == b.input_slot &&
            ((a.scalar_fp == b.scalar_fp) || (a.scalar_fp != a.scalar_fp && b.scalar_fp != b.scalar_fp)) && a.output_dtype == b.output_dtype &&
            a.compute_dtype == b.compute_dtype && a.reduction_axes == b.reduction_axes && a.squeeze_axes == b.squeeze_axes &&
-           a.unsqueeze_axes == b.unsqueeze_axes && a.reshape_dims == b.reshape_dims;
+           a.unsqueeze_axes == b.unsqueeze_axes && a.reshape_dims == b.reshape_dims && a.stop_gradient == b.stop_gradient;
 }
 
 // Appends a node unless a structurally identical one exists already (common sub-expressions are
@@ -210,6 +210,7 @@ Expression Expression::reduction(ExprOp op, const std::vector<uint64_t>& reducti
     if (!isReductionOp(op)) throw std::invalid_argument("Expression::reduction requires a reduction op");
     std::vector<uint64_t> axes = reduction_axes;
     std::sort(axes.begin(), axes.end());
+    if (axes.size() > 1 && axes.back() == kAxesFromOne) throw std::invalid_argument("Expression::reduction: the all-but-first sentinel stands alone");
     if (std::adjacent_find(axes.begin(), axes.end()) != axes.end()) throw std::invalid_argument("Expression::reduction axes must be unique");
     auto g = std::make_shared<PhysicalExpression>(*expr_);
     ExprNode n;
@@ -219,6 +220,68 @@ Expression Expression::reduction(ExprOp op, const std::vector<uint64_t>& reducti
     n.squeeze_axes = squeeze_axes;
     n.compute_dtype = compute_dtype;
     return Expression(g, appendShared(*g, n));
+}
+
+std::vector<bool> reducedAxesMask(const ExprNode& reduction, size_t rank) {
+    const auto& axes = reduction.reduction_axes;
+    if (axes.size() == 1 && axes[0] == kAxesFromOne) {
+        std::vector<bool> mask(rank, true);
+        if (rank > 0) mask[0] = false;
+        return mask;
+    }
+    std::vector<bool> mask(rank, axes.empty());
+    for (uint64_t ax : axes) {
+        if (ax >= rank) throw std::logic_error("reduction axis out of range");
+        mask[ax] = true;
+    }
+    return mask;
+}
+
+namespace {
+Expression softmaxComposite(const Expression& x, SoftmaxAlgorithm algorithm, SoftmaxMode mode) {
+    const std::vector<uint64_t> axes = mode == SoftmaxMode::CHANNEL ? std::vector<uint64_t>{1} : std::vector<uint64_t>{kAxesFromOne};
+    const Expression xf = x.cast(DataType::FP32);
+    Expression y = xf;
+    if (algorithm == SoftmaxAlgorithm::FAST) {
+        const Expression e = xf.exp();
+        y = e / e.reduce_sum(axes);
+    } else {
+        // softmax is invariant to the shift, so the row maximum carries no gradient
+        auto gm = std::make_shared<PhysicalExpression>(*xf.graph());
+        ExprNode mx;
+        mx.op = ExprOp::REDUCE_MAX;
+        mx.lhs = xf.nodeIndex();
+        mx.reduction_axes = axes;
+        mx.stop_gradient = true;
+        gm->nodes.push_back(mx);
+        const Expression row_max = Expression::fromPhysicalNode(gm, static_cast<uint32_t>(gm->nodes.size() - 1));
+        const Expression d = xf - row_max;
+        const Expression e = d.exp();
+        y = algorithm == SoftmaxAlgorithm::LOG ? d - e.reduce_sum(axes).ln() : e / e.reduce_sum(axes);
+    }
+    // store in the operand's dtype: a cast whose target is read from the operand when dtypes are resolved
+    auto g = std::make_shared<PhysicalExpression>(*y.graph());
+    ExprNode n;
+    n.op = ExprOp::CAST;
+    n.lhs = y.nodeIndex();
+    n.aux = mergeInto(*g, *x.graph(), x.nodeIndex());
+    g->nodes.push_back(n);
+    return Expression::fromPhysicalNode(g, static_cast<uint32_t>(g->nodes.size() - 1));
+}
+}  // namespace
+
+Expression Expression::softmax(SoftmaxAlgorithm algorithm, SoftmaxMode mode) const {
+    if (algorithm == SoftmaxAlgorithm::LOG)
+        throw std::invalid_argument("Expression::softmax computes ordinary softmax; use Expression::logSoftmax for the log algorithm.");
+    if (algorithm != SoftmaxAlgorithm::FAST && algorithm != SoftmaxAlgorithm::ACCURATE)
+        throw std::invalid_argument("Expression::softmax received an unsupported algorithm.");
+    if (mode != SoftmaxMode::CHANNEL && mode != SoftmaxMode::INSTANCE) throw std::invalid_argument("Expression::softmax received an unsupported mode.");
+    return softmaxComposite(*this, algorithm, mode);
+}
+
+Expression Expression::logSoftmax(SoftmaxMode mode) const {
+    if (mode != SoftmaxMode::CHANNEL && mode != SoftmaxMode::INSTANCE) throw std::invalid_argument("Expression::logSoftmax received an unsupported mode.");
+    return softmaxComposite(*this, SoftmaxAlgorithm::LOG, mode);
 }
 
 Outputs Expression::outputs(const std::vector<std::pair<std::string, Expression>>& named_exprs) {
@@ -359,6 +422,11 @@ void resolveOutputsDTypesInPlace(PhysicalOutputs& outputs, const std::vector<Dat
             node.compute_dtype = compute;
             resolved[i] = out;
             continue;
+        }
+        if (node.op == ExprOp::CAST && node.aux != UINT32_MAX) {
+            // "store like that node": the target dtype becomes explicit and the reference to the node is dropped
+            if (!node.output_dtype.has_value()) node.output_dtype = resolved[node.aux];
+            node.aux = UINT32_MAX;
         }
         const DataType out = resolveNodeOutputDType(node, expr.nodes, resolved);
         const DataType logical_in = resolveLogicalInputDType(node, expr.nodes, resolved);

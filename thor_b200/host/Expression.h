@@ -22,6 +22,7 @@ enum class ExprOp : uint16_t {
     GREATER_EQUAL, LOGICAL_AND, LOGICAL_OR, LOGICAL_NOT, CAST, WHERE, NEG, ABS, CEIL, FLOOR, ROUND, TRUNC, SIN, COS, TAN, ASIN, ACOS, ATAN,
     SINH, COSH, ASINH, ACOSH, ATANH, ERF, ERFC, ERFCX, ERFINV, ERFCINV, TGAMMA, LGAMMA, DIGAMMA, EXP, EXPM1, EXP2, EXP10, LN, LOG1P, LOG2,
     LOG10, SQRT, TANH, NORMCDF,
+    SOFTMAX = 60,  // never stored in a graph: Expression::softmax / logSoftmax build the composite directly
     RESHAPE = 62, UNSQUEEZE = 65, SQUEEZE = 66,
     MIN = 69, MAX, MIN_GRAD_LEFT, MIN_GRAD_RIGHT, MAX_GRAD_LEFT, MAX_GRAD_RIGHT,
     REDUCE_SUM = 83, REDUCE_PROD, REDUCE_MIN, REDUCE_MAX, REDUCE_ARGMIN, REDUCE_ARGMAX,
@@ -44,6 +45,10 @@ inline bool isBinaryOp(ExprOp op) {
 }
 const char* opName(ExprOp op);
 
+// Sentinel reduction-axis list {kAxesFromOne}: every axis except the first (the "instance" mode of
+// the softmax op, whose rank is known only when shapes are bound).
+constexpr uint64_t kAxesFromOne = UINT64_MAX - 1;
+
 // Sentinel squeeze list meaning "squeeze every singleton axis" (StampedEquation.cpp:4308-4363).
 constexpr uint64_t kSqueezeAll = UINT64_MAX;
 
@@ -51,7 +56,7 @@ struct ExprNode {
     ExprOp op = ExprOp::INPUT;
     uint32_t lhs = UINT32_MAX;
     uint32_t rhs = UINT32_MAX;
-    uint32_t aux = UINT32_MAX;
+    uint32_t aux = UINT32_MAX;  // WHERE: false branch.  CAST before dtype resolution: node whose output dtype the cast takes
     uint32_t input_slot = UINT32_MAX;
     double scalar_fp = 0.0;
     std::optional<DataType> input_tensor_dtype;  // INPUT / *_RUNTIME_SCALAR: dtype of the bound value (filled at resolution)
@@ -61,7 +66,15 @@ struct ExprNode {
     std::vector<uint64_t> squeeze_axes;    // reductions / SQUEEZE
     std::vector<uint64_t> unsqueeze_axes;  // UNSQUEEZE
     std::vector<uint64_t> reshape_dims;    // RESHAPE
+    bool stop_gradient = false;            // autodiff treats the node as a constant (the shift term of softmax)
 };
+
+// Which axes of a rank-`rank` operand the reduction node reduces (empty list = all axes).
+std::vector<bool> reducedAxesMask(const ExprNode& reduction, size_t rank);
+
+// cudnnSoftmaxAlgorithm_t / cudnnSoftmaxMode_t values, which the reference's softmax op takes (Expression.h:736-738).
+enum class SoftmaxAlgorithm : int { FAST = 0, ACCURATE = 1, LOG = 2 };
+enum class SoftmaxMode : int { INSTANCE = 0, CHANNEL = 1 };
 
 struct NamedInput {
     enum class Kind : uint8_t { Tensor, RuntimeScalarFp32, TensorRuntimeScalar };
@@ -168,6 +181,12 @@ class Expression {
     Expression relu6() const;
     Expression hardTanh(double min_value = -1.0, double max_value = 1.0) const;
     Expression clamp(double lower_bound, double upper_bound) const;
+
+    // Softmax over axis 1 (CHANNEL) or over every axis but the first (INSTANCE), computed in fp32 and stored in
+    // the operand's dtype (Expression.cpp:3724-3748).  The reference hands this op to cuDNN as a stage of its own;
+    // here it is the composite max / exp / sum / divide, which the planner runs as one row program.
+    Expression softmax(SoftmaxAlgorithm algorithm = SoftmaxAlgorithm::ACCURATE, SoftmaxMode mode = SoftmaxMode::CHANNEL) const;
+    Expression logSoftmax(SoftmaxMode mode = SoftmaxMode::CHANNEL) const;
 
     Expression reshape(const std::vector<uint64_t>& new_dims) const;
     Expression unsqueeze(const std::vector<uint64_t>& axes) const;

@@ -81,11 +81,7 @@ std::vector<std::vector<uint64_t>> inferNodeShapes(const PhysicalExpression& exp
             shape[k] = {};
         } else if (isReductionOp(n.op)) {
             const auto& in = shape[n.lhs];
-            std::vector<bool> reduced(in.size(), n.reduction_axes.empty());
-            for (uint64_t ax : n.reduction_axes) {
-                if (ax >= in.size()) throw std::logic_error("reduction axis out of range");
-                reduced[ax] = true;
-            }
+            const std::vector<bool> reduced = reducedAxesMask(n, in.size());
             std::vector<uint64_t> kept(in);
             for (size_t i = 0; i < in.size(); ++i)
                 if (reduced[i]) kept[i] = 1;
@@ -472,8 +468,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             const Tensor& src = node_tensor[nd.lhs];
             if (!src.isInitialized()) throw std::logic_error("FusedEquation::stamp: reduction input is not materialised");
             const auto& in_shape = shape[nd.lhs];
-            std::vector<bool> reduced(in_shape.size(), nd.reduction_axes.empty());
-            for (uint64_t ax : nd.reduction_axes) reduced[ax] = true;
+            const std::vector<bool> reduced = reducedAxesMask(nd, in_shape.size());
             // [outer, reduction, inner] needs the non-singleton reduced axes to form one contiguous block
             uint64_t outer = 1, red = 1, inner = 1;
             int phase = 0;

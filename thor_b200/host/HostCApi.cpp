@@ -148,6 +148,8 @@ THB_API int thb_composite(const char* name, const Expression* a, double p0, doub
         else if (n == "relu6") r = a->relu6();
         else if (n == "hard_tanh") r = a->hardTanh(p0, p1);
         else if (n == "clamp") r = a->clamp(p0, p1);
+        else if (n == "softmax") r = a->softmax(static_cast<SoftmaxAlgorithm>(static_cast<int>(p0)), static_cast<SoftmaxMode>(static_cast<int>(p1)));
+        else if (n == "log_softmax") r = a->logSoftmax(static_cast<SoftmaxMode>(static_cast<int>(p1)));
         else throw std::invalid_argument("thb_composite: unknown composite '" + n + "'");
         *out = new Expression(r);
     });

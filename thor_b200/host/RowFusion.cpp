@@ -33,12 +33,45 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
         for (uint32_t p : {g.nodes[k].lhs, g.nodes[k].rhs, g.nodes[k].aux})
             if (p != UINT32_MAX) needed[p] = true;
     }
-    // the [rows, cols] frame: the argument of the first reduction
+    // The [rows, cols] frame: the shape of the first reduction's argument, cut at `split` into leading axes
+    // (rows) and trailing axes (cols).  The cut comes from the first reduction that reduces exactly a
+    // trailing block of axes (row statistics: softmax over the last axis, instance softmax, LayerNorm over
+    // the last two axes ...) or exactly a leading block (column sums); the last axis otherwise.
     std::vector<uint64_t> frame;
     for (size_t k = 0; k < n && frame.empty(); ++k)
         if (needed[k] && isReductionOp(g.nodes[k].op)) frame = ctx.shape[g.nodes[k].lhs];
-    if (frame.empty() || frame.size() < 1) return {};
-    const uint64_t cols = frame.back();
+    if (frame.empty()) return {};
+    size_t split = frame.size() - 1;
+    for (size_t k = 0; k < n; ++k) {
+        if (!needed[k] || !isValueReductionOp(g.nodes[k].op) || ctx.shape[g.nodes[k].lhs] != frame) continue;
+        const std::vector<bool> reduced = reducedAxesMask(g.nodes[k], frame.size());
+        size_t first_red = frame.size(), last_red = 0, first_keep = frame.size(), last_keep = 0;
+        bool any_red = false, any_keep = false;
+        for (size_t i = 0; i < frame.size(); ++i) {
+            if (frame[i] == 1) continue;
+            if (reduced[i]) {
+                if (!any_red) first_red = i;
+                last_red = i;
+                any_red = true;
+            } else {
+                if (!any_keep) first_keep = i;
+                last_keep = i;
+                any_keep = true;
+            }
+        }
+        if (!any_red || !any_keep) continue;  // reduces everything or nothing: tells nothing about the cut
+        if (last_keep < first_red) {
+            split = first_red;
+            break;
+        }
+        if (last_red < first_keep) {
+            split = first_keep;
+            break;
+        }
+        return {};  // interleaved reduced and kept axes
+    }
+    uint64_t cols = 1;
+    for (size_t i = split; i < frame.size(); ++i) cols *= frame[i];
     const uint64_t total = numelOf(frame);
     const uint64_t rows = total / cols;
 
@@ -50,10 +83,10 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
         bool full = true, row = true, col = true;
         for (size_t i = 0; i < frame.size(); ++i) {
             const uint64_t v = i < pad ? 1 : d[i - pad];
-            const bool last = i + 1 == frame.size();
+            const bool trailing = i >= split;
             if (v != frame[i]) full = false;
-            if (last ? v != 1 : v != frame[i]) row = false;
-            if (last ? v != frame[i] : v != 1) col = false;
+            if (trailing ? v != 1 : v != frame[i]) row = false;
+            if (trailing ? v != frame[i] : v != 1) col = false;
         }
         if (full) return THOR_B200_SHAPE_FULL;
         if (row) return THOR_B200_SHAPE_ROW;
@@ -124,12 +157,11 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
             if (classify(in_shape) != THOR_B200_SHAPE_FULL) return {};
             const size_t pad = frame.size() - in_shape.size();
             if (pad != 0) return {};
-            std::vector<bool> reduced(in_shape.size(), nd.reduction_axes.empty());
-            for (uint64_t ax : nd.reduction_axes) reduced[ax] = true;
+            const std::vector<bool> reduced = reducedAxesMask(nd, in_shape.size());
             bool only_last = true, all_but_last = true, all = true;
             for (size_t i = 0; i < in_shape.size(); ++i) {
                 if (in_shape[i] == 1) continue;
-                const bool last = i + 1 == in_shape.size();
+                const bool last = i >= split;  // trailing block = the columns of the frame
                 if (last ? !reduced[i] : reduced[i]) only_last = false;
                 if (last ? reduced[i] : !reduced[i]) all_but_last = false;
                 if (!reduced[i]) all = false;
