@@ -271,6 +271,34 @@ THOR_B200_API int thor_b200_argreduce_launch(const thor_b200_argreduce_plan* pla
 THOR_B200_API void thor_b200_argreduce_plan_destroy(thor_b200_argreduce_plan* plan);
 
 /* ---------------------------------------------------------------------------------------------
+ * Backward of a dense min / max reduction.
+ * Replaces the three steps the reference stamps for it (StampedEquation.h:1143-1179): zero-fill of
+ * the input gradient, the arg reduction that finds each segment's winner, and
+ * launchReduceMinMaxBackwardScatter (Utilities/Expression/ReduceMinMaxBackwardKernel.h:28-34).
+ * input is [outer, reduction, inner] dense, grad_output [outer, inner], grad_input
+ * [outer, reduction, inner]: the winner of every (outer, inner) segment -- arg-reduction rule: NaN
+ * beats numbers, lowest index among equals -- receives the segment's gradient (converted through
+ * fp32), every other element exactly zero.  Two kernels: the arg reduction (reads input once) and a
+ * streaming route kernel (writes grad_input once, reading only winners and gradients).
+ * workspace_bytes covers the arg reduction's workspace plus outer * inner uint32 winners.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct thor_b200_minmax_backward_desc {
+    int32_t is_max;            /* 0 = backward of a min reduction, 1 = of a max reduction */
+    int32_t input_dtype;       /* fp8 / fp16 / bf16 / fp32: dtype of the forward input */
+    int32_t grad_output_dtype; /* fp16 / bf16 / fp32 */
+    int32_t grad_input_dtype;  /* fp16 / bf16 / fp32 */
+    uint64_t outer, reduction, inner;
+} thor_b200_minmax_backward_desc;
+
+typedef struct thor_b200_minmax_backward_plan thor_b200_minmax_backward_plan;
+
+THOR_B200_API int thor_b200_minmax_backward_plan_create(const thor_b200_minmax_backward_desc* desc, thor_b200_minmax_backward_plan** out_plan,
+                                                        size_t* workspace_bytes);
+THOR_B200_API int thor_b200_minmax_backward_launch(const thor_b200_minmax_backward_plan* plan, const void* input, const void* grad_output,
+                                                   void* grad_input, void* workspace, size_t workspace_bytes, void* stream);
+THOR_B200_API void thor_b200_minmax_backward_plan_destroy(thor_b200_minmax_backward_plan* plan);
+
+/* ---------------------------------------------------------------------------------------------
  * Row programs: "elementwise -> row reduction -> elementwise" chains as ONE single-pass kernel.
  * No counterpart in the reference, which makes every reduction a stage boundary
  * (EquationCompiler.cpp:684-688) and therefore runs a composed softmax as 4 kernels and a composed

@@ -87,6 +87,14 @@ def test_row_programs_cover_reductions_over_a_trailing_block_of_axes():
     assert plan.output_spec() == ([128, 32, 64], DT.fp32)
 
 
+def test_backward_of_reduce_max_plans_a_route_stage():
+    eq = ex.compile({"m": (ex.input("x") * 2.0).reduce_max([1])})
+    bwd = eq.compile_backward(["x"]).plan({"x": ((512, 1024), DT.bf16), "__grad_output": ((512, 1), DT.fp32)})
+    assert bwd.stage_kind_names() == ["FusedKernel", "ReduceMinMaxBackward", "FusedKernel"]
+    assert bwd.physical_stage_names()[1] == "minmax_backward"
+    assert bwd.output_spec("x_grad") == ([512, 1024], DT.bf16)
+
+
 def test_argmax_stage_yields_uint32_indices():
     plan = ex.compile(ex.input("x").argmax([1], squeeze_axes=[1])).plan({"x": ((1024, 4096), DT.fp32)})
     assert plan.stage_kind_names() == ["ArgMinMax"]

@@ -236,6 +236,15 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
                 accumulate(nd.lhs, Gk);
                 break;
             }
+            case ExprOp::REDUCE_MIN: case ExprOp::REDUCE_MAX: {
+                if (!wants(nd.lhs)) break;
+                // the whole gradient of a segment goes to its winner (AutoDiff.cpp:5036-5050)
+                if (numelOf(b.shapeOf(G)) != numelOf(b.fwd_shape[k]))
+                    throw std::runtime_error("Thor expressions autodiff: min/max reduction backward needs one gradient value per reduced segment.");
+                accumulate(nd.lhs, Expression::reduceMinMaxBackward(nd.op == ExprOp::REDUCE_MIN ? ExprOp::REDUCE_MIN_BACKWARD : ExprOp::REDUCE_MAX_BACKWARD,
+                                                                   b.forward(nd.lhs), G, nd.reduction_axes, nd.squeeze_axes));
+                break;
+            }
             default:
                 throw std::runtime_error(std::string("Thor expressions autodiff does not support backward for op ") + opName(nd.op) + ".");
         }

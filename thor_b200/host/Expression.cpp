@@ -15,6 +15,7 @@ const char* opName(ExprOp op) {
         case ExprOp::POW: return "pow"; case ExprOp::EQUAL: return "eq"; case ExprOp::NOT_EQUAL: return "ne"; case ExprOp::LESS: return "lt";
         case ExprOp::LESS_EQUAL: return "le"; case ExprOp::GREATER: return "gt"; case ExprOp::GREATER_EQUAL: return "ge";
         case ExprOp::LOGICAL_AND: return "and"; case ExprOp::LOGICAL_OR: return "or"; case ExprOp::LOGICAL_NOT: return "not";
+        case ExprOp::REDUCE_MIN_BACKWARD: return "reduce_min_backward"; case ExprOp::REDUCE_MAX_BACKWARD: return "reduce_max_backward";
         case ExprOp::CAST: return "cast"; case ExprOp::WHERE: return "where"; case ExprOp::NEG: return "neg"; case ExprOp::ABS: return "abs";
         case ExprOp::EXP: return "exp"; case ExprOp::LN: return "ln"; case ExprOp::SQRT: return "sqrt"; case ExprOp::TANH: return "tanh";
         case ExprOp::MIN: return "min"; case ExprOp::MAX: return "max"; case ExprOp::RESHAPE: return "reshape";
@@ -284,6 +285,19 @@ Expression Expression::logSoftmax(SoftmaxMode mode) const {
     return softmaxComposite(*this, SoftmaxAlgorithm::LOG, mode);
 }
 
+Expression Expression::reduceMinMaxBackward(ExprOp op, const Expression& forward_input, const Expression& grad, const std::vector<uint64_t>& reduction_axes,
+                                             const std::vector<uint64_t>& squeeze_axes) {
+    if (!isMinMaxBackwardOp(op)) throw std::invalid_argument("Expression::reduceMinMaxBackward requires REDUCE_MIN_BACKWARD or REDUCE_MAX_BACKWARD");
+    auto g = std::make_shared<PhysicalExpression>(*forward_input.expr_);
+    ExprNode n;
+    n.op = op;
+    n.lhs = forward_input.node_;
+    n.rhs = mergeInto(*g, *grad.expr_, grad.node_);
+    n.reduction_axes = reduction_axes;
+    n.squeeze_axes = squeeze_axes;
+    return Expression(g, appendShared(*g, n));
+}
+
 Outputs Expression::outputs(const std::vector<std::pair<std::string, Expression>>& named_exprs) {
     if (named_exprs.empty()) throw std::invalid_argument("Expression::outputs requires at least one output");
     auto g = std::make_shared<PhysicalExpression>();
@@ -316,7 +330,7 @@ DataType toSupportedComputeDType(ExprOp op, DataType requested) {
     }
     if (op == ExprOp::CAST || isViewOp(op)) return requested;
     if (!isFusionFloat(requested)) throw std::runtime_error(std::string("Unsupported dtype in toSupportedComputeDType: ") + dataTypeName(requested));
-    if (isReductionOp(op)) return DataType::FP32;
+    if (isReductionOp(op) || isMinMaxBackwardOp(op)) return DataType::FP32;
     switch (requested) {
         case DataType::BF16: return DataType::BF16;
         case DataType::FP32: return DataType::FP32;
@@ -336,6 +350,11 @@ DataType resolveNodeOutputDType(const ExprNode& node, const std::vector<ExprNode
         return out;
     }
     if (isBooleanOutputOp(node.op)) return node.output_dtype.value_or(DataType::BOOLEAN);
+    if (isMinMaxBackwardOp(node.op)) {
+        const DataType in = resolved[node.lhs];
+        const bool storable = in == DataType::FP32 || in == DataType::FP16 || in == DataType::BF16;
+        return node.output_dtype.value_or(storable ? in : DataType::FP32);
+    }
     auto isScalarParent = [&](uint32_t p) { return isScalarLeafOp(nodes[p].op); };
     if (node.op == ExprOp::WHERE) {
         if (resolved[node.lhs] != DataType::BOOLEAN) throw std::runtime_error("Where condition must have BOOLEAN dtype");
@@ -433,7 +452,7 @@ void resolveOutputsDTypesInPlace(PhysicalOutputs& outputs, const std::vector<Dat
         DataType requested;
         if (node.op == ExprOp::CAST || isViewOp(node.op)) {
             requested = out;
-        } else if (isArgReductionOp(node.op)) {
+        } else if (isArgReductionOp(node.op) || isMinMaxBackwardOp(node.op)) {
             requested = DataType::FP32;
         } else if (isComparisonOp(node.op)) {
             if (node.compute_dtype.has_value()) requested = *node.compute_dtype;
@@ -469,7 +488,7 @@ void resolveOutputsDTypesInPlace(PhysicalOutputs& outputs, const std::vector<Dat
             if (!explicit_compute[i]) node.compute_dtype = promoteRequiredComputeDType(node.op, *node.compute_dtype, propagated);
             propagated = *node.compute_dtype;
         }
-        if (node.op == ExprOp::CAST) continue;
+        if (node.op == ExprOp::CAST || isMinMaxBackwardOp(node.op)) continue;
         if (isReductionOp(node.op)) {
             const ExprNode& producer = expr.nodes[node.lhs];
             if (producer.compute_dtype.has_value()) seedRequired(required[node.lhs], *producer.compute_dtype);

@@ -26,6 +26,7 @@ enum class ExprOp : uint16_t {
     RESHAPE = 62, UNSQUEEZE = 65, SQUEEZE = 66,
     MIN = 69, MAX, MIN_GRAD_LEFT, MIN_GRAD_RIGHT, MAX_GRAD_LEFT, MAX_GRAD_RIGHT,
     REDUCE_SUM = 83, REDUCE_PROD, REDUCE_MIN, REDUCE_MAX, REDUCE_ARGMIN, REDUCE_ARGMAX,
+    REDUCE_MIN_BACKWARD = 89, REDUCE_MAX_BACKWARD = 90,  // lhs = forward input, rhs = gradient of the reduced value
     REDUCE_AVG = 95, REDUCE_NORM1, REDUCE_NORM2,
 };
 
@@ -35,6 +36,7 @@ inline bool isValueReductionOp(ExprOp op) {
 }
 inline bool isArgReductionOp(ExprOp op) { return op == ExprOp::REDUCE_ARGMIN || op == ExprOp::REDUCE_ARGMAX; }
 inline bool isReductionOp(ExprOp op) { return isValueReductionOp(op) || isArgReductionOp(op); }
+inline bool isMinMaxBackwardOp(ExprOp op) { return op == ExprOp::REDUCE_MIN_BACKWARD || op == ExprOp::REDUCE_MAX_BACKWARD; }
 inline bool isViewOp(ExprOp op) { return op == ExprOp::RESHAPE || op == ExprOp::UNSQUEEZE || op == ExprOp::SQUEEZE; }
 inline bool isScalarLeafOp(ExprOp op) { return op == ExprOp::SCALAR_FP || op == ExprOp::RUNTIME_SCALAR || op == ExprOp::TENSOR_RUNTIME_SCALAR; }
 inline bool isLeafOp(ExprOp op) { return op == ExprOp::INPUT || isScalarLeafOp(op); }
@@ -209,6 +211,11 @@ class Expression {
     THOR_B200_REDUCTION(argmin, REDUCE_ARGMIN)
     THOR_B200_REDUCTION(argmax, REDUCE_ARGMAX)
 #undef THOR_B200_REDUCTION
+    // Gradient of a min / max reduction with respect to its input: the winner of every reduced segment (arg-reduction
+    // rule) receives that segment's gradient, everything else zero (AutoDiff.cpp:5036-5050).  `forward_input` is the
+    // tensor that was reduced, `grad` has the shape of the reduction's result.
+    static Expression reduceMinMaxBackward(ExprOp op, const Expression& forward_input, const Expression& grad, const std::vector<uint64_t>& reduction_axes,
+                                           const std::vector<uint64_t>& squeeze_axes);
     // Request a storage dtype for this node's value (reductions default to FP32, ExpressionDTypeResolution.cpp:777-791).
     Expression withOutputDType(DataType dtype) const;
 

@@ -64,6 +64,10 @@ struct ReducePlanHandle {
     thor_b200_reduce_plan* h = nullptr;
     ~ReducePlanHandle() { thor_b200_reduce_plan_destroy(h); }
 };
+struct MinMaxBackwardPlanHandle {
+    thor_b200_minmax_backward_plan* h = nullptr;
+    ~MinMaxBackwardPlanHandle() { thor_b200_minmax_backward_plan_destroy(h); }
+};
 struct ArgReducePlanHandle {
     thor_b200_argreduce_plan* h = nullptr;
     ~ArgReducePlanHandle() { thor_b200_argreduce_plan_destroy(h); }
@@ -94,6 +98,8 @@ std::vector<std::vector<uint64_t>> inferNodeShapes(const PhysicalExpression& exp
             }
             if (out.empty()) out.push_back(1);
             shape[k] = out;
+        } else if (isMinMaxBackwardOp(n.op)) {
+            shape[k] = shape[n.lhs];
         } else if (n.op == ExprOp::RESHAPE) {
             if (numelOf(n.reshape_dims) != numelOf(shape[n.lhs])) throw std::logic_error("reshape changes the element count");
             shape[k] = n.reshape_dims;
@@ -143,6 +149,8 @@ struct PhysicalStage {
     // Reduction / ArgMinMax
     std::shared_ptr<ReducePlanHandle> reduce;
     std::shared_ptr<ArgReducePlanHandle> argreduce;
+    std::shared_ptr<MinMaxBackwardPlanHandle> minmax_backward;
+    const void* in2 = nullptr;  // ReduceMinMaxBackward: gradient of the reduced value
     const void* in = nullptr;
     void* out = nullptr;
     Tensor workspace;
@@ -181,6 +189,10 @@ void StampedExecutionPlan::runOn(const Stream& stream) {
             case StageKind::ArgMinMax:
                 check(thor_b200_argreduce_launch(s.argreduce->h, s.in, nullptr, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream.handle),
                       "StampedExecutionPlan::run arg reduction");
+                break;
+            case StageKind::ReduceMinMaxBackward:
+                check(thor_b200_minmax_backward_launch(s.minmax_backward->h, s.in, s.in2, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream.handle),
+                      "StampedExecutionPlan::run min/max backward");
                 break;
             case StageKind::FusedRows: s.custom_launch(stream.handle); break;
             case StageKind::View: break;
@@ -288,13 +300,14 @@ struct Planner {
             if (isBoundary(k)) {
                 lv += 1;  // a boundary op consumes a tensor that exists after level lv's fused stages
                 if (isElementwise(nd.lhs)) materialize[nd.lhs] = true;
+                if (isMinMaxBackwardOp(nd.op) && isElementwise(nd.rhs)) materialize[nd.rhs] = true;
             }
             level[k] = lv;
         }
         for (const auto& o : outs)
             if (isElementwise(o.node_idx)) materialize[o.node_idx] = true;
     }
-    bool isBoundary(size_t k) const { return isReductionOp(g.nodes[k].op) || isViewOp(g.nodes[k].op); }
+    bool isBoundary(size_t k) const { return isReductionOp(g.nodes[k].op) || isViewOp(g.nodes[k].op) || isMinMaxBackwardOp(g.nodes[k].op); }
     bool isElementwise(size_t k) const { return !isBoundary(k) && !isLeafOp(g.nodes[k].op); }
 };
 
@@ -407,12 +420,16 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
         for (uint32_t k = 0; k < g.nodes.size(); ++k) {
             if (!plan.needed[k] || !plan.isBoundary(k) || plan.level[k] != lv + 1) continue;
             const ExprOp op = g.nodes[k].op;
-            logical.push_back({isViewOp(op) ? StageKind::View : (isArgReductionOp(op) ? StageKind::ArgMinMax : StageKind::Reduction), {k}});
+            logical.push_back({isViewOp(op) ? StageKind::View
+                               : isArgReductionOp(op) ? StageKind::ArgMinMax
+                               : isMinMaxBackwardOp(op) ? StageKind::ReduceMinMaxBackward : StageKind::Reduction,
+                               {k}});
         }
     }
     for (const auto& ls : logical) {
         impl->logical_stage_names.push_back(ls.kind == StageKind::FusedKernel ? "FusedKernel" : ls.kind == StageKind::Reduction ? "Reduction"
-                                            : ls.kind == StageKind::ArgMinMax ? "ArgMinMax" : "View");
+                                            : ls.kind == StageKind::ArgMinMax ? "ArgMinMax"
+                                            : ls.kind == StageKind::ReduceMinMaxBackward ? "ReduceMinMaxBackward" : "View");
     }
 
     // Optional physical fusion of row-reduction chains (softmax / LayerNorm class).
@@ -462,7 +479,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             if (output_name_of.count(k)) impl->outputs[output_name_of[k]] = node_tensor[k];
             continue;
         }
-        if (ls.kind == StageKind::Reduction || ls.kind == StageKind::ArgMinMax) {
+        if (ls.kind == StageKind::Reduction || ls.kind == StageKind::ArgMinMax || ls.kind == StageKind::ReduceMinMaxBackward) {
             const uint32_t k = ls.nodes[0];
             const ExprNode& nd = g.nodes[k];
             const Tensor& src = node_tensor[nd.lhs];
@@ -495,7 +512,26 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             st.out = dst.getMemPtr();
             impl->keep_alive.push_back(src);
             size_t ws = 1;
-            if (ls.kind == StageKind::Reduction) {
+            if (ls.kind == StageKind::ReduceMinMaxBackward) {
+                const Tensor& grad = node_tensor[nd.rhs];
+                if (!grad.isInitialized()) throw std::logic_error("FusedEquation::stamp: min/max backward gradient is not materialised");
+                if (grad.getTotalNumElements() != outer * inner)
+                    throw std::logic_error("FusedEquation::stamp: min/max backward needs a gradient with one value per reduced segment");
+                thor_b200_minmax_backward_desc d{};
+                d.is_max = nd.op == ExprOp::REDUCE_MAX_BACKWARD ? 1 : 0;
+                d.input_dtype = static_cast<int>(src.getDataType());
+                d.grad_output_dtype = static_cast<int>(grad.getDataType());
+                d.grad_input_dtype = static_cast<int>(*nd.output_dtype);
+                d.outer = outer;
+                d.reduction = red;
+                d.inner = inner;
+                st.minmax_backward = std::make_shared<MinMaxBackwardPlanHandle>();
+                check(thor_b200_minmax_backward_plan_create(&d, &st.minmax_backward->h, &ws), "FusedEquation::stamp min/max backward plan");
+                st.physical_name = "minmax_backward";
+                st.launches = 2;
+                st.in2 = grad.getMemPtr();
+                impl->keep_alive.push_back(grad);
+            } else if (ls.kind == StageKind::Reduction) {
                 thor_b200_reduce_desc d{};
                 d.op = reduceOpFor(nd.op);
                 d.input_dtype = static_cast<int>(src.getDataType());

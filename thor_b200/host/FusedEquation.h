@@ -32,7 +32,7 @@ struct RuntimeInputValue {
     RuntimeInputValue(double v) : scalar(static_cast<float>(v)), is_scalar(true) {}  // NOLINT
 };
 
-enum class StageKind { FusedKernel, Reduction, ArgMinMax, View, FusedRows };
+enum class StageKind { FusedKernel, Reduction, ArgMinMax, View, FusedRows, ReduceMinMaxBackward };
 
 struct FusedEquationOptions {
     bool use_fast_math = false;

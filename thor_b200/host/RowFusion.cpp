@@ -105,7 +105,7 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
     for (uint32_t k = 0; k < n; ++k) {
         if (!needed[k]) continue;
         const ExprNode& nd = g.nodes[k];
-        if (isArgReductionOp(nd.op)) return {};
+        if (isArgReductionOp(nd.op) || isMinMaxBackwardOp(nd.op)) return {};
         if (isViewOp(nd.op)) {
             // squeeze / unsqueeze / reshape of a value whose class does not change is an alias
             const int a = classify(ctx.shape[nd.lhs]), b = classify(ctx.shape[k]);

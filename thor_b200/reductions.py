@@ -154,3 +154,47 @@ class CubArgReduction:
         value = torch.empty(out_shape, dtype=input_t.dtype, device=input_t.device) if self.produce_value else None
         workspace = torch.empty(max(16, ws.value), dtype=torch.uint8, device=input_t.device)
         return StampedCubArgReduction(plan, input_t, index, value, workspace, ws.value, stream)
+
+
+# ---- backward of dense min / max reductions ---------------------------------------------------------
+class _MinMaxBackwardDesc(C.Structure):
+    _fields_ = [("is_max", C.c_int32), ("input_dtype", C.c_int32), ("grad_output_dtype", C.c_int32), ("grad_input_dtype", C.c_int32),
+                ("outer", C.c_uint64), ("reduction", C.c_uint64), ("inner", C.c_uint64)]
+
+
+_lib.thor_b200_minmax_backward_plan_create.argtypes = [C.POINTER(_MinMaxBackwardDesc), C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
+_lib.thor_b200_minmax_backward_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+_lib.thor_b200_minmax_backward_plan_destroy.argtypes = [C.c_void_p]
+_lib.thor_b200_minmax_backward_plan_destroy.restype = None
+
+
+class ReduceMinMaxBackward:
+    """Routes the gradient of a min / max reduction over `[outer, reduction, inner]` to each segment's winner
+    (the reference stamps a zero fill, an arg reduction and launchReduceMinMaxBackwardScatter for this,
+    Utilities/Expression/ReduceMinMaxBackwardKernel.h:28-34)."""
+
+    def __init__(self, is_max: bool, input_t: torch.Tensor, grad_output: torch.Tensor, outer: int, reduction: int, inner: int,
+                 grad_input_dtype: Optional[DataType] = None, stream=None):
+        if input_t.numel() != outer * reduction * inner or grad_output.numel() != outer * inner:
+            raise _native.ThorB200InvalidArgument("ReduceMinMaxBackward: tensor sizes do not match [outer, reduction, inner]")
+        self._input, self._grad_output, self._stream = input_t, grad_output, stream
+        gi = grad_input_dtype if grad_input_dtype is not None else from_torch(input_t.dtype)
+        d = _MinMaxBackwardDesc(int(bool(is_max)), int(from_torch(input_t.dtype)), int(from_torch(grad_output.dtype)), int(gi), outer, reduction, inner)
+        self._plan = C.c_void_p()
+        ws = C.c_size_t()
+        _native.check(_lib.thor_b200_minmax_backward_plan_create(C.byref(d), C.byref(self._plan), C.byref(ws)))
+        self._ws_bytes = ws.value
+        self._workspace = torch.empty(max(1, ws.value), dtype=torch.uint8, device=input_t.device)
+        self.grad_input = torch.empty(input_t.shape, dtype=to_torch(gi), device=input_t.device)
+
+    def __del__(self):
+        try:
+            if self._plan:
+                _lib.thor_b200_minmax_backward_plan_destroy(self._plan)
+        except Exception:
+            pass
+
+    def run(self) -> torch.Tensor:
+        _native.check(_lib.thor_b200_minmax_backward_launch(self._plan, self._input.data_ptr(), self._grad_output.data_ptr(), self.grad_input.data_ptr(),
+                                                            self._workspace.data_ptr(), self._ws_bytes, _native.stream_handle(self._stream)))
+        return self.grad_input
