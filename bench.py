@@ -247,6 +247,35 @@ class C1Cast(Workload):
     def e2e_bytes(self): return self.N * 4, self.N * 2
 
 
+class C1CastReferenceGpu(C1Cast):
+    """Baseline, not product: the reference's own TypeConverterKernels.cu, compiled unmodified for sm_100a into
+    oracle/_ref, on the same buffers and timing protocol as C1 (only listed when that build is present)."""
+    name = "c1_cast_fp32_fp16_reference_gpu_kernels"
+    description = "the reference's TypeConverter::gpuConvertType fp32->fp16, n=2^24 (baseline beside c1)"
+
+    def setup(self):
+        import torch
+
+        import oracle
+        from thor_b200.workloads import cast_input
+
+        if oracle.reference_gpu_cast_lib() is None:
+            raise RuntimeError("oracle/_ref/libthor_ref_gpu_cast.so is not built")
+        self.n = self.N
+        host = torch.from_numpy(cast_input(self.n, seed=self.dist.rank))
+        k = self.n_sets(self.algorithmic_bytes())
+        pad = 64  # the reference's kernels may read a few elements past n (it pads every tensor)
+        self.sets = []
+        for _ in range(k):
+            src = torch.zeros(self.n + pad, dtype=torch.float32, device="cuda")
+            src[: self.n] = host.cuda()
+            self.sets.append((src, torch.empty(self.n + pad, dtype=torch.float16, device="cuda")))
+        stream = torch.cuda.current_stream().cuda_stream
+        self.convert = lambda s, d: oracle.reference_gpu_cast(s.data_ptr(), d.data_ptr(), oracle.FP32, oracle.FP16, self.n, stream)
+        self.launches_per_step = 1
+        self.kernel_kind = ["reference convertOutOfPlaceKernel"]
+
+
 class C2FusedExpr(Workload):
     name = "c2_fused_relu_axb_sigmoid"
     description = "y = relu(a*x + b) * sigmoid(z): x,z,y fp16 [8192,8192] per GPU, a fp16 [8192] per column, b fp32 runtime scalar 0.1"
@@ -480,7 +509,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
-             "c5_bwd": C5LayerNormBwd}
+             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu}
 
 
 # ---------------------------------------------------------------------------------------------------------

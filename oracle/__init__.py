@@ -74,6 +74,31 @@ def reference_cast_lib():
     return _ref
 
 
+_ref_gpu = None
+
+
+def reference_gpu_cast_lib():
+    """The reference's own GPU cast kernels (TypeConverter::gpuConvertType), or None when oracle/_ref holds no build of them."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        path = HERE / "_ref" / "libthor_ref_gpu_cast.so"
+        if not path.exists():
+            return None
+        _ref_gpu = ctypes.CDLL(str(path))
+        _ref_gpu.thor_ref_gpu_convert.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_long, ctypes.c_void_p]
+        _ref_gpu.thor_ref_gpu_convert.restype = ctypes.c_int
+    return _ref_gpu
+
+
+def reference_gpu_cast(src_ptr: int, dst_ptr: int, src_dtype: int, dst_dtype: int, n: int, stream: int = 0) -> None:
+    """Launches the reference's GPU conversion of n elements between two device buffers (asynchronous on `stream`).
+    The reference's kernels may read up to 7 elements past n (they rely on padded tensors): give it padded buffers."""
+    ref = reference_gpu_cast_lib()
+    assert ref is not None, "oracle/_ref/libthor_ref_gpu_cast.so has not been built"
+    rc = ref.thor_ref_gpu_convert(ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr), src_dtype, dst_dtype, n, ctypes.c_void_p(stream))
+    assert rc == 0, f"reference GPU conversion failed ({rc})"
+
+
 def _ptr(a: np.ndarray) -> ctypes.c_void_p:
     return ctypes.c_void_p(a.ctypes.data)
 

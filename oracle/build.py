@@ -4,6 +4,9 @@
 * ``_ref/libthor_ref_cast.so``   — the REFERENCE's own CPU cast path, compiled from the reference
   checkout where it lies (only when that checkout is present; the output is git-ignored and is
   carried to the GPU machine as a built file).  Nothing is copied out of the reference tree.
+* ``_ref/libthor_ref_gpu_cast.so`` — the REFERENCE's own GPU cast kernels (TypeConverterKernels.cu,
+  nvcc for sm_100a, about 90 s), same rules; the parity tests compare against it bit for bit and the
+  benchmark times it beside our kernel.
 
 Run as ``python oracle/build.py``.  The reference checkout is looked up in
 ``$THOR_REFERENCE_DIR`` (default: ``/root/reference``).
@@ -78,8 +81,37 @@ def build_reference_cast(force: bool = False) -> Path | None:
     return out
 
 
+def build_reference_gpu_cast(force: bool = False) -> Path | None:
+    """Compile the reference's GPU TypeConverter kernels into _ref/; None when they cannot be built here."""
+    out = REF_OUT / "libthor_ref_gpu_cast.so"
+    src = HERE / "ref_gpu_cast.cu"
+    ref_src = REFERENCE_DIR / "Utilities/TensorOperations/DataTypeConversions/TypeConverterKernels.cu"
+    nvcc = shutil.which("nvcc") or str(Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "bin" / "nvcc")
+    if not ref_src.exists() or not Path(nvcc).exists():
+        return out if out.exists() else None
+    REF_OUT.mkdir(exist_ok=True)
+    if not force and not _stale(out, [src, ref_src]):
+        return out
+    verdir = REF_OUT / "generated"
+    verdir.mkdir(exist_ok=True)
+    (verdir / "ThorVersion.h").write_text('#pragma once\n#define THOR_VERSION "0.0.33"\n#define THOR_GIT_VERSION "unknown"\n')
+    cmd = [nvcc, "-std=c++20", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+           "-Xlinker", "-z,defs", "-I", str(REFERENCE_DIR), "-I", str(verdir)]
+    for d in _site_include_dirs():
+        cmd += ["-I", str(d)]
+    cmd += [str(src), "-o", str(out)]
+    _run(cmd)
+    return out
+
+
 def build_all(force: bool = False) -> dict:
     result = {"oracle": str(build_oracle(force))}
+    try:
+        ref_gpu = build_reference_gpu_cast(force)
+        result["reference_gpu_cast"] = str(ref_gpu) if ref_gpu else None
+    except RuntimeError as exc:
+        result["reference_gpu_cast"] = None
+        result["reference_gpu_cast_error"] = str(exc)[-2000:]
     try:
         ref = build_reference_cast(force)
         result["reference_cast"] = str(ref) if ref else None

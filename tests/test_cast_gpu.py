@@ -138,6 +138,44 @@ def test_in_place_between_element_sizes_matches_out_of_place(src, dst, n):
     assert np.array_equal(want.cpu().numpy().view(_NP[dst]), o.cast(x, src, dst))
 
 
+@pytest.mark.skipif(o.reference_gpu_cast_lib() is None, reason="the reference's GPU cast kernels are not built (oracle/_ref)")
+@pytest.mark.parametrize("src,dst", [(o.FP32, o.FP16), (o.FP32, o.BF16), (o.FP16, o.FP32), (o.BF16, o.FP16), (o.FP32, o.FP8_E4M3), (o.FP16, o.FP8_E5M2),
+                                     (o.FP32, o.INT32), (o.INT32, o.FP16), (o.UINT8, o.FP32), (o.FP32, o.BOOLEAN)])
+def test_bit_identical_to_the_reference_gpu_kernels(src, dst):
+    """Our kernel against TypeConverter::gpuConvertType itself (the reference's TypeConverterKernels.cu compiled
+    for sm_100a), same device buffers, compared bit for bit."""
+    n = (1 << 20) + 8 * 37
+    if src == o.FP32:
+        x = cast_input(n, seed=5)
+        if dst == o.INT32:
+            x = np.clip(np.nan_to_num(x, nan=0.0, posinf=1e6, neginf=-1e6), -1e6, 1e6).astype(np.float32)
+        raw = x
+    elif src in (o.FP16, o.BF16):
+        raw = o.cast(cast_input(n, seed=6), o.FP32, src)
+    elif src == o.INT32:
+        raw = np.random.default_rng(7).integers(-70000, 70000, n).astype(np.int32)
+    else:
+        raw = np.random.default_rng(8).integers(0, 256, n).astype(np.uint8)
+    pad = 64
+    s_bytes, d_bytes = raw.itemsize, np.dtype(o.STORAGE[dst]).itemsize
+    src_d = torch.zeros((n + pad) * s_bytes, dtype=torch.uint8, device="cuda")
+    src_d[: n * s_bytes] = torch.from_numpy(raw.view(np.uint8)).cuda()
+    ours = torch.zeros((n + pad) * d_bytes, dtype=torch.uint8, device="cuda")
+    theirs = torch.zeros((n + pad) * d_bytes, dtype=torch.uint8, device="cuda")
+    TypeConverter.convert_type_raw(src_d.data_ptr(), ours.data_ptr(), DataType(src), DataType(dst), n)
+    o.reference_gpu_cast(src_d.data_ptr(), theirs.data_ptr(), src, dst, n, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    a, b = ours[: n * d_bytes].cpu().numpy(), theirs[: n * d_bytes].cpu().numpy()
+    if dst in (o.FP16, o.BF16, o.FP32) and src in o.FLOAT_DTYPES:
+        # NaN payloads are not pinned by the reference's tests: compare NaN-ness there, bits everywhere else
+        av, bv = o.to_float64(a.view(o.STORAGE[dst]), dst), o.to_float64(b.view(o.STORAGE[dst]), dst)
+        assert np.array_equal(np.isnan(av), np.isnan(bv))
+        keep = np.repeat(~np.isnan(av), d_bytes)
+        assert np.array_equal(a[keep], b[keep])
+    else:
+        assert np.array_equal(a, b)
+
+
 def test_unaligned_views_use_the_scalar_path():
     x = cast_input(5000, seed=11)
     d = torch.from_numpy(x).cuda()
