@@ -187,7 +187,7 @@ std::string analyse(Program& p) {
 // only when the reduction's depth drops.  The value changes by fp32 re-association only.
 struct LinearTerm {
     std::vector<std::pair<uint32_t, bool>> coeffs;  // row-constant factors (node, is divisor)
-    uint32_t atom;                                  // row-varying factor
+    uint32_t atom;                                  // row-varying factor; THOR_B200_NO_NODE: the constant 1
     bool negative;
 };
 
@@ -198,9 +198,20 @@ void decomposeLinear(const Program& p, uint32_t k, std::vector<std::pair<uint32_
     auto rowConst = [&](uint32_t i) { return p.shape[i] == ROW || p.shape[i] == SCALAR; };
     if (p.shape[k] == FULL && isF32Node(nd)) {
         if (nd.op == THOR_B200_OP_NEG) return decomposeLinear(p, nd.lhs, coeffs, !negative, out);
-        if ((nd.op == THOR_B200_OP_ADD || nd.op == THOR_B200_OP_SUB) && !rowConst(nd.lhs) && !rowConst(nd.rhs)) {
-            decomposeLinear(p, nd.lhs, coeffs, negative, out);
-            decomposeLinear(p, nd.rhs, coeffs, nd.op == THOR_B200_OP_SUB ? !negative : negative, out);
+        if (nd.op == THOR_B200_OP_ADD || nd.op == THOR_B200_OP_SUB) {
+            // a row-constant operand c contributes c once per column: a term whose row-varying factor is 1
+            const bool rhs_negative = nd.op == THOR_B200_OP_SUB ? !negative : negative;
+            for (int side = 0; side < 2; ++side) {
+                const uint32_t operand = side == 0 ? nd.lhs : nd.rhs;
+                const bool neg = side == 0 ? negative : rhs_negative;
+                if (rowConst(operand)) {
+                    auto with = coeffs;
+                    with.push_back({operand, false});
+                    out.push_back({with, THOR_B200_NO_NODE, neg});
+                } else {
+                    decomposeLinear(p, operand, coeffs, neg, out);
+                }
+            }
             return;
         }
         if (nd.op == THOR_B200_OP_MUL && (rowConst(nd.lhs) != rowConst(nd.rhs))) {
@@ -244,7 +255,7 @@ bool hoistLinearRowSums(Program& p) {
         int new_depth = 0;
         bool any_coeff = false;
         for (const auto& t : terms) {
-            new_depth = std::max(new_depth, p.depth[t.atom] + 1);
+            if (t.atom != THOR_B200_NO_NODE) new_depth = std::max(new_depth, p.depth[t.atom] + 1);
             for (const auto& c : t.coeffs) {
                 new_depth = std::max(new_depth, p.depth[c.first]);
                 any_coeff = true;
@@ -254,15 +265,36 @@ bool hoistLinearRowSums(Program& p) {
             // value = sum over terms of (+-) reduce(atom) * c1 * c2 / d1 ...
             uint32_t total = THOR_B200_NO_NODE;
             std::vector<std::pair<uint32_t, uint32_t>> reduced;  // atom (new index) -> reduce node
+            auto scalar = [&](double value) {
+                thor_b200_expr_node sn = f32(THOR_B200_OP_SCALAR_FP, THOR_B200_NO_NODE, THOR_B200_NO_NODE);
+                sn.scalar_fp = value;
+                return push(sn);
+            };
+            const double n_cols = static_cast<double>(p.cols);
             for (const auto& t : terms) {
-                const uint32_t atom = remap[t.atom];
                 uint32_t r = THOR_B200_NO_NODE;
-                for (const auto& pr : reduced)
-                    if (pr.first == atom) r = pr.second;
-                if (r == THOR_B200_NO_NODE) {
-                    thor_b200_expr_node rn = f32(nd.op, atom, THOR_B200_NO_NODE);
-                    rn.input_slot = 0;
-                    r = push(rn);
+                if (t.atom == THOR_B200_NO_NODE) {
+                    // sum of the constant 1 over the row: cols for a sum, 1 for a mean
+                    r = scalar(nd.op == THOR_B200_OP_REDUCE_SUM ? n_cols : 1.0);
+                } else {
+                    const uint32_t atom = remap[t.atom];
+                    for (const auto& pr : reduced)
+                        if (pr.first == atom) r = pr.second;
+                    if (r == THOR_B200_NO_NODE) {
+                        // a sum or a mean of the same values that the program already computes serves, scaled by the row length
+                        for (uint32_t e = 0; e < out_nodes.size() && r == THOR_B200_NO_NODE; ++e) {
+                            const auto& en = out_nodes[e];
+                            if (!isReduce(en.op) || en.input_slot != 0 || en.lhs != atom || en.output_dtype != THOR_B200_FP32) continue;
+                            if (en.op == nd.op) r = e;
+                            else if (en.op == THOR_B200_OP_REDUCE_AVG && nd.op == THOR_B200_OP_REDUCE_SUM) r = push(f32(THOR_B200_OP_MUL, e, scalar(n_cols)));
+                            else if (en.op == THOR_B200_OP_REDUCE_SUM && nd.op == THOR_B200_OP_REDUCE_AVG) r = push(f32(THOR_B200_OP_DIV, e, scalar(n_cols)));
+                        }
+                    }
+                    if (r == THOR_B200_NO_NODE) {
+                        thor_b200_expr_node rn = f32(nd.op, atom, THOR_B200_NO_NODE);
+                        rn.input_slot = 0;
+                        r = push(rn);
+                    }
                     reduced.push_back({atom, r});
                 }
                 uint32_t v = r;
