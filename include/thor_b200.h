@@ -271,6 +271,30 @@ THOR_B200_API int thor_b200_argreduce_launch(const thor_b200_argreduce_plan* pla
 THOR_B200_API void thor_b200_argreduce_plan_destroy(thor_b200_argreduce_plan* plan);
 
 /* ---------------------------------------------------------------------------------------------
+ * Reductions over axes that are not adjacent (the reference's StridedFixedSegment path:
+ * CubReductionOperation.cuh:2946-2958, 3038-3050; index map CubReductionIndexing.cuh:33-53;
+ * arg variant CubArgReductionOperation.cuh:1119-1178).  input is a dense row-major tensor of
+ * `rank` dims; output is dense over the kept axes in their order.  Stateless: no plan, no
+ * workspace, one kernel, the same numeric rules as the planned reductions (fp32 accumulation in
+ * a fixed order, NaN-propagating min / max; arg: NaN wins, lowest flattened index of the reduced
+ * axes in row-major order among equals).  Geometries that reduce one adjacent block of axes are
+ * accepted too, but the planned reductions above are the fast path for those.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct thor_b200_strided_reduce_desc {
+    int32_t op;           /* thor_b200_reduce_op; ignored for arg reductions */
+    int32_t arg_op;       /* -1: value reduction, 0: argmin, 1: argmax */
+    int32_t input_dtype;  /* fp8 / fp16 / bf16 / fp32 */
+    int32_t output_dtype; /* value reductions: fp8 / fp16 / bf16 / fp32; arg reductions: uint32 or uint64 */
+    uint32_t rank;        /* 1..8 */
+    uint32_t reserved;
+    uint64_t dims[THOR_B200_MAX_RANK];
+    uint8_t reduced[THOR_B200_MAX_RANK]; /* 1 = the axis is reduced */
+} thor_b200_strided_reduce_desc;
+
+THOR_B200_API int thor_b200_strided_reduce_launch(const thor_b200_strided_reduce_desc* desc, const void* input, void* output, float output_scale,
+                                                  void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Backward of a dense min / max reduction.
  * Replaces the three steps the reference stamps for it (StampedEquation.h:1143-1179): zero-fill of
  * the input gradient, the arg reduction that finds each segment's winner, and

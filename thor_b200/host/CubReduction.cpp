@@ -86,6 +86,22 @@ CubReductionGeometry CubReduction::analyzeGeometry(const std::vector<uint64_t>& 
     return g;
 }
 
+namespace {
+thor_b200_strided_reduce_desc stridedDesc(const Tensor& input, const std::vector<uint32_t>& axes, int op, int arg_op, DataType output_dtype) {
+    thor_b200_strided_reduce_desc d{};
+    const auto& dims = input.getDimensions();
+    if (dims.size() > THOR_B200_MAX_RANK) throw std::invalid_argument("reductions over non-adjacent axes support rank <= 8");
+    d.op = op;
+    d.arg_op = arg_op;
+    d.input_dtype = static_cast<int>(input.getDataType());
+    d.output_dtype = static_cast<int>(output_dtype);
+    d.rank = static_cast<uint32_t>(dims.size());
+    for (size_t i = 0; i < dims.size(); ++i) d.dims[i] = dims[i];
+    for (uint32_t ax : axes) d.reduced[ax] = 1;
+    return d;
+}
+}  // namespace
+
 StampedCubReduction CubReduction::stamp(const Tensor& input, const Stream& stream) const {
     const CubReductionGeometry g = analyzeGeometry(input.getDimensions(), axes_);
     Tensor out = Tensor::allocate(resolveOutputDataType(input.getDataType()), g.output_dimensions, input.getGpuNum());
@@ -96,9 +112,15 @@ StampedCubReduction CubReduction::stamp(const Tensor& input, const Tensor& outpu
     if (!input.isInitialized() || !output.isInitialized()) throw std::invalid_argument("CubReduction::stamp requires initialized tensors.");
     StampedCubReduction s;
     s.geometry_ = analyzeGeometry(input.getDimensions(), axes_);
-    if (s.geometry_.path == CubReductionPath::StridedFixedSegment)
-        throw std::logic_error("CubReduction::stamp: reductions over non-adjacent axes (StridedFixedSegment) are not provided by this build");
     if (output.getTotalNumElements() != s.geometry_.output_elements) throw std::invalid_argument("CubReduction::stamp output has the wrong number of elements.");
+    if (s.geometry_.path == CubReductionPath::StridedFixedSegment) {
+        s.strided_ = std::make_shared<thor_b200_strided_reduce_desc>(stridedDesc(input, axes_, static_cast<int>(op_), -1, output.getDataType()));
+        s.input_ = input;
+        s.output_ = output;
+        s.stream_ = stream;
+        s.output_scale_ = output_scale_;
+        return s;
+    }
     thor_b200_reduce_desc d{};
     d.op = static_cast<int>(op_);
     d.input_dtype = static_cast<int>(input.getDataType());
@@ -122,12 +144,16 @@ StampedCubReduction CubReduction::stamp(const Tensor& input, const Tensor& outpu
 void StampedCubReduction::run() { runOn(stream_, output_scale_); }
 
 void StampedCubReduction::runOn(const Stream& stream, float output_scale) {
+    if (strided_) {
+        check(thor_b200_strided_reduce_launch(strided_.get(), input_.getMemPtr(), output_.getMemPtr(), output_scale, stream.handle), "StampedCubReduction::run");
+        return;
+    }
     check(thor_b200_reduce_launch(plan_.get(), input_.getMemPtr(), output_.getMemPtr(), workspace_.getMemPtr(), workspace_bytes_, output_scale,
                                   stream.handle),
           "StampedCubReduction::run");
 }
 
-const char* StampedCubReduction::kernelKind() const { return thor_b200_reduce_plan_kind(plan_.get()); }
+const char* StampedCubReduction::kernelKind() const { return strided_ ? "strided" : thor_b200_reduce_plan_kind(plan_.get()); }
 
 CubArgReduction::CubArgReduction(CubArgReductionOp op, std::vector<uint32_t> axes, CubArgReductionOutputOptions options)
     : op_(op), axes_(std::move(axes)), options_(options) {
@@ -141,9 +167,23 @@ CubArgReduction::CubArgReduction(CubArgReductionOp op, std::vector<uint32_t> axe
 
 StampedCubArgReduction CubArgReduction::stamp(const Tensor& input, const Stream& stream) const {
     const CubReductionGeometry g = CubReduction::analyzeGeometry(input.getDimensions(), axes_);
-    if (g.path == CubReductionPath::StridedFixedSegment)
-        throw std::logic_error("CubArgReduction::stamp: reductions over non-adjacent axes are not provided by this build");
     StampedCubArgReduction s;
+    if (g.path == CubReductionPath::StridedFixedSegment) {
+        const DataType vdt = options_.value_output_dtype.value_or(input.getDataType());
+        s.input_ = input;
+        s.stream_ = stream;
+        if (options_.produce_index) {
+            s.index_ = Tensor::allocate(options_.index_output_dtype, g.output_dimensions, input.getGpuNum());
+            s.strided_index_ = std::make_shared<thor_b200_strided_reduce_desc>(stridedDesc(input, axes_, 0, static_cast<int>(op_), options_.index_output_dtype));
+        }
+        if (options_.produce_value) {
+            // the winner's value is the NaN-propagating min / max of the segment
+            s.value_ = Tensor::allocate(vdt, g.output_dimensions, input.getGpuNum());
+            s.strided_value_ = std::make_shared<thor_b200_strided_reduce_desc>(
+                stridedDesc(input, axes_, op_ == CubArgReductionOp::ArgMax ? THOR_B200_REDUCE_MAX : THOR_B200_REDUCE_MIN, -1, vdt));
+        }
+        return s;
+    }
     thor_b200_argreduce_desc d{};
     d.op = static_cast<int>(op_);
     d.input_dtype = static_cast<int>(input.getDataType());
@@ -167,6 +207,11 @@ StampedCubArgReduction CubArgReduction::stamp(const Tensor& input, const Stream&
 }
 
 void StampedCubArgReduction::run() {
+    if (strided_index_ || strided_value_) {
+        if (strided_index_) check(thor_b200_strided_reduce_launch(strided_index_.get(), input_.getMemPtr(), index_.getMemPtr(), 1.0f, stream_.handle), "StampedCubArgReduction::run");
+        if (strided_value_) check(thor_b200_strided_reduce_launch(strided_value_.get(), input_.getMemPtr(), value_.getMemPtr(), 1.0f, stream_.handle), "StampedCubArgReduction::run");
+        return;
+    }
     check(thor_b200_argreduce_launch(plan_.get(), input_.getMemPtr(), value_.getMemPtr(), index_.getMemPtr(), workspace_.getMemPtr(), workspace_bytes_,
                                      stream_.handle),
           "StampedCubArgReduction::run");

@@ -11,6 +11,7 @@
 
 struct thor_b200_reduce_plan;
 struct thor_b200_argreduce_plan;
+struct thor_b200_strided_reduce_desc;
 
 namespace ThorB200 {
 
@@ -42,6 +43,7 @@ class StampedCubReduction {
    private:
     friend class CubReduction;
     std::shared_ptr<thor_b200_reduce_plan> plan_;
+    std::shared_ptr<thor_b200_strided_reduce_desc> strided_;  // StridedFixedSegment path: stateless launch, no plan
     Tensor input_, output_, workspace_;
     size_t workspace_bytes_ = 1;
     Stream stream_;
@@ -85,6 +87,7 @@ class StampedCubArgReduction {
    private:
     friend class CubArgReduction;
     std::shared_ptr<thor_b200_argreduce_plan> plan_;
+    std::shared_ptr<thor_b200_strided_reduce_desc> strided_index_, strided_value_;  // StridedFixedSegment path
     Tensor input_, index_, value_, workspace_;
     size_t workspace_bytes_ = 1;
     Stream stream_;

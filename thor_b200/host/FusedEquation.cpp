@@ -183,10 +183,18 @@ void StampedExecutionPlan::runOn(const Stream& stream) {
                       "StampedExecutionPlan::run fused stage");
                 break;
             case StageKind::Reduction:
+                if (s.custom_launch) {
+                    s.custom_launch(stream.handle);
+                    break;
+                }
                 check(thor_b200_reduce_launch(s.reduce->h, s.in, s.out, s.workspace.getMemPtr(), s.workspace_bytes, 1.0f, stream.handle),
                       "StampedExecutionPlan::run reduction");
                 break;
             case StageKind::ArgMinMax:
+                if (s.custom_launch) {
+                    s.custom_launch(stream.handle);
+                    break;
+                }
                 check(thor_b200_argreduce_launch(s.argreduce->h, s.in, nullptr, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream.handle),
                       "StampedExecutionPlan::run arg reduction");
                 break;
@@ -486,13 +494,15 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             if (!src.isInitialized()) throw std::logic_error("FusedEquation::stamp: reduction input is not materialised");
             const auto& in_shape = shape[nd.lhs];
             const std::vector<bool> reduced = reducedAxesMask(nd, in_shape.size());
-            // [outer, reduction, inner] needs the non-singleton reduced axes to form one contiguous block
+            // [outer, reduction, inner] needs the non-singleton reduced axes to form one contiguous block;
+            // anything else takes the strided kernels (the reference's StridedFixedSegment path)
             uint64_t outer = 1, red = 1, inner = 1;
             int phase = 0;
+            bool strided = false;
             for (size_t i = 0; i < in_shape.size(); ++i) {
                 if (in_shape[i] == 1) continue;
                 if (reduced[i]) {
-                    if (phase == 2) throw std::logic_error("FusedEquation::stamp: reduction over non-adjacent axes is not provided (StridedFixedSegment path)");
+                    if (phase == 2) strided = true;
                     phase = 1;
                     red *= in_shape[i];
                 } else if (phase == 0) {
@@ -501,6 +511,35 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
                     phase = 2;
                     inner *= in_shape[i];
                 }
+            }
+            if (strided) {
+                if (ls.kind == StageKind::ReduceMinMaxBackward) throw std::logic_error("FusedEquation::stamp: min/max backward over non-adjacent axes is not provided");
+                if (in_shape.size() > THOR_B200_MAX_RANK) throw std::logic_error("FusedEquation::stamp: reductions over non-adjacent axes support rank <= 8");
+                const bool is_out_s = output_name_of.count(k) != 0;
+                Tensor dst_s = allocateFor(k, is_out_s);
+                node_tensor[k] = dst_s;
+                if (is_out_s) impl->outputs[output_name_of[k]] = dst_s;
+                auto d = std::make_shared<thor_b200_strided_reduce_desc>();
+                d->op = ls.kind == StageKind::Reduction ? reduceOpFor(nd.op) : 0;
+                d->arg_op = ls.kind == StageKind::ArgMinMax ? (nd.op == ExprOp::REDUCE_ARGMAX ? 1 : 0) : -1;
+                d->input_dtype = static_cast<int>(src.getDataType());
+                d->output_dtype = static_cast<int>(*nd.output_dtype);
+                d->rank = static_cast<uint32_t>(in_shape.size());
+                for (size_t i = 0; i < in_shape.size(); ++i) {
+                    d->dims[i] = in_shape[i];
+                    d->reduced[i] = reduced[i] ? 1 : 0;
+                }
+                PhysicalStage st;
+                st.kind = ls.kind;
+                st.physical_name = ls.kind == StageKind::Reduction ? "strided" : "arg_strided";
+                const void* in_ptr = src.getMemPtr();
+                void* out_ptr = dst_s.getMemPtr();
+                st.custom_launch = [d, in_ptr, out_ptr](void* stream) {
+                    check(thor_b200_strided_reduce_launch(d.get(), in_ptr, out_ptr, 1.0f, stream), "StampedExecutionPlan::run strided reduction");
+                };
+                impl->keep_alive.push_back(src);
+                impl->stages.push_back(std::move(st));
+                continue;
             }
             const bool is_out = output_name_of.count(k) != 0;
             Tensor dst = allocateFor(k, is_out);

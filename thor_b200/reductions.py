@@ -37,6 +37,25 @@ _lib.thor_b200_argreduce_plan_destroy.argtypes = [C.c_void_p]
 _lib.thor_b200_argreduce_plan_destroy.restype = None
 
 
+class _StridedDesc(C.Structure):
+    _fields_ = [("op", C.c_int32), ("arg_op", C.c_int32), ("input_dtype", C.c_int32), ("output_dtype", C.c_int32), ("rank", C.c_uint32),
+                ("reserved", C.c_uint32), ("dims", C.c_uint64 * 8), ("reduced", C.c_uint8 * 8)]
+
+
+_lib.thor_b200_strided_reduce_launch.argtypes = [C.POINTER(_StridedDesc), C.c_void_p, C.c_void_p, C.c_float, C.c_void_p]
+
+
+def _strided_desc(shape, axes, op: int, arg_op: int, in_dt: DataType, out_dt: DataType) -> _StridedDesc:
+    if len(shape) > 8:
+        raise _native.ThorB200InvalidArgument("reductions over non-adjacent axes support rank <= 8")
+    d = _StridedDesc()
+    d.op, d.arg_op, d.input_dtype, d.output_dtype, d.rank = int(op), int(arg_op), int(in_dt), int(out_dt), len(shape)
+    for i, v in enumerate(shape):
+        d.dims[i] = int(v)
+        d.reduced[i] = 1 if i in axes else 0
+    return d
+
+
 class CubReductionOp(enum.IntEnum):
     Sum = 0
     Min = 1
@@ -132,6 +151,21 @@ class StampedCubArgReduction:
                                                       _native.stream_handle(self._stream)))
 
 
+class StampedStridedCubArgReduction:
+    """Arg reduction over non-adjacent axes (StridedFixedSegment): stateless launches, the winner's value is the
+    NaN-propagating min / max of the segment."""
+
+    def __init__(self, index_desc, value_desc, input_t, index, value, stream):
+        self._index_desc, self._value_desc, self._in, self.index, self.value, self._stream = index_desc, value_desc, input_t, index, value, stream
+
+    def run(self) -> None:
+        st = _native.stream_handle(self._stream)
+        if self._index_desc is not None:
+            _native.check(_lib.thor_b200_strided_reduce_launch(C.byref(self._index_desc), self._in.data_ptr(), self.index.data_ptr(), C.c_float(1.0), st))
+        if self._value_desc is not None:
+            _native.check(_lib.thor_b200_strided_reduce_launch(C.byref(self._value_desc), self._in.data_ptr(), self.value.data_ptr(), C.c_float(1.0), st))
+
+
 class CubArgReduction:
     def __init__(self, op: CubArgReductionOp, axes: Union[int, Sequence[int]], produce_value: bool = True, produce_index: bool = True,
                  index_dtype: DataType = DataType.uint32):
@@ -143,7 +177,13 @@ class CubArgReduction:
         in_dt = DataType(input_dtype) if input_dtype is not None else from_torch(input_t.dtype)
         outer, red, inner, path = analyze_geometry(list(input_t.shape), self.axes)
         if path == CubReductionPath.StridedFixedSegment:
-            raise _native.ThorB200InvalidArgument("CubArgReduction: reductions over non-adjacent axes are not provided by this build")
+            out_shape = [1 if i in self.axes else d for i, d in enumerate(input_t.shape)]
+            index = torch.empty(out_shape, dtype=to_torch(self.index_dtype), device=input_t.device) if self.produce_index else None
+            value = torch.empty(out_shape, dtype=input_t.dtype, device=input_t.device) if self.produce_value else None
+            idesc = _strided_desc(input_t.shape, self.axes, 0, int(self.op), in_dt, self.index_dtype) if self.produce_index else None
+            vop = CubReductionOp.Max if self.op == CubArgReductionOp.ArgMax else CubReductionOp.Min
+            vdesc = _strided_desc(input_t.shape, self.axes, int(vop), -1, in_dt, in_dt) if self.produce_value else None
+            return StampedStridedCubArgReduction(idesc, vdesc, input_t, index, value, stream)
         desc = _ArgDesc(int(self.op), int(in_dt), int(in_dt) if self.produce_value else 0, int(self.index_dtype), outer, red, inner)
         plan = C.c_void_p()
         ws = C.c_size_t()
