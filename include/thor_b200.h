@@ -312,6 +312,8 @@ typedef struct thor_b200_minmax_backward_desc {
     int32_t grad_output_dtype; /* fp16 / bf16 / fp32 */
     int32_t grad_input_dtype;  /* fp16 / bf16 / fp32 */
     uint64_t outer, reduction, inner;
+    int32_t grad_mode;         /* 0: grad_output holds outer * inner values; 1: one value for every segment; 2: no tensor, grad_value is used */
+    float grad_value;          /* grad_mode 2: the gradient of every segment (the default seed 1 of a backward pass) */
 } thor_b200_minmax_backward_desc;
 
 typedef struct thor_b200_minmax_backward_plan thor_b200_minmax_backward_plan;

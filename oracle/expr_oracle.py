@@ -1,11 +1,13 @@
 """Eager numpy restatement of the reference's expression semantics — TEST INFRASTRUCTURE ONLY.
 
-An ``OTensor`` carries values already rounded to its storage dtype (held as float32/float64
-numpy arrays) plus that dtype.  Every operation applies the reference's per-node rule
-(Utilities/Expression/ExpressionDTypeResolution.cpp:1012-1128): pick the output dtype by promoting
-the TENSOR operands (scalars never promote, :506-515, :793-805), compute in
-toSupportedComputeDType(promote(input, output)) (fp8 computes in fp16, :95-220), round the result to
-the output dtype.  Arithmetic is done in float64 (exact for + - * on <= 24-bit significands) and
+An ``OTensor`` carries its output dtype plus the values as the reference's kernels hold them: leaves,
+casts and reduction results in their output dtype, every other arithmetic node in its COMPUTE dtype
+(CudaSourceEmitter.cpp:2077-2083) -- a value is rounded to its output dtype only where it is
+materialised: read as a result (``.v``), consumed by a reduction, an arg reduction or a view.  Every
+operation applies the reference's per-node rule (Utilities/Expression/ExpressionDTypeResolution.cpp:1012-1128):
+pick the output dtype by promoting the TENSOR operands (scalars never promote, :506-515, :793-805) and compute
+in toSupportedComputeDType(promote(input, output)) (fp8 computes in fp16, :95-220).  For fp16 / bf16 / fp32
+graphs compute and output dtype coincide, so the distinction only shows with fp8 storage.  Arithmetic is done in float64 (exact for + - * on <= 24-bit significands) and
 rounded ONCE to the compute dtype, which equals correctly-rounded fp16 / bf16 / fp32 arithmetic;
 transcendental functions are evaluated in float64 and rounded, i.e. "ideal" libdevice results --
 the CUDA functions differ from that by their documented ulp error, which is what the parity
@@ -73,9 +75,15 @@ def compute_dtype_for(dtype: int) -> int:
 
 
 class OTensor:
-    def __init__(self, values, dtype: int):
+    def __init__(self, values, dtype: int, held: Optional[int] = None):
         self.dtype = dtype
-        self.v = round_to(values, dtype)
+        self.held = dtype if held is None else held
+        self._h = round_to(values, self.held)
+
+    @property
+    def v(self) -> np.ndarray:
+        """The materialised values: rounded to the output dtype."""
+        return self._h if self.held == self.dtype else round_to(self._h, self.dtype)
 
     # ---- construction -------------------------------------------------------------------------------
     @staticmethod
@@ -101,23 +109,23 @@ class OTensor:
         if isinstance(other, OTensor):
             out = out_dtype or promote(self.dtype, other.dtype)
             cd = compute or compute_dtype_for(promote(promote(self.dtype, other.dtype), out))
-            a, b = round_to(self.v, cd), round_to(other.v, cd)
+            a, b = round_to(self._h, cd), round_to(other._h, cd)
         else:
             out = out_dtype or self.dtype
             cd = compute or compute_dtype_for(out)
             # literal: double -> float literal -> compute dtype (CudaSourceEmitter.cpp:4034-4043)
-            a, b = round_to(self.v, cd), round_to(round_to(np.float64(other), FP32), cd)
+            a, b = round_to(self._h, cd), round_to(round_to(np.float64(other), FP32), cd)
         if swap:
             a, b = b, a
         with np.errstate(all="ignore"):
             r = fn(a, b)
-        return OTensor(round_to(r, cd), out)
+        return OTensor(r, out, held=cd)
 
     def _unary(self, fn, compute: Optional[int] = None) -> "OTensor":
         cd = compute or compute_dtype_for(self.dtype)
         with np.errstate(all="ignore"):
-            r = fn(round_to(self.v, cd))
-        return OTensor(round_to(r, cd), self.dtype)
+            r = fn(round_to(self._h, cd))
+        return OTensor(r, self.dtype, held=cd)
 
     def __add__(self, o): return self._binary(o, np.add)
     def __radd__(self, o): return self._binary(o, np.add, swap=True)
@@ -137,10 +145,10 @@ class OTensor:
     def _compare(self, o, fn) -> "OTensor":
         if isinstance(o, OTensor):
             cd = compute_dtype_for(promote(self.dtype, o.dtype))
-            a, b = round_to(self.v, cd), round_to(o.v, cd)
+            a, b = round_to(self._h, cd), round_to(o._h, cd)
         else:
             cd = compute_dtype_for(self.dtype)
-            a, b = round_to(self.v, cd), round_to(round_to(np.float64(o), FP32), cd)
+            a, b = round_to(self._h, cd), round_to(round_to(np.float64(o), FP32), cd)
         return OTensor(fn(a, b).astype(np.float64), BOOLEAN)
 
     def __lt__(self, o): return self._compare(o, np.less)
@@ -158,12 +166,13 @@ class OTensor:
     def where(cond: "OTensor", t, f) -> "OTensor":
         branches = [x.dtype for x in (t, f) if isinstance(x, OTensor)]
         out = FP32 if not branches else (branches[0] if len(branches) == 1 else promote(branches[0], branches[1]))
-        tv = t.v if isinstance(t, OTensor) else round_to(round_to(np.float64(t), FP32), out)
-        fv = f.v if isinstance(f, OTensor) else round_to(round_to(np.float64(f), FP32), out)
-        return OTensor(np.where(cond.v != 0, tv, fv), out)
+        cd = compute_dtype_for(out)
+        tv = t._h if isinstance(t, OTensor) else round_to(round_to(np.float64(t), FP32), out)
+        fv = f._h if isinstance(f, OTensor) else round_to(round_to(np.float64(f), FP32), out)
+        return OTensor(np.where(cond.v != 0, round_to(tv, cd), round_to(fv, cd)), out, held=cd)
 
     def cast(self, dtype: int) -> "OTensor":
-        return OTensor(self.v, dtype)
+        return OTensor(self._h, dtype)
 
     def abs(self): return self._unary(np.abs)
     def ceil(self): return self._unary(np.ceil)

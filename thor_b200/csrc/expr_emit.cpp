@@ -233,11 +233,25 @@ void decideV2(Plan& p) {
 
 std::string nodeVar(size_t k) { return "v" + std::to_string(k); }
 
+// Type in which a node's value lives inside a kernel (CudaSourceEmitter.cpp:2077-2083): leaves and
+// casts carry their output dtype; every other arithmetic node stays in its compute dtype and is
+// rounded to its output dtype only where it is materialised -- when a stage stores it, or when a
+// reduction consumes it.  fp16 / bf16 / fp32 graphs compute and store in one type, so this only shows
+// in fp8 graphs (compute fp16, store fp8) and on nodes with an explicitly requested output dtype.
+int valueDTypeImpl(const std::vector<thor_b200_expr_node>& nodes, size_t k) {
+    const auto& nd = nodes[k];
+    if (isLeaf(nd.op) || nd.op == THOR_B200_OP_CAST) return nd.output_dtype;
+    if (isComparison(nd.op) || isLogicalBinary(nd.op) || nd.op == THOR_B200_OP_LOGICAL_NOT) return nd.output_dtype;
+    if (!isKnownOp(nd.op)) return nd.output_dtype;  // reductions of row programs: their result is a stored value
+    return isArithCompute(nd.compute_dtype) ? nd.compute_dtype : nd.output_dtype;
+}
+
 // ---- scalar body -------------------------------------------------------------------------------
 std::string scalarNodeExprImpl(const std::vector<thor_b200_expr_node>& nodes, const std::vector<thor_b200_expr_input>& inputs, size_t k) {
     const auto& nd = nodes[k];
-    const int C = nd.compute_dtype, O = nd.output_dtype;
-    auto parent = [&](uint32_t idx, int to) { return cvt(nodeVar(idx), nodes[idx].output_dtype, to); };
+    const int C = nd.compute_dtype;
+    const int O = valueDTypeImpl(nodes, k);  // the type the value is kept in
+    auto parent = [&](uint32_t idx, int to) { return cvt(nodeVar(idx), valueDTypeImpl(nodes, idx), to); };
     switch (nd.op) {
         case THOR_B200_OP_INPUT: return cvt("x" + std::to_string(nd.input_slot), inputs[nd.input_slot].dtype, O);
         case THOR_B200_OP_RUNTIME_SCALAR: return cvt("s" + std::to_string(nd.input_slot), THOR_B200_FP32, O);
@@ -362,10 +376,13 @@ void emitBody(const Plan& p, std::ostringstream& os) {
     os << ") {\n";
     for (size_t k = 0; k < st.nodes.size(); ++k) {
         if (!p.live[k]) continue;
-        const std::string type = p.v2 ? T2 : std::string(ctype(st.nodes[k].output_dtype));
+        const std::string type = p.v2 ? T2 : std::string(ctype(valueDTypeImpl(st.nodes, k)));
         os << "    const " << type << " " << nodeVar(k) << " = " << (p.v2 ? v2NodeExpr(p, k) : scalarNodeExpr(p, k)) << ";\n";
     }
-    for (size_t o = 0; o < st.outputs.size(); ++o) os << "    y" << o << " = " << nodeVar(st.outputs[o].node) << ";\n";
+    for (size_t o = 0; o < st.outputs.size(); ++o) {
+        const uint32_t k = st.outputs[o].node;
+        os << "    y" << o << " = " << (p.v2 ? nodeVar(k) : cvt(nodeVar(k), valueDTypeImpl(st.nodes, k), st.outputs[o].dtype)) << ";\n";
+    }
     os << "}\n\n";
 }
 
@@ -717,6 +734,7 @@ std::string scalarNodeExpression(const std::vector<thor_b200_expr_node>& nodes, 
     return scalarNodeExprImpl(nodes, inputs, k);
 }
 const char* cTypeName(int dtype) { return ctype(dtype); }
+int nodeValueDType(const std::vector<thor_b200_expr_node>& nodes, size_t k) { return valueDTypeImpl(nodes, k); }
 std::string convertExpression(const std::string& e, int src, int dst) { return cvt(e, src, dst); }
 bool isFusedStageOp(uint16_t op) { return isKnownOp(op); }
 

@@ -53,6 +53,8 @@ const char* kindName(Kind k);
 // typed as its output dtype; tensor inputs are "x<slot>", scalars "s<slot>".
 std::string scalarNodeExpression(const std::vector<thor_b200_expr_node>& nodes, const std::vector<thor_b200_expr_input>& inputs, size_t k);
 const char* cTypeName(int dtype);
+// dtype in which node k's value is held inside a kernel (compute dtype for arithmetic nodes, output dtype for leaves and casts)
+int nodeValueDType(const std::vector<thor_b200_expr_node>& nodes, size_t k);
 std::string convertExpression(const std::string& e, int src, int dst);
 bool isFusedStageOp(uint16_t op);
 

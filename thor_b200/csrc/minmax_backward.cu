@@ -20,10 +20,20 @@ __device__ __forceinline__ T gradFromFloat(float v) {
     return static_cast<T>(v);
 }
 
+// Where a segment's gradient comes from: one value per segment, one value for all, or a literal.
+struct GradSource {
+    int mode;
+    float value;
+};
+template <class G>
+__device__ __forceinline__ float segmentGrad(const G* grad_output, uint64_t seg, GradSource gs) {
+    return gs.mode == 2 ? gs.value : gradToFloat(grad_output[gs.mode == 1 ? 0 : seg]);
+}
+
 // inner == 1: rows of `reduction` elements, P elements per pack, reduction % P == 0.
 template <class G, class O, int P>
 __global__ void __launch_bounds__(256) routeRowsKernel(const G* __restrict__ grad_output, const uint32_t* __restrict__ winners, O* __restrict__ grad_input,
-                                                        uint64_t packs_per_row, uint64_t n_packs) {
+                                                        uint64_t packs_per_row, uint64_t n_packs, GradSource gs) {
     gridDependencyWait();
     gridLaunchDependents();
     const uint64_t p = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -37,7 +47,7 @@ __global__ void __launch_bounds__(256) routeRowsKernel(const G* __restrict__ gra
 #pragma unroll
     for (int e = 0; e < P; ++e) lanes[e] = zero;
     if (hit < static_cast<uint32_t>(P)) {
-        const O g = gradFromFloat<O>(gradToFloat(grad_output[row]));
+        const O g = gradFromFloat<O>(segmentGrad(grad_output, row, gs));
 #pragma unroll
         for (int e = 0; e < P; ++e)
             if (static_cast<uint32_t>(e) == hit) lanes[e] = g;
@@ -48,7 +58,7 @@ __global__ void __launch_bounds__(256) routeRowsKernel(const G* __restrict__ gra
 // inner > 1, inner % P == 0: a pack covers P neighbouring `inner` positions of one (outer, r) line.
 template <class G, class O, int P>
 __global__ void __launch_bounds__(256) routeInnerKernel(const G* __restrict__ grad_output, const uint32_t* __restrict__ winners, O* __restrict__ grad_input,
-                                                         uint64_t reduction, uint64_t packs_per_line, uint64_t n_packs) {
+                                                         uint64_t reduction, uint64_t packs_per_line, uint64_t n_packs, GradSource gs) {
     gridDependencyWait();
     gridLaunchDependents();
     const uint64_t p = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -63,7 +73,7 @@ __global__ void __launch_bounds__(256) routeInnerKernel(const G* __restrict__ gr
 #pragma unroll
     for (int e = 0; e < P; ++e) {
         const bool hit = winners[seg + e] == r;
-        lanes[e] = gradFromFloat<O>(hit ? gradToFloat(grad_output[seg + e]) : 0.0f);
+        lanes[e] = gradFromFloat<O>(hit ? segmentGrad(grad_output, seg + e, gs) : 0.0f);
     }
     storePack(grad_input + p * P, out);
 }
@@ -71,7 +81,7 @@ __global__ void __launch_bounds__(256) routeInnerKernel(const G* __restrict__ gr
 // Any shape: one element per thread step, index arithmetic per element.
 template <class G, class O>
 __global__ void __launch_bounds__(256) routeGenericKernel(const G* __restrict__ grad_output, const uint32_t* __restrict__ winners, O* __restrict__ grad_input,
-                                                           uint64_t reduction, uint64_t inner, uint64_t n) {
+                                                           uint64_t reduction, uint64_t inner, uint64_t n, GradSource gs) {
     gridDependencyWait();
     gridLaunchDependents();
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 256;
@@ -81,7 +91,7 @@ __global__ void __launch_bounds__(256) routeGenericKernel(const G* __restrict__ 
         const uint64_t o = line / reduction;
         const uint32_t r = static_cast<uint32_t>(line - o * reduction);
         const uint64_t seg = o * inner + i;
-        grad_input[f] = gradFromFloat<O>(winners[seg] == r ? gradToFloat(grad_output[seg]) : 0.0f);
+        grad_input[f] = gradFromFloat<O>(winners[seg] == r ? segmentGrad(grad_output, seg, gs) : 0.0f);
     }
 }
 
@@ -92,22 +102,23 @@ int launchRoute(const thor_b200_minmax_backward_desc& d, const void* grad_output
     constexpr int P = 16 / sizeof(O);
     const uint64_t n = d.outer * d.reduction * d.inner;
     const bool aligned = isAligned(grad_input_v, 16);
+    const GradSource gs{d.grad_mode, d.grad_value};
     if (aligned && d.inner == 1 && d.reduction % P == 0) {
         const uint64_t packs = n / P;
         const uint64_t blocks = (packs + 255) / 256;
         TB_REQUIRE(blocks <= 0x7FFFFFFFull, "minmax_backward: too many elements for one grid");
         TB_CUDA(launchDependent(routeRowsKernel<G, O, P>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, grad_output, winners, grad_input,
-                                d.reduction / P, packs));
+                                d.reduction / P, packs, gs));
     } else if (aligned && d.inner > 1 && d.inner % P == 0) {
         const uint64_t packs = n / P;
         const uint64_t blocks = (packs + 255) / 256;
         TB_REQUIRE(blocks <= 0x7FFFFFFFull, "minmax_backward: too many elements for one grid");
         TB_CUDA(launchDependent(routeInnerKernel<G, O, P>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, grad_output, winners, grad_input,
-                                d.reduction, d.inner / P, packs));
+                                d.reduction, d.inner / P, packs, gs));
     } else {
         const uint64_t blocks = std::min<uint64_t>((n + 255) / 256, 148ull * 32);
         TB_CUDA(launchDependent(routeGenericKernel<G, O>, dim3(static_cast<unsigned>(std::max<uint64_t>(1, blocks))), dim3(256), 0, stream, grad_output, winners,
-                                grad_input, d.reduction, d.inner, n));
+                                grad_input, d.reduction, d.inner, n, gs));
     }
     countLaunch();
     return THOR_B200_OK;
@@ -143,7 +154,9 @@ int thor_b200_minmax_backward_plan_create(const thor_b200_minmax_backward_desc* 
     *out_plan = nullptr;
     TB_REQUIRE(d->outer > 0 && d->reduction > 0 && d->inner > 0, "minmax_backward_plan_create: zero-sized dimension");
     TB_REQUIRE(d->reduction <= 0xFFFFFFFFull, "minmax_backward_plan_create: reduction length exceeds the 32-bit winner index");
-    TB_REQUIRE(gradDtypeOk(d->grad_output_dtype) && gradDtypeOk(d->grad_input_dtype), "minmax_backward_plan_create: gradient dtypes must be fp32, fp16 or bf16");
+    TB_REQUIRE(d->grad_mode >= 0 && d->grad_mode <= 2, "minmax_backward_plan_create: grad_mode must be 0, 1 or 2");
+    TB_REQUIRE((d->grad_mode == 2 || gradDtypeOk(d->grad_output_dtype)) && gradDtypeOk(d->grad_input_dtype),
+               "minmax_backward_plan_create: gradient dtypes must be fp32, fp16 or bf16");
     thor_b200_argreduce_desc a{};
     a.op = d->is_max ? 1 : 0;
     a.input_dtype = d->input_dtype;
@@ -170,13 +183,13 @@ int thor_b200_minmax_backward_launch(const thor_b200_minmax_backward_plan* plan,
                                      size_t workspace_bytes, void* stream_v) {
     using namespace tb;
     TB_REQUIRE(plan != nullptr, "minmax_backward_launch: null plan");
-    TB_REQUIRE(input != nullptr && grad_output != nullptr && grad_input != nullptr, "minmax_backward_launch: null tensor pointer");
+    TB_REQUIRE(input != nullptr && grad_input != nullptr && (grad_output != nullptr || plan->desc.grad_mode == 2), "minmax_backward_launch: null tensor pointer");
     TB_REQUIRE(workspace != nullptr && workspace_bytes >= plan->arg_workspace + plan->winners_bytes, "minmax_backward_launch: workspace too small");
     TB_REQUIRE(isAligned(workspace, 256), "minmax_backward_launch: workspace must be 256-byte aligned");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     uint32_t* winners = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + plan->arg_workspace);
     if (int st = thor_b200_argreduce_launch(plan->arg, input, nullptr, winners, workspace, plan->arg_workspace, stream)) return st;
-    switch (plan->desc.grad_output_dtype) {
+    switch (plan->desc.grad_mode == 2 ? THOR_B200_FP32 : plan->desc.grad_output_dtype) {
         case THOR_B200_FP32: return dispatchOut<float>(plan->desc, grad_output, winners, grad_input, stream);
         case THOR_B200_FP16: return dispatchOut<__half>(plan->desc, grad_output, winners, grad_input, stream);
         case THOR_B200_BF16: return dispatchOut<__nv_bfloat16>(plan->desc, grad_output, winners, grad_input, stream);

@@ -319,9 +319,16 @@ bool hoistLinearRowSums(Program& p) {
     return true;
 }
 
+// dtype a node's value is held in inside the kernel, and the fp32 view a reduction takes of its argument:
+// reductions consume materialised values, i.e. rounded to the argument node's output dtype first
+int vdt(const Program& p, uint32_t k) { return tb::expr::nodeValueDType(p.nodes, k); }
+std::string reduceArgF32(const Program& p, uint32_t a, const std::string& name) {
+    return convertExpression(convertExpression(name, vdt(p, a), p.nodes[a].output_dtype), p.nodes[a].output_dtype, THOR_B200_FP32);
+}
+
 // Statements "const T vK = <expr>;" for the given nodes (already in topological order).
 void emitStatements(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
-    for (uint32_t k : ids) os << indent << "const " << cTypeName(p.nodes[k].output_dtype) << " v" << k << " = " << scalarNodeExpression(p.nodes, p.inputs, k) << ";\n";
+    for (uint32_t k : ids) os << indent << "const " << cTypeName(vdt(p, k)) << " v" << k << " = " << scalarNodeExpression(p.nodes, p.inputs, k) << ";\n";
 }
 
 // ---- pair mode ---------------------------------------------------------------------------------
@@ -357,14 +364,14 @@ bool elementLevel(const Program& p, uint32_t k) { return p.shape[k] == FULL || p
 
 // float2 view of node `idx` for a packed fp32 instruction.
 std::string pairAsFloat2(const Program& p, uint32_t idx) {
-    const int d = p.nodes[idx].output_dtype;
+    const int d = vdt(p, idx);
     if (elementLevel(p, idx)) return convertPair("p" + std::to_string(idx), d, THOR_B200_FP32);
     return "tb_both(" + convertExpression("v" + std::to_string(idx), d, THOR_B200_FP32) + ")";
 }
 bool packedMul(const Program& p, uint32_t idx) {
     if (idx == THOR_B200_NO_NODE || !elementLevel(p, idx)) return false;
     const auto& m = p.nodes[idx];
-    return m.op == THOR_B200_OP_MUL && m.compute_dtype == THOR_B200_FP32 && m.output_dtype == THOR_B200_FP32;
+    return m.op == THOR_B200_OP_MUL && m.compute_dtype == THOR_B200_FP32;
 }
 // fp32 value of node `idx` plus `addend` (a float2 expression), with the multiply folded into an fma when `idx` is one.
 std::string pairPlus(const Program& p, uint32_t idx, const std::string& addend) {
@@ -372,10 +379,24 @@ std::string pairPlus(const Program& p, uint32_t idx, const std::string& addend) 
     return "__fadd2_rn(" + pairAsFloat2(p, idx) + ", " + addend + ")";
 }
 
+// float2 expression of reduction argument `a` as the reduction sees it: rounded to the node's output dtype when that
+// differs from the dtype the value is held in (emits the rounding as a statement of its own in that case).
+std::string pairReduceArg(const Program& p, uint32_t a, const std::string& indent, std::ostringstream& os) {
+    const int V = vdt(p, a), O = p.nodes[a].output_dtype;
+    if (V == O || !elementLevel(p, a)) {
+        if (!elementLevel(p, a)) return "tb_both(" + reduceArgF32(p, a, "v" + std::to_string(a)) + ")";
+        return pairAsFloat2(p, a);
+    }
+    const std::string m = "m" + std::to_string(a);
+    os << indent << "const " << pairType(O) << " " << m << " = " << convertPair("p" + std::to_string(a), V, O) << ";\n";
+    return convertPair(m, O, THOR_B200_FP32);
+}
+bool storedAsHeld(const Program& p, uint32_t a) { return vdt(p, a) == static_cast<int>(p.nodes[a].output_dtype); }
+
 void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
     for (uint32_t k : ids) {
         const auto& nd = p.nodes[k];
-        const int O = nd.output_dtype;
+        const int O = vdt(p, k);
         const std::string name = "p" + std::to_string(k);
         std::string packed;  // float2 expression when the node has a packed form
         if (nd.op == THOR_B200_OP_INPUT) {
@@ -383,7 +404,7 @@ void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, cons
             continue;
         }
         if (nd.op == THOR_B200_OP_CAST && elementLevel(p, nd.lhs)) {
-            os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("p" + std::to_string(nd.lhs), p.nodes[nd.lhs].output_dtype, O) << ";\n";
+            os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("p" + std::to_string(nd.lhs), vdt(p, nd.lhs), O) << ";\n";
             continue;
         }
         if (nd.compute_dtype == THOR_B200_FP32) {
@@ -392,7 +413,7 @@ void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, cons
                 else packed = pairPlus(p, nd.rhs, pairAsFloat2(p, nd.lhs));
             } else if (nd.op == THOR_B200_OP_SUB && !elementLevel(p, nd.rhs)) {
                 // the negated row value is loop invariant
-                packed = "__fadd2_rn(" + pairAsFloat2(p, nd.lhs) + ", tb_both(-" + convertExpression("v" + std::to_string(nd.rhs), p.nodes[nd.rhs].output_dtype, THOR_B200_FP32) + "))";
+                packed = "__fadd2_rn(" + pairAsFloat2(p, nd.lhs) + ", tb_both(-" + convertExpression("v" + std::to_string(nd.rhs), vdt(p, nd.rhs), THOR_B200_FP32) + "))";
             } else if (nd.op == THOR_B200_OP_SUB) {
                 packed = "__ffma2_rn(" + pairAsFloat2(p, nd.rhs) + ", tb_both(-1.0f), " + pairAsFloat2(p, nd.lhs) + ")";  // a - b, exact
             } else if (nd.op == THOR_B200_OP_MUL) {
@@ -417,7 +438,7 @@ void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, cons
             for (uint32_t par : {nd.lhs, nd.rhs, nd.aux}) {
                 if (par == THOR_B200_NO_NODE || !elementLevel(p, par) || std::find(seen.begin(), seen.end(), par) != seen.end()) continue;
                 seen.push_back(par);
-                os << "const " << cTypeName(p.nodes[par].output_dtype) << " v" << par << " = p" << par << lane << "; ";
+                os << "const " << cTypeName(vdt(p, par)) << " v" << par << " = p" << par << lane << "; ";
             }
             os << name << lane << " = " << expr << "; }\n";
         }
@@ -662,16 +683,23 @@ std::string emit(Program& p) {
                 const uint32_t a = p.nodes[k].lhs;
                 const uint16_t op = p.nodes[k].op;
                 const std::string acc = "q" + std::to_string(k);
-                if (op == THOR_B200_OP_REDUCE_SUM || op == THOR_B200_OP_REDUCE_AVG) {
-                    os << I << "            " << acc << " = " << pairPlus(p, a, acc) << ";\n";
+                const std::string II = I + "            ";
+                if ((op == THOR_B200_OP_REDUCE_SUM || op == THOR_B200_OP_REDUCE_AVG) && storedAsHeld(p, a) && elementLevel(p, a)) {
+                    os << II << acc << " = " << pairPlus(p, a, acc) << ";\n";
+                } else if (op == THOR_B200_OP_REDUCE_SUM || op == THOR_B200_OP_REDUCE_AVG) {
+                    const std::string arg = pairReduceArg(p, a, II, os);
+                    os << II << acc << " = __fadd2_rn(" << arg << ", " << acc << ");\n";
                 } else if (op == THOR_B200_OP_REDUCE_NORM2) {
-                    os << I << "            { const float2 a" << k << " = " << pairAsFloat2(p, a) << "; " << acc << " = __ffma2_rn(a" << k << ", a" << k << ", " << acc << "); }\n";
+                    const std::string arg = pairReduceArg(p, a, II, os);
+                    os << I << "            { const float2 a" << k << " = " << arg << "; " << acc << " = __ffma2_rn(a" << k << ", a" << k << ", " << acc << "); }\n";
                 } else if (isMinMax(k)) {
                     const char* fn = op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf";
-                    os << I << "            { const float2 a" << k << " = " << pairAsFloat2(p, a) << "; nan" << k << " = nan" << k << " || (a" << k << ".x != a" << k << ".x) || (a" << k
+                    const std::string arg = pairReduceArg(p, a, II, os);
+                    os << I << "            { const float2 a" << k << " = " << arg << "; nan" << k << " = nan" << k << " || (a" << k << ".x != a" << k << ".x) || (a" << k
                        << ".y != a" << k << ".y); " << acc << ".x = " << fn << "(" << acc << ".x, a" << k << ".x); " << acc << ".y = " << fn << "(" << acc << ".y, a" << k << ".y); }\n";
                 } else {
-                    os << I << "            { const float2 a" << k << " = " << pairAsFloat2(p, a) << "; " << acc << ".x = " << combineExpr(op) << "(" << acc << ".x, "
+                    const std::string arg = pairReduceArg(p, a, II, os);
+                    os << I << "            { const float2 a" << k << " = " << arg << "; " << acc << ".x = " << combineExpr(op) << "(" << acc << ".x, "
                        << transformExpr(op, "a" + std::to_string(k) + ".x") << "); " << acc << ".y = " << combineExpr(op) << "(" << acc << ".y, "
                        << transformExpr(op, "a" + std::to_string(k) + ".y") << "); }\n";
                 }
@@ -680,7 +708,7 @@ std::string emit(Program& p) {
             emitStatements(p, closure, I + "            ", os);
             for (uint32_t k : round) {
                 const uint32_t a = p.nodes[k].lhs;
-                const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
+                const std::string f = reduceArgF32(p, a, "v" + std::to_string(a));
                 if (isMinMax(k))
                     os << I << "            { const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
                        << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
@@ -732,16 +760,23 @@ std::string emit(Program& p) {
             emitPairStatements(p, closure, I + "            ", os);
             for (size_t o = 0; o < p.outputs.size(); ++o)
                 if (p.shape[p.outputs[o].node] == FULL)
-                    os << I << "            reinterpret_cast<" << pairType(p.outputs[o].dtype) << "*>(&w" << o << ")[j >> 1] = p" << p.outputs[o].node << ";\n";
-            for (uint32_t k : p.col_reduces) os << I << "            acc" << k << "[k][j >> 1] = " << pairPlus(p, p.nodes[k].lhs, "acc" + std::to_string(k) + "[k][j >> 1]") << ";\n";
+                    os << I << "            reinterpret_cast<" << pairType(p.outputs[o].dtype) << "*>(&w" << o << ")[j >> 1] = "
+                       << convertPair("p" + std::to_string(p.outputs[o].node), vdt(p, p.outputs[o].node), p.outputs[o].dtype) << ";\n";
+            for (uint32_t k : p.col_reduces) {
+                const uint32_t a = p.nodes[k].lhs;
+                const std::string slot = "acc" + std::to_string(k) + "[k][j >> 1]";
+                if (storedAsHeld(p, a) && elementLevel(p, a)) os << I << "            " << slot << " = " << pairPlus(p, a, slot) << ";\n";
+                else os << I << "            " << slot << " = __fadd2_rn(" << pairReduceArg(p, a, I + "            ", os) << ", " << slot << ");\n";
+            }
         } else {
             emitStatements(p, closure, I + "            ", os);
             for (size_t o = 0; o < p.outputs.size(); ++o)
                 if (p.shape[p.outputs[o].node] == FULL)
-                    os << I << "            reinterpret_cast<" << cTypeName(p.outputs[o].dtype) << "*>(&w" << o << ")[j] = v" << p.outputs[o].node << ";\n";
+                    os << I << "            reinterpret_cast<" << cTypeName(p.outputs[o].dtype) << "*>(&w" << o << ")[j] = "
+                       << convertExpression("v" + std::to_string(p.outputs[o].node), vdt(p, p.outputs[o].node), p.outputs[o].dtype) << ";\n";
             for (uint32_t k : p.col_reduces) {
                 const uint32_t a = p.nodes[k].lhs;
-                os << I << "            acc" << k << "[k][j] += " << convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32) << ";\n";
+                os << I << "            acc" << k << "[k][j] += " << reduceArgF32(p, a, "v" + std::to_string(a)) << ";\n";
             }
         }
         os << I << "        }\n";
@@ -751,7 +786,8 @@ std::string emit(Program& p) {
     }
     // ROW outputs
     for (size_t o = 0; o < p.outputs.size(); ++o)
-        if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0 && row_ok) out" << o << "[row] = v" << p.outputs[o].node << ";\n";
+        if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0 && row_ok) out" << o << "[row] = "
+                                                      << convertExpression("v" + std::to_string(p.outputs[o].node), vdt(p, p.outputs[o].node), p.outputs[o].dtype) << ";\n";
     if (p.persistent) os << I << "red_set ^= 1;\n";
     if (p.persistent && p.stage_smem) {
         os << I << "buf ^= 1;\n";
@@ -831,7 +867,7 @@ std::string emitFlat(Program& p) {
         emitStatements(p, closure, indent, os);
         for (uint32_t k : p.all_reduces) {
             const uint32_t a = p.nodes[k].lhs;
-            const std::string f = convertExpression("v" + std::to_string(a), p.nodes[a].output_dtype, THOR_B200_FP32);
+            const std::string f = reduceArgF32(p, a, "v" + std::to_string(a));
             if (isMinMax(k)) {
                 os << indent << "{ const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
                    << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";

@@ -102,8 +102,9 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
     const auto& outs = forward.namedOutputs();
     for (const NamedOutput& o : outs) {
         const std::string name = outs.size() == 1 ? upstream_prefix : upstream_prefix + "_" + o.name;
-        if (!input_dims.count(name)) throw std::logic_error("buildBackwardOutputs: upstream gradient '" + name + "' is not bound");
-        accumulate(o.node_idx, Expression::input(name));
+        // an upstream gradient that is not bound seeds the output with 1, the reference's default seed (AutoDiff.cpp:3819)
+        if (!input_dims.count(name)) grad.emplace(o.node_idx, Expression(1.0));
+        else accumulate(o.node_idx, Expression::input(name));
     }
     // which nodes reach a requested input
     std::vector<bool> reaches(g.nodes.size(), false);
@@ -217,7 +218,8 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
                 }
                 break;
             case ExprOp::RESHAPE: case ExprOp::UNSQUEEZE: case ExprOp::SQUEEZE:
-                if (wants(nd.lhs)) accumulate(nd.lhs, G.reshape(b.fwd_shape[nd.lhs]));
+                // a gradient with fewer elements than the view (a broadcast seed) passes through unchanged
+                if (wants(nd.lhs)) accumulate(nd.lhs, numelOf(b.shapeOf(G)) == numelOf(b.fwd_shape[nd.lhs]) ? G.reshape(b.fwd_shape[nd.lhs]) : G);
                 break;
             case ExprOp::REDUCE_SUM: case ExprOp::REDUCE_AVG: {
                 if (!wants(nd.lhs)) break;
@@ -231,7 +233,8 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
                         count *= in_shape[i];
                         keep[i] = 1;
                     }
-                Expression Gk = b.shapeOf(G) == keep ? G : G.reshape(keep);
+                const std::vector<uint64_t> gs = b.shapeOf(G);
+                Expression Gk = (gs == keep || numelOf(gs) != numelOf(keep)) ? G : G.reshape(keep);
                 if (nd.op == ExprOp::REDUCE_AVG) Gk = Gk / Expression(static_cast<double>(count));
                 accumulate(nd.lhs, Gk);
                 break;
@@ -239,8 +242,8 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
             case ExprOp::REDUCE_MIN: case ExprOp::REDUCE_MAX: {
                 if (!wants(nd.lhs)) break;
                 // the whole gradient of a segment goes to its winner (AutoDiff.cpp:5036-5050)
-                if (numelOf(b.shapeOf(G)) != numelOf(b.fwd_shape[k]))
-                    throw std::runtime_error("Thor expressions autodiff: min/max reduction backward needs one gradient value per reduced segment.");
+                if (numelOf(b.shapeOf(G)) != numelOf(b.fwd_shape[k]) && numelOf(b.shapeOf(G)) != 1)
+                    throw std::runtime_error("Thor expressions autodiff: min/max reduction backward needs one gradient value per reduced segment, or one for all.");
                 accumulate(nd.lhs, Expression::reduceMinMaxBackward(nd.op == ExprOp::REDUCE_MIN ? ExprOp::REDUCE_MIN_BACKWARD : ExprOp::REDUCE_MAX_BACKWARD,
                                                                    b.forward(nd.lhs), G, nd.reduction_axes, nd.squeeze_axes));
                 break;
@@ -262,14 +265,19 @@ Outputs buildBackwardOutputs(const Outputs& forward, const std::vector<std::stri
             Expression e = it->second;
             const std::vector<uint64_t> es = b.shapeOf(e);
             if (es != b.fwd_shape[k]) {
-                if (numelOf(es) == numelOf(b.fwd_shape[k])) e = e.reshape(b.fwd_shape[k]);
-                else throw std::logic_error("buildBackwardOutputs: gradient of '" + w + "' needs an explicit broadcast, which this build does not provide");
+                if (numelOf(es) == numelOf(b.fwd_shape[k])) {
+                    e = e.reshape(b.fwd_shape[k]);
+                } else {
+                    // explicit broadcast to the input's shape: a select whose condition is constantly true takes its
+                    // shape from both branches and its value from the first; the generated kernel never reads the second
+                    e = Expression::where(Expression(1.0) > Expression(0.0), e, b.forward(k));
+                }
             }
             // terminal dtype = dtype of the forward input; a terminal reduction stores it directly
             auto dt = input_dtypes.find(w);
             if (dt != input_dtypes.end() && isFusionFloat(dt->second)) {
                 const ExprNode& term = e.graph()->nodes[e.nodeIndex()];
-                e = isValueReductionOp(term.op) ? e.withOutputDType(dt->second) : e.cast(dt->second);
+                e = (isValueReductionOp(term.op) || isMinMaxBackwardOp(term.op)) ? e.withOutputDType(dt->second) : e.cast(dt->second);
             }
             named.emplace_back(w + "_grad", e);
             break;

@@ -552,24 +552,32 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             impl->keep_alive.push_back(src);
             size_t ws = 1;
             if (ls.kind == StageKind::ReduceMinMaxBackward) {
-                const Tensor& grad = node_tensor[nd.rhs];
-                if (!grad.isInitialized()) throw std::logic_error("FusedEquation::stamp: min/max backward gradient is not materialised");
-                if (grad.getTotalNumElements() != outer * inner)
-                    throw std::logic_error("FusedEquation::stamp: min/max backward needs a gradient with one value per reduced segment");
                 thor_b200_minmax_backward_desc d{};
                 d.is_max = nd.op == ExprOp::REDUCE_MAX_BACKWARD ? 1 : 0;
                 d.input_dtype = static_cast<int>(src.getDataType());
-                d.grad_output_dtype = static_cast<int>(grad.getDataType());
                 d.grad_input_dtype = static_cast<int>(*nd.output_dtype);
                 d.outer = outer;
                 d.reduction = red;
                 d.inner = inner;
+                if (g.nodes[nd.rhs].op == ExprOp::SCALAR_FP) {
+                    // a literal gradient (the default seed 1 of a backward pass) needs no tensor
+                    d.grad_mode = 2;
+                    d.grad_value = static_cast<float>(g.nodes[nd.rhs].scalar_fp);
+                    d.grad_output_dtype = static_cast<int>(DataType::FP32);
+                } else {
+                    const Tensor& grad = node_tensor[nd.rhs];
+                    if (!grad.isInitialized()) throw std::logic_error("FusedEquation::stamp: min/max backward gradient is not materialised");
+                    if (grad.getTotalNumElements() == outer * inner) d.grad_mode = 0;
+                    else if (grad.getTotalNumElements() == 1) d.grad_mode = 1;
+                    else throw std::logic_error("FusedEquation::stamp: min/max backward needs one gradient value per reduced segment, or one for all");
+                    d.grad_output_dtype = static_cast<int>(grad.getDataType());
+                    st.in2 = grad.getMemPtr();
+                    impl->keep_alive.push_back(grad);
+                }
                 st.minmax_backward = std::make_shared<MinMaxBackwardPlanHandle>();
                 check(thor_b200_minmax_backward_plan_create(&d, &st.minmax_backward->h, &ws), "FusedEquation::stamp min/max backward plan");
                 st.physical_name = "minmax_backward";
                 st.launches = 2;
-                st.in2 = grad.getMemPtr();
-                impl->keep_alive.push_back(grad);
             } else if (ls.kind == StageKind::Reduction) {
                 thor_b200_reduce_desc d{};
                 d.op = reduceOpFor(nd.op);

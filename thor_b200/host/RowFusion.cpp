@@ -23,7 +23,69 @@ struct ProgHandle {
 
 }  // namespace
 
+namespace {
+std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx);
+}
+
+// The whole equation is tried as one row program first (three full reductions of one tensor share a
+// single pass that way).  If it does not fit, the outputs are split into groups that share computed
+// nodes (sharing only inputs does not tie two outputs together); every group is tried as a row program
+// of its own, and groups that do not fit run through the ordinary stage list.
+// {"y": softmax(x), "idx": argmax(x)} therefore still gets its single-pass softmax.
 std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
+    {
+        std::vector<RowFusionMatch> whole = matchOutputs(ctx);
+        if (!whole.empty() || ctx.outputs.size() < 2) return whole;
+    }
+    const PhysicalExpression& g = ctx.graph;
+    const size_t n = g.nodes.size();
+    const size_t n_out = ctx.outputs.size();
+    std::vector<std::vector<bool>> reach(n_out, std::vector<bool>(n, false));
+    for (size_t o = 0; o < n_out; ++o) {
+        reach[o][ctx.outputs[o].node_idx] = true;
+        for (size_t k = n; k-- > 0;) {
+            if (!reach[o][k]) continue;
+            for (uint32_t p : {g.nodes[k].lhs, g.nodes[k].rhs, g.nodes[k].aux})
+                if (p != UINT32_MAX) reach[o][p] = true;
+        }
+    }
+    std::vector<int> group(n_out, -1);
+    int n_groups = 0;
+    for (size_t o = 0; o < n_out; ++o) {
+        if (group[o] >= 0) continue;
+        group[o] = n_groups;
+        bool grew = true;
+        while (grew) {
+            grew = false;
+            for (size_t a = 0; a < n_out; ++a) {
+                if (group[a] != n_groups) continue;
+                for (size_t b = 0; b < n_out; ++b) {
+                    if (group[b] >= 0) continue;
+                    bool shared = false;
+                    for (size_t k = 0; k < n && !shared; ++k) shared = reach[a][k] && reach[b][k] && !isLeafOp(g.nodes[k].op);
+                    if (shared) {
+                        group[b] = n_groups;
+                        grew = true;
+                    }
+                }
+            }
+        }
+        ++n_groups;
+    }
+    std::vector<RowFusionMatch> all;
+    for (int gi = 0; gi < n_groups; ++gi) {
+        std::vector<NamedOutput> subset;
+        for (size_t o = 0; o < n_out; ++o)
+            if (group[o] == gi) subset.push_back(ctx.outputs[o]);
+        RowFusionContext sub{ctx.graph, subset, ctx.shape, ctx.bound, ctx.device_num, ctx.use_fast_math};
+        for (RowFusionMatch& m : matchOutputs(sub)) all.push_back(std::move(m));
+    }
+    return all;
+}
+
+namespace {
+
+std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
     const PhysicalExpression& g = ctx.graph;
     const size_t n = g.nodes.size();
     std::vector<bool> needed(n, false);
@@ -246,5 +308,7 @@ std::vector<RowFusionMatch> matchRowFusions(const RowFusionContext& ctx) {
     out.push_back(std::move(m));
     return out;
 }
+
+}  // namespace
 
 }  // namespace ThorB200

@@ -199,7 +199,7 @@ class CubArgReduction:
 # ---- backward of dense min / max reductions ---------------------------------------------------------
 class _MinMaxBackwardDesc(C.Structure):
     _fields_ = [("is_max", C.c_int32), ("input_dtype", C.c_int32), ("grad_output_dtype", C.c_int32), ("grad_input_dtype", C.c_int32),
-                ("outer", C.c_uint64), ("reduction", C.c_uint64), ("inner", C.c_uint64)]
+                ("outer", C.c_uint64), ("reduction", C.c_uint64), ("inner", C.c_uint64), ("grad_mode", C.c_int32), ("grad_value", C.c_float)]
 
 
 _lib.thor_b200_minmax_backward_plan_create.argtypes = [C.POINTER(_MinMaxBackwardDesc), C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
@@ -219,7 +219,7 @@ class ReduceMinMaxBackward:
             raise _native.ThorB200InvalidArgument("ReduceMinMaxBackward: tensor sizes do not match [outer, reduction, inner]")
         self._input, self._grad_output, self._stream = input_t, grad_output, stream
         gi = grad_input_dtype if grad_input_dtype is not None else from_torch(input_t.dtype)
-        d = _MinMaxBackwardDesc(int(bool(is_max)), int(from_torch(input_t.dtype)), int(from_torch(grad_output.dtype)), int(gi), outer, reduction, inner)
+        d = _MinMaxBackwardDesc(int(bool(is_max)), int(from_torch(input_t.dtype)), int(from_torch(grad_output.dtype)), int(gi), outer, reduction, inner, 0, 0.0)
         self._plan = C.c_void_p()
         ws = C.c_size_t()
         _native.check(_lib.thor_b200_minmax_backward_plan_create(C.byref(d), C.byref(self._plan), C.byref(ws)))
