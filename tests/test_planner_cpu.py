@@ -54,6 +54,31 @@ def test_mixed_fp16_bf16_promotes_to_fp32_and_scalars_do_not_promote():
     assert plan.output_spec("scaled")[1] == DT.fp16
 
 
+# the promotion table of the reference's own dtype tests (test_expression_dynamic_dtypes.py:180-191)
+@pytest.mark.parametrize("lhs,rhs,want", [(DT.fp8_e4m3, DT.fp8_e4m3, DT.fp8_e4m3), (DT.fp8_e4m3, DT.fp8_e5m2, DT.fp16), (DT.fp8_e4m3, DT.fp16, DT.fp16),
+                                           (DT.fp8_e5m2, DT.bf16, DT.bf16), (DT.fp16, DT.bf16, DT.fp32), (DT.fp16, DT.fp32, DT.fp32),
+                                           (DT.bf16, DT.fp32, DT.fp32)])
+def test_pairwise_tensor_promotion(lhs, rhs, want):
+    plan = ex.compile(ex.input("x") + ex.input("y")).plan({"x": ((3, 5), lhs), "y": ((3, 5), rhs)})
+    assert plan.output_spec() == ([3, 5], want)
+
+
+@pytest.mark.parametrize("dtype", [DT.fp32, DT.fp16, DT.bf16, DT.fp8_e4m3, DT.fp8_e5m2])
+def test_single_input_keeps_its_storage_dtype_and_constants_never_promote(dtype):
+    x = ex.input("x")
+    for expr in (((x + 1.0) * (x - 0.5)) + 2.0, (x + 1.0) * 2.0 - 0.25):
+        plan = ex.compile(expr).plan({"x": ((17,), dtype)})
+        assert plan.output_spec() == ([17], dtype)
+        assert plan.stage_kind_names() == ["FusedKernel"]
+
+
+def test_mixed_dtype_outputs_of_one_stage_keep_distinct_dtypes():
+    x, y, z = ex.input("x"), ex.input("y"), ex.input("z")
+    plan = ex.compile({"sum16": x + y, "mix32": x + z, "shift16": x + 1.0}).plan({"x": ((17,), DT.fp16), "y": ((17,), DT.fp16), "z": ((17,), DT.fp32)})
+    assert plan.output_spec("sum16")[1] == DT.fp16 and plan.output_spec("mix32")[1] == DT.fp32 and plan.output_spec("shift16")[1] == DT.fp16
+    assert plan.stage_kind_names() == ["FusedKernel"] and plan.kernel_launches_per_run() == 1
+
+
 def test_softmax_is_one_row_program_or_four_stages():
     shapes = {"x": ((65536, 4096), DT.fp32)}
     fused = ex.compile(_softmax()).plan(shapes)
