@@ -403,6 +403,20 @@ class C3Softmax(Workload):
     def step(self, i): self.sets[i % len(self.sets)][0].run()
 
 
+class C3SoftmaxWithArgmax(C3Softmax):
+    """Softmax and row argmax of the same tensor as ONE equation: the arg reduction joins the first round of the row
+    program, so x is read once for both results (reported beside the two separate operations)."""
+    name = "c3_softmax_and_argmax_one_pass_fp32"
+    description = "softmax rows + row argmax of fp32 [65536,4096] per GPU in one row program"
+
+    def build(self, ex):
+        x = ex.input("x")
+        e = (x - x.reduce_max([1])).exp()
+        return {"y": e / e.reduce_sum([1]), "idx": x.argmax([1], squeeze_axes=[1])}
+
+    def algorithmic_bytes(self): return 2 * self.ROWS * self.COLS * 4 + self.ROWS * 4
+
+
 class C3Argmax(C3Softmax):
     name = "c3_row_argmax_fp32"
     description = "row argmax of fp32 [65536,4096] per GPU -> uint32 [65536]"
@@ -545,7 +559,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
             combine_partials(sums=torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()]))
 
 
-WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
+WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
              "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu}
 
 

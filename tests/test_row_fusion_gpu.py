@@ -195,3 +195,42 @@ def test_full_reductions_of_one_tensor_share_one_pass():
         assert abs(float(plan.output("sumsq")) - q) <= 1e-5 * abs(q)
         assert float(plan.output("max")) == m
     assert fused.intermediate_bytes() < (1 << 20) and staged.intermediate_bytes() >= 2 * n
+
+
+def test_softmax_and_argmax_of_one_tensor_share_one_pass():
+    """{"y": softmax(x), "idx": argmax(x)}: one row program reads x once for both (the arg reduction joins the
+    first round); the index follows the arg rule (NaN wins, lowest index among equals)."""
+    rows, cols = 513, 4096
+    x = torch.randint(-8, 8, (rows, cols), device="cuda").float()  # many ties
+    x[7, 100] = float("nan")
+    x[7, 50] = float("nan")
+    xi = ex.input("x")
+    e = (xi - xi.reduce_max([1])).exp()
+    both = ex.compile({"y": e / e.reduce_sum([1]), "idx": xi.argmax([1], squeeze_axes=[1])}).stamp({"x": x})
+    alone = ex.compile(xi.argmax([1], squeeze_axes=[1])).stamp({"x": x})
+    both.run()
+    alone.run()
+    torch.cuda.synchronize()
+    assert both.physical_stage_names() == ["row_program"] and both.kernel_launches_per_run() == 1
+    assert alone.physical_stage_names() == ["arg_reduce"]
+    idx = both.output("idx").cpu().numpy()
+    assert idx.dtype == np.uint32
+    assert np.array_equal(idx, alone.output().cpu().numpy())
+    assert np.array_equal(idx, eo.arg_reduce_rows(x.cpu().numpy(), True).astype(np.uint32))
+    assert idx[7] == 50
+    y = both.output("y").cpu().numpy()
+    want, _ = o.softmax_rows(np.delete(x.cpu().numpy(), 7, axis=0), want_argmax=False)
+    np.testing.assert_allclose(np.delete(y, 7, axis=0), want, rtol=1e-5, atol=1e-12)
+
+
+def test_argmin_inside_a_bf16_row_program_with_short_rows():
+    rows, cols = 300, 96
+    x = torch.randn(rows, cols, device="cuda").bfloat16()
+    xi = ex.input("x")
+    plan = ex.compile({"m": xi.reduce_mean([1]), "idx": (xi * xi).argmin([1], squeeze_axes=[1])}).stamp({"x": x})
+    plan.run()
+    torch.cuda.synchronize()
+    assert plan.physical_stage_names() == ["row_program"]
+    sq = (x * x).float().cpu().numpy()  # the bf16-rounded product is what the arg reduction sees
+    assert np.array_equal(plan.output("idx").cpu().numpy(), eo.arg_reduce_rows(sq, False).astype(np.uint32))
+    np.testing.assert_allclose(plan.output("m").cpu().numpy().reshape(-1), x.float().mean(dim=1).cpu().numpy(), rtol=1e-5, atol=1e-6)

@@ -191,6 +191,78 @@ __device__ __forceinline__ float tb_team_reduce_stage1(float v, float* smem) {
     if (TEAM > 32 && (threadIdx.x & 31) == 0) smem[(threadIdx.x % TEAM) >> 5] = v;
     return v;
 }
+// Arg reductions: candidates are (value, index); NaN beats numbers, then the better value, then the lower index
+// (the rule of the arg-reduction seam).  index 0xffffffff marks "no candidate".
+template <bool IS_MAX>
+__device__ __forceinline__ bool tb_arg_better(float v, tb_u32 i, float bv, tb_u32 bi) {
+    if (bi == 0xffffffffu) return true;
+    if (i == 0xffffffffu) return false;
+    const bool vn = v != v, bn = bv != bv;
+    if (vn != bn) return vn;
+    if (!vn && v != bv) return IS_MAX ? v > bv : v < bv;
+    return i < bi;
+}
+template <bool IS_MAX>
+__device__ __forceinline__ void tb_arg_update(float& bv, tb_u32& bi, float v, tb_u32 i) {
+    if (tb_arg_better<IS_MAX>(v, i, bv, bi)) {
+        bv = v;
+        bi = i;
+    }
+}
+// Scan of one thread's elements, which it visits in increasing column order: a strict compare keeps the lowest
+// index among equals, the first NaN is remembered on the side.  tb_arg_scan_finish turns the pair into a candidate:
+// a NaN wins; a thread whose values never beat the starting value (all -inf for max / +inf for min) offers its first one.
+template <bool IS_MAX>
+__device__ __forceinline__ void tb_arg_scan(float& bv, tb_u32& bi, tb_u32& nan_i, float v, tb_u32 col) {
+    if (IS_MAX ? v > bv : v < bv) {
+        bv = v;
+        bi = col;
+    }
+    nan_i = min(nan_i, v != v ? col : 0xffffffffu);
+}
+template <bool IS_MAX>
+__device__ __forceinline__ void tb_arg_scan_finish(float& bv, tb_u32& bi, tb_u32 nan_i, bool has_elements, tb_u32 first_col) {
+    if (nan_i != 0xffffffffu) {
+        bv = __int_as_float(0x7fffffff);
+        bi = nan_i;
+    } else if (bi == 0xffffffffu && has_elements) {
+        bi = first_col;
+    }
+}
+// Team combine of arg candidates: each thread's candidate becomes one 64-bit key whose unsigned order is the
+// arg rule -- NaN above everything, then the value in its float order (reversed for arg-min, -0 and +0 equal),
+// then the LOWER index (stored complemented) -- so lanes and warps combine with a plain 64-bit max.
+// 0 means "no candidate".  Only the team's first thread needs the result: it folds the warp keys.
+template <bool IS_MAX>
+__device__ __forceinline__ tb_u64 tb_arg_key(float v, tb_u32 i) {
+    if (i == 0xffffffffu) return 0ull;
+    tb_u32 b = v == 0.0f ? 0u : __float_as_uint(v);
+    tb_u32 k = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // ascending with the float order
+    if (!IS_MAX) k = ~k;
+    if (v != v) k = 0xffffffffu;
+    return ((tb_u64)k << 32) | (tb_u64)(tb_u32)~i;
+}
+template <int TEAM>
+__device__ __forceinline__ tb_u64 tb_team_arg_stage1(tb_u64 key, tb_u64* smem) {
+    constexpr int SPAN = TEAM < 32 ? TEAM : 32;
+#pragma unroll
+    for (int off = SPAN / 2; off > 0; off >>= 1) {
+        const tb_u64 other = __shfl_xor_sync(0xffffffffu, key, off, SPAN);
+        key = other > key ? other : key;
+    }
+    if (TEAM > 32 && (threadIdx.x & 31) == 0) smem[(threadIdx.x % TEAM) >> 5] = key;
+    return key;
+}
+template <int TEAM>
+__device__ __forceinline__ tb_u32 tb_team_arg_stage2(tb_u64 key, const tb_u64* smem) {
+    if (TEAM > 32) {
+        key = smem[0];
+#pragma unroll
+        for (int w = 1; w < TEAM / 32; ++w) key = smem[w] > key ? smem[w] : key;
+    }
+    return ~(tb_u32)key;
+}
+
 // Stage 2 (after a __syncthreads): every thread folds the warp values in warp order.
 template <int TEAM, float (*OP)(float, float)>
 __device__ __forceinline__ float tb_team_reduce_stage2(float v, const float* smem) {

@@ -31,7 +31,16 @@ namespace {
 
 enum Shape { FULL = THOR_B200_SHAPE_FULL, ROW = THOR_B200_SHAPE_ROW, COL = THOR_B200_SHAPE_COL, SCALAR = THOR_B200_SHAPE_SCALAR };
 
-bool isReduce(uint16_t op) { return (op >= THOR_B200_OP_REDUCE_SUM && op <= THOR_B200_OP_REDUCE_MAX) || (op >= THOR_B200_OP_REDUCE_AVG && op <= THOR_B200_OP_REDUCE_NORM2); }
+// value reductions and arg reductions (the latter only along the columns of a row program, as [rows] uint32 outputs)
+bool isReduce(uint16_t op) {
+    return (op >= THOR_B200_OP_REDUCE_SUM && op <= THOR_B200_OP_REDUCE_ARGMAX) || (op >= THOR_B200_OP_REDUCE_AVG && op <= THOR_B200_OP_REDUCE_NORM2) || op == 0xF001;
+}
+bool isArgReduce(uint16_t op) { return op == THOR_B200_OP_REDUCE_ARGMIN || op == THOR_B200_OP_REDUCE_ARGMAX; }
+// Internal op: index of the first column whose value equals the row's min / max, which another node of the program
+// (rhs) already computes.  An arg reduction that sits beside the matching value reduction is rewritten to this: the
+// search costs a compare and an integer min per element and runs one round after the value reduction.
+constexpr uint16_t kOpFirstMatch = 0xF001;
+bool isIndexReduce(uint16_t op) { return isArgReduce(op) || op == kOpFirstMatch; }
 bool isLeaf(uint16_t op) { return op >= THOR_B200_OP_INPUT && op <= THOR_B200_OP_SCALAR_FP; }
 
 struct Program {
@@ -93,7 +102,7 @@ std::string analyse(Program& p) {
     for (size_t k = n; k-- > 0;) {
         if (!p.live[k]) continue;
         for (uint32_t par : {p.nodes[k].lhs, p.nodes[k].rhs, p.nodes[k].aux})
-            if (par != THOR_B200_NO_NODE && !(isReduce(p.nodes[k].op) && par != p.nodes[k].lhs)) {
+            if (par != THOR_B200_NO_NODE && !(isReduce(p.nodes[k].op) && par != p.nodes[k].lhs && !(p.nodes[k].op == kOpFirstMatch && par == p.nodes[k].rhs))) {
                 if (par >= k) return "nodes are not topologically ordered";
                 p.live[par] = true;
             }
@@ -114,10 +123,15 @@ std::string analyse(Program& p) {
         if (isReduce(nd.op)) {
             const int ps = p.shape[nd.lhs];
             consumers[nd.lhs]++;
+            if (isIndexReduce(nd.op) && (nd.input_slot != 0 || nd.output_dtype != THOR_B200_UINT32)) return "arg reductions of a row program run along the columns and yield uint32";
             if (nd.input_slot == 0) {
                 if (ps != FULL) return "a row reduction needs a [rows, cols] argument";
                 p.shape[k] = ROW;
                 p.depth[k] = p.depth[nd.lhs] + 1;
+                if (nd.op == kOpFirstMatch) {
+                    consumers[nd.rhs]++;
+                    p.depth[k] = std::max(p.depth[nd.lhs], p.depth[nd.rhs]) + 1;
+                }
                 p.row_reduces.push_back(static_cast<uint32_t>(k));
             } else if (nd.input_slot == 1) {
                 if (ps != FULL) return "a column reduction needs a [rows, cols] argument";
@@ -151,6 +165,8 @@ std::string analyse(Program& p) {
     }
     for (uint32_t k : p.col_reduces)
         if (consumers[k] != 0) return "a column reduction may only be an output";
+    for (uint32_t k : p.row_reduces)
+        if (isIndexReduce(p.nodes[k].op) && consumers[k] != 0) return "an arg reduction may only be an output";
     if (!p.all_reduces.empty()) {
         // flat reduce program: every output is a reduction over all elements of an elementwise expression
         if (!p.row_reduces.empty() || !p.col_reduces.empty()) return "full reductions cannot be mixed with row or column reductions";
@@ -307,7 +323,8 @@ bool hoistLinearRowSums(Program& p) {
             continue;
         }
         for (uint32_t* par : {&nd.lhs, &nd.rhs, &nd.aux})
-            if (*par != THOR_B200_NO_NODE && !(isReduce(nd.op) && par != &nd.lhs)) *par = remap[*par] != THOR_B200_NO_NODE ? remap[*par] : *par;
+            if (*par != THOR_B200_NO_NODE && !(isReduce(nd.op) && par != &nd.lhs && !(nd.op == kOpFirstMatch && par == &nd.rhs)))
+                *par = remap[*par] != THOR_B200_NO_NODE ? remap[*par] : *par;
         remap[k] = push(nd);
     }
     if (!changed) return false;
@@ -550,8 +567,15 @@ std::string emit(Program& p) {
     // persistent programs alternate between two sets of exchange slots from row to row, so that a row's
     // slots are not rewritten before every thread has passed a barrier of the row in between
     os << "    __shared__ float red_smem_all[" << (p.persistent ? 2 : 1) << "][" << std::max<size_t>(1, p.row_reduces.size()) << "][TEAMS][TEAM > 32 ? TEAM / 32 : 1];\n";
+    bool any_arg = false;
+    for (uint32_t k : p.row_reduces) any_arg = any_arg || isIndexReduce(p.nodes[k].op);
+    if (any_arg)
+        os << "    __shared__ tb_u64 red_key_all[" << (p.persistent ? 2 : 1) << "][" << p.row_reduces.size() << "][TEAMS][TEAM > 32 ? TEAM / 32 : 1];\n";
     if (p.persistent) os << "    int red_set = 0;\n";
-    else os << "    float (*red_smem)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_smem_all[0];\n";
+    else {
+        os << "    float (*red_smem)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_smem_all[0];\n";
+        if (any_arg) os << "    tb_u64 (*red_key)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_key_all[0];\n";
+    }
     os << "    const int t = threadIdx.x % TEAM, team_id = threadIdx.x / TEAM;\n";
     for (size_t s = 0; s < p.inputs.size(); ++s)
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == SCALAR))
@@ -638,7 +662,10 @@ std::string emit(Program& p) {
         declareFull("f", I);
         loadFull("f", "row", guard, I);
     }
-    if (p.persistent) os << I << "float (*red_smem)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_smem_all[red_set];\n";
+    if (p.persistent) {
+        os << I << "float (*red_smem)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_smem_all[red_set];\n";
+        if (any_arg) os << I << "tb_u64 (*red_key)[TEAMS][TEAM > 32 ? TEAM / 32 : 1] = red_key_all[red_set];\n";
+    }
     // ROW inputs
     for (size_t s = 0; s < p.inputs.size(); ++s)
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == ROW)
@@ -669,6 +696,17 @@ std::string emit(Program& p) {
         os << I << "// round " << d << ": " << round.size() << " row reduction(s)\n";
         auto isMinMax = [&](uint32_t k) { return p.nodes[k].op == THOR_B200_OP_REDUCE_MIN || p.nodes[k].op == THOR_B200_OP_REDUCE_MAX; };
         for (uint32_t k : round) {
+            if (p.nodes[k].op == kOpFirstMatch) {
+                const uint32_t m = p.nodes[k].rhs;
+                os << I << "tb_u32 i" << k << " = 0xffffffffu;\n" << I << "const float m" << k << " = " << convertExpression("v" + std::to_string(m), p.nodes[m].output_dtype, THOR_B200_FP32)
+                   << ";\n" << I << "const bool mnan" << k << " = m" << k << " != m" << k << ";  // a NaN extreme matches the first NaN\n";
+                continue;
+            }
+            if (isArgReduce(p.nodes[k].op)) {
+                os << I << "float r" << k << " = " << (p.nodes[k].op == THOR_B200_OP_REDUCE_ARGMAX ? "__int_as_float(0xff800000)" : "__int_as_float(0x7f800000)") << ";\n"
+                   << I << "tb_u32 i" << k << " = 0xffffffffu, n" << "an_i" << k << " = 0xffffffffu;  // no candidate, no NaN yet\n";
+                continue;
+            }
             if (p.pairs) os << I << "float2 q" << k << " = tb_both(" << identityExpr(p.nodes[k].op) << ");  // one partial per lane\n";
             else os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
             if (isMinMax(k)) os << I << "bool nan" << k << " = false;  // min / max: fminf / fmaxf plus a sticky NaN predicate per element\n";
@@ -684,6 +722,20 @@ std::string emit(Program& p) {
                 const uint16_t op = p.nodes[k].op;
                 const std::string acc = "q" + std::to_string(k);
                 const std::string II = I + "            ";
+                if (op == kOpFirstMatch) {
+                    const std::string arg = pairReduceArg(p, a, II, os);
+                    os << II << "{ const float2 a" << k << " = " << arg << "; i" << k << " = min(i" << k << ", (a" << k << ".x == m" << k << " || (mnan" << k << " && a" << k << ".x != a" << k
+                       << ".x)) ? (tb_u32)(q * VEC + j) : 0xffffffffu); i" << k << " = min(i" << k << ", (a" << k << ".y == m" << k << " || (mnan" << k << " && a" << k << ".y != a" << k
+                       << ".y)) ? (tb_u32)(q * VEC + j + 1) : 0xffffffffu); }\n";
+                    continue;
+                }
+                if (isArgReduce(op)) {
+                    const std::string arg = pairReduceArg(p, a, II, os);
+                    const char* mx = op == THOR_B200_OP_REDUCE_ARGMAX ? "true" : "false";
+                    os << II << "{ const float2 a" << k << " = " << arg << "; tb_arg_scan<" << mx << ">(r" << k << ", i" << k << ", nan_i" << k << ", a" << k
+                       << ".x, q * VEC + j); tb_arg_scan<" << mx << ">(r" << k << ", i" << k << ", nan_i" << k << ", a" << k << ".y, q * VEC + j + 1); }\n";
+                    continue;
+                }
                 if ((op == THOR_B200_OP_REDUCE_SUM || op == THOR_B200_OP_REDUCE_AVG) && storedAsHeld(p, a) && elementLevel(p, a)) {
                     os << II << acc << " = " << pairPlus(p, a, acc) << ";\n";
                 } else if (op == THOR_B200_OP_REDUCE_SUM || op == THOR_B200_OP_REDUCE_AVG) {
@@ -709,7 +761,13 @@ std::string emit(Program& p) {
             for (uint32_t k : round) {
                 const uint32_t a = p.nodes[k].lhs;
                 const std::string f = reduceArgF32(p, a, "v" + std::to_string(a));
-                if (isMinMax(k))
+                if (p.nodes[k].op == kOpFirstMatch)
+                    os << I << "            { const float a" << k << " = " << f << "; i" << k << " = min(i" << k << ", (a" << k << " == m" << k << " || (mnan" << k << " && a" << k << " != a" << k
+                       << ")) ? (tb_u32)(q * VEC + j) : 0xffffffffu); }\n";
+                else if (isArgReduce(p.nodes[k].op))
+                    os << I << "            tb_arg_scan<" << (p.nodes[k].op == THOR_B200_OP_REDUCE_ARGMAX ? "true" : "false") << ">(r" << k << ", i" << k << ", nan_i" << k << ", " << f
+                       << ", q * VEC + j);\n";
+                else if (isMinMax(k))
                     os << I << "            { const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
                        << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
                 else
@@ -719,6 +777,7 @@ std::string emit(Program& p) {
         os << I << "        }\n" << I << "    }\n" << I << "}\n";
         if (p.pairs)
             for (uint32_t k : round) {
+                if (isIndexReduce(p.nodes[k].op)) continue;
                 const bool mm = isMinMax(k);
                 os << I << "float r" << k << " = " << (mm ? (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") : combineExpr(p.nodes[k].op)) << "(q" << k << ".x, q" << k << ".y);\n";
             }
@@ -727,13 +786,27 @@ std::string emit(Program& p) {
         for (uint32_t k : round) {
             if (isMinMax(k)) os << I << "if (nan" << k << ") r" << k << " = __int_as_float(0x7fffffff);\n";
             const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
-            os << I << "r" << k << " = tb_team_reduce_stage1<TEAM, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][team_id]);\n";
+            if (p.nodes[k].op == kOpFirstMatch)
+                os << I << "tb_u64 key" << k << " = tb_team_arg_stage1<TEAM>((tb_u64)(tb_u32)~i" << k << ", red_key[" << idx << "][team_id]);  // max of ~index = lowest index\n";
+            else if (isArgReduce(p.nodes[k].op))
+                os << I << "tb_arg_scan_finish<" << (p.nodes[k].op == THOR_B200_OP_REDUCE_ARGMAX ? "true" : "false") << ">(r" << k << ", i" << k << ", nan_i" << k
+                   << ", row_ok && (tb_u32)t < PPR, (tb_u32)t * VEC);\n"
+                   << I << "tb_u64 key" << k << " = tb_team_arg_stage1<TEAM>(tb_arg_key<" << (p.nodes[k].op == THOR_B200_OP_REDUCE_ARGMAX ? "true" : "false") << ">(r" << k
+                   << ", i" << k << "), red_key[" << idx << "][team_id]);\n";
+            else
+                os << I << "r" << k << " = tb_team_reduce_stage1<TEAM, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][team_id]);\n";
             ++slot;
         }
         os << I << "if (TEAM > 32) __syncthreads();\n";
         for (uint32_t k : round) {
             const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
             const auto& nd = p.nodes[k];
+            if (isIndexReduce(nd.op)) {
+                // only the team's first thread stores the index, so only it folds the warp keys
+                os << I << "tb_u32 v" << k << " = 0u;\n" << I << "if (t == 0) v" << k << " = tb_team_arg_stage2<TEAM>(key" << k << ", red_key[" << idx << "][team_id]);\n";
+                emitted[k] = true;
+                continue;
+            }
             os << I << "r" << k << " = tb_team_reduce_stage2<TEAM, " << combineExpr(nd.op) << ">(r" << k << ", red_smem[" << idx << "][team_id]);\n";
             std::string fin = "r" + std::to_string(k);
             if (nd.op == THOR_B200_OP_REDUCE_AVG) fin = "(" + fin + " / " + std::to_string(p.cols) + ".0f)";
@@ -1010,6 +1083,20 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         TB_REQUIRE(p.inputs[s].kind >= 0 && p.inputs[s].kind <= 2, "rowprog_compile: input %zu has an unknown kind", s);
         TB_REQUIRE(dtypeSize(p.inputs[s].dtype) != 0 && p.inputs[s].dtype != THOR_B200_FP64, "rowprog_compile: input %zu has an unsupported dtype", s);
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR) TB_REQUIRE(p.input_shape[s] >= 0 && p.input_shape[s] <= 3, "rowprog_compile: input %zu has an unknown shape class", s);
+    }
+    // an arg reduction beside the min / max of the same values becomes "first column that equals that min / max"
+    for (size_t k = 0; k < p.nodes.size(); ++k) {
+        auto& nd = p.nodes[k];
+        if (!isArgReduce(nd.op) || nd.input_slot != 0) continue;
+        const uint16_t value_op = nd.op == THOR_B200_OP_REDUCE_ARGMAX ? THOR_B200_OP_REDUCE_MAX : THOR_B200_OP_REDUCE_MIN;
+        for (size_t m = 0; m < k; ++m) {
+            const auto& vm = p.nodes[m];
+            if (vm.op == value_op && vm.input_slot == 0 && vm.lhs == nd.lhs && vm.output_dtype == THOR_B200_FP32) {
+                nd.op = kOpFirstMatch;
+                nd.rhs = static_cast<uint32_t>(m);
+                break;
+            }
+        }
     }
     std::string why = analyse(p);
     if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());

@@ -167,7 +167,8 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
     for (uint32_t k = 0; k < n; ++k) {
         if (!needed[k]) continue;
         const ExprNode& nd = g.nodes[k];
-        if (isArgReductionOp(nd.op) || isMinMaxBackwardOp(nd.op)) return {};
+        if (isMinMaxBackwardOp(nd.op)) return {};
+        if (isArgReductionOp(nd.op) && *nd.output_dtype != DataType::UINT32) return {};
         if (isViewOp(nd.op)) {
             // squeeze / unsqueeze / reshape of a value whose class does not change is an alias
             const int a = classify(ctx.shape[nd.lhs]), b = classify(ctx.shape[k]);
@@ -214,7 +215,7 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
         } else if (nd.op == ExprOp::SCALAR_FP) {
             cn.op = THOR_B200_OP_SCALAR_FP;
             cn.scalar_fp = nd.scalar_fp;
-        } else if (isValueReductionOp(nd.op)) {
+        } else if (isReductionOp(nd.op)) {
             const auto& in_shape = ctx.shape[nd.lhs];
             if (classify(in_shape) != THOR_B200_SHAPE_FULL) return {};
             const size_t pad = frame.size() - in_shape.size();
@@ -229,6 +230,7 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
                 if (!reduced[i]) all = false;
             }
             if (!only_last && !all_but_last && !all) return {};
+            if (isArgReductionOp(nd.op) && !only_last) return {};  // arg reductions are fused along the columns only
             cn.op = static_cast<uint16_t>(nd.op);
             cn.lhs = remap.at(nd.lhs);
             cn.input_slot = all ? 2u : (only_last ? 0u : 1u);
@@ -241,6 +243,12 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
         }
         remap[k] = static_cast<uint32_t>(nodes.size());
         nodes.push_back(cn);
+    }
+    // an equation whose only reductions are arg reductions keeps the dedicated arg-reduction kernels
+    {
+        bool any_value_reduction = false;
+        for (uint32_t k = 0; k < n; ++k) any_value_reduction = any_value_reduction || (needed[k] && isValueReductionOp(g.nodes[k].op));
+        if (!any_value_reduction) return {};
     }
     std::vector<thor_b200_expr_output> outs;
     for (const auto& o : ctx.outputs) {
