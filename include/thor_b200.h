@@ -394,6 +394,21 @@ THOR_B200_API void thor_b200_rowprog_destroy(thor_b200_rowprog* prog);
 THOR_B200_API int thor_b200_reduce_full_noalloc(int op, const void* input, int input_dtype, uint64_t n, void* output, int output_dtype,
                                                 float output_scale, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Multi-GPU: the one collective of the path.  Rows / flat ranges shard across GPUs without any
+ * communication; only values reduced over the sharded dimension (full reductions, LayerNorm
+ * dgamma / dbeta column sums) are combined, with one in-place fp32 allreduce of the per-GPU
+ * partials over NCCL (one process per GPU).  No counterpart in the reference, which is single-GPU
+ * on this path.  NCCL is loaded at run time (libnccl.so.2, or $THOR_B200_NCCL_LIB); rank 0 obtains
+ * the 128-byte id and hands it to the other ranks by any host channel.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct thor_b200_comm thor_b200_comm;
+THOR_B200_API int thor_b200_comm_unique_id(void* out_id_128_bytes);
+THOR_B200_API int thor_b200_comm_init(int nranks, int rank, const void* unique_id_128_bytes, thor_b200_comm** out_comm);
+/* op: 0 = sum, 1 = max, 2 = min.  Asynchronous on `stream`; every rank must make the same calls in the same order. */
+THOR_B200_API int thor_b200_comm_allreduce_f32(thor_b200_comm* comm, void* buffer, uint64_t count, int op, void* stream);
+THOR_B200_API void thor_b200_comm_destroy(thor_b200_comm* comm);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,70 @@
+"""The C ABI's NCCL allreduce of fp32 partials (thor_b200_comm_*): one rank on one GPU, and two ranks as two
+processes when the machine has two GPUs (NVLS off, plain rings: the ranks only exchange 64 KiB)."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_single_rank_allreduce_is_the_identity():
+    from thor_b200.sharding import Communicator
+
+    comm = Communicator(1, 0, Communicator.unique_id())
+    x = torch.arange(16384, dtype=torch.float32, device="cuda")
+    want = x.clone()
+    for op in ("sum", "max", "min"):
+        comm.allreduce(x, op)
+    torch.cuda.synchronize()
+    assert torch.equal(x, want)
+    comm.close()
+
+
+_RANK_SCRIPT = r"""
+import os, sys, time, torch
+rank, world, id_path = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+torch.cuda.set_device(rank)
+from thor_b200.sharding import Communicator
+if rank == 0:
+    uid = Communicator.unique_id()
+    with open(id_path + ".tmp", "wb") as f: f.write(uid)
+    os.replace(id_path + ".tmp", id_path)
+else:
+    for _ in range(600):
+        if os.path.exists(id_path): break
+        time.sleep(0.05)
+    uid = open(id_path, "rb").read()
+comm = Communicator(world, rank, uid)
+sums = torch.full((16384,), float(rank + 1), device="cuda")
+maxima = torch.tensor([float(rank), -float(rank)], device="cuda")
+comm.allreduce(sums, "sum")
+comm.allreduce(maxima, "max")
+torch.cuda.synchronize()
+assert bool((sums == sum(range(1, world + 1))).all()), sums[:4]
+assert maxima.tolist() == [float(world - 1), 0.0], maxima
+comm.close()
+print("rank", rank, "ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_combine_partials():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    with tempfile.TemporaryDirectory() as d:
+        id_path = os.path.join(d, "nccl_id")
+        procs = [subprocess.Popen([sys.executable, "-c", _RANK_SCRIPT, str(r), "2", id_path], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                 for r in range(2)]
+        outs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=120)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                out, _ = p.communicate()
+            outs.append(out)
+        for r, (p, out) in enumerate(zip(procs, outs)):
+            assert p.returncode == 0 and f"rank {r} ok" in out, out[-2000:]

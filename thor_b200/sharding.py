@@ -44,3 +44,52 @@ def finalize_mean(total: torch.Tensor, global_count: int) -> torch.Tensor:
     """Mean of a sharded reduction: divide the allreduced fp32 sum by the global element count (fp32 division,
     like the reduction seam's finaliser)."""
     return total / torch.tensor(float(global_count), dtype=torch.float32, device=total.device)
+
+
+class Communicator:
+    """The C ABI's NCCL allreduce (thor_b200_comm_*), for callers that do not go through torch.distributed.
+    Rank 0 creates the id with ``Communicator.unique_id()`` and hands the 128 bytes to the other ranks."""
+
+    def __init__(self, nranks: int, rank: int, unique_id: bytes):
+        import ctypes as C
+
+        from . import _native
+
+        self._lib = _native.lib
+        self._lib.thor_b200_comm_init.argtypes = [C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)]
+        self._lib.thor_b200_comm_allreduce_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
+        self._lib.thor_b200_comm_destroy.argtypes = [C.c_void_p]
+        self._lib.thor_b200_comm_destroy.restype = None
+        if len(unique_id) != 128:
+            raise ValueError("the NCCL id is 128 bytes")
+        self._h = C.c_void_p()
+        _native.check(self._lib.thor_b200_comm_init(nranks, rank, unique_id, C.byref(self._h)))
+
+    @staticmethod
+    def unique_id() -> bytes:
+        import ctypes as C
+
+        from . import _native
+
+        buf = C.create_string_buffer(128)
+        _native.lib.thor_b200_comm_unique_id.argtypes = [C.c_char_p]
+        _native.check(_native.lib.thor_b200_comm_unique_id(buf))
+        return buf.raw
+
+    def allreduce(self, t: torch.Tensor, op: str = "sum", stream=None) -> None:
+        from . import _native
+
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError("allreduce takes a contiguous fp32 CUDA tensor")
+        _native.check(self._lib.thor_b200_comm_allreduce_f32(self._h, t.data_ptr(), t.numel(), {"sum": 0, "max": 1, "min": 2}[op], _native.stream_handle(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.thor_b200_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
