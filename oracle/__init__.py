@@ -99,6 +99,44 @@ def reference_gpu_cast(src_ptr: int, dst_ptr: int, src_dtype: int, dst_dtype: in
     assert rc == 0, f"reference GPU conversion failed ({rc})"
 
 
+_ref_emit = None
+
+
+def reference_emitter_lib():
+    """The reference's own flat fused-kernel emitter behind a dumper, or None when oracle/_ref holds no build of it."""
+    global _ref_emit
+    if _ref_emit is None:
+        path = HERE / "_ref" / "libthor_ref_emit.so"
+        if not path.exists():
+            return None
+        _ref_emit = ctypes.CDLL(str(path))
+        c = ctypes
+        _ref_emit.thor_ref_emit_flat.argtypes = [c.c_char_p, c.POINTER(c.c_char_p), c.POINTER(c.c_int), c.c_int, c.POINTER(c.c_char_p), c.POINTER(c.c_uint),
+                                                 c.POINTER(c.c_int), c.POINTER(c.c_int)]
+        _ref_emit.thor_ref_emit_flat.restype = c.c_int
+    return _ref_emit
+
+
+def reference_emit_flat(program: str, input_dtypes: dict):
+    """CUDA source that the reference's CudaSourceEmitter::emitFlat generates for a postfix `program`
+    (tokens: in:<name> rs:<name> lit:<value> cast:<dtype> add sub mul div pow min max and the unary op names).
+    `input_dtypes` maps every tensor input / fp32 runtime scalar name to its dtype.
+    Returns (source, elements_per_thread, input names in kernel-parameter order, output dtype)."""
+    lib_ = reference_emitter_lib()
+    assert lib_ is not None, "oracle/_ref/libthor_ref_emit.so has not been built"
+    names = list(input_dtypes.keys())
+    c = ctypes
+    arr_n = (c.c_char_p * len(names))(*[n.encode() for n in names])
+    arr_d = (c.c_int * len(names))(*[int(input_dtypes[n]) for n in names])
+    src, ept, out_dt = c.c_char_p(), c.c_uint(), c.c_int()
+    order = (c.c_int * max(1, len(names)))(*([-1] * max(1, len(names))))
+    rc = lib_.thor_ref_emit_flat(program.encode(), arr_n, arr_d, len(names), c.byref(src), c.byref(ept), order, c.byref(out_dt))
+    text = src.value.decode()
+    if rc != 0:
+        raise RuntimeError("reference emitter: " + text)
+    return text, int(ept.value), [names[i] for i in order if i >= 0], int(out_dt.value)
+
+
 def _ptr(a: np.ndarray) -> ctypes.c_void_p:
     return ctypes.c_void_p(a.ctypes.data)
 

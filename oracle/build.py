@@ -4,6 +4,9 @@
 * ``_ref/libthor_ref_cast.so``   — the REFERENCE's own CPU cast path, compiled from the reference
   checkout where it lies (only when that checkout is present; the output is git-ignored and is
   carried to the GPU machine as a built file).  Nothing is copied out of the reference tree.
+* ``_ref/libthor_ref_emit.so``  — the REFERENCE's own expression builder, dtype resolution and CUDA source emitter
+  (three host sources, g++) behind a dumper: the tests compile the kernels it emits with NVRTC and run them
+  beside ours on the same buffers.
 * ``_ref/libthor_ref_gpu_cast.so`` — the REFERENCE's own GPU cast kernels (TypeConverterKernels.cu,
   nvcc for sm_100a, about 90 s), same rules; the parity tests compare against it bit for bit and the
   benchmark times it beside our kernel.
@@ -104,8 +107,45 @@ def build_reference_gpu_cast(force: bool = False) -> Path | None:
     return out
 
 
+def build_reference_emitter(force: bool = False) -> Path | None:
+    """Compile the reference's expression builder, dtype resolution and CUDA source emitter (three host sources,
+    g++ -std=c++23, about 15 s) with the dumper in ref_emit.cpp into _ref/; None when that cannot be done here."""
+    out = REF_OUT / "libthor_ref_emit.so"
+    shim = HERE / "ref_emit.cpp"
+    ref_srcs = [REFERENCE_DIR / "Utilities/Expression" / n for n in ("CudaSourceEmitter.cpp", "Expression.cpp", "ExpressionDTypeResolution.cpp")]
+    if not all(p.exists() for p in ref_srcs):
+        return out if out.exists() else None
+    REF_OUT.mkdir(exist_ok=True)
+    if not force and not _stale(out, [shim, *ref_srcs]):
+        return out
+    verdir = REF_OUT / "generated"
+    verdir.mkdir(exist_ok=True)
+    (verdir / "ThorVersion.h").write_text('#pragma once\n#define THOR_VERSION "0.0.33"\n#define THOR_GIT_VERSION "unknown"\n')
+    objdir = REF_OUT / "obj"
+    objdir.mkdir(exist_ok=True)
+    common = ["g++", "-std=c++23", "-O1", "-fopenmp", "-fPIC", "-fvisibility=hidden", "-ffunction-sections", "-fdata-sections",
+              "-I", str(REFERENCE_DIR), "-I", str(verdir), "-I", str(CUDA_INCLUDE)]
+    for d in _site_include_dirs():
+        common += ["-I", str(d)]
+    objs = []
+    for src in [shim, *ref_srcs]:
+        obj = objdir / (src.stem + ".o")
+        _run(common + ["-c", str(src), "-o", str(obj)])
+        objs.append(obj)
+    # only the dumper's entry point is exported; everything it cannot reach is dropped, and -z defs proves the rest resolves
+    _run(["g++", "-shared", "-fopenmp", "-o", str(out), *map(str, objs), "-Wl,--gc-sections", "-Wl,-z,defs"])
+    shutil.rmtree(objdir, ignore_errors=True)
+    return out
+
+
 def build_all(force: bool = False) -> dict:
     result = {"oracle": str(build_oracle(force))}
+    try:
+        emit = build_reference_emitter(force)
+        result["reference_emitter"] = str(emit) if emit else None
+    except RuntimeError as exc:
+        result["reference_emitter"] = None
+        result["reference_emitter_error"] = str(exc)[-2000:]
     try:
         ref_gpu = build_reference_gpu_cast(force)
         result["reference_gpu_cast"] = str(ref_gpu) if ref_gpu else None

@@ -1,0 +1,98 @@
+"""Our fused stages against the kernels that the REFERENCE's own emitter generates for the same expressions
+(CudaSourceEmitter::emitFlat compiled from the reference checkout into oracle/_ref, NVRTC with the reference's
+flags), on the same device buffers.  16-bit stages use the same pair intrinsics and must agree bit for bit;
+fp32 stages call the same libdevice functions under -fmad=true and must agree within 2 fp32 ulp with almost
+all elements identical (the compiler may place a fused multiply-add differently in the two sources)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from oracle import expr_oracle as eo
+from thor_b200 import DataType
+from thor_b200.expression import Expression as ex
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(o.reference_emitter_lib() is None, reason="the reference's emitter is not built (oracle/_ref)")]
+
+from _refkernel import run_reference_flat  # noqa: E402
+
+_T = {o.FP32: torch.float32, o.FP16: torch.float16, o.BF16: torch.bfloat16}
+
+
+def _ours(program: str, tensors, scalars):
+    """The same postfix program through this repository's Expression API."""
+    stack = []
+    for tok in program.split():
+        if tok.startswith("in:"):
+            stack.append(ex.input(tok[3:]))
+        elif tok.startswith("rs:"):
+            stack.append(ex.runtime_scalar(tok[3:]))
+        elif tok.startswith("lit:"):
+            stack.append(float(tok[4:]))
+        elif tok.startswith("cast:"):
+            stack.append(stack.pop().cast(DataType(int(tok[5:]))))
+        elif tok in ("add", "sub", "mul", "div", "pow", "min", "max"):
+            b, a = stack.pop(), stack.pop()
+            if isinstance(a, float):
+                a = ex.scalar(a)
+            stack.append({"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "div": lambda: a / b, "pow": lambda: a.pow(b),
+                          "min": lambda: a.min(b), "max": lambda: a.max(b)}[tok]())
+        elif tok == "neg":
+            stack.append(-stack.pop())
+        elif tok == "ln":
+            stack.append(stack.pop().ln())
+        else:
+            stack.append(getattr(stack.pop(), tok)())
+    plan = ex.compile(stack.pop()).stamp({**tensors, **scalars})
+    plan.run()
+    return plan
+
+
+PROGRAMS = [
+    ("c2", "in:a in:x mul rs:b add lit:0 max in:z sigmoid mul", {"b": 0.1}),
+    ("affine_tanh", "in:x in:a mul in:z add tanh", {}),
+    ("softplus_swish", "in:x softplus in:z swish mul", {}),
+    ("gelu_selu", "in:x gelu in:z selu add", {}),
+    ("exp_log", "in:x exp lit:1 add ln in:a abs sqrt mul", {}),
+    ("div_pow", "in:x in:a abs lit:0.5 add div in:z abs lit:1.5 pow add", {}),
+    ("minmax_neg", "in:x in:z min in:a neg max lit:0.25 mul", {}),
+    ("erf_expm1", "in:x erf in:z lit:0.5 mul expm1 sub", {}),
+]
+
+
+@pytest.mark.parametrize("dtype", [o.FP16, o.BF16, o.FP32])
+@pytest.mark.parametrize("name,program,scalars", PROGRAMS, ids=[p[0] for p in PROGRAMS])
+def test_fused_stage_matches_the_reference_emitted_kernel(dtype, name, program, scalars):
+    n, pad = (1 << 18) + 24, 64
+    g = torch.Generator(device="cuda").manual_seed(11)
+    tensors = {k: torch.randn(n + pad, device="cuda", generator=g).to(_T[dtype]) for k in ("a", "x", "z") if f"in:{k}" in program}
+    dts = {k: dtype for k in tensors}
+    dts.update({k: o.FP32 for k in scalars})
+    theirs, out_dtype = run_reference_flat(program, {**tensors, **scalars}, dts, n, pad)
+    plan = _ours(program, {k: v[:n] for k, v in tensors.items()}, scalars)
+    torch.cuda.synchronize()
+    ours = plan.output()
+    assert int(out_dtype) == dtype and ours.dtype == _T[dtype]
+    a = ours.float().cpu().numpy().astype(np.float64)
+    b = theirs[:n].float().cpu().numpy().astype(np.float64)
+    assert np.array_equal(np.isnan(a), np.isnan(b))
+    if dtype in (o.FP16, o.BF16):
+        same = ours.view(torch.int16).cpu().numpy() == theirs[:n].view(torch.int16).cpu().numpy()
+        assert bool((same | np.isnan(a)).all()), f"{(~same).sum()} of {n} elements differ from the reference kernel"
+    else:
+        d = eo.ulp_distance(a, b, o.FP32)
+        assert float(d.max()) <= 2.0, float(d.max())
+        assert float((d == 0).mean()) > 0.999
+
+
+def test_mixed_dtypes_and_casts_match_the_reference_emitted_kernel():
+    n, pad = 100003, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(n + pad, device="cuda", generator=g).half()
+    y = torch.randn(n + pad, device="cuda", generator=g).bfloat16()
+    program = "in:x in:y add lit:2 mul cast:10"  # fp16 + bf16 -> fp32, stored as fp16
+    theirs, out_dtype = run_reference_flat(program, {"x": x, "y": y}, {"x": o.FP16, "y": o.BF16}, n, pad)
+    plan = _ours(program, {"x": x[:n], "y": y[:n]}, {})
+    torch.cuda.synchronize()
+    assert int(out_dtype) == o.FP16
+    assert torch.equal(plan.output().view(torch.int16), theirs[:n].view(torch.int16))
