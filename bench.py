@@ -250,6 +250,7 @@ class C1Cast(Workload):
 class C1CastReferenceGpu(C1Cast):
     """Baseline, not product: the reference's own TypeConverterKernels.cu, compiled unmodified for sm_100a into
     oracle/_ref, on the same buffers and timing protocol as C1 (only listed when that build is present)."""
+    is_baseline = True
     name = "c1_cast_fp32_fp16_reference_gpu_kernels"
     description = "the reference's TypeConverter::gpuConvertType fp32->fp16, n=2^24 (baseline beside c1)"
 
@@ -369,6 +370,40 @@ class C2FusedExpr(Workload):
         oracle.c2_fused(a, x, 0.1, z, True, threads)
         dt = time.perf_counter() - t0
         return (3 * rows * self.COLS * 2 + self.COLS * 2) / dt / 1e9, f"{rows} of {self.ROWS} rows x {self.COLS} cols, one pass"
+
+
+class C2ReferenceGpu(C2FusedExpr):
+    """Baseline, not product: the kernel that the reference's own CudaSourceEmitter::emitSpecializedBroadcast generates
+    for configuration 2 (built from the reference checkout into oracle/_ref, compiled with NVRTC and the reference's
+    flags, launched with its geometry: one half2 per thread, 131072 CTAs), on the same buffers and timing protocol."""
+    is_baseline = True
+    name = "c2_fused_relu_axb_sigmoid_reference_gpu_kernel"
+    description = "the reference's emitted specialized-broadcast kernel for configuration 2 (baseline beside c2)"
+
+    def setup(self):
+        import torch
+
+        import oracle
+        from oracle.refkernel import ReferenceBroadcastKernel
+
+        if oracle.reference_emitter_lib() is None:
+            raise RuntimeError("oracle/_ref/libthor_ref_emit.so is not built")
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(1234 + self.dist.rank)
+        self.a = torch.empty(C, device="cuda", dtype=torch.float32).uniform_(0.5, 1.5, generator=gen).half()
+        self.ref = ReferenceBroadcastKernel("in:a in:x mul rs:b add lit:0 max in:z sigmoid mul", {"a": oracle.FP16, "x": oracle.FP16, "b": oracle.FP32, "z": oracle.FP16},
+                                            {"a": (C,), "x": (R, C), "z": (R, C)})
+        self.sets = []
+        for _ in range(self.n_sets(self.algorithmic_bytes())):
+            x = torch.randn(R, C, device="cuda", dtype=torch.float32, generator=gen).half()
+            z = torch.randn(R, C, device="cuda", dtype=torch.float32, generator=gen).half()
+            self.sets.append((None, x, z, torch.empty(R, C, device="cuda", dtype=torch.float16)))
+        self.launches_per_step = 1
+        self.kernel_kind = ["reference specialized broadcast (half2 per thread)"]
+
+    def step(self, i):
+        _, x, z, y = self.sets[i % len(self.sets)]
+        self.ref.launch({"a": self.a, "x": x, "b": 0.1, "z": z}, y)
 
 
 class C3Softmax(Workload):
@@ -560,7 +595,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
-             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu}
+             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu}
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -659,14 +694,14 @@ def main():
 
     if not args.no_extras:
         # end to end: pinned host buffers -> H2D -> kernel -> D2H inside the timed region
-        if hasattr(wl, "e2e_step"):
+        if hasattr(wl, "e2e_step") and not getattr(wl, "is_baseline", False):
             k = max(3, min(10, args.steps))
             e_ms, _, _ = time_steps(dist, wl.e2e_step, k, 3)
             h2d, d2h = wl.e2e_bytes()
             line["e2e"] = {"value": total_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                            "ms_per_step": e_ms}
         # CPU baseline on rank 0 at N = 1: bounded sample of the same workload
-        if world == 1 and hasattr(wl, "cpu_sample"):
+        if world == 1 and hasattr(wl, "cpu_sample") and not getattr(wl, "is_baseline", False):
             import oracle
 
             threads = oracle.host_threads()

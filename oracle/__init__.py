@@ -114,7 +114,34 @@ def reference_emitter_lib():
         _ref_emit.thor_ref_emit_flat.argtypes = [c.c_char_p, c.POINTER(c.c_char_p), c.POINTER(c.c_int), c.c_int, c.POINTER(c.c_char_p), c.POINTER(c.c_uint),
                                                  c.POINTER(c.c_int), c.POINTER(c.c_int)]
         _ref_emit.thor_ref_emit_flat.restype = c.c_int
+        _ref_emit.thor_ref_emit_broadcast.argtypes = [c.c_char_p, c.POINTER(c.c_char_p), c.POINTER(c.c_int), c.POINTER(c.c_ulonglong), c.c_int, c.POINTER(c.c_char_p),
+                                                      c.POINTER(c.c_uint), c.POINTER(c.c_int), c.POINTER(c.c_int), c.POINTER(c.c_ulonglong)]
+        _ref_emit.thor_ref_emit_broadcast.restype = c.c_int
     return _ref_emit
+
+
+def reference_emit_broadcast(program: str, input_dtypes: dict, input_dims: dict):
+    """CUDA source that the reference's CudaSourceEmitter::emitSpecializedBroadcast generates for `program` with
+    concrete dense input shapes (`input_dims[name]`, () for runtime scalars).  Returns
+    (source, elements_per_thread, input names in kernel-parameter order, output dtype, output numel)."""
+    lib_ = reference_emitter_lib()
+    assert lib_ is not None, "oracle/_ref/libthor_ref_emit.so has not been built"
+    names = list(input_dtypes.keys())
+    c = ctypes
+    arr_n = (c.c_char_p * len(names))(*[n.encode() for n in names])
+    arr_d = (c.c_int * len(names))(*[int(input_dtypes[n]) for n in names])
+    flat = []
+    for n in names:
+        dims = tuple(input_dims.get(n, ()))
+        flat += [len(dims), *dims]
+    arr_dims = (c.c_ulonglong * max(1, len(flat)))(*flat)
+    src, ept, out_dt, numel = c.c_char_p(), c.c_uint(), c.c_int(), c.c_ulonglong()
+    order = (c.c_int * max(1, len(names)))(*([-1] * max(1, len(names))))
+    rc = lib_.thor_ref_emit_broadcast(program.encode(), arr_n, arr_d, arr_dims, len(names), c.byref(src), c.byref(ept), order, c.byref(out_dt), c.byref(numel))
+    text = src.value.decode()
+    if rc != 0:
+        raise RuntimeError("reference emitter: " + text)
+    return text, int(ept.value), [names[i] for i in order if i >= 0], int(out_dt.value), int(numel.value)
 
 
 def reference_emit_flat(program: str, input_dtypes: dict):

@@ -14,7 +14,7 @@ from thor_b200.expression import Expression as ex
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(o.reference_emitter_lib() is None, reason="the reference's emitter is not built (oracle/_ref)")]
 
-from _refkernel import run_reference_flat  # noqa: E402
+from oracle.refkernel import ReferenceBroadcastKernel, run_reference_flat  # noqa: E402
 
 _T = {o.FP32: torch.float32, o.FP16: torch.float16, o.BF16: torch.bfloat16}
 
@@ -96,3 +96,38 @@ def test_mixed_dtypes_and_casts_match_the_reference_emitted_kernel():
     torch.cuda.synchronize()
     assert int(out_dtype) == o.FP16
     assert torch.equal(plan.output().view(torch.int16), theirs[:n].view(torch.int16))
+
+
+@pytest.mark.parametrize("rows,cols", [(512, 8192), (8192, 8192)])
+def test_configuration_2_matches_the_reference_broadcast_kernel_bit_for_bit(rows, cols):
+    """relu(a*x + b) * sigmoid(z) with a broadcast over the rows: the kernel CudaSourceEmitter::emitSpecializedBroadcast
+    generates for these shapes (one half2 per thread, shapes baked in) against our tiled stage, same buffers."""
+    program = "in:a in:x mul rs:b add lit:0 max in:z sigmoid mul"
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(rows, cols, device="cuda", generator=g).half()
+    z = torch.randn(rows, cols, device="cuda", generator=g).half()
+    a = (torch.rand(cols, device="cuda", generator=g) + 0.5).half()
+    ref = ReferenceBroadcastKernel(program, {"a": o.FP16, "x": o.FP16, "b": o.FP32, "z": o.FP16}, {"a": (cols,), "x": (rows, cols), "z": (rows, cols)})
+    assert ref.ept == 2 and ref.numel == rows * cols and ref.out_dtype == o.FP16
+    theirs = torch.empty(rows, cols, device="cuda", dtype=torch.float16)
+    ref.launch({"a": a, "x": x, "b": 0.1, "z": z}, theirs)
+    plan = _ours(program, {"a": a, "x": x, "z": z}, {"b": 0.1})
+    torch.cuda.synchronize()
+    assert plan.physical_stage_names() == ["bcast_tiled_v2"]
+    assert torch.equal(plan.output().view(torch.int16), theirs.view(torch.int16))
+
+
+def test_row_and_column_broadcasts_in_fp32_match_the_reference_broadcast_kernel():
+    program = "in:x in:r sub exp in:c mul"
+    rows, cols = 300, 1000
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(rows, cols, device="cuda", generator=g)
+    r = torch.randn(rows, 1, device="cuda", generator=g)
+    c = torch.randn(cols, device="cuda", generator=g)
+    ref = ReferenceBroadcastKernel(program, {"x": o.FP32, "r": o.FP32, "c": o.FP32}, {"x": (rows, cols), "r": (rows, 1), "c": (cols,)})
+    theirs = torch.empty(rows, cols, device="cuda")
+    ref.launch({"x": x, "r": r, "c": c}, theirs)
+    plan = _ours(program, {"x": x, "r": r, "c": c}, {})
+    torch.cuda.synchronize()
+    d = eo.ulp_distance(plan.output().double().cpu().numpy(), theirs.double().cpu().numpy(), o.FP32)
+    assert float(d.max()) <= 2.0 and float((d == 0).mean()) > 0.999
