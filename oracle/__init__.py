@@ -120,6 +120,24 @@ def reference_emitter_lib():
     return _ref_emit
 
 
+def reference_resolve_dtypes(program: str, input_dtypes: dict):
+    """(op, output dtype, compute dtype) of every node after the reference's resolveOutputsDTypesInPlace, in its node order."""
+    lib_ = reference_emitter_lib()
+    assert lib_ is not None, "oracle/_ref/libthor_ref_emit.so has not been built"
+    c = ctypes
+    lib_.thor_ref_resolve_dtypes.argtypes = [c.c_char_p, c.POINTER(c.c_char_p), c.POINTER(c.c_int), c.c_int, c.POINTER(c.c_int), c.c_int]
+    lib_.thor_ref_resolve_dtypes.restype = c.c_int
+    names = list(input_dtypes.keys())
+    arr_n = (c.c_char_p * len(names))(*[n.encode() for n in names])
+    arr_d = (c.c_int * len(names))(*[int(input_dtypes[n]) for n in names])
+    cap = 1024
+    buf = (c.c_int * (3 * cap))()
+    n = lib_.thor_ref_resolve_dtypes(program.encode(), arr_n, arr_d, len(names), buf, cap)
+    if n < 0:
+        raise RuntimeError("reference dtype resolution failed")
+    return [(buf[3 * k], buf[3 * k + 1], buf[3 * k + 2]) for k in range(n)]
+
+
 def reference_emit_broadcast(program: str, input_dtypes: dict, input_dims: dict):
     """CUDA source that the reference's CudaSourceEmitter::emitSpecializedBroadcast generates for `program` with
     concrete dense input shapes (`input_dims[name]`, () for runtime scalars).  Returns

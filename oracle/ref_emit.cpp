@@ -211,6 +211,36 @@ extern "C" __attribute__((visibility("default"))) int thor_ref_emit_broadcast(co
     }
 }
 
+// Runs the reference's dtype resolution on `program` and returns (op, output dtype, compute dtype) of every node of the
+// reference's graph, three ints per node, in its node order.  Returns the number of nodes, or -1 on error.
+extern "C" __attribute__((visibility("default"))) int thor_ref_resolve_dtypes(const char* program, const char* const* input_names, const int* input_dtypes,
+                                                                              int n_inputs, int* triplets, int capacity_nodes) {
+    try {
+        Expression e = buildFromPostfix(program);
+        PhysicalOutputs outputs = Expression::outputs({{"output", e}}).physicalOutputs();
+        std::vector<DataType> dtypes(outputs.expr->inputs.size(), DataType::FP32);
+        for (const NamedInput& in : outputs.expr->inputs) {
+            int found = -1;
+            for (int i = 0; i < n_inputs; ++i)
+                if (in.name == input_names[i]) found = i;
+            if (found < 0) throw std::invalid_argument("no dtype given for input '" + in.name + "'");
+            dtypes[in.slot] = static_cast<DataType>(input_dtypes[found]);
+        }
+        resolveOutputsDTypesInPlace(outputs, dtypes);
+        const auto& nodes = outputs.expr->nodes;
+        if (static_cast<int>(nodes.size()) > capacity_nodes) return -1;
+        for (size_t k = 0; k < nodes.size(); ++k) {
+            triplets[3 * k + 0] = static_cast<int>(nodes[k].op);
+            triplets[3 * k + 1] = nodes[k].output_dtype.has_value() ? static_cast<int>(nodes[k].output_dtype.value()) : 0;
+            triplets[3 * k + 2] = nodes[k].compute_dtype.has_value() ? static_cast<int>(nodes[k].compute_dtype.value()) : 0;
+        }
+        return static_cast<int>(nodes.size());
+    } catch (const std::exception& ex) {
+        g_text = ex.what();
+        return -1;
+    }
+}
+
 // Emits the flat fused kernel "fused_kernel" for `program`.  input_names / input_dtypes give the dtype of every
 // tensor input and fp32 runtime scalar by name.  On success returns 0, *source points at the generated CUDA source
 // (valid until the next call on this thread), *elements_per_thread is the reference's launch geometry

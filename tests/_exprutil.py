@@ -105,3 +105,30 @@ def assert_ulp(got: np.ndarray, want: "eo.OTensor", max_ulp: float, frac_within_
     if frac_within_1:
         frac = float((d <= 1.0).mean())
         assert frac >= frac_within_1, f"only {frac:.6f} of the elements are within 1 ulp"
+
+
+def build_postfix(program: str):
+    """The postfix mini-language of the reference-emitter dumper (oracle/ref_emit.cpp) through this repository's Expression API."""
+    from thor_b200 import DataType
+    from thor_b200.expression import Expression as ex
+
+    stack = []
+    for tok in program.split():
+        if tok.startswith("in:"):
+            stack.append(ex.input(tok[3:]))
+        elif tok.startswith("rs:"):
+            stack.append(ex.runtime_scalar(tok[3:]))
+        elif tok.startswith("lit:"):
+            stack.append(ex.scalar(float(tok[4:])))
+        elif tok.startswith("cast:"):
+            stack.append(stack.pop().cast(DataType(int(tok[5:]))))
+        elif tok in ("add", "sub", "mul", "div", "pow", "min", "max"):
+            b, a = stack.pop(), stack.pop()
+            stack.append({"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "div": lambda: a / b, "pow": lambda: a.pow(b),
+                          "min": lambda: a.min(b), "max": lambda: a.max(b)}[tok]())
+        elif tok == "neg":
+            stack.append(-stack.pop())
+        else:
+            stack.append(getattr(stack.pop(), tok)())
+    assert len(stack) == 1
+    return stack[0]

@@ -35,3 +35,32 @@ def test_fp32_stage_uses_libdevice_functions_and_four_elements_per_thread():
 def test_mixed_16_bit_inputs_promote_to_fp32_in_the_reference_too():
     _, _, _, out_dtype = o.reference_emit_flat("in:x in:y add", {"x": o.FP16, "y": o.BF16})
     assert out_dtype == o.FP32
+
+
+RESOLUTION_CASES = [
+    (C2, {"a": o.FP16, "x": o.FP16, "b": o.FP32, "z": o.FP16}),
+    (C2, {"a": o.BF16, "x": o.BF16, "b": o.FP32, "z": o.BF16}),
+    (C2, {"a": o.FP16, "x": o.FP32, "b": o.FP32, "z": o.BF16}),
+    ("in:x in:y add lit:2 mul exp", {"x": o.FP8_E4M3, "y": o.FP8_E5M2}),
+    ("in:x in:y add lit:2 mul exp", {"x": o.FP8_E4M3, "y": o.FP8_E4M3}),
+    ("in:x in:y mul cast:24 in:z add tanh", {"x": o.FP16, "y": o.FP16, "z": o.FP32}),
+    ("in:x softplus in:y gelu mul in:z selu sub", {"x": o.BF16, "y": o.FP16, "z": o.BF16}),
+    ("in:x lit:0.5 pow in:y abs sqrt div cast:10", {"x": o.FP32, "y": o.BF16}),
+    ("in:x in:y min in:z max neg expm1", {"x": o.FP8_E5M2, "y": o.BF16, "z": o.BF16}),
+]
+
+
+@pytest.mark.parametrize("program,dtypes", RESOLUTION_CASES)
+def test_dtype_resolution_agrees_with_the_reference_node_for_node(program, dtypes):
+    """Our resolveOutputsDTypesInPlace against the reference's own (ExpressionDTypeResolution.cpp:1012-1148): the set of
+    (op, output dtype, compute dtype) over all nodes is identical (the reference keeps duplicate nodes that our builder
+    shares, so multiplicities are not compared) and so is the output node."""
+    from _exprutil import build_postfix
+    from thor_b200 import DataType
+    from thor_b200.expression import resolve_dtypes
+
+    theirs = o.reference_resolve_dtypes(program, dtypes)
+    ours = resolve_dtypes({"output": build_postfix(program)}, {k: DataType(v) for k, v in dtypes.items()})
+    ours = [(int(op), int(out), int(comp)) for op, out, comp in ours]
+    assert set(ours) == set(theirs), (sorted(set(ours) - set(theirs)), sorted(set(theirs) - set(ours)))
+    assert ours[-1] == theirs[-1]

@@ -21,29 +21,9 @@ _T = {o.FP32: torch.float32, o.FP16: torch.float16, o.BF16: torch.bfloat16}
 
 def _ours(program: str, tensors, scalars):
     """The same postfix program through this repository's Expression API."""
-    stack = []
-    for tok in program.split():
-        if tok.startswith("in:"):
-            stack.append(ex.input(tok[3:]))
-        elif tok.startswith("rs:"):
-            stack.append(ex.runtime_scalar(tok[3:]))
-        elif tok.startswith("lit:"):
-            stack.append(float(tok[4:]))
-        elif tok.startswith("cast:"):
-            stack.append(stack.pop().cast(DataType(int(tok[5:]))))
-        elif tok in ("add", "sub", "mul", "div", "pow", "min", "max"):
-            b, a = stack.pop(), stack.pop()
-            if isinstance(a, float):
-                a = ex.scalar(a)
-            stack.append({"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "div": lambda: a / b, "pow": lambda: a.pow(b),
-                          "min": lambda: a.min(b), "max": lambda: a.max(b)}[tok]())
-        elif tok == "neg":
-            stack.append(-stack.pop())
-        elif tok == "ln":
-            stack.append(stack.pop().ln())
-        else:
-            stack.append(getattr(stack.pop(), tok)())
-    plan = ex.compile(stack.pop()).stamp({**tensors, **scalars})
+    from _exprutil import build_postfix
+
+    plan = ex.compile(build_postfix(program)).stamp({**tensors, **scalars})
     plan.run()
     return plan
 
