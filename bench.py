@@ -452,6 +452,48 @@ class C3SoftmaxWithArgmax(C3Softmax):
     def algorithmic_bytes(self): return 2 * self.ROWS * self.COLS * 4 + self.ROWS * 4
 
 
+class C3ReferenceStagePipeline(C3Softmax):
+    """Baseline, not product: the reference's stage list for the composed softmax -- Reduction(max), Fused(exp(x - m)),
+    Reduction(sum), Fused(e / s) -- with the two fused stages being the kernels the reference's own emitter generates
+    (oracle/_ref) and, because the reference's CUB reductions cannot be built with this toolkit, OUR row-reduction kernels
+    standing in for the two reductions.  A lower bound of what the reference's pipeline costs on this GPU: four kernels,
+    two materialised [rows, cols] fp32 intermediates."""
+    is_baseline = True
+    name = "c3_softmax_rows_fp32_reference_stage_list"
+    description = "reference stage list for softmax: its emitted fused kernels + our reductions standing in for CUB (baseline beside c3)"
+
+    def setup(self):
+        import torch
+
+        import oracle
+        from oracle.refkernel import ReferenceBroadcastKernel
+        from thor_b200.reductions import CubReduction, CubReductionOp
+
+        if oracle.reference_emitter_lib() is None:
+            raise RuntimeError("oracle/_ref/libthor_ref_emit.so is not built")
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(77 + self.dist.rank)
+        f32 = oracle.FP32
+        self.k_exp = ReferenceBroadcastKernel("in:x in:m sub exp", {"x": f32, "m": f32}, {"x": (R, C), "m": (R, 1)})
+        self.k_div = ReferenceBroadcastKernel("in:e in:s div", {"e": f32, "s": f32}, {"e": (R, C), "s": (R, 1)})
+        self.x = torch.randn(R, C, device="cuda", generator=gen) * 3.0
+        self.e = torch.empty(R, C, device="cuda")
+        self.y = torch.empty(R, C, device="cuda")
+        self.m = torch.empty(R, 1, device="cuda")
+        self.s = torch.empty(R, 1, device="cuda")
+        self.r_max = CubReduction(CubReductionOp.Max, [1]).stamp(self.x, output=self.m)
+        self.r_sum = CubReduction(CubReductionOp.Sum, [1]).stamp(self.e, output=self.s)
+        self.sets = [None]  # one buffer set: 1 GiB per tensor, far beyond L2
+        self.launches_per_step = 4
+        self.kernel_kind = ["rows reduction (ours)", "reference fused exp(x - m)", "rows reduction (ours)", "reference fused e / s"]
+
+    def step(self, i):
+        self.r_max.run()
+        self.k_exp.launch({"x": self.x, "m": self.m}, self.e)
+        self.r_sum.run()
+        self.k_div.launch({"e": self.e, "s": self.s}, self.y)
+
+
 class C3Argmax(C3Softmax):
     name = "c3_row_argmax_fp32"
     description = "row argmax of fp32 [65536,4096] per GPU -> uint32 [65536]"
@@ -564,6 +606,49 @@ class C5LayerNormFwd(Workload):
     def step(self, i): self.sets[i % len(self.sets)][0].run()
 
 
+class C5FwdReferenceStagePipeline(C5LayerNormFwd):
+    """Baseline, not product: the reference's stage list for the LayerNorm forward DAG -- Reduction(mean), Fused((x - mean)^2)
+    into an fp32 [rows, cols] temporary, Reduction(mean), Fused(normalise, scale, shift, cast) -- with the reference's own
+    emitted fused kernels and our row reductions standing in for its CUB reductions (which this toolkit cannot build)."""
+    is_baseline = True
+    name = "c5_layernorm_forward_bf16_reference_stage_list"
+    description = "reference stage list for LayerNorm forward: its emitted fused kernels + our reductions standing in for CUB (baseline beside c5 forward)"
+
+    def setup(self):
+        import torch
+
+        import oracle
+        from oracle.refkernel import ReferenceBroadcastKernel
+        from thor_b200 import DataType
+        from thor_b200.reductions import CubReduction, CubReductionOp
+
+        if oracle.reference_emitter_lib() is None:
+            raise RuntimeError("oracle/_ref/libthor_ref_emit.so is not built")
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(55 + self.dist.rank)
+        self.x, self.gamma, self.beta = self._inputs(gen)
+        f32, b16 = oracle.FP32, oracle.BF16
+        self.k_sq = ReferenceBroadcastKernel("in:x in:mean sub in:x in:mean sub mul", {"x": b16, "mean": f32}, {"x": (R, C), "mean": (R, 1)})
+        self.k_out = ReferenceBroadcastKernel("in:x in:mean sub lit:1 in:var lit:1e-05 add sqrt div mul in:gamma mul in:beta add cast:24",
+                                              {"x": b16, "mean": f32, "var": f32, "gamma": b16, "beta": b16},
+                                              {"x": (R, C), "mean": (R, 1), "var": (R, 1), "gamma": (C,), "beta": (C,)})
+        self.sq = torch.empty(R, C, device="cuda", dtype=torch.float32)
+        self.y = torch.empty(R, C, device="cuda", dtype=torch.bfloat16)
+        self.mean = torch.empty(R, 1, device="cuda")
+        self.var = torch.empty(R, 1, device="cuda")
+        self.r_mean = CubReduction(CubReductionOp.Mean, [1], output_dtype=DataType.fp32).stamp(self.x, output=self.mean)
+        self.r_var = CubReduction(CubReductionOp.Mean, [1]).stamp(self.sq, output=self.var)
+        self.sets = [None]
+        self.launches_per_step = 4
+        self.kernel_kind = ["rows reduction (ours)", "reference fused (x - mean)^2", "rows reduction (ours)", "reference fused normalise"]
+
+    def step(self, i):
+        self.r_mean.run()
+        self.k_sq.launch({"x": self.x, "mean": self.mean}, self.sq)
+        self.r_var.run()
+        self.k_out.launch({"x": self.x, "mean": self.mean, "var": self.var, "gamma": self.gamma, "beta": self.beta}, self.y)
+
+
 class C5LayerNormBwd(C5LayerNormFwd):
     name = "c5_layernorm_backward_bf16"
     description = "autodiff-generated LayerNorm backward (dx, dgamma, dbeta) over bf16 [32768,8192] per GPU; dgamma/dbeta allreduced when N > 1"
@@ -595,7 +680,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
-             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu}
+             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c5_fwd_ref_stages": C5FwdReferenceStagePipeline}
 
 
 # ---------------------------------------------------------------------------------------------------------
