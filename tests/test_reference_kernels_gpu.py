@@ -111,3 +111,31 @@ def test_row_and_column_broadcasts_in_fp32_match_the_reference_broadcast_kernel(
     torch.cuda.synchronize()
     d = eo.ulp_distance(plan.output().double().cpu().numpy(), theirs.double().cpu().numpy(), o.FP32)
     assert float(d.max()) <= 2.0 and float((d == 0).mean()) > 0.999
+
+
+def test_reference_stage_lists_compute_what_our_row_programs_compute():
+    """The benchmark's reference stage-list baselines (reference-emitted fused kernels + our reductions standing in for
+    CUB) produce the results our single row programs produce, so their times compare like with like."""
+    import bench
+
+    class _Single:
+        rank, world, enabled, local_rank = 0, 1, False, 0
+
+    sm = bench.C3ReferenceStagePipeline(_Single(), 1.0 / 256)
+    sm.setup()
+    sm.step(0)
+    xi = ex.input("x")
+    e = (xi - xi.reduce_max([1])).exp()
+    ours = ex.compile(e / e.reduce_sum([1])).stamp({"x": sm.x})
+    ours.run()
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(sm.y.cpu().numpy(), ours.output().cpu().numpy(), rtol=1e-5, atol=1e-12)
+
+    ln = bench.C5FwdReferenceStagePipeline(_Single(), 1.0 / 256)
+    ln.setup()
+    ln.step(0)
+    ours = ex.compile({"y": bench._layernorm_expr(ex)}).stamp({"x": ln.x, "gamma": ln.gamma, "beta": ln.beta})
+    ours.run()
+    torch.cuda.synchronize()
+    d = eo.ulp_distance(ours.output("y").float().cpu().numpy().astype(np.float64), ln.y.float().cpu().numpy().astype(np.float64), o.BF16)
+    assert float(d.max()) <= 1.0 and float((d == 0).mean()) > 0.99
