@@ -137,5 +137,7 @@ def test_reference_stage_lists_compute_what_our_row_programs_compute():
     ours = ex.compile({"y": bench._layernorm_expr(ex)}).stamp({"x": ln.x, "gamma": ln.gamma, "beta": ln.beta})
     ours.run()
     torch.cuda.synchronize()
-    d = eo.ulp_distance(ours.output("y").float().cpu().numpy().astype(np.float64), ln.y.float().cpu().numpy().astype(np.float64), o.BF16)
+    a, b = ours.output("y").float().cpu().numpy().astype(np.float64), ln.y.float().cpu().numpy().astype(np.float64)
+    d = eo.ulp_distance(a, b, o.BF16)
+    d = np.where(np.abs(a - b) <= 1e-7, 0.0, d)  # results that cancel to ~0: the fp32 noise of the two summation orders, not a bf16 step
     assert float(d.max()) <= 1.0 and float((d == 0).mean()) > 0.99
