@@ -141,3 +141,21 @@ def test_reference_stage_lists_compute_what_our_row_programs_compute():
     d = eo.ulp_distance(a, b, o.BF16)
     d = np.where(np.abs(a - b) <= 1e-7, 0.0, d)  # results that cancel to ~0: the fp32 noise of the two summation orders, not a bf16 step
     assert float(d.max()) <= 1.0 and float((d == 0).mean()) > 0.99
+
+
+@pytest.mark.parametrize("dtype", [o.FP8_E4M3, o.FP8_E5M2])
+@pytest.mark.parametrize("program", ["in:x in:z add lit:0.5 mul", "in:x sigmoid in:z mul", "in:x in:z max exp"])
+def test_fp8_stages_match_the_reference_emitted_kernel_bit_for_bit(dtype, program):
+    """fp8 storage computes in fp16 and is rounded to fp8 only at the store; the reference's vectorised fp8 kernels
+    (16 elements per thread) and ours must produce the same bytes."""
+    n, pad = (1 << 16) + 48, 64
+    tdt = torch.float8_e4m3fn if dtype == o.FP8_E4M3 else torch.float8_e5m2
+    g = torch.Generator(device="cuda").manual_seed(21)
+    tensors = {k: (torch.randn(n + pad, device="cuda", generator=g) * 2.0).to(tdt) for k in ("x", "z")}
+    theirs, out_dtype = run_reference_flat(program, tensors, {k: dtype for k in tensors}, n, pad)
+    plan = _ours(program, {k: v[:n] for k, v in tensors.items()}, {})
+    torch.cuda.synchronize()
+    assert int(out_dtype) == dtype and plan.output().dtype == tdt
+    a, b = plan.output().view(torch.uint8).cpu().numpy(), theirs[:n].view(torch.uint8).cpu().numpy()
+    nan = np.isnan(plan.output().float().cpu().numpy())
+    assert bool(((a == b) | nan).all()), f"{int((a != b).sum())} of {n} bytes differ from the reference kernel"
