@@ -159,3 +159,31 @@ def test_fp8_stages_match_the_reference_emitted_kernel_bit_for_bit(dtype, progra
     a, b = plan.output().view(torch.uint8).cpu().numpy(), theirs[:n].view(torch.uint8).cpu().numpy()
     nan = np.isnan(plan.output().float().cpu().numpy())
     assert bool(((a == b) | nan).all()), f"{int((a != b).sum())} of {n} bytes differ from the reference kernel"
+
+
+LAYOUTS = [
+    ("col_vector", "in:x in:c mul in:x add", {"x": (64, 300), "c": (300,)}),
+    ("middle_axis", "in:x in:m sub in:r mul", {"x": (8, 32, 64), "m": (8, 1, 64), "r": (32, 1)}),
+    ("two_way", "in:x in:y add tanh", {"x": (16, 1, 128), "y": (1, 24, 128)}),
+    ("row_scalar_4d", "in:x in:s div in:b add", {"x": (4, 6, 10, 16), "s": (4, 6, 1, 1), "b": (16,)}),
+]
+
+
+@pytest.mark.parametrize("dtype", [o.FP16, o.BF16, o.FP32])
+@pytest.mark.parametrize("name,program,dims", LAYOUTS, ids=[c[0] for c in LAYOUTS])
+def test_broadcast_layouts_match_the_reference_broadcast_kernel(dtype, name, program, dims):
+    g = torch.Generator(device="cuda").manual_seed(31)
+    tensors = {k: (torch.randn(*shape, device="cuda", generator=g) + (2.0 if k == "s" else 0.0)).to(_T[dtype]) for k, shape in dims.items()}
+    ref = ReferenceBroadcastKernel(program, {k: dtype for k in dims}, dims)
+    out_shape = torch.broadcast_shapes(*dims.values())
+    theirs = torch.zeros(out_shape, device="cuda", dtype=_T[dtype])
+    ref.launch(tensors, theirs)
+    plan = _ours(program, tensors, {})
+    torch.cuda.synchronize()
+    ours = plan.output()
+    assert tuple(ours.shape) == tuple(out_shape) and ref.numel == theirs.numel()
+    if dtype == o.FP32:
+        d = eo.ulp_distance(ours.double().cpu().numpy(), theirs.double().cpu().numpy(), o.FP32)
+        assert float(d.max()) <= 2.0 and float((d == 0).mean()) > 0.999
+    else:
+        assert torch.equal(ours.view(torch.int16), theirs.view(torch.int16)), plan.physical_stage_names()
