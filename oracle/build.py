@@ -12,7 +12,7 @@
   benchmark times it beside our kernel.
 
 Run as ``python oracle/build.py``.  The reference checkout is looked up in
-``$THOR_REFERENCE_DIR`` (default: ``/root/reference``).
+``$THOR_REFERENCE_DIR`` (the default is the REFERENCE_DIR constant below).
 """
 from __future__ import annotations
 
