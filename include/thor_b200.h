@@ -371,6 +371,11 @@ THOR_B200_API int thor_b200_rowprog_launch(thor_b200_rowprog* prog, const void* 
 THOR_B200_API const char* thor_b200_rowprog_source(const thor_b200_rowprog* prog);
 /* Kernels one launch of the program runs (1, or 2 when column reductions need the fold kernel). */
 THOR_B200_API uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* prog);
+/* Programs whose rows arrive by bulk copies wait on shared-memory barriers; every such wait has a time limit, and a
+ * wait that ran out is counted on the device instead of hanging the kernel.  Synchronises with the device and
+ * stores the count since the program was loaded (0 for programs without such waits, or never launched); a
+ * non-zero count means the outputs of the launches so far are not to be trusted. */
+THOR_B200_API int thor_b200_rowprog_waits_expired(thor_b200_rowprog* prog, uint32_t* count);
 THOR_B200_API void thor_b200_rowprog_destroy(thor_b200_rowprog* prog);
 
 /* ---------------------------------------------------------------------------------------------

@@ -165,6 +165,49 @@ __device__ __forceinline__ float tb_mul(float a, float b) { return a * b; }
 __device__ __forceinline__ float tb_nanmin(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 __device__ __forceinline__ float tb_nanmax(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
 
+// ---- bulk copies through the TMA engine (no tensor map) into a ring of row buffers, completion on an mbarrier ----
+// Every wait is bounded by wall-clock time: a wait that runs out counts in tb_wait_expired (read by the host),
+// raises the CTA's flag so that later waits give up quickly, and lets the kernel run to its end on stale data.
+#ifdef TB_BULK_RING
+__device__ unsigned int tb_wait_expired = 0;
+__device__ __forceinline__ unsigned tb_smem_addr(const void* ptr) { return static_cast<unsigned>(__cvta_generic_to_shared(ptr)); }
+__device__ __forceinline__ void tb_mbar_init(tb_u64* bar, unsigned arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tb_smem_addr(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void tb_mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tb_mbar_expect(tb_u64* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tb_smem_addr(bar)), "r"(bytes) : "memory");
+}
+// source and destination 16-byte aligned, size a multiple of 16 bytes
+__device__ __forceinline__ void tb_bulk_load(void* smem, const void* gmem, unsigned bytes, tb_u64* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(tb_smem_addr(smem)), "l"(gmem), "r"(bytes),
+                 "r"(tb_smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ tb_u64 tb_now_ns() {
+    tb_u64 ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    return ns;
+}
+__device__ __forceinline__ void tb_mbar_wait(tb_u64* bar, unsigned parity, volatile int* gave_up) {
+    const unsigned addr = tb_smem_addr(bar);
+    unsigned done = 0;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return;
+    const tb_u64 start = tb_now_ns();
+    const tb_u64 limit_ns = *gave_up ? 100000ull : 2000000000ull;
+    while (tb_now_ns() - start < limit_ns) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return;
+    }
+    if (!*gave_up) atomicAdd(&tb_wait_expired, 1u);
+    *gave_up = 1;
+}
+#endif
+
 // 16-byte asynchronous global -> shared copy (LDGSTS, bypasses registers and L1) and its group fences.
 __device__ __forceinline__ void tb_cp_async16(void* smem, const void* gmem) {
     const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));

@@ -14,6 +14,7 @@
 // accumulate per-column fp32 partials, which a small fold kernel sums in CTA order.
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <memory>
 #include <sstream>
 
@@ -62,6 +63,8 @@ struct Program {
     bool prefetch_l2 = false;  // persistent programs: only pull row r + stride into L2 (costs no registers)
     int min_ctas = 0;       // second __launch_bounds__ argument, 0 = none
     bool pairs = false;     // element loops handle two neighbouring elements per step; fp32 + - * map onto the packed f32x2 instructions
+    int ring_stages = 0;  // persistent programs: > 0 = rows arrive by bulk copies in a ring of this many shared-memory buffers
+    size_t ring_stage_bytes = 0;
     bool stage_smem = false;  // persistent programs: rows are staged in shared memory with cp.async (double buffer)
     size_t smem_bytes = 0;
     uint32_t grid = 0;
@@ -88,6 +91,30 @@ std::string transformExpr(uint16_t op, const std::string& f) {
     if (op == THOR_B200_OP_REDUCE_NORM1) return "fabsf(" + f + ")";
     if (op == THOR_B200_OP_REDUCE_NORM2) return "(" + f + " * " + f + ")";
     return f;
+}
+
+// Structurally equal nodes become one (reverse-mode differentiation repeats sub-expressions, and a repeated row sum
+// would otherwise cost an accumulator, a shuffle tree and an exchange slot of its own).  Duplicates stay in the list, dead.
+void mergeDuplicates(Program& p) {
+    const size_t n = p.nodes.size();
+    std::vector<uint32_t> canon(n);
+    auto same = [](const thor_b200_expr_node& a, const thor_b200_expr_node& b) {
+        return a.op == b.op && a.output_dtype == b.output_dtype && a.compute_dtype == b.compute_dtype && a.input_dtype == b.input_dtype && a.lhs == b.lhs &&
+               a.rhs == b.rhs && a.aux == b.aux && a.input_slot == b.input_slot && std::memcmp(&a.scalar_fp, &b.scalar_fp, sizeof(double)) == 0;
+    };
+    for (uint32_t k = 0; k < n; ++k) {
+        auto& nd = p.nodes[k];
+        const bool reduce = isReduce(nd.op);
+        for (uint32_t* par : {&nd.lhs, &nd.rhs, &nd.aux})
+            if (*par != THOR_B200_NO_NODE && *par < k && !(reduce && par != &nd.lhs && !(nd.op == kOpFirstMatch && par == &nd.rhs))) *par = canon[*par];
+        canon[k] = k;
+        for (uint32_t m = 0; m < k; ++m)
+            if (canon[m] == m && same(p.nodes[m], nd)) {
+                canon[k] = m;
+                break;
+            }
+    }
+    for (auto& o : p.outputs) o.node = canon[o.node];
 }
 
 std::string analyse(Program& p) {
@@ -545,6 +572,7 @@ std::string emit(Program& p) {
 
     os << "// generated by thor_b200: row program, " << p.nodes.size() << " nodes, rows = " << p.rows << ", cols = " << p.cols << ", team = " << TEAM
        << " threads, " << VPT << " packs of " << VEC << " per thread" << (p.persistent ? ", persistent" : "") << "\n";
+    if (p.ring_stages > 0) os << "#define TB_BULK_RING 1\n";
     os << "#include \"tb_prelude.cuh\"\n#include \"tb_rowprog.cuh\"\n\n";
     // kernel signature
     os << "extern \"C\" __global__ void __launch_bounds__(" << CTA << (p.min_ctas > 0 ? ", " + std::to_string(p.min_ctas) : std::string()) << ") row_kernel(";
@@ -613,6 +641,7 @@ std::string emit(Program& p) {
         os << indent << "    }\n" << indent << "}\n";
     };
     const std::string guard = "row_ok && q < PPR";
+    std::string ring_refill;  // ring mode: statements that refill the consumed buffer, emitted after the first barrier of the iteration
     if (p.persistent && p.stage_smem) {
         os << "    extern __shared__ uint4 tb_stage[];  // [full input][2 buffers][VPT][CTA threads] 16-byte packs, slot private to its thread\n";
         os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
@@ -635,6 +664,70 @@ std::string emit(Program& p) {
         os << I << "// the copy of this team's next row runs while the current row is computed\n";
         issue("row + row_stride", "(buf ^ 1)", I);
         os << I << "tb_cp_async_wait<1>();\n";
+    } else if (p.persistent && p.ring_stages > 0) {
+        // Rows of all [rows, cols] inputs arrive by bulk copies (one per input and iteration, covering the CTA's TEAMS
+        // consecutive rows) in a ring of STAGES buffers; a buffer is copied to registers, then refilled for the
+        // iteration STAGES ahead, so STAGES iterations of traffic are in flight per SM at no register cost.
+        os << "    constexpr int STAGES = " << p.ring_stages << ";\n    constexpr tb_u32 STAGE_BYTES = " << p.ring_stage_bytes << "u;\n";
+        os << "    extern __shared__ __align__(128) unsigned char tb_ring[];  // [STAGES][full input][TEAMS][COLS]\n";
+        os << "    __shared__ tb_u64 tb_full[STAGES];\n    __shared__ int tb_gave_up;\n";
+        os << "    const tb_u64 row_stride = (tb_u64)gridDim.x * TEAMS;\n";
+        std::ostringstream fill;  // body of: refill buffer `stage` with the rows from `r0`
+        {
+            size_t off = 0;
+            std::string total;
+            for (size_t s = 0; s < p.inputs.size(); ++s)
+                if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) total += (total.empty() ? "" : " + ") + std::to_string(p.cols * dtypeSize(p.inputs[s].dtype)) + "u";
+            fill << "const tb_u32 rows_here = ROWS - r0 < TEAMS ? (tb_u32)(ROWS - r0) : (tb_u32)TEAMS;\n";
+            fill << "tb_mbar_expect(&tb_full[stage], rows_here * (" << total << "));\n";
+            for (size_t s = 0; s < p.inputs.size(); ++s)
+                if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
+                    const size_t row_bytes = p.cols * dtypeSize(p.inputs[s].dtype);
+                    fill << "tb_bulk_load(tb_ring + stage * STAGE_BYTES + " << off << "u, in" << s << " + r0 * COLS, rows_here * " << row_bytes << "u, &tb_full[stage]);\n";
+                    off += row_bytes * teams_per_cta;
+                }
+        }
+        auto emitFill = [&](const std::string& indent) {
+            std::istringstream lines(fill.str());
+            std::string line;
+            while (std::getline(lines, line)) os << indent << line << "\n";
+        };
+        os << "    if (threadIdx.x == 0) {\n#pragma unroll\n        for (int s = 0; s < STAGES; ++s) tb_mbar_init(&tb_full[s], 1);\n        tb_gave_up = 0;\n        tb_mbar_init_fence();\n    }\n";
+        os << "    __syncthreads();\n";
+        os << "    if (threadIdx.x == 0) {\n        for (int stage = 0; stage < STAGES; ++stage) {\n            const tb_u64 r0 = (tb_u64)blockIdx.x * TEAMS + stage * row_stride;\n"
+           << "            if (r0 < ROWS) {\n";
+        emitFill("                ");
+        os << "            }\n        }\n    }\n";
+        declareFull("f", "    ");
+        os << "    tb_u32 stage = 0, parity = 0;\n";
+        os << "    for (tb_u64 row0 = (tb_u64)blockIdx.x * TEAMS; row0 < ROWS; row0 += row_stride) {  // same trip count for every team of the CTA\n";
+        os << I << "const tb_u64 row = row0 + team_id;\n" << I << "const bool row_ok = " << (teams_per_cta == 1 ? "true" : "row < ROWS") << ";\n";
+        os << I << "tb_mbar_wait(&tb_full[stage], parity, &tb_gave_up);\n";
+        os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (q < PPR) {\n";
+        {
+            size_t off = 0;
+            for (size_t s = 0; s < p.inputs.size(); ++s)
+                if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
+                    const size_t es = dtypeSize(p.inputs[s].dtype);
+                    os << I << "        f" << s << "[k] = *reinterpret_cast<const tb_pack<VEC * " << es << ">*>(tb_ring + stage * STAGE_BYTES + " << off << "u + ((tb_u32)team_id * (tb_u32)COLS + q * VEC) * "
+                       << es << "u);\n";
+                    off += p.cols * es * teams_per_cta;
+                }
+        }
+        os << I << "    }\n" << I << "}\n";
+        // the buffer can take the rows of the iteration STAGES ahead once every thread holds its packs: after the
+        // barrier of the first reduction round when the program has one, after a barrier of its own otherwise
+        {
+            std::ostringstream refill;
+            refill << I << "if (threadIdx.x == 0) {\n" << I << "    const tb_u64 r0 = row0 + STAGES * row_stride;\n" << I << "    if (r0 < ROWS) {\n";
+            std::istringstream lines(fill.str());
+            std::string line;
+            while (std::getline(lines, line)) refill << I << "        " << line << "\n";
+            refill << I << "    }\n" << I << "}\n";
+            refill << I << "if (++stage == STAGES) {\n" << I << "    stage = 0;\n" << I << "    parity ^= 1;\n" << I << "}\n";
+            if (TEAM > 32 && max_depth >= 1) ring_refill = refill.str();
+            else os << I << "__syncthreads();\n" << refill.str();
+        }
     } else if (p.persistent && p.prefetch) {
         os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
         declareFull("f", "    ");
@@ -798,6 +891,10 @@ std::string emit(Program& p) {
             ++slot;
         }
         os << I << "if (TEAM > 32) __syncthreads();\n";
+        if (!ring_refill.empty()) {
+            os << ring_refill;
+            ring_refill.clear();
+        }
         for (uint32_t k : round) {
             const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
             const auto& nd = p.nodes[k];
@@ -864,6 +961,8 @@ std::string emit(Program& p) {
     if (p.persistent) os << I << "red_set ^= 1;\n";
     if (p.persistent && p.stage_smem) {
         os << I << "buf ^= 1;\n";
+    } else if (p.persistent && p.ring_stages > 0) {
+        // nothing to hand over: the next iteration reads its own buffer
     } else if (p.persistent && p.prefetch) {
         os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n";
         for (size_t s = 0; s < p.inputs.size(); ++s)
@@ -1098,10 +1197,12 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
             }
         }
     }
+    mergeDuplicates(p);
     std::string why = analyse(p);
     if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
     if (getenv("THOR_B200_ROWPROG_HOIST") == nullptr || atoi(getenv("THOR_B200_ROWPROG_HOIST")) != 0) {
         for (int pass = 0; pass < 4 && hoistLinearRowSums(p); ++pass) {
+            mergeDuplicates(p);
             why = analyse(p);
             if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
         }
@@ -1190,6 +1291,32 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         p.stage_smem = p.persistent && wanted && packs16 && n_full > 0 && bytes <= 200 * 1024;
         p.smem_bytes = p.stage_smem ? bytes : 0;
     }
+    {
+        // Ring of bulk-copied row buffers: needs 16-byte rows, as many stages as fit in 200 KB (at least 3, at most 8).
+        const uint64_t teams = p.cta / p.team;
+        size_t stage_bytes = 0;
+        bool rows16 = true;
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
+                const size_t row_bytes = p.cols * dtypeSize(p.inputs[s].dtype);
+                rows16 = rows16 && row_bytes % 16 == 0;
+                stage_bytes += row_bytes * teams;
+            }
+        const int wanted = envInt("THOR_B200_ROWPROG_RING", 0);  // 0 off, -1 as many stages as fit, n > 0 at most n stages
+        if (p.persistent && !p.stage_smem && wanted != 0 && rows16 && stage_bytes > 0 && stage_bytes < (1u << 20)) {
+            // programs without column reductions run two CTAs per SM, which share the SM's shared memory
+            int ctas_per_sm = p.col_reduces.empty() ? 2 : 1;
+            if (const int per_sm = envInt("THOR_B200_ROWPROG_CTAS_PER_SM", 0)) ctas_per_sm = per_sm;
+            int stages = static_cast<int>(std::min<size_t>(8, (200 * 1024 / ctas_per_sm) / stage_bytes));
+            if (wanted > 0) stages = std::min(stages, wanted);
+            if (stages >= 3) {
+                p.ring_stages = stages;
+                p.ring_stage_bytes = stage_bytes;
+                p.smem_bytes = stage_bytes * stages;
+                p.prefetch = p.prefetch_l2 = false;
+            }
+        }
+    }
     const uint64_t teams_per_cta = p.cta / p.team;
     const uint64_t ctas_for_rows = (p.rows + teams_per_cta - 1) / teams_per_cta;
     int sms = 148;
@@ -1263,7 +1390,7 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
     const void* ws_ptr = workspace;
     args[n++] = &ws_ptr;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (p.smem_bytes > 48 * 1024) {
+    if (p.smem_bytes > 0) {  // static shared memory counts against the 48 KB default too
         int dev = 0;
         TB_CUDA(cudaGetDevice(&dev));
         if (!h->smem_opted_in[dev & 63]) {
@@ -1314,6 +1441,19 @@ const char* thor_b200_rowprog_source(const thor_b200_rowprog* h) { return h ? h-
 
 uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) {
     return h ? 1u + static_cast<uint32_t>(h->prog.col_reduces.size() + h->prog.all_reduces.size()) : 0u;
+}
+
+int thor_b200_rowprog_waits_expired(thor_b200_rowprog* h, uint32_t* count) {
+    TB_REQUIRE(h != nullptr && count != nullptr, "rowprog_waits_expired: null argument");
+    *count = 0;
+    if (h->prog.ring_stages == 0 || !h->module || h->module->library == nullptr) return THOR_B200_OK;
+    void* flag = nullptr;
+    size_t bytes = 0;
+    TB_CUDA(cudaLibraryGetGlobal(&flag, &bytes, h->module->library, "tb_wait_expired"));
+    TB_REQUIRE(bytes == sizeof(uint32_t), "rowprog_waits_expired: unexpected size of the device counter");
+    TB_CUDA(cudaDeviceSynchronize());
+    TB_CUDA(cudaMemcpy(count, flag, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    return THOR_B200_OK;
 }
 
 void thor_b200_rowprog_destroy(thor_b200_rowprog* h) { delete h; }

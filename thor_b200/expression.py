@@ -28,6 +28,8 @@ _host.thb_plan_intermediate_bytes.restype = C.c_uint64
 _host.thb_plan_intermediate_bytes.argtypes = [C.c_void_p]
 _host.thb_plan_launches.restype = C.c_uint64
 _host.thb_plan_launches.argtypes = [C.c_void_p]
+_host.thb_plan_waits_expired.restype = C.c_int
+_host.thb_plan_waits_expired.argtypes = [C.c_void_p, C.POINTER(C.c_uint64)]
 _host.thb_cub_reduction_kind.restype = C.c_char_p
 _host.thb_cub_reduction_kind.argtypes = [C.c_void_p]
 _host.thb_cub_reduction_workspace_bytes.restype = C.c_uint64
@@ -337,6 +339,12 @@ class StampedExecutionPlan:
 
     def intermediate_bytes(self) -> int: return int(_host.thb_plan_intermediate_bytes(self._h))
     def kernel_launches_per_run(self) -> int: return int(_host.thb_plan_launches(self._h))
+
+    def waits_expired(self) -> int:
+        """Bounded device-side waits that ran out in the launches so far (synchronises); 0 on a healthy run."""
+        count = C.c_uint64(0)
+        _check(_host.thb_plan_waits_expired(self._h, C.byref(count)))
+        return int(count.value)
 
     def output(self, name: str = "output") -> torch.Tensor:
         """The named output as a torch tensor aliasing the plan's memory (valid while the plan lives)."""

@@ -158,6 +158,7 @@ struct PhysicalStage {
     // FusedRows
     std::function<void(void* stream)> custom_launch;
     std::shared_ptr<std::vector<float>> shared_scalars;  // FusedRows: runtime scalars the launch closure reads
+    std::function<uint32_t()> waits_expired;             // FusedRows: bounded device-side waits that ran out
     uint64_t launches = 1;
 };
 
@@ -241,6 +242,12 @@ std::vector<std::string> StampedExecutionPlan::stageSources() const {
     return out;
 }
 uint64_t StampedExecutionPlan::intermediateBytes() const { return impl_->intermediate_bytes; }
+uint64_t StampedExecutionPlan::waitsExpired() const {
+    uint64_t n = 0;
+    for (const auto& s : impl_->stages)
+        if (s.waits_expired) n += s.waits_expired();
+    return n;
+}
 uint64_t StampedExecutionPlan::kernelLaunchesPerRun() const {
     uint64_t n = 0;
     for (const auto& s : impl_->stages)
@@ -462,6 +469,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             }
             for (uint32_t node : m.absorbed) covered[node] = true;
             st.custom_launch = m.bind(node_tensor, impl->keep_alive, impl->intermediate_bytes);
+            st.waits_expired = m.waits_expired;
             impl->stages.push_back(std::move(st));
         }
     }

@@ -64,6 +64,9 @@ class StampedExecutionPlan {
     std::vector<std::string> stageSources() const;
     uint64_t intermediateBytes() const;
     uint64_t kernelLaunchesPerRun() const;
+    // Kernels that wait on device-side barriers bound every wait in time; this is how many such waits ran out in the
+    // launches so far (synchronises with the device).  Anything but 0 means the outputs are not to be trusted.
+    uint64_t waitsExpired() const;
 
    private:
     std::shared_ptr<Impl> impl_;

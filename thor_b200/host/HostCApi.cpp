@@ -282,6 +282,9 @@ THB_API const char* thb_plan_strings(Plan* p, int kind) {
 }
 THB_API uint64_t thb_plan_intermediate_bytes(Plan* p) { return p->plan.intermediateBytes(); }
 THB_API uint64_t thb_plan_launches(Plan* p) { return p->plan.kernelLaunchesPerRun(); }
+THB_API int thb_plan_waits_expired(Plan* p, uint64_t* count) {
+    return guarded([&] { *count = p->plan.waitsExpired(); });
+}
 
 // ---- dtype resolution probe (no GPU needed) ---------------------------------------------------------
 // Resolves dtypes for the given input dtypes and writes (op, output_dtype, compute_dtype) triples of every node.

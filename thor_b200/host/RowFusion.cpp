@@ -285,6 +285,11 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
     m.launches = thor_b200_rowprog_launch_count(prog->h);
     m.scalar_names = scalar_names;
     m.scalars = scalars;
+    m.waits_expired = [prog]() {
+        uint32_t count = 0;
+        if (thor_b200_rowprog_waits_expired(prog->h, &count) != THOR_B200_OK) throw std::runtime_error(std::string("row program: ") + thor_b200_last_error());
+        return count;
+    };
     std::vector<uint32_t> out_nodes;
     for (const auto& o : ctx.outputs) {
         m.produced.push_back({o.node_idx, true});

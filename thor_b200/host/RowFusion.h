@@ -33,6 +33,8 @@ struct RowFusionMatch {
     std::shared_ptr<std::vector<float>> scalars;      // runtime scalar values by program input slot
     // Called once the produced tensors exist; returns the launch closure (no allocation inside it).
     std::function<std::function<void(void*)>(std::vector<Tensor>& node_tensor, std::vector<Tensor>& keep_alive, uint64_t& intermediate_bytes)> bind;
+    // Device-side waits of the program that ran out of time so far (synchronises; 0 for programs without such waits).
+    std::function<uint32_t()> waits_expired;
 };
 
 // Tries to run the whole equation as one row program; returns no match when it does not fit.
