@@ -826,8 +826,8 @@ TRAFFIC_BYTES = {
     "c3_softmax_and_argmax_one_pass_fp32": 8 * 217_500_000,         # 8192 of 65536 rows captured
     "c3_row_argmax_fp32": 8 * 138_300_000,
     "c4_full_reductions_bf16": 16 * 272_400_000,     # 2^27 of 2^31 elements captured
-    "c5_layernorm_forward_bf16": 8 * 84_300_000,     # 4096 of 32768 rows captured
-    "c5_layernorm_backward_bf16": 8 * 169_200_000,
+    "c5_layernorm_forward_bf16": 8 * 78_900_000,     # 4096 of 32768 rows captured
+    "c5_layernorm_backward_bf16": 8 * 170_100_000,
     "c2_fused_relu_axb_sigmoid_reference_gpu_kernel": 2 * 173_900_000,
 }
 
