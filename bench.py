@@ -452,15 +452,51 @@ class C3SoftmaxWithArgmax(C3Softmax):
     def algorithmic_bytes(self): return 2 * self.ROWS * self.COLS * 4 + self.ROWS * 4
 
 
+class _ReferenceReduction:
+    """One stamped launch of the REFERENCE's own reduction device code (oracle/_ref, baseline arms only): its CUB call or
+    tiled kernel over a dense [outer, reduction, inner] input, workspace sized by its own query."""
+
+    def __init__(self, op, x, out, outer, reduction, inner):
+        import torch
+
+        import oracle
+
+        dt = {torch.float32: oracle.FP32, torch.float16: oracle.FP16, torch.bfloat16: oracle.BF16}
+        self.args = (op, x, dt[x.dtype], out, dt[out.dtype], outer, reduction, inner)
+        self.path, self.ws_bytes = oracle.reference_cub_reduce_workspace(op, dt[x.dtype], dt[out.dtype], outer, reduction, inner)
+        self.ws = torch.empty(max(1, self.ws_bytes), dtype=torch.uint8, device="cuda")
+
+    def run(self):
+        import torch
+
+        import oracle
+
+        op, x, xd, out, od, outer, reduction, inner = self.args
+        oracle.reference_cub_reduce(op, self.path, x.data_ptr(), xd, out.data_ptr(), od, outer, reduction, inner, self.ws.data_ptr(), self.ws_bytes,
+                                    torch.cuda.current_stream().cuda_stream)
+
+
+def _row_reduction_for_baseline(op, x, out, rows, cols):
+    """(launcher, label): the reference's own reduction when oracle/_ref holds it, else ours standing in."""
+    import oracle
+
+    if oracle.reference_cub_reduce_lib() is not None:
+        return _ReferenceReduction(op, x, out, rows, cols, 1), "reference CUB segmented reduce"
+    from thor_b200.reductions import CubReduction, CubReductionOp
+
+    ours = {"max": CubReductionOp.Max, "sum": CubReductionOp.Sum, "mean": CubReductionOp.Mean}[op]
+    return CubReduction(ours, [1]).stamp(x, output=out), "rows reduction (ours)"
+
+
 class C3ReferenceStagePipeline(C3Softmax):
     """Baseline, not product: the reference's stage list for the composed softmax -- Reduction(max), Fused(exp(x - m)),
     Reduction(sum), Fused(e / s) -- with the two fused stages being the kernels the reference's own emitter generates
-    (oracle/_ref) and, because the reference's CUB reductions cannot be built with this toolkit, OUR row-reduction kernels
-    standing in for the two reductions.  A lower bound of what the reference's pipeline costs on this GPU: four kernels,
-    two materialised [rows, cols] fp32 intermediates."""
+    (oracle/_ref) and the two reductions its own CUB calls (cub::DeviceSegmentedReduce with its operators and iterators,
+    compiled from its header into oracle/_ref; our row-reduction kernels stand in only where that library is not built).
+    What the reference's pipeline costs on this GPU: four kernels, two materialised [rows, cols] fp32 intermediates."""
     is_baseline = True
     name = "c3_softmax_rows_fp32_reference_stage_list"
-    description = "reference stage list for softmax: its emitted fused kernels + our reductions standing in for CUB (baseline beside c3)"
+    description = "reference stage list for softmax: its emitted fused kernels + its CUB reductions (baseline beside c3)"
 
     def setup(self):
         import torch
@@ -481,11 +517,11 @@ class C3ReferenceStagePipeline(C3Softmax):
         self.y = torch.empty(R, C, device="cuda")
         self.m = torch.empty(R, 1, device="cuda")
         self.s = torch.empty(R, 1, device="cuda")
-        self.r_max = CubReduction(CubReductionOp.Max, [1]).stamp(self.x, output=self.m)
-        self.r_sum = CubReduction(CubReductionOp.Sum, [1]).stamp(self.e, output=self.s)
+        self.r_max, label = _row_reduction_for_baseline("max", self.x, self.m, R, C)
+        self.r_sum, _ = _row_reduction_for_baseline("sum", self.e, self.s, R, C)
         self.sets = [None]  # one buffer set: 1 GiB per tensor, far beyond L2
         self.launches_per_step = 4
-        self.kernel_kind = ["rows reduction (ours)", "reference fused exp(x - m)", "rows reduction (ours)", "reference fused e / s"]
+        self.kernel_kind = [label, "reference fused exp(x - m)", label, "reference fused e / s"]
 
     def step(self, i):
         self.r_max.run()
@@ -554,6 +590,46 @@ class C4FullReduce(Workload):
             combine_partials(sums=torch_cat(self.outs[:2]), maxima=self.outs[2])
 
 
+class C4ReferenceStagePipeline(C4FullReduce):
+    """Baseline, not product: what the reference runs for the three statistics -- its full reduction (cub::DeviceReduce::
+    TransformReduce with its fp32 operators) for the sum, its emitted flat kernel materialising x * x as bf16 followed by
+    the same reduction for the sum of squares, and its NaN-propagating maximum: four kernels, three reads of x."""
+    is_baseline = True
+    name = "c4_full_reductions_bf16_reference_stage_list"
+    description = "reference stage list for sum / sum of squares / max: its CUB full reductions + its emitted x*x kernel (baseline beside c4)"
+
+    def setup(self):
+        import torch
+
+        import oracle
+        from oracle.refkernel import ReferenceFlatKernel
+
+        if oracle.reference_emitter_lib() is None or oracle.reference_cub_reduce_lib() is None:
+            raise RuntimeError("oracle/_ref holds no build of the reference's emitter / reductions")
+        gen = torch.Generator(device="cuda").manual_seed(99 + self.dist.rank)
+        pad = 64
+        self.x = torch.zeros(self.N + pad, device="cuda", dtype=torch.bfloat16)
+        chunk = min(self.N, 1 << 28)
+        for s in range(0, self.N, chunk):
+            n = min(chunk, self.N - s)
+            self.x[s:s + n] = (torch.randn(n, device="cuda", generator=gen) + 0.01).bfloat16()
+        self.sq = torch.zeros(self.N + pad, device="cuda", dtype=torch.bfloat16)
+        self.k_sq = ReferenceFlatKernel("in:x in:x mul", {"x": oracle.BF16}, self.N)
+        self.outs = [torch.empty(1, device="cuda") for _ in range(3)]
+        self.r_sum = _ReferenceReduction("sum", self.x, self.outs[0], 1, self.N, 1)
+        self.r_sumsq = _ReferenceReduction("sum", self.sq, self.outs[1], 1, self.N, 1)
+        self.r_max = _ReferenceReduction("max", self.x, self.outs[2], 1, self.N, 1)
+        self.sets = [None]
+        self.launches_per_step = 4
+        self.kernel_kind = ["reference CUB transform-reduce (sum)", "reference fused x * x", "reference CUB transform-reduce (sum)", "reference CUB transform-reduce (max)"]
+
+    def step(self, i):
+        self.r_sum.run()
+        self.k_sq.launch({"x": self.x}, self.sq)
+        self.r_sumsq.run()
+        self.r_max.run()
+
+
 def torch_cat(ts):
     import torch
 
@@ -609,10 +685,10 @@ class C5LayerNormFwd(Workload):
 class C5FwdReferenceStagePipeline(C5LayerNormFwd):
     """Baseline, not product: the reference's stage list for the LayerNorm forward DAG -- Reduction(mean), Fused((x - mean)^2)
     into an fp32 [rows, cols] temporary, Reduction(mean), Fused(normalise, scale, shift, cast) -- with the reference's own
-    emitted fused kernels and our row reductions standing in for its CUB reductions (which this toolkit cannot build)."""
+    emitted fused kernels and its own CUB reductions (ours stand in only where oracle/_ref holds no build of them)."""
     is_baseline = True
     name = "c5_layernorm_forward_bf16_reference_stage_list"
-    description = "reference stage list for LayerNorm forward: its emitted fused kernels + our reductions standing in for CUB (baseline beside c5 forward)"
+    description = "reference stage list for LayerNorm forward: its emitted fused kernels + its CUB reductions (baseline beside c5 forward)"
 
     def setup(self):
         import torch
@@ -636,11 +712,14 @@ class C5FwdReferenceStagePipeline(C5LayerNormFwd):
         self.y = torch.empty(R, C, device="cuda", dtype=torch.bfloat16)
         self.mean = torch.empty(R, 1, device="cuda")
         self.var = torch.empty(R, 1, device="cuda")
-        self.r_mean = CubReduction(CubReductionOp.Mean, [1], output_dtype=DataType.fp32).stamp(self.x, output=self.mean)
-        self.r_var = CubReduction(CubReductionOp.Mean, [1]).stamp(self.sq, output=self.var)
+        if oracle.reference_cub_reduce_lib() is not None:
+            self.r_mean, label = _row_reduction_for_baseline("mean", self.x, self.mean, R, C)
+        else:
+            self.r_mean, label = CubReduction(CubReductionOp.Mean, [1], output_dtype=DataType.fp32).stamp(self.x, output=self.mean), "rows reduction (ours)"
+        self.r_var, _ = _row_reduction_for_baseline("mean", self.sq, self.var, R, C)
         self.sets = [None]
         self.launches_per_step = 4
-        self.kernel_kind = ["rows reduction (ours)", "reference fused (x - mean)^2", "rows reduction (ours)", "reference fused normalise"]
+        self.kernel_kind = [label, "reference fused (x - mean)^2", label, "reference fused normalise"]
 
     def step(self, i):
         self.r_mean.run()
@@ -680,7 +759,8 @@ class C5LayerNormBwd(C5LayerNormFwd):
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
-             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c5_fwd_ref_stages": C5FwdReferenceStagePipeline}
+             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c4_ref_stages": C4ReferenceStagePipeline,
+             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline}
 
 
 # ---------------------------------------------------------------------------------------------------------

@@ -99,6 +99,52 @@ def reference_gpu_cast(src_ptr: int, dst_ptr: int, src_dtype: int, dst_dtype: in
     assert rc == 0, f"reference GPU conversion failed ({rc})"
 
 
+_ref_cub = None
+
+
+def reference_cub_reduce_lib():
+    """The reference's own value reductions (its fp32 operators, CUB calls and tiled kernels), or None when oracle/_ref
+    holds no build of them."""
+    global _ref_cub
+    if _ref_cub is None:
+        path = HERE / "_ref" / "libthor_ref_cub_reduce.so"
+        if not path.exists():
+            return None
+        _ref_cub = ctypes.CDLL(str(path))
+        c = ctypes
+        _ref_cub.thor_ref_cub_reduce.argtypes = [c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_ulonglong, c.c_ulonglong, c.c_ulonglong, c.c_void_p,
+                                                 c.POINTER(c.c_size_t), c.c_void_p]
+        _ref_cub.thor_ref_cub_reduce.restype = c.c_int
+    return _ref_cub
+
+
+REF_REDUCE_OPS = {"sum": 0, "mean": 1, "max": 2, "min": 3}
+
+
+def reference_cub_reduce_workspace(op: str, input_dtype: int, output_dtype: int, outer: int, reduction: int, inner: int) -> tuple[int, int]:
+    """(path, workspace bytes) of the reference's reduction of a dense [outer, reduction, inner] input over the middle
+    axis.  The path follows its geometry analysis (CubReduction.cpp:755-912): one output -> DeviceTransformReduce (0),
+    inner == 1 -> ContiguousFixedSegment (1), otherwise TiledFixedSegment (2)."""
+    ref = reference_cub_reduce_lib()
+    assert ref is not None, "oracle/_ref/libthor_ref_cub_reduce.so has not been built"
+    path = 0 if outer * inner == 1 else (1 if inner == 1 else 2)
+    size = ctypes.c_size_t(0)
+    rc = ref.thor_ref_cub_reduce(REF_REDUCE_OPS[op], path, None, input_dtype, None, output_dtype, outer, reduction, inner, None, ctypes.byref(size), None)
+    assert rc == 0, f"reference reduction workspace query failed ({rc})"
+    return path, int(size.value)
+
+
+def reference_cub_reduce(op: str, path: int, in_ptr: int, input_dtype: int, out_ptr: int, output_dtype: int, outer: int, reduction: int, inner: int, temp_ptr: int,
+                         temp_bytes: int, stream: int = 0) -> None:
+    """Launches the reference's reduction on device buffers (asynchronous on `stream`); workspace from reference_cub_reduce_workspace."""
+    ref = reference_cub_reduce_lib()
+    assert ref is not None, "oracle/_ref/libthor_ref_cub_reduce.so has not been built"
+    size = ctypes.c_size_t(temp_bytes)
+    rc = ref.thor_ref_cub_reduce(REF_REDUCE_OPS[op], path, ctypes.c_void_p(in_ptr), input_dtype, ctypes.c_void_p(out_ptr), output_dtype, outer, reduction, inner,
+                                 ctypes.c_void_p(temp_ptr), ctypes.byref(size), ctypes.c_void_p(stream))
+    assert rc == 0, f"reference reduction failed ({rc})"
+
+
 _ref_emit = None
 
 

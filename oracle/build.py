@@ -107,6 +107,45 @@ def build_reference_gpu_cast(force: bool = False) -> Path | None:
     return out
 
 
+def _cccl3_include_dirs() -> list[Path]:
+    """A CCCL 3.x header tree (the reference's reductions need <cuda/iterator>, which the toolkit's own CCCL 2.x lacks);
+    some Python wheels carry one."""
+    for sp in site.getsitepackages() + [sysconfig.get_paths()["purelib"]]:
+        base = Path(sp) / "flashinfer" / "data" / "cccl"
+        if (base / "libcudacxx" / "include" / "cuda" / "iterator").exists():
+            return [base / "libcudacxx" / "include", base / "cub", base / "thrust"]
+    return []
+
+
+def build_reference_cub_reduce(force: bool = False) -> Path | None:
+    """Compile the reference's reduction templates (CubReductionOperation.cuh: its fp32 operators, output iterator,
+    CUB calls and tiled kernels) behind the C symbol of ref_cub_reduce.cu into _ref/ (nvcc, about 4 minutes); None when
+    the reference checkout, nvcc or a CCCL 3.x header tree is missing."""
+    out = REF_OUT / "libthor_ref_cub_reduce.so"
+    src = HERE / "ref_cub_reduce.cu"
+    ref_src = REFERENCE_DIR / "Utilities/TensorOperations/Cub/CubReductionOperation.cuh"
+    nvcc = shutil.which("nvcc") or str(Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "bin" / "nvcc")
+    cccl = _cccl3_include_dirs()
+    if not ref_src.exists() or not Path(nvcc).exists() or not cccl:
+        return out if out.exists() else None
+    REF_OUT.mkdir(exist_ok=True)
+    if not force and not _stale(out, [src, ref_src]):
+        return out
+    verdir = REF_OUT / "generated"
+    verdir.mkdir(exist_ok=True)
+    (verdir / "ThorVersion.h").write_text('#pragma once\n#define THOR_VERSION "0.0.33"\n#define THOR_GIT_VERSION "unknown"\n')
+    cmd = [nvcc, "-std=c++20", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+           "-Xlinker", "-z,defs"]
+    for d in cccl:
+        cmd += ["-I", str(d)]
+    cmd += ["-I", str(REFERENCE_DIR), "-I", str(verdir)]
+    for d in _site_include_dirs():
+        cmd += ["-I", str(d)]
+    cmd += [str(src), "-o", str(out)]
+    _run(cmd)
+    return out
+
+
 def build_reference_emitter(force: bool = False) -> Path | None:
     """Compile the reference's expression builder, dtype resolution and CUDA source emitter (three host sources,
     g++ -std=c++23, about 15 s) with the dumper in ref_emit.cpp into _ref/; None when that cannot be done here."""
@@ -152,6 +191,12 @@ def build_all(force: bool = False) -> dict:
     except RuntimeError as exc:
         result["reference_gpu_cast"] = None
         result["reference_gpu_cast_error"] = str(exc)[-2000:]
+    try:
+        ref_red = build_reference_cub_reduce(force)
+        result["reference_cub_reduce"] = str(ref_red) if ref_red else None
+    except RuntimeError as exc:
+        result["reference_cub_reduce"] = None
+        result["reference_cub_reduce_error"] = str(exc)[-2000:]
     try:
         ref = build_reference_cast(force)
         result["reference_cast"] = str(ref) if ref else None

@@ -101,6 +101,22 @@ class ReferenceBroadcastKernel:
         _launch(self.source, self.ept, self.order, out, inputs, self.numel, stream)
 
 
+class ReferenceFlatKernel:
+    """The reference's flat (same-shape) fused kernel for `program`, ready to launch repeatedly on caller-provided buffers;
+    every tensor must hold numel + 64 elements (the reference's kernels read whole packs and rely on padded tensors)."""
+
+    def __init__(self, program: str, input_dtypes: Dict[str, int], numel: int):
+        from thor_b200.dtypes import DataType, to_torch
+
+        self.source, self.ept, self.order, self.out_dtype = reference_emit_flat(program, input_dtypes)
+        self.torch_out_dtype = to_torch(DataType(self.out_dtype))
+        self.numel = numel
+        compile_reference_kernel(self.source)
+
+    def launch(self, inputs: Dict[str, Union[torch.Tensor, float]], out: torch.Tensor, stream=None) -> None:
+        _launch(self.source, self.ept, self.order, out, inputs, self.numel, stream)
+
+
 def run_reference_flat(program: str, inputs: Dict[str, Union[torch.Tensor, float]], input_dtypes: Dict[str, int], numel: int, pad: int = 64):
     """Emits, compiles and launches the reference's flat kernel for `program`; tensors must hold numel + pad elements
     (the reference's kernels read whole packs and rely on padded tensors).  Returns (output tensor incl. padding, output dtype)."""
