@@ -114,8 +114,9 @@ def test_row_and_column_broadcasts_in_fp32_match_the_reference_broadcast_kernel(
 
 
 def test_reference_stage_lists_compute_what_our_row_programs_compute():
-    """The benchmark's reference stage-list baselines (reference-emitted fused kernels + our reductions standing in for
-    CUB) produce the results our single row programs produce, so their times compare like with like."""
+    """The benchmark's reference stage-list baselines (reference-emitted fused kernels + the reference's own CUB
+    reductions where oracle/_ref holds them, ours standing in otherwise) produce the results our single row programs
+    produce, so their times compare like with like."""
     import bench
 
     class _Single:
@@ -141,6 +142,20 @@ def test_reference_stage_lists_compute_what_our_row_programs_compute():
     d = eo.ulp_distance(a, b, o.BF16)
     d = np.where(np.abs(a - b) <= 1e-7, 0.0, d)  # results that cancel to ~0: the fp32 noise of the two summation orders, not a bf16 step
     assert float(d.max()) <= 1.0 and float((d == 0).mean()) > 0.99
+
+    if o.reference_cub_reduce_lib() is not None:
+        st = bench.C4ReferenceStagePipeline(_Single(), 1.0 / 256)
+        st.setup()
+        st.step(0)
+        x = st.x[: st.N]
+        xi = ex.input("x")
+        ours = ex.compile({"sum": xi.reduce_sum(), "sumsq": (xi * xi).reduce_sum(), "max": xi.reduce_max()}).stamp({"x": x})
+        ours.run()
+        torch.cuda.synchronize()
+        mag = float(x.double().abs().sum())
+        assert abs(float(ours.output("sum")) - float(st.outs[0])) <= 1e-5 * abs(float(st.outs[0])) + 1e-6 * mag
+        assert abs(float(ours.output("sumsq")) - float(st.outs[1])) <= 1e-5 * float(st.outs[1])
+        assert float(ours.output("max")) == float(st.outs[2])
 
 
 @pytest.mark.parametrize("dtype", [o.FP8_E4M3, o.FP8_E5M2])
