@@ -590,6 +590,41 @@ class C4FullReduce(Workload):
             combine_partials(sums=torch_cat(self.outs[:2]), maxima=self.outs[2])
 
 
+class C3ArgmaxReferenceGpu(C3Argmax):
+    """Baseline, not product: the reference's own row argmax -- cub::DeviceSegmentedReduce over its counting + transform
+    iterator of {u64 index, float} candidates with its NaN-wins / lowest-index operator (oracle/_ref)."""
+    is_baseline = True
+    name = "c3_row_argmax_fp32_reference_gpu"
+    description = "reference CUB arg reduction for the row argmax of fp32 [65536,4096] (baseline beside c3_argmax)"
+
+    def setup(self):
+        import torch
+
+        import oracle
+
+        lib_ = oracle.reference_cub_reduce_lib()
+        if lib_ is None or not hasattr(lib_, "thor_ref_cub_argreduce"):
+            raise RuntimeError("oracle/_ref holds no build of the reference's arg reductions")
+        R, C = self.ROWS, self.COLS
+        gen = torch.Generator(device="cuda").manual_seed(78 + self.dist.rank)
+        self.path, self.ws_bytes = oracle.reference_cub_argreduce_workspace(True, oracle.FP32, R, C, 1, oracle.UINT32)
+        self.ws = torch.empty(max(1, self.ws_bytes), dtype=torch.uint8, device="cuda")
+        self.sets = []
+        for _ in range(2):
+            self.sets.append((torch.randn(R, C, device="cuda", generator=gen) * 3.0, torch.empty(R, dtype=torch.int32, device="cuda")))
+        self.launches_per_step = 1
+        self.kernel_kind = ["reference CUB segmented arg reduce"]
+
+    def step(self, i):
+        import torch
+
+        import oracle
+
+        x, idx = self.sets[i % len(self.sets)]
+        oracle.reference_cub_argreduce(True, self.path, x.data_ptr(), oracle.FP32, 0, oracle.FP32, idx.data_ptr(), oracle.UINT32, self.ROWS, self.COLS, 1, self.ws.data_ptr(),
+                                       self.ws_bytes, torch.cuda.current_stream().cuda_stream)
+
+
 class C4ReferenceStagePipeline(C4FullReduce):
     """Baseline, not product: what the reference runs for the three statistics -- its full reduction (cub::DeviceReduce::
     TransformReduce with its fp32 operators) for the sum, its emitted flat kernel materialising x * x as bf16 followed by
@@ -759,7 +794,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
-             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c4_ref_stages": C4ReferenceStagePipeline,
+             "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c3_argmax_ref_gpu": C3ArgmaxReferenceGpu, "c4_ref_stages": C4ReferenceStagePipeline,
              "c5_fwd_ref_stages": C5FwdReferenceStagePipeline}
 
 

@@ -115,6 +115,10 @@ def reference_cub_reduce_lib():
         _ref_cub.thor_ref_cub_reduce.argtypes = [c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_ulonglong, c.c_ulonglong, c.c_ulonglong, c.c_void_p,
                                                  c.POINTER(c.c_size_t), c.c_void_p]
         _ref_cub.thor_ref_cub_reduce.restype = c.c_int
+        if hasattr(_ref_cub, "thor_ref_cub_argreduce"):
+            _ref_cub.thor_ref_cub_argreduce.argtypes = [c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_ulonglong, c.c_ulonglong,
+                                                        c.c_ulonglong, c.c_void_p, c.POINTER(c.c_size_t), c.c_void_p]
+            _ref_cub.thor_ref_cub_argreduce.restype = c.c_int
     return _ref_cub
 
 
@@ -143,6 +147,29 @@ def reference_cub_reduce(op: str, path: int, in_ptr: int, input_dtype: int, out_
     rc = ref.thor_ref_cub_reduce(REF_REDUCE_OPS[op], path, ctypes.c_void_p(in_ptr), input_dtype, ctypes.c_void_p(out_ptr), output_dtype, outer, reduction, inner,
                                  ctypes.c_void_p(temp_ptr), ctypes.byref(size), ctypes.c_void_p(stream))
     assert rc == 0, f"reference reduction failed ({rc})"
+
+
+def reference_cub_argreduce_workspace(is_max: bool, input_dtype: int, outer: int, reduction: int, inner: int, index_dtype: int) -> tuple[int, int]:
+    """(path, workspace bytes) of the reference's arg reduction of a dense [outer, reduction, inner] input over the middle axis."""
+    ref = reference_cub_reduce_lib()
+    assert ref is not None and hasattr(ref, "thor_ref_cub_argreduce"), "oracle/_ref holds no build of the reference's arg reductions"
+    path = 0 if outer * inner == 1 else (1 if inner == 1 else 2)
+    size = ctypes.c_size_t(0)
+    rc = ref.thor_ref_cub_argreduce(int(is_max), path, None, input_dtype, None, FP32, None, index_dtype, outer, reduction, inner, None, ctypes.byref(size), None)
+    assert rc == 0, f"reference arg reduction workspace query failed ({rc})"
+    return path, int(size.value)
+
+
+def reference_cub_argreduce(is_max: bool, path: int, in_ptr: int, input_dtype: int, value_ptr: int, value_dtype: int, index_ptr: int, index_dtype: int, outer: int,
+                            reduction: int, inner: int, temp_ptr: int, temp_bytes: int, stream: int = 0) -> None:
+    """Launches the reference's arg reduction on device buffers (value_ptr or index_ptr may be 0)."""
+    ref = reference_cub_reduce_lib()
+    assert ref is not None and hasattr(ref, "thor_ref_cub_argreduce"), "oracle/_ref holds no build of the reference's arg reductions"
+    size = ctypes.c_size_t(temp_bytes)
+    rc = ref.thor_ref_cub_argreduce(int(is_max), path, ctypes.c_void_p(in_ptr), input_dtype, ctypes.c_void_p(value_ptr or None), value_dtype,
+                                    ctypes.c_void_p(index_ptr or None), index_dtype, outer, reduction, inner, ctypes.c_void_p(temp_ptr), ctypes.byref(size),
+                                    ctypes.c_void_p(stream))
+    assert rc == 0, f"reference arg reduction failed ({rc})"
 
 
 _ref_emit = None

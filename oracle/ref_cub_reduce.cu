@@ -9,6 +9,10 @@
 //   path 0  DeviceTransformReduce   cub::DeviceReduce::TransformReduce over the whole input
 //   path 1  ContiguousFixedSegment  cub::DeviceSegmentedReduce::Reduce, fixed segment size
 //   path 2  TiledFixedSegment       the reference's own [outer, reduction, inner] kernels
+// Arg reductions the same way from CubArgReductionOperation.cuh: candidate operators (:24-73), the store functor
+// (:89-105), the candidate input functors (:115-134) wrapped in the iterators its helper functions build from them
+// (:107-113, :152-162), the tiled dispatcher launchTiledFixedSegmentArgReduction (:1030-1060) and the initial
+// candidates of CubArgReductionMax.cu / CubArgReductionMin.cu, as launchArgReductionForInput (:1119-1178) calls them.
 // launchReductionForInput itself takes the reference's Tensor objects, whose implementation drags in
 // the whole runtime, so the three calls are made on raw pointers instead.  The reference needs
 // <cuda/iterator> (CCCL 3.x); the build points the compiler at a CCCL copy of that generation.
@@ -43,6 +47,7 @@
 #include <omp.h>
 
 #include "Utilities/TensorOperations/Cub/CubReductionOperation.cuh"
+#include "Utilities/TensorOperations/Cub/CubArgReductionOperation.cuh"
 
 #include <cuda/std/functional>
 
@@ -108,6 +113,53 @@ int reduceOp(int op, int path, const void* input, void* output, DataType output_
     }
 }
 
+template <typename InputT, typename ReductionOpT>
+int argReduceTyped(int path, const void* input, void* value_output, DataType value_dtype, void* index_output, DataType index_dtype, uint64_t outer, uint64_t reduction, uint64_t inner,
+                   ReductionOpT op, ArgReductionCandidateFp32 init, void* temp, size_t* temp_bytes, cudaStream_t stream) {
+    const InputT* in = static_cast<const InputT*>(input);
+    auto out_it = cuda::make_tabulate_output_iterator(StoreArgReductionResultRuntime{value_output, value_dtype, index_output, index_dtype});
+    size_t bytes = temp ? *temp_bytes : 0;
+    cudaError_t st = cudaSuccess;
+    if (path == 0) {
+        auto in_it = thrust::make_transform_iterator(thrust::counting_iterator<int64_t>(0), DeviceArgCandidateInput<InputT>{in});
+        st = cub::DeviceReduce::Reduce(temp, bytes, in_it, out_it, static_cast<int64_t>(outer * reduction * inner), op, init, stream);
+    } else if (path == 1) {
+        auto in_it = thrust::make_transform_iterator(thrust::counting_iterator<int64_t>(0), ContiguousArgCandidateInput<InputT>{in, reduction});
+        st = cub::DeviceSegmentedReduce::Reduce(temp, bytes, in_it, out_it, static_cast<int64_t>(outer), static_cast<int>(reduction), op, init, stream);
+    } else {
+        if (temp == nullptr) {
+            *temp_bytes = 1;
+            return 0;
+        }
+        CubReductionGeometry g;
+        g.rank = 3;
+        g.axes = {1};
+        g.reduced_axes_are_contiguous = true;
+        g.outer_size = outer;
+        g.reduction_size = reduction;
+        g.inner_size = inner;
+        g.input_elements = outer * reduction * inner;
+        g.output_elements = outer * inner;
+        g.tiled_output_outer_stride = inner;
+        g.tiled_output_inner_stride = 1;
+        g.path = CubReductionPath::TiledFixedSegment;
+        launchTiledFixedSegmentArgReduction<InputT>(in, value_output, value_dtype, index_output, index_dtype, g, op, init, stream);
+        st = cudaGetLastError();
+    }
+    if (temp == nullptr) *temp_bytes = std::max<size_t>(bytes, 1);
+    return st == cudaSuccess ? 0 : 2;
+}
+
+template <typename InputT>
+int argReduceOp(int is_max, int path, const void* input, void* value_output, DataType value_dtype, void* index_output, DataType index_dtype, uint64_t outer, uint64_t reduction,
+                uint64_t inner, void* temp, size_t* temp_bytes, cudaStream_t stream) {
+    if (is_max)
+        return argReduceTyped<InputT>(path, input, value_output, value_dtype, index_output, index_dtype, outer, reduction, inner, ArgMaximumCandidateFp32{},
+                                      ArgReductionCandidateFp32{std::numeric_limits<uint64_t>::max(), -std::numeric_limits<float>::infinity()}, temp, temp_bytes, stream);
+    return argReduceTyped<InputT>(path, input, value_output, value_dtype, index_output, index_dtype, outer, reduction, inner, ArgMinimumCandidateFp32{},
+                                  ArgReductionCandidateFp32{std::numeric_limits<uint64_t>::max(), std::numeric_limits<float>::infinity()}, temp, temp_bytes, stream);
+}
+
 }  // namespace
 
 // op: 0 sum, 1 mean, 2 max, 3 min.  path: see the header of this file.  input dtype: the reference's DataType value of
@@ -121,6 +173,25 @@ extern "C" __attribute__((visibility("default"))) int thor_ref_cub_reduce(int op
             case DataType::FP32: return reduceOp<float>(op, path, input, output, out, outer, reduction, inner, temp, temp_bytes, s);
             case DataType::BF16: return reduceOp<__nv_bfloat16>(op, path, input, output, out, outer, reduction, inner, temp, temp_bytes, s);
             case DataType::FP16: return reduceOp<__half>(op, path, input, output, out, outer, reduction, inner, temp, temp_bytes, s);
+            default: return 3;
+        }
+    } catch (...) {
+        return 1;
+    }
+}
+
+// Arg reduction over the middle axis of a dense [outer, reduction, inner] input: value_output (fp32 / fp16 / bf16) and / or
+// index_output (the reference's UINT32 or UINT64 DataType value) may be NULL.  Same path and workspace conventions.
+extern "C" __attribute__((visibility("default"))) int thor_ref_cub_argreduce(int is_max, int path, const void* input, int input_dtype, void* value_output, int value_dtype,
+                                                                             void* index_output, int index_dtype, unsigned long long outer, unsigned long long reduction,
+                                                                             unsigned long long inner, void* temp, size_t* temp_bytes, void* stream) {
+    try {
+        const DataType vd = static_cast<DataType>(value_dtype), id = static_cast<DataType>(index_dtype);
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        switch (static_cast<DataType>(input_dtype)) {
+            case DataType::FP32: return argReduceOp<float>(is_max, path, input, value_output, vd, index_output, id, outer, reduction, inner, temp, temp_bytes, s);
+            case DataType::BF16: return argReduceOp<__nv_bfloat16>(is_max, path, input, value_output, vd, index_output, id, outer, reduction, inner, temp, temp_bytes, s);
+            case DataType::FP16: return argReduceOp<__half>(is_max, path, input, value_output, vd, index_output, id, outer, reduction, inner, temp, temp_bytes, s);
             default: return 3;
         }
     } catch (...) {

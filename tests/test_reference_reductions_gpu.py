@@ -105,3 +105,48 @@ def test_paths_follow_the_reference_geometry_rule():
     assert _reference("sum", x, DataType.fp32)[1] == 0
     assert _reference("sum", torch.randn(16, 64, 1, device="cuda"), DataType.fp32)[1] == 1
     assert _reference("sum", torch.randn(2, 64, 8, device="cuda"), DataType.fp32)[1] == 2
+
+
+# ---- arg reductions: value and index must be identical (NaN wins, lowest index among equals) ----
+
+def _reference_arg(is_max, x3):
+    outer, red, inner = x3.shape
+    in_dtype = {torch.float32: DataType.fp32, torch.float16: DataType.fp16, torch.bfloat16: DataType.bf16}[x3.dtype]
+    path, ws_bytes = o.reference_cub_argreduce_workspace(is_max, int(in_dtype), outer, red, inner, o.UINT32)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    val = torch.full((outer * inner,), float("nan"), device="cuda")
+    idx = torch.full((outer * inner,), -1, dtype=torch.int32, device="cuda")
+    o.reference_cub_argreduce(is_max, path, x3.data_ptr(), int(in_dtype), val.data_ptr(), o.FP32, idx.data_ptr(), o.UINT32, outer, red, inner, ws.data_ptr(), ws_bytes,
+                              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return val.cpu().numpy(), idx.cpu().numpy().view(np.uint32)
+
+
+ARG_SHAPES = [(1, 100003, 1), (1, 9, 1), (4096, 4096, 1), (333, 1000, 1), (10000, 36, 1), (1, 2048, 1000), (8, 100, 64), (5, 333, 7), (2, 50, 4096)]
+
+
+@pytest.mark.skipif(o.reference_cub_reduce_lib() is None or not hasattr(o.reference_cub_reduce_lib(), "thor_ref_cub_argreduce"), reason="no build of the reference's arg reductions")
+@pytest.mark.parametrize("outer,red,inner", ARG_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("is_max", [True, False])
+def test_arg_reductions_match_the_reference_device_code(is_max, dtype, outer, red, inner):
+    from thor_b200.reductions import CubArgReduction, CubArgReductionOp
+
+    g = torch.Generator(device="cuda").manual_seed(outer + red * 3 + inner * 5)
+    # few distinct values, so that ties are everywhere; some NaN and infinities
+    x = torch.randint(-6, 7, (outer, red, inner), device="cuda", generator=g).to(torch.float32) * 0.5
+    flat = x.reshape(-1)
+    n = flat.numel()
+    pick = torch.randint(0, n, (max(1, n // 5000),), device="cuda", generator=g)
+    flat[pick[::3]] = float("nan")
+    flat[pick[1::3]] = float("inf")
+    flat[pick[2::3]] = float("-inf")
+    x = x.to(dtype)
+    want_v, want_i = _reference_arg(is_max, x)
+    s = CubArgReduction(CubArgReductionOp.ArgMax if is_max else CubArgReductionOp.ArgMin, [1]).stamp(x)
+    s.run()
+    torch.cuda.synchronize()
+    got_i = s.index.cpu().numpy().reshape(-1).astype(np.uint32)
+    got_v = s.value.float().cpu().numpy().reshape(-1)
+    assert np.array_equal(got_i, want_i), int((got_i != want_i).sum())
+    assert np.array_equal(got_v, want_v, equal_nan=True)
