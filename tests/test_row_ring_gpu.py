@@ -102,3 +102,20 @@ def test_programs_without_waits_report_zero():
     plan = ex.compile(e / e.reduce_sum([1])).stamp({"x": x})
     plan.run()
     assert plan.waits_expired() == 0
+
+
+@pytest.mark.parametrize("backward", [False, True])
+def test_a_wait_that_runs_out_is_counted_and_the_device_stays_usable(backward):
+    """Failure on the host side of the ring: one CTA's generated code lacks the request for one iteration's rows, so the
+    wait on that buffer's barrier can never be satisfied.  The wait gives up after its limit (20 ms here), the kernel
+    runs to its end, the host reads the count, and the next launches on the same context are healthy."""
+    env = {"THOR_B200_ROWPROG_WAIT_LIMIT_MS": "20", "THOR_B200_ROWPROG_TEST_DROP_FILL": "6"}
+    plan, _ = _run(4096, 8192, env, backward)
+    assert "blockIdx.x == 0 && r0 ==" in plan.stage_sources()[0]
+    assert plan.waits_expired() >= 1
+    # the same shapes without the injected fault: correct results, nothing counted
+    healthy, got = _run(4096, 8192, {}, backward)
+    _, want = _run(4096, 8192, {"THOR_B200_ROWPROG_RING": "0"}, backward)
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)
+    assert healthy.waits_expired() == 0

@@ -169,6 +169,9 @@ __device__ __forceinline__ float tb_nanmax(float a, float b) { return a != a ? a
 // Every wait is bounded by wall-clock time: a wait that runs out counts in tb_wait_expired (read by the host),
 // raises the CTA's flag so that later waits give up quickly, and lets the kernel run to its end on stale data.
 #ifdef TB_BULK_RING
+#ifndef TB_WAIT_LIMIT_NS
+#define TB_WAIT_LIMIT_NS 2000000000ull  // two seconds: far beyond any copy, short enough that the device keeps answering
+#endif
 __device__ unsigned int tb_wait_expired = 0;
 __device__ __forceinline__ unsigned tb_smem_addr(const void* ptr) { return static_cast<unsigned>(__cvta_generic_to_shared(ptr)); }
 __device__ __forceinline__ void tb_mbar_init(tb_u64* bar, unsigned arrivals) {
@@ -198,7 +201,7 @@ __device__ __forceinline__ void tb_mbar_wait(tb_u64* bar, unsigned parity, volat
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return;
     const tb_u64 start = tb_now_ns();
-    const tb_u64 limit_ns = *gave_up ? 100000ull : 2000000000ull;
+    const tb_u64 limit_ns = *gave_up ? 100000ull : (tb_u64)TB_WAIT_LIMIT_NS;
     while (tb_now_ns() - start < limit_ns) {
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return;

@@ -66,6 +66,8 @@ struct Program {
     int ring_stages = 0;  // persistent programs: > 0 = rows arrive by bulk copies in a ring of this many shared-memory buffers
     size_t ring_stage_bytes = 0;
     std::vector<size_t> ring_offset;         // ring mode: byte offset of each [rows, cols] input inside a buffer, by input slot
+    int wait_limit_ms = 0;         // ring mode: time limit of a barrier wait (0 = the prelude's default of two seconds)
+    int drop_fill_iteration = -1;  // ring mode, tests only: CTA 0 never requests the rows of this iteration
     bool pipeline_wanted = true;
     bool pipelined = false;                  // ring mode: round 1 of the next row shares the last round of the current row
     bool elements_from_next_buffer = false;  // emission state: element operands come from the next ring buffer, not from registers
@@ -607,7 +609,10 @@ std::string emit(Program& p) {
 
     os << "// generated by thor_b200: row program, " << p.nodes.size() << " nodes, rows = " << p.rows << ", cols = " << p.cols << ", team = " << TEAM
        << " threads, " << VPT << " packs of " << VEC << " per thread" << (p.persistent ? ", persistent" : "") << "\n";
-    if (p.ring_stages > 0) os << "#define TB_BULK_RING 1\n";
+    if (p.ring_stages > 0) {
+        os << "#define TB_BULK_RING 1\n";
+        if (p.wait_limit_ms > 0) os << "#define TB_WAIT_LIMIT_NS " << static_cast<unsigned long long>(p.wait_limit_ms) * 1000000ull << "ull\n";
+    }
     os << "#include \"tb_prelude.cuh\"\n#include \"tb_rowprog.cuh\"\n\n";
     // kernel signature
     os << "extern \"C\" __global__ void __launch_bounds__(" << CTA << (p.min_ctas > 0 ? ", " + std::to_string(p.min_ctas) : std::string()) << ") row_kernel(";
@@ -762,7 +767,12 @@ std::string emit(Program& p) {
         // barrier of the first reduction round when the program has one, after a barrier of its own otherwise
         {
             std::ostringstream refill;
-            refill << I << "if (threadIdx.x == 0) {\n" << I << "    const tb_u64 r0 = row0 + STAGES * row_stride;\n" << I << "    if (r0 < ROWS) {\n";
+            refill << I << "if (threadIdx.x == 0) {\n" << I << "    const tb_u64 r0 = row0 + STAGES * row_stride;\n";
+            // host-side fault injection for the tests of the bounded waits: the generated kernel simply lacks one copy
+            // (CTA 0, one iteration), so that a wait on its barrier runs out and the counter is raised
+            if (p.drop_fill_iteration >= 0)
+                refill << I << "    if (r0 < ROWS && !(blockIdx.x == 0 && r0 == (tb_u64)" << p.drop_fill_iteration << " * row_stride)) {\n";
+            else refill << I << "    if (r0 < ROWS) {\n";
             std::istringstream lines(fill.str());
             std::string line;
             while (std::getline(lines, line)) refill << I << "        " << line << "\n";
@@ -1451,6 +1461,8 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
                 p.smem_bytes = stage_bytes * stages;
                 p.prefetch = p.prefetch_l2 = false;
                 p.pipeline_wanted = pipeline;
+                p.wait_limit_ms = envInt("THOR_B200_ROWPROG_WAIT_LIMIT_MS", 0);
+                p.drop_fill_iteration = envInt("THOR_B200_ROWPROG_TEST_DROP_FILL", -1);
             }
         }
     }
