@@ -66,6 +66,9 @@ struct Program {
     int ring_stages = 0;  // persistent programs: > 0 = rows arrive by bulk copies in a ring of this many shared-memory buffers
     size_t ring_stage_bytes = 0;
     std::vector<size_t> ring_offset;         // ring mode: byte offset of each [rows, cols] input inside a buffer, by input slot
+    std::vector<uint8_t> cache_state;  // per node: 1 = its [rows, cols] fp32 value is kept in registers once computed, 2 = it has been
+    bool cache_wanted = true;
+    bool reciprocal_division = false;  // x / (row value) in fp32 becomes x * (1 / row value): one rounding more than the reference's division
     int wait_limit_ms = 0;         // ring mode: time limit of a barrier wait (0 = the prelude's default of two seconds)
     int drop_fill_iteration = -1;  // ring mode, tests only: CTA 0 never requests the rows of this iteration
     bool pipeline_wanted = true;
@@ -449,6 +452,11 @@ void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, cons
         const int O = vdt(p, k);
         const std::string name = "p" + std::to_string(k);
         std::string packed;  // float2 expression when the node has a packed form
+        const uint8_t cached = p.cache_state.empty() ? 0 : p.cache_state[k];
+        if (cached == 2) {
+            os << indent << "const float2 " << name << " = h" << k << "[k][j >> 1];\n";
+            continue;
+        }
         if (nd.op == THOR_B200_OP_INPUT) {
             os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("px" + std::to_string(nd.input_slot), p.inputs[nd.input_slot].dtype, O) << ";\n";
             continue;
@@ -468,11 +476,15 @@ void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, cons
                 packed = "__ffma2_rn(" + pairAsFloat2(p, nd.rhs) + ", tb_both(-1.0f), " + pairAsFloat2(p, nd.lhs) + ")";  // a - b, exact
             } else if (nd.op == THOR_B200_OP_MUL) {
                 packed = "__fmul2_rn(" + pairAsFloat2(p, nd.lhs) + ", " + pairAsFloat2(p, nd.rhs) + ")";
+            } else if (nd.op == THOR_B200_OP_DIV && p.reciprocal_division && elementLevel(p, nd.lhs) && !elementLevel(p, nd.rhs)) {
+                // the reciprocal of the row value is loop invariant
+                packed = "__fmul2_rn(" + pairAsFloat2(p, nd.lhs) + ", tb_both(__frcp_rn(" + convertExpression("v" + std::to_string(nd.rhs), vdt(p, nd.rhs), THOR_B200_FP32) + ")))";
             }
         }
         if (!packed.empty()) {
             if (O == THOR_B200_FP32) {
                 os << indent << "const float2 " << name << " = " << packed << ";\n";
+                if (cached == 1) os << indent << "h" << k << "[k][j >> 1] = " << name << ";\n";
             } else {
                 os << indent << "const float2 t" << k << " = " << packed << ";\n";
                 os << indent << "const " << pairType(O) << " " << name << " = " << convertPair("t" + std::to_string(k), THOR_B200_FP32, O) << ";\n";
@@ -492,6 +504,7 @@ void emitPairStatements(const Program& p, const std::vector<uint32_t>& ids, cons
             }
             os << name << lane << " = " << expr << "; }\n";
         }
+        if (cached == 1) os << indent << "h" << k << "[k][j >> 1] = " << name << ";\n";
     }
 }
 
@@ -507,6 +520,7 @@ std::vector<uint32_t> elementClosure(const Program& p, const std::vector<uint32_
         if (sh == ROW || sh == SCALAR) continue;  // row-scope values: already computed, referenced by name
         need[k] = true;
         if (isLeaf(p.nodes[k].op) || isReduce(p.nodes[k].op)) continue;
+        if (!p.cache_state.empty() && p.cache_state[k] == 2) continue;  // kept in registers by an earlier element loop
         for (uint32_t par : {p.nodes[k].lhs, p.nodes[k].rhs, p.nodes[k].aux})
             if (par != THOR_B200_NO_NODE) stack.push_back(par);
     }
@@ -606,6 +620,37 @@ std::string emit(Program& p) {
     int max_depth = 0;
     for (uint32_t k : p.row_reduces) max_depth = std::max(max_depth, p.depth[k]);
     p.pipelined = p.persistent && p.ring_stages > 0 && p.pipeline_wanted && canPipeline(p);
+    // Element loops recompute what they need from the row's registers.  A transcendental (or a division) that more than
+    // one loop needs -- exp(x - max) of a softmax, needed by the sum and by the output -- is kept in registers instead
+    // when the program is not already short of them: non-persistent programs, at most 32 floats per thread.
+    p.cache_state.assign(p.nodes.size(), 0);
+    if (!p.persistent && p.pairs && p.cache_wanted) {
+        auto expensive = [](uint16_t op) {
+            return op == THOR_B200_OP_DIV || op == THOR_B200_OP_POW || (op >= THOR_B200_OP_SIN && op <= THOR_B200_OP_NORMCDF);
+        };
+        std::vector<int> uses(p.nodes.size(), 0);
+        auto count = [&](const std::vector<uint32_t>& targets) {
+            if (targets.empty()) return;
+            for (uint32_t k : elementClosure(p, targets)) ++uses[k];
+        };
+        for (int d = 1; d <= max_depth; ++d) {
+            std::vector<uint32_t> args;
+            for (uint32_t k : p.row_reduces)
+                if (p.depth[k] == d) args.push_back(p.nodes[k].lhs);
+            count(args);
+        }
+        std::vector<uint32_t> finals;
+        for (const auto& o : p.outputs)
+            if (p.shape[o.node] == FULL) finals.push_back(o.node);
+        count(finals);
+        int budget = 32;
+        for (uint32_t k = static_cast<uint32_t>(p.nodes.size()); k-- > 0;) {
+            if (uses[k] < 2 || p.shape[k] != FULL || !expensive(p.nodes[k].op) || vdt(p, k) != THOR_B200_FP32) continue;
+            if (budget < VPT * VEC) break;
+            budget -= VPT * VEC;
+            p.cache_state[k] = 1;
+        }
+    }
 
     os << "// generated by thor_b200: row program, " << p.nodes.size() << " nodes, rows = " << p.rows << ", cols = " << p.cols << ", team = " << TEAM
        << " threads, " << VPT << " packs of " << VEC << " per thread" << (p.persistent ? ", persistent" : "") << "\n";
@@ -816,6 +861,8 @@ std::string emit(Program& p) {
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == ROW)
             os << I << "const " << cTypeName(p.inputs[s].dtype) << " x" << s << " = row_ok ? in" << s << "[row] : " << cTypeName(p.inputs[s].dtype) << "();\n";
 
+    for (uint32_t k = 0; k < p.nodes.size(); ++k)
+        if (p.cache_state[k] == 1) os << I << "float2 h" << k << "[VPT][VEC / 2];  // kept from the first element loop that computes it\n";
     // row-scope nodes are emitted as soon as their depth is reached
     std::vector<bool> emitted(p.nodes.size(), false);
     auto emitRowScope = [&](int d) {
@@ -915,6 +962,8 @@ std::string emit(Program& p) {
             }
         }
         os << I << "        }\n" << I << "    }\n" << I << "}\n";
+        for (uint32_t k : closure)
+            if (p.cache_state[k] == 1) p.cache_state[k] = 2;  // later loops read the registers
     };
     auto roundLaneFold = [&](const std::vector<uint32_t>& round) {
         if (p.pairs)
@@ -1414,6 +1463,10 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     p.prefetch_l2 = p.persistent && prefetch_mode == 2;
     p.min_ctas = envInt("THOR_B200_ROWPROG_MIN_CTAS", d->options.min_ctas_per_sm);
     p.pairs = envInt("THOR_B200_ROWPROG_PAIRS", 1) != 0;
+    p.cache_wanted = envInt("THOR_B200_ROWPROG_CACHE", 1) != 0;
+    // off unless the caller asked for fast math: the reference divides, and so do we (measured: softmax + argmax in one
+    // pass 352 us with the division, 310 us with the reciprocal; softmax alone is at the memory bound either way)
+    p.reciprocal_division = envInt("THOR_B200_ROWPROG_RCP", p.fast_math ? 1 : 0) != 0;
     {
         // Staging rows in shared memory (cp.async, thread-private slots) frees the registers of both row buffers.
         bool packs16 = true;
