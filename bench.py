@@ -150,8 +150,10 @@ class Dist:
             self.dist.destroy_process_group()
 
 
-def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler | None = None, sample: bool = False):
-    """W untimed + K timed calls of step(i); returns (device ms per step as max over ranks, wall ms per step)."""
+def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler | None = None, sample: bool = False, drain=None):
+    """W untimed + K timed calls of step(i); returns (device ms per step as max over ranks, wall ms per step).
+    `drain` (optional) makes the timing stream wait for work the steps put on side streams, so that it ends inside the
+    timed region."""
     import torch
 
     for i in range(warmup):
@@ -164,6 +166,8 @@ def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler 
     e0.record()
     for i in range(steps):
         step(warmup + i)
+    if drain is not None:
+        drain()
     e1.record()
     dist.barrier()
     wall = (time.perf_counter() - t0) * 1e3 / steps
@@ -584,10 +588,15 @@ class C4FullReduce(Workload):
     def step(self, i):
         self.plan.run()
         if self.dist.enabled:
-            # per-GPU fp32 partials -> one allreduce each (sum for the additive statistics, max for the maximum)
-            from thor_b200.sharding import combine_partials
+            # per-GPU fp32 partials -> one allreduce each (sum for the additive statistics, max for the maximum), on a side
+            # stream: the collective of step i overlaps the kernel of step i + 1
+            if not hasattr(self, "side"):
+                self.side = _SideCollective()
+            self.side.submit(sums=torch_cat(self.outs[:2]), maxima=self.outs[2].clone())
 
-            combine_partials(sums=torch_cat(self.outs[:2]), maxima=self.outs[2])
+    def drain(self):
+        if hasattr(self, "side"):
+            self.side.drain()
 
 
 class C3ArgmaxReferenceGpu(C3Argmax):
@@ -663,6 +672,34 @@ class C4ReferenceStagePipeline(C4FullReduce):
         self.k_sq.launch({"x": self.x}, self.sq)
         self.r_sumsq.run()
         self.r_max.run()
+
+
+class _SideCollective:
+    """Allreduce of a step's packed partials on a side stream, so that it overlaps the next step's kernel (the partials
+    are packed on the main stream first, which also frees the step's output buffers for the next launch)."""
+
+    def __init__(self):
+        import torch
+
+        self.stream = torch.cuda.Stream()
+
+    def submit(self, **partials):
+        import torch
+
+        from thor_b200.sharding import combine_partials
+
+        ready = torch.cuda.Event()
+        ready.record()
+        self.stream.wait_event(ready)
+        with torch.cuda.stream(self.stream):
+            combine_partials(**partials)
+        for t in partials.values():
+            t.record_stream(self.stream)
+
+    def drain(self):
+        import torch
+
+        torch.cuda.current_stream().wait_stream(self.stream)
 
 
 def torch_cat(ts):
@@ -788,9 +825,14 @@ class C5LayerNormBwd(C5LayerNormFwd):
         plan = self.sets[i % len(self.sets)][0]
         plan.run()
         if self.dist.enabled:
-            from thor_b200.sharding import combine_partials
+            # the packed fp32 [dgamma, dbeta] partials are allreduced on a side stream, overlapping the next step's kernel
+            if not hasattr(self, "side"):
+                self.side = _SideCollective()
+            self.side.submit(sums=torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()]))
 
-            combine_partials(sums=torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()]))
+    def drain(self):
+        if hasattr(self, "side"):
+            self.side.drain()
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
@@ -845,7 +887,7 @@ def run_workload(dist: Dist, cls, steps: int, warmup: int, sample_clocks: bool, 
     wl.setup()
     before = thor_b200.launch_count()
     sampler = ClockSampler(dist.local_rank if dist.enabled else 0) if (sample_clocks and dist.rank == 0) else None
-    ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler, sample_clocks)
+    ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler, sample_clocks, getattr(wl, "drain", None))
     del before
     launches = wl.launches_per_step * steps  # kernels of this library inside the timed region
     return wl, ms, wall, clocks, launches
