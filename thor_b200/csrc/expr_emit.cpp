@@ -18,6 +18,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <algorithm>
 #include <cstdlib>
 #include <sstream>
 
@@ -160,6 +161,11 @@ struct Plan {
     // value-range facts used to pick cheaper bit-identical routines: "<= 0 or NaN" / ">= 0 or NaN"
     std::vector<bool> nonpos, nonneg;
     bool lean_pair_math = true;
+    // half2 bodies: node k = exp(-max(-z, 0)) takes its value from node exp_twin[k] = exp(-|z|) of the same z (node
+    // exp_twin_z[k]) where z < 0 and is 1 elsewhere; `order` is the emission order (such a node moves behind its twin)
+    std::vector<int> exp_twin;
+    std::vector<uint32_t> exp_twin_z;
+    std::vector<uint32_t> order;
     explicit Plan(const Stage& s) : st(s) {}
 };
 
@@ -303,6 +309,67 @@ std::string scalarNodeExprImpl(const std::vector<thor_b200_expr_node>& nodes, co
 std::string scalarNodeExpr(const Plan& p, size_t k) { return scalarNodeExprImpl(p.st.nodes, p.st.inputs, k); }
 
 // ---- half2 / bfloat162 body --------------------------------------------------------------------
+// The reference's overflow-safe sigmoid (Expression.h:1077-1088) is exp(-max(-z, 0)) / (1 + exp(-|z|)).  For z < 0 both
+// exponentials have the same argument (z itself); elsewhere (z >= 0, -0, NaN) the first is exp(-0) = 1.  So the first
+// is a select of the second: one exponential per element instead of two, with identical bits.
+void findExpTwins(Plan& p) {
+    const auto& n = p.st.nodes;
+    p.exp_twin.assign(n.size(), -1);
+    p.exp_twin_z.assign(n.size(), THOR_B200_NO_NODE);
+    p.order.clear();
+    for (uint32_t k = 0; k < n.size(); ++k) p.order.push_back(k);
+    if (!p.v2 || p.v2_dtype != THOR_B200_FP16 || !p.lean_pair_math) return;
+    auto strip = [&](uint32_t i) {
+        while (i != THOR_B200_NO_NODE && n[i].op == THOR_B200_OP_CAST) i = n[i].lhs;
+        return i;
+    };
+    auto isZero = [&](uint32_t i) { return i != THOR_B200_NO_NODE && n[i].op == THOR_B200_OP_SCALAR_FP && n[i].scalar_fp == 0.0; };
+    auto negOf = [&](uint32_t i) -> uint32_t {  // z when node i is -z
+        i = strip(i);
+        return i != THOR_B200_NO_NODE && n[i].op == THOR_B200_OP_NEG ? strip(n[i].lhs) : THOR_B200_NO_NODE;
+    };
+    auto clampedForm = [&](uint32_t i) -> uint32_t {  // z when node i is exp(-max(-z, 0))
+        if (n[i].op != THOR_B200_OP_EXP) return THOR_B200_NO_NODE;
+        const uint32_t m = negOf(n[i].lhs);
+        if (m == THOR_B200_NO_NODE || n[m].op != THOR_B200_OP_MAX) return THOR_B200_NO_NODE;
+        const uint32_t a = strip(n[m].lhs), b = strip(n[m].rhs);
+        if (isZero(b)) return negOf(a);
+        if (isZero(a)) return negOf(b);
+        return THOR_B200_NO_NODE;
+    };
+    auto absForm = [&](uint32_t i) -> uint32_t {  // z when node i is exp(-|z|), |z| spelled abs(z) or max(z, -z)
+        if (n[i].op != THOR_B200_OP_EXP) return THOR_B200_NO_NODE;
+        const uint32_t m = negOf(n[i].lhs);
+        if (m == THOR_B200_NO_NODE) return THOR_B200_NO_NODE;
+        if (n[m].op == THOR_B200_OP_ABS) return strip(n[m].lhs);
+        if (n[m].op != THOR_B200_OP_MAX) return THOR_B200_NO_NODE;
+        const uint32_t a = strip(n[m].lhs), b = strip(n[m].rhs);
+        if (a != THOR_B200_NO_NODE && negOf(b) == a) return a;
+        if (b != THOR_B200_NO_NODE && negOf(a) == b) return b;
+        return THOR_B200_NO_NODE;
+    };
+    for (uint32_t k = 0; k < n.size(); ++k) {
+        if (!p.live[k]) continue;
+        const uint32_t z = clampedForm(k);
+        if (z == THOR_B200_NO_NODE) continue;
+        for (uint32_t m = 0; m < n.size(); ++m) {
+            if (m == k || !p.live[m] || p.exp_twin[m] >= 0 || absForm(m) != z) continue;
+            // k is emitted behind m: every consumer of k must come later still
+            bool ok = true;
+            for (uint32_t j = 0; j <= m && ok; ++j)
+                for (uint32_t par : {n[j].lhs, n[j].rhs, n[j].aux}) ok = ok && !(par == k && p.live[j]);
+            if (!ok) continue;
+            p.exp_twin[k] = static_cast<int>(m);
+            p.exp_twin_z[k] = z;
+            if (m > k) {
+                p.order.erase(std::find(p.order.begin(), p.order.end(), k));
+                p.order.insert(std::find(p.order.begin(), p.order.end(), m) + 1, k);
+            }
+            break;
+        }
+    }
+}
+
 std::string v2NodeExpr(const Plan& p, size_t k) {
     const auto& nd = p.st.nodes[k];
     const int D = p.v2_dtype;
@@ -322,6 +389,8 @@ std::string v2NodeExpr(const Plan& p, size_t k) {
         case THOR_B200_OP_CAST: return nodeVar(nd.lhs);
         default: break;
     }
+    if (!p.exp_twin.empty() && p.exp_twin[k] >= 0)
+        return "tb_h2sel_neg(" + nodeVar(p.exp_twin_z[k]) + ", " + nodeVar(static_cast<size_t>(p.exp_twin[k])) + ", __half2half2(__float2half_rn(1.0f)))";
     const std::string a = nodeVar(nd.lhs);
     const std::string b = nd.rhs != THOR_B200_NO_NODE ? nodeVar(nd.rhs) : std::string();
     switch (nd.op) {
@@ -374,7 +443,7 @@ void emitBody(const Plan& p, std::ostringstream& os) {
         os << (p.v2 ? T2 : std::string(ctype(st.outputs[o].dtype))) << "& y" << o;
     }
     os << ") {\n";
-    for (size_t k = 0; k < st.nodes.size(); ++k) {
+    for (size_t k : p.order) {
         if (!p.live[k]) continue;
         const std::string type = p.v2 ? T2 : std::string(ctype(valueDTypeImpl(st.nodes, k)));
         os << "    const " << type << " " << nodeVar(k) << " = " << (p.v2 ? v2NodeExpr(p, k) : scalarNodeExpr(p, k)) << ";\n";
@@ -798,6 +867,12 @@ std::string emit(const Stage& st, bool force_generic, Emitted* out) {
     decideV2(p);
     analyseSigns(p);
     if (const char* e = getenv("THOR_B200_LEAN_PAIR_MATH")) p.lean_pair_math = atoi(e) != 0;
+    findExpTwins(p);
+    if (const char* e = getenv("THOR_B200_EXP_TWINS"))
+        if (atoi(e) == 0) {
+            std::fill(p.exp_twin.begin(), p.exp_twin.end(), -1);
+            std::sort(p.order.begin(), p.order.end());
+        }
     std::ostringstream os;
     os << "// generated by thor_b200: fused stage, " << st.nodes.size() << " nodes, " << st.inputs.size() << " inputs, " << st.outputs.size() << " outputs\n";
     os << "#include \"tb_prelude.cuh\"\n\n";

@@ -112,6 +112,13 @@ __device__ __forceinline__ __half2 tb_h2exp_nonpos(const __half2 a) {
     r = tb_h2exp_fix(a, r, 0xC1EFC1EFu, 0x02000200u);
     return r;
 }
+// Lane-wise z < 0 ? if_negative : otherwise (false for -0 and NaN, like the comparison).
+__device__ __forceinline__ __half2 tb_h2sel_neg(const __half2 z, const __half2 if_negative, const __half2 otherwise) {
+    const unsigned int m = __hlt2_mask(z, __half2half2(__ushort_as_half((unsigned short)0)));
+    const unsigned int a = *reinterpret_cast<const unsigned int*>(&if_negative), b = *reinterpret_cast<const unsigned int*>(&otherwise);
+    const unsigned int r = (a & m) | (b & ~m);
+    return *reinterpret_cast<const __half2*>(&r);
+}
 __device__ __forceinline__ __half2 tb_h2div(const __half2 a, const __half2 b) {
     const float2 fa = __half22float2(a), fb = __half22float2(b);
     float rx, ry;
