@@ -318,7 +318,7 @@ void findExpTwins(Plan& p) {
     p.exp_twin_z.assign(n.size(), THOR_B200_NO_NODE);
     p.order.clear();
     for (uint32_t k = 0; k < n.size(); ++k) p.order.push_back(k);
-    if (!p.v2 || p.v2_dtype != THOR_B200_FP16 || !p.lean_pair_math) return;
+    if (!p.v2) return;  // the same routine evaluates both exponentials, whichever it is, so equal arguments give equal bits
     auto strip = [&](uint32_t i) {
         while (i != THOR_B200_NO_NODE && n[i].op == THOR_B200_OP_CAST) i = n[i].lhs;
         return i;
@@ -390,7 +390,7 @@ std::string v2NodeExpr(const Plan& p, size_t k) {
         default: break;
     }
     if (!p.exp_twin.empty() && p.exp_twin[k] >= 0)
-        return "tb_h2sel_neg(" + nodeVar(p.exp_twin_z[k]) + ", " + nodeVar(static_cast<size_t>(p.exp_twin[k])) + ", __half2half2(__float2half_rn(1.0f)))";
+        return "tb_h2sel_neg(" + nodeVar(p.exp_twin_z[k]) + ", " + nodeVar(static_cast<size_t>(p.exp_twin[k])) + ", " + dup + "(" + cvt("1.0f", THOR_B200_FP32, D) + "))";
     const std::string a = nodeVar(nd.lhs);
     const std::string b = nd.rhs != THOR_B200_NO_NODE ? nodeVar(nd.rhs) : std::string();
     switch (nd.op) {

@@ -119,6 +119,12 @@ __device__ __forceinline__ __half2 tb_h2sel_neg(const __half2 z, const __half2 i
     const unsigned int r = (a & m) | (b & ~m);
     return *reinterpret_cast<const __half2*>(&r);
 }
+__device__ __forceinline__ __nv_bfloat162 tb_h2sel_neg(const __nv_bfloat162 z, const __nv_bfloat162 if_negative, const __nv_bfloat162 otherwise) {
+    const unsigned int m = __hlt2_mask(z, __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)0)));
+    const unsigned int a = *reinterpret_cast<const unsigned int*>(&if_negative), b = *reinterpret_cast<const unsigned int*>(&otherwise);
+    const unsigned int r = (a & m) | (b & ~m);
+    return *reinterpret_cast<const __nv_bfloat162*>(&r);
+}
 __device__ __forceinline__ __half2 tb_h2div(const __half2 a, const __half2 b) {
     const float2 fa = __half22float2(a), fb = __half22float2(b);
     float rx, ry;
