@@ -318,7 +318,21 @@ void findExpTwins(Plan& p) {
     p.exp_twin_z.assign(n.size(), THOR_B200_NO_NODE);
     p.order.clear();
     for (uint32_t k = 0; k < n.size(); ++k) p.order.push_back(k);
-    if (!p.v2) return;  // the same routine evaluates both exponentials, whichever it is, so equal arguments give equal bits
+    // the same routine evaluates both exponentials, whichever it is, so equal arguments give equal bits; in scalar bodies
+    // the nodes of both chains must also round alike (same compute and output dtype everywhere)
+    auto sameDTypes = [&](uint32_t k, uint32_t m) {
+        if (p.v2) return true;
+        auto chainOk = [&](uint32_t e) {
+            uint32_t i = e;
+            for (int hops = 0; hops < 3 && i != THOR_B200_NO_NODE; ++hops) {  // exp, neg, max / abs
+                if (n[i].op == THOR_B200_OP_CAST) return false;
+                if (n[i].compute_dtype != n[e].compute_dtype || n[i].output_dtype != n[e].output_dtype) return false;
+                i = n[i].lhs;
+            }
+            return true;
+        };
+        return chainOk(k) && chainOk(m) && n[k].compute_dtype == n[m].compute_dtype && n[k].output_dtype == n[m].output_dtype && isArithCompute(n[k].compute_dtype);
+    };
     auto strip = [&](uint32_t i) {
         while (i != THOR_B200_NO_NODE && n[i].op == THOR_B200_OP_CAST) i = n[i].lhs;
         return i;
@@ -353,7 +367,7 @@ void findExpTwins(Plan& p) {
         const uint32_t z = clampedForm(k);
         if (z == THOR_B200_NO_NODE) continue;
         for (uint32_t m = 0; m < n.size(); ++m) {
-            if (m == k || !p.live[m] || p.exp_twin[m] >= 0 || absForm(m) != z) continue;
+            if (m == k || !p.live[m] || p.exp_twin[m] >= 0 || absForm(m) != z || !sameDTypes(k, m)) continue;
             // k is emitted behind m: every consumer of k must come later still
             bool ok = true;
             for (uint32_t j = 0; j <= m && ok; ++j)
@@ -446,6 +460,13 @@ void emitBody(const Plan& p, std::ostringstream& os) {
     for (size_t k : p.order) {
         if (!p.live[k]) continue;
         const std::string type = p.v2 ? T2 : std::string(ctype(valueDTypeImpl(st.nodes, k)));
+        if (!p.v2 && !p.exp_twin.empty() && p.exp_twin[k] >= 0) {
+            // exp(-max(-z, 0)) from its twin exp(-|z|): identical where z < 0, exactly 1 elsewhere
+            const int V = valueDTypeImpl(st.nodes, k);
+            os << "    const " << type << " " << nodeVar(k) << " = (" << cvt(nodeVar(p.exp_twin_z[k]), valueDTypeImpl(st.nodes, p.exp_twin_z[k]), THOR_B200_FP32) << " < 0.0f) ? "
+               << nodeVar(static_cast<size_t>(p.exp_twin[k])) << " : " << cvt("1.0f", THOR_B200_FP32, V) << ";\n";
+            continue;
+        }
         os << "    const " << type << " " << nodeVar(k) << " = " << (p.v2 ? v2NodeExpr(p, k) : scalarNodeExpr(p, k)) << ";\n";
     }
     for (size_t o = 0; o < st.outputs.size(); ++o) {
