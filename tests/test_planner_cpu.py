@@ -167,3 +167,29 @@ def test_shape_errors_surface_at_plan_time():
         ex.compile(x + y).plan({"x": ((64, 3), DT.fp32), "y": ((64, 4), DT.fp32)})
     with pytest.raises((_native.ThorB200Error, _native.ThorB200InvalidArgument)):
         ex.compile(x + y).plan({"x": ((64, 3), DT.fp32)})
+
+
+def test_stable_sigmoid_costs_one_exponential_per_element():
+    """exp(-max(-z, 0)) of the overflow-safe sigmoid is emitted as a select of exp(-|z|) (equal arguments where z < 0,
+    exactly 1 elsewhere): half2, bfloat162 and fp32 scalar bodies."""
+    plan = ex.compile(_c2()).plan({"a": ((8192,), DT.fp16), "x": ((8192, 8192), DT.fp16), "b": ((8192,), DT.fp16), "z": ((8192, 8192), DT.fp16)})
+    body = plan.stage_sources()[0].split("extern \"C\"")[0]
+    assert body.count("tb_h2exp") == 1 and "tb_h2sel_neg(" in body
+    x = ex.input("x")
+    for dtype, exp_name, select in ((DT.bf16, "h2exp(", "tb_h2sel_neg("), (DT.fp32, "expf(", "< 0.0f) ?")):
+        body = ex.compile(x * x.sigmoid()).plan({"x": ((1 << 20,), dtype)}).stage_sources()[0].split("extern \"C\"")[0]
+        assert body.count(exp_name) == 1 and select in body, body
+
+
+def test_layernorm_programs_take_rows_through_the_bulk_copy_ring_and_softmax_keeps_its_exponential():
+    shapes = {"x": ((32768, 8192), DT.bf16), "gamma": ((8192,), DT.bf16), "beta": ((8192,), DT.bf16)}
+    fwd_eq = ex.compile({"y": _layernorm()})
+    fwd = fwd_eq.plan(shapes).stage_sources()[0]
+    assert "cp.async.bulk" not in fwd  # the instruction lives in the prelude; the program calls the wrappers
+    assert "tb_bulk_load(" in fwd and "tb_mbar_wait(" in fwd and "constexpr int STAGES = 3;" in fwd and "ran with the previous row" in fwd
+    bwd = fwd_eq.compile_backward(["x", "gamma", "beta"]).plan({**shapes, "__grad_output": ((32768, 8192), DT.bf16)}).stage_sources()[0]
+    assert "tb_bulk_load(" in bwd and "constexpr int STAGES = 4;" in bwd and "ran with the previous row" not in bwd
+    xi = ex.input("x")
+    e = (xi - xi.reduce_max([1])).exp()
+    sm = ex.compile(e / e.reduce_sum([1])).plan({"x": ((65536, 4096), DT.fp32)}).stage_sources()[0]
+    assert sm.count("expf(") == 2 and "kept from the first element loop" in sm  # two lanes of one pair, once
