@@ -703,7 +703,8 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
         else cls[s] = outer_zero ? OneElem : RowScalar;
         dense += cls[s] == Dense;
     }
-    int U = dense <= 2 ? 4 : (dense <= 4 ? 2 : 1);
+    // rows per thread, measured on relu(a*x+b)*sigmoid(z) fp16 [8192, 8192] (two dense inputs): 1 -> 65.1 us, 2 -> 65.0 us, 4 -> 66.1 us, 8 -> 72.0 us
+    int U = dense <= 1 ? 4 : (dense <= 4 ? 2 : 1);
     if (st.rows_per_thread == 1 || st.rows_per_thread == 2 || st.rows_per_thread == 4 || st.rows_per_thread == 8) U = st.rows_per_thread;
     while (U > 1 && static_cast<uint64_t>(ty) * (U / 2) >= rows) U /= 2;
     out->kind = p.v2 ? Kind::TiledV2 : Kind::TiledScalar;
