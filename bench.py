@@ -33,6 +33,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 L2_BYTES = 126 * 1024 * 1024
+ROW_PROGRAM = None  # --row-program: layout fields of the row programs (A/B runs of one kernel shape against another)
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -740,7 +741,7 @@ class C5LayerNormFwd(Workload):
         from thor_b200.expression import Expression as ex
 
         gen = torch.Generator(device="cuda").manual_seed(55 + self.dist.rank)
-        eq = ex.compile({"y": _layernorm_expr(ex)})
+        eq = ex.compile({"y": _layernorm_expr(ex)}, row_program=ROW_PROGRAM)
         self.sets = []
         for _ in range(2):
             x, gamma, beta = self._inputs(gen)
@@ -810,7 +811,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
         from thor_b200.expression import Expression as ex
 
         gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
-        bwd = ex.compile({"y": _layernorm_expr(ex)}).compile_backward(["x", "gamma", "beta"])
+        bwd = ex.compile({"y": _layernorm_expr(ex)}, row_program=ROW_PROGRAM).compile_backward(["x", "gamma", "beta"])
         self.sets = []
         for _ in range(2):
             x, gamma, beta = self._inputs(gen)
@@ -902,8 +903,12 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations, the end-to-end leg and the CPU baseline")
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of the workload's leading dimension (smaller cases for profiler captures only)")
+    ap.add_argument("--row-program", default="", help="row-program layout fields, e.g. rows_per_iteration=1,ring_buffers=4 (comparison runs)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    if args.row_program:
+        global ROW_PROGRAM
+        ROW_PROGRAM = {k: int(v) for k, v in (kv.split("=") for kv in args.row_program.split(","))}
     if args.impl == "reference":
         reference_arm(args)
         return

@@ -348,6 +348,22 @@ typedef enum thor_b200_row_shape {
     THOR_B200_SHAPE_FULL = 0, THOR_B200_SHAPE_ROW = 1, THOR_B200_SHAPE_COL = 2, THOR_B200_SHAPE_SCALAR = 3
 } thor_b200_row_shape;
 
+/* How a persistent row program (per-column operands or column reductions) moves its rows.  All zero = the measured
+ * defaults; every combination computes the same values (the layouts differ in how operands reach the registers and
+ * in which barriers are shared, not in the arithmetic), which the tests use to compare them bit for bit. */
+typedef struct thor_b200_rowprog_tuning {
+    int32_t ring_buffers;        /* rows arrive by bulk copies in a ring of shared-memory buffers: 0 = default, -1 = off
+                                  * (register double buffer), -2 = as many as fit, n >= 3 = at most n buffers */
+    int32_t pipeline_round_one;  /* round 1 of the next row shares the last round of the current row: 0 = default, 1 = on, -1 = off */
+    int32_t copy_warpgroup;      /* ring mode: the copies are requested by a warpgroup of their own instead of a team thread: 0 = default, 1 = on, -1 = off */
+    int32_t keep_values;         /* transcendental element values needed by several loops stay in registers: 0 = default (on), -1 = off */
+    int32_t reciprocal_division; /* x / row value as x * (1 / row value): 0 = default (only with use_fast_math), 1 = on, -1 = off */
+    int32_t wait_limit_ms;       /* time limit of a wait on a ring buffer's barrier; 0 = two seconds */
+    int32_t test_skip_fill;      /* tests of the bounded waits only: n > 0 makes CTA 0's code lack the copy request of loop
+                                  * iteration n, so the wait for that buffer runs out; 0 = none */
+    int32_t reserved;            /* must be zero */
+} thor_b200_rowprog_tuning;
+
 typedef struct thor_b200_rowprog_desc {
     const thor_b200_expr_node* nodes;
     uint32_t n_nodes;
@@ -358,6 +374,7 @@ typedef struct thor_b200_rowprog_desc {
     uint32_t n_outputs;
     uint64_t rows, cols;
     thor_b200_expr_options options;
+    thor_b200_rowprog_tuning tuning;
 } thor_b200_rowprog_desc;
 
 typedef struct thor_b200_rowprog thor_b200_rowprog;

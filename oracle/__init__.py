@@ -255,6 +255,46 @@ def reference_emit_flat(program: str, input_dtypes: dict):
     return text, int(ept.value), [names[i] for i in order if i >= 0], int(out_dt.value)
 
 
+_ref_autodiff = None
+
+
+def reference_autodiff_lib():
+    """The reference's own reverse-mode differentiation behind a graph dumper, or None when oracle/_ref holds no build of it."""
+    global _ref_autodiff
+    if _ref_autodiff is None:
+        path = HERE / "_ref" / "libthor_ref_autodiff.so"
+        if not path.exists():
+            return None
+        _ref_autodiff = ctypes.CDLL(str(path))
+        c = ctypes
+        _ref_autodiff.thor_ref_backward_graph.argtypes = [c.c_char_p, c.POINTER(c.c_char_p), c.POINTER(c.c_int), c.POINTER(c.c_ulonglong), c.c_int,
+                                                          c.POINTER(c.c_char_p), c.c_int, c.c_int, c.POINTER(c.c_char_p)]
+        _ref_autodiff.thor_ref_backward_graph.restype = c.c_int
+    return _ref_autodiff
+
+
+def reference_backward_graph(program: str, inputs: dict, wrt, upstream_dtype: int) -> dict:
+    """The dtype-resolved backward graph that the reference's buildBackwardOutputs (AutoDiff.cpp:6210) produces for the
+    forward `program` (postfix, ref_postfix.h) with `inputs` = {name: (dims, dtype)}: {"inputs", "outputs", "nodes"}."""
+    import json
+
+    lib_ = reference_autodiff_lib()
+    assert lib_ is not None, "oracle/_ref/libthor_ref_autodiff.so has not been built"
+    c = ctypes
+    names = list(inputs)
+    flat = []
+    for n in names:
+        dims = inputs[n][0]
+        flat += [len(dims), *dims]
+    text = c.c_char_p()
+    rc = lib_.thor_ref_backward_graph(program.encode(), (c.c_char_p * len(names))(*[n.encode() for n in names]),
+                                      (c.c_int * len(names))(*[int(inputs[n][1]) for n in names]), (c.c_ulonglong * max(1, len(flat)))(*flat), len(names),
+                                      (c.c_char_p * len(wrt))(*[w.encode() for w in wrt]), len(wrt), int(upstream_dtype), c.byref(text))
+    if rc != 0:
+        raise RuntimeError("reference buildBackwardOutputs: " + text.value.decode())
+    return json.loads(text.value.decode())
+
+
 def _ptr(a: np.ndarray) -> ctypes.c_void_p:
     return ctypes.c_void_p(a.ctypes.data)
 

@@ -11,8 +11,11 @@
   nvcc for sm_100a, about 90 s), same rules; the parity tests compare against it bit for bit and the
   benchmark times it beside our kernel.
 
-Run as ``python oracle/build.py``.  The reference checkout is looked up in
-``$THOR_REFERENCE_DIR`` (the default is the REFERENCE_DIR constant below).
+* ``_ref/libthor_ref_autodiff.so`` — the REFERENCE's own reverse-mode differentiation (AutoDiff.cpp) behind a graph
+  dumper: the tests compare the host layer's backward graphs with it and use its graphs as a second gradient oracle.
+
+Run as ``python oracle/build.py``.  The reference checkout is looked up in ``$THOR_REFERENCE_DIR``, else in a folder
+named ``reference`` beside this repository.
 """
 from __future__ import annotations
 
@@ -27,7 +30,14 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 BUILD = HERE / "_build"
 REF_OUT = HERE / "_ref"
-REFERENCE_DIR = Path(os.environ.get("THOR_REFERENCE_DIR", "/root/reference"))
+def _reference_dir() -> Path:
+    """The reference checkout: $THOR_REFERENCE_DIR, else a folder named `reference` beside this repository.  When neither
+    exists the _ref libraries are simply not (re)built and prebuilt ones are used as they are."""
+    env = os.environ.get("THOR_REFERENCE_DIR")
+    return Path(env) if env else HERE.parent.parent / "reference"
+
+
+REFERENCE_DIR = _reference_dir()
 CUDA_INCLUDE = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
 
 
@@ -155,7 +165,7 @@ def build_reference_emitter(force: bool = False) -> Path | None:
     if not all(p.exists() for p in ref_srcs):
         return out if out.exists() else None
     REF_OUT.mkdir(exist_ok=True)
-    if not force and not _stale(out, [shim, *ref_srcs]):
+    if not force and not _stale(out, [shim, HERE / "ref_postfix.h", *ref_srcs]):
         return out
     verdir = REF_OUT / "generated"
     verdir.mkdir(exist_ok=True)
@@ -163,7 +173,7 @@ def build_reference_emitter(force: bool = False) -> Path | None:
     objdir = REF_OUT / "obj"
     objdir.mkdir(exist_ok=True)
     common = ["g++", "-std=c++23", "-O1", "-fopenmp", "-fPIC", "-fvisibility=hidden", "-ffunction-sections", "-fdata-sections",
-              "-I", str(REFERENCE_DIR), "-I", str(verdir), "-I", str(CUDA_INCLUDE)]
+              "-I", str(REFERENCE_DIR), "-I", str(HERE), "-I", str(verdir), "-I", str(CUDA_INCLUDE)]
     for d in _site_include_dirs():
         common += ["-I", str(d)]
     objs = []
@@ -177,6 +187,43 @@ def build_reference_emitter(force: bool = False) -> Path | None:
     return out
 
 
+def build_reference_autodiff(force: bool = False) -> Path | None:
+    """Compile the reference's reverse-mode differentiation (AutoDiff.cpp with the expression builder, dtype resolution,
+    SqueezeAxes.cpp and BatchedMatmulPlan.cpp it calls; five host sources, g++ -std=c++23, about 25 s) with the graph dumper
+    in ref_autodiff.cpp into _ref/; None when that cannot be done here."""
+    out = REF_OUT / "libthor_ref_autodiff.so"
+    shim = HERE / "ref_autodiff.cpp"
+    ref_srcs = [REFERENCE_DIR / "Utilities/Expression" / n
+                for n in ("AutoDiff.cpp", "Expression.cpp", "ExpressionDTypeResolution.cpp", "SqueezeAxes.cpp", "BatchedMatmulPlan.cpp")]
+    if not all(p.exists() for p in ref_srcs):
+        return out if out.exists() else None
+    REF_OUT.mkdir(exist_ok=True)
+    if not force and not _stale(out, [shim, HERE / "ref_postfix.h", *ref_srcs]):
+        return out
+    verdir = REF_OUT / "generated"
+    verdir.mkdir(exist_ok=True)
+    (verdir / "ThorVersion.h").write_text('#pragma once\n#define THOR_VERSION "0.0.33"\n#define THOR_GIT_VERSION "unknown"\n')
+    objdir = REF_OUT / "obj_autodiff"
+    objdir.mkdir(exist_ok=True)
+    common = ["g++", "-std=c++23", "-O1", "-fopenmp", "-fPIC", "-fvisibility=hidden", "-ffunction-sections", "-fdata-sections",
+              "-I", str(REFERENCE_DIR), "-I", str(HERE), "-I", str(verdir), "-I", str(CUDA_INCLUDE)]
+    for d in _site_include_dirs():
+        common += ["-I", str(d)]
+    objs = []
+    procs = []
+    for src in [shim, *ref_srcs]:
+        obj = objdir / (src.stem + ".o")
+        procs.append(subprocess.Popen(common + ["-c", str(src), "-o", str(obj)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        objs.append(obj)
+    for proc in procs:
+        log, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise RuntimeError("compiling the reference's autodiff failed:\n" + log[-4000:])
+    _run(["g++", "-shared", "-fopenmp", "-o", str(out), *map(str, objs), "-Wl,--gc-sections", "-Wl,-z,defs"])
+    shutil.rmtree(objdir, ignore_errors=True)
+    return out
+
+
 def build_all(force: bool = False) -> dict:
     result = {"oracle": str(build_oracle(force))}
     try:
@@ -185,6 +232,12 @@ def build_all(force: bool = False) -> dict:
     except RuntimeError as exc:
         result["reference_emitter"] = None
         result["reference_emitter_error"] = str(exc)[-2000:]
+    try:
+        ad = build_reference_autodiff(force)
+        result["reference_autodiff"] = str(ad) if ad else None
+    except RuntimeError as exc:
+        result["reference_autodiff"] = None
+        result["reference_autodiff_error"] = str(exc)[-2000:]
     try:
         ref_gpu = build_reference_gpu_cast(force)
         result["reference_gpu_cast"] = str(ref_gpu) if ref_gpu else None

@@ -187,8 +187,18 @@ def test_layernorm_programs_take_rows_through_the_bulk_copy_ring_and_softmax_kee
     fwd = fwd_eq.plan(shapes).stage_sources()[0]
     assert "cp.async.bulk" not in fwd  # the instruction lives in the prelude; the program calls the wrappers
     assert "tb_bulk_load(" in fwd and "tb_mbar_wait(" in fwd and "constexpr int STAGES = 3;" in fwd and "ran with the previous row" in fwd
-    bwd = fwd_eq.compile_backward(["x", "gamma", "beta"]).plan({**shapes, "__grad_output": ((32768, 8192), DT.bf16)}).stage_sources()[0]
+    assert "tb_release_registers" not in fwd  # two CTAs per SM: thread 0 requests the copies
+    bwd_eq = fwd_eq.compile_backward(["x", "gamma", "beta"])
+    bwd_shapes = {**shapes, "__grad_output": ((32768, 8192), DT.bf16)}
+    bwd = bwd_eq.plan(bwd_shapes).stage_sources()[0]
     assert "tb_bulk_load(" in bwd and "constexpr int STAGES = 4;" in bwd and "ran with the previous row" not in bwd
+    # the backward program (per-column accumulators, one CTA per SM) gives the copies a warpgroup of their own: 256 team
+    # threads + 128, registers handed over, buffers released through "empty" barriers, team-only barriers in the rounds
+    for needle in ("__launch_bounds__(384, 1)", "tb_release_registers();", "tb_claim_registers();", "tb_mbar_arrive(&tb_empty[stage]);", "tb_named_barrier<1, CONSUMERS>();"):
+        assert needle in bwd, needle
+    assert bwd.count("__syncthreads()") == 1  # the set-up barrier before the warpgroups part
+    plain = ex.compile({"y": _layernorm()}, row_program={"copy_warpgroup": -1}).compile_backward(["x", "gamma", "beta"]).plan(bwd_shapes).stage_sources()[0]
+    assert "__launch_bounds__(256)" in plain and "tb_release_registers" not in plain and "if (threadIdx.x == 0) {\n            const tb_u64 r0 = row0 + STAGES * row_stride;" in plain
     xi = ex.input("x")
     e = (xi - xi.reduce_max([1])).exp()
     sm = ex.compile(e / e.reduce_sum([1])).plan({"x": ((65536, 4096), DT.fp32)}).stage_sources()[0]

@@ -240,28 +240,20 @@ def test_values_kept_across_element_loops_do_not_change_the_result():
     """exp(x - max) is kept in registers from the sum round to the output loop; the arithmetic is the one of the
     recomputing form, so the outputs are bit-identical.  Under the fast-math option the division by the row sum becomes a
     multiplication by its reciprocal: one rounding more, within 2 ulp of the division (checked with the reciprocal alone)."""
-    import os
-
     x = (torch.randn(777, 4096, device="cuda") * 3.0).contiguous()
 
-    def run(env, fast=False):
-        saved = {k: os.environ.get(k) for k in env}
-        try:
-            os.environ.update(env)
-            plan = ex.compile(_softmax_expr(), use_fast_math=fast).stamp({"x": x})
-            plan.run()
-            torch.cuda.synchronize()
-            return plan.stage_sources()[0], plan.output().clone()
-        finally:
-            for k, v in saved.items():
-                os.environ.pop(k, None) if v is None else os.environ.__setitem__(k, v)
+    def run(tuning, fast=False):
+        plan = ex.compile(_softmax_expr(), use_fast_math=fast, row_program=tuning).stamp({"x": x})
+        plan.run()
+        torch.cuda.synchronize()
+        return plan.stage_sources()[0], plan.output().clone()
 
     src_keep, kept = run({})
-    src_re, recomputed = run({"THOR_B200_ROWPROG_CACHE": "0"})
+    src_re, recomputed = run({"keep_values": -1})
     assert "kept from the first element loop" in src_keep and "kept from the first element loop" not in src_re
     assert src_keep.count("expf(") < src_re.count("expf(")
     assert torch.equal(kept, recomputed)
-    src_rcp, rcp = run({"THOR_B200_ROWPROG_RCP": "1"})  # what the fast-math option switches on, without its approximate expf
+    src_rcp, rcp = run({"reciprocal_division": 1})  # what the fast-math option switches on, without its approximate expf
     assert "__frcp_rn" in src_rcp and "__frcp_rn" not in src_keep
     d = eo.ulp_distance(rcp.double().cpu().numpy(), kept.double().cpu().numpy(), o.FP32)
     assert float(d.max()) <= 2.0

@@ -4,8 +4,6 @@ The ring changes how operands reach the registers, not the arithmetic: per-threa
 exchange and the element expressions are the ones of the register double buffer, so the two modes
 must agree bit for bit (with and without round 1 of the next row riding on the last round of the
 current one).  Every device-side wait is bounded in time; a healthy run reports no expired wait."""
-import os
-
 import numpy as np
 import pytest
 import torch
@@ -23,20 +21,6 @@ def _layernorm():
     return {"y": (xc * rstd * gamma + beta).cast(DataType.bf16)}
 
 
-def _with_env(values, fn):
-    saved = {k: os.environ.get(k) for k in values}
-    try:
-        for k, v in values.items():
-            os.environ[k] = v
-        return fn()
-    finally:
-        for k, v in saved.items():
-            if v is None:
-                os.environ.pop(k, None)
-            else:
-                os.environ[k] = v
-
-
 def _inputs(rows, cols, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     x = (torch.randn(rows, cols, device="cuda", generator=g) * 2.0 + 0.5).bfloat16()
@@ -46,10 +30,10 @@ def _inputs(rows, cols, seed):
     return x, gamma, beta, dy
 
 
-def _run(rows, cols, env, backward):
+def _run(rows, cols, tuning, backward):
     def go():
         x, gamma, beta, dy = _inputs(rows, cols, 7)
-        eq = ex.compile(_layernorm())
+        eq = ex.compile(_layernorm(), row_program=tuning)
         if backward:
             plan = eq.compile_backward(["x", "gamma", "beta"]).stamp({"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy})
             names = ["x_grad", "gamma_grad", "beta_grad"]
@@ -62,7 +46,7 @@ def _run(rows, cols, env, backward):
         assert plan.physical_stage_names() == ["row_program"]
         return plan, [plan.output(n).view(torch.uint16).cpu().numpy().copy() for n in names]
 
-    return _with_env(env, go)
+    return go()
 
 
 # rows that do not fill the last iteration of the persistent CTAs, rows shorter than a warp's span (several
@@ -70,17 +54,24 @@ def _run(rows, cols, env, backward):
 SHAPES = [(4096, 8192), (1000, 1024), (333, 256), (77, 64), (5000, 40)]
 
 
+RING_OFF = {"ring_buffers": -1}
+
+
 @pytest.mark.parametrize("rows,cols", SHAPES)
 @pytest.mark.parametrize("backward", [False, True])
 def test_ring_modes_agree_bit_for_bit_with_the_register_double_buffer(rows, cols, backward):
-    _, want = _run(rows, cols, {"THOR_B200_ROWPROG_RING": "0"}, backward)
-    for env in ({"THOR_B200_ROWPROG_RING": "3", "THOR_B200_ROWPROG_PIPELINE": "1"},
-                {"THOR_B200_ROWPROG_RING": "4", "THOR_B200_ROWPROG_PIPELINE": "0"},
-                {"THOR_B200_ROWPROG_RING": "-1", "THOR_B200_ROWPROG_PIPELINE": "1"}):
-        plan, got = _run(rows, cols, env, backward)
+    _, want = _run(rows, cols, RING_OFF, backward)
+    for tuning in ({"ring_buffers": 3, "pipeline_round_one": 1, "copy_warpgroup": -1},
+                   {"ring_buffers": 4, "pipeline_round_one": -1, "copy_warpgroup": -1},
+                   {"ring_buffers": -2, "pipeline_round_one": 1, "copy_warpgroup": -1},
+                   {"ring_buffers": 4, "pipeline_round_one": -1, "copy_warpgroup": 1},
+                   {"ring_buffers": 3, "pipeline_round_one": 1, "copy_warpgroup": 1}):
+        plan, got = _run(rows, cols, tuning, backward)
         source = plan.stage_sources()[0]
         assert "tb_bulk_load" in source and "tb_mbar_wait" in source, "the ring was not used"
-        assert ("ran with the previous row" in source) == (env["THOR_B200_ROWPROG_PIPELINE"] == "1")
+        assert ("ran with the previous row" in source) == (tuning["pipeline_round_one"] == 1)
+        # a copy warpgroup exists only beside the teams of a program with per-column accumulators (the backward program)
+        assert ("tb_release_registers();" in source) == (tuning["copy_warpgroup"] == 1 and backward)
         for g, w in zip(got, want):
             assert np.array_equal(g, w)
         assert plan.waits_expired() == 0
@@ -91,7 +82,8 @@ def test_the_default_is_the_ring_for_layernorm_and_no_wait_expires():
     assert "tb_bulk_load" in plan.stage_sources()[0] and "ran with the previous row" in plan.stage_sources()[0]
     assert plan.waits_expired() == 0
     plan, _ = _run(2048, 8192, {}, True)
-    assert "tb_bulk_load" in plan.stage_sources()[0]
+    # programs with per-column accumulators run one CTA per SM and give the copies a warpgroup of their own
+    assert "tb_bulk_load" in plan.stage_sources()[0] and "tb_release_registers();" in plan.stage_sources()[0]
     assert plan.waits_expired() == 0
 
 
@@ -108,14 +100,14 @@ def test_programs_without_waits_report_zero():
 def test_a_wait_that_runs_out_is_counted_and_the_device_stays_usable(backward):
     """Failure on the host side of the ring: one CTA's generated code lacks the request for one iteration's rows, so the
     wait on that buffer's barrier can never be satisfied.  The wait gives up after its limit (20 ms here), the kernel
-    runs to its end, the host reads the count, and the next launches on the same context are healthy."""
-    env = {"THOR_B200_ROWPROG_WAIT_LIMIT_MS": "20", "THOR_B200_ROWPROG_TEST_DROP_FILL": "6"}
-    plan, _ = _run(4096, 8192, env, backward)
-    assert "blockIdx.x == 0 && r0 ==" in plan.stage_sources()[0]
+    runs to its end, the host reads the count, and the next launches on the same context are healthy.  The fault is asked
+    for through the program's tuning options of this one equation; nothing in the process environment can trigger it."""
+    plan, _ = _run(4096, 8192, {"wait_limit_ms": 20, "test_skip_fill": 6}, backward)
+    assert "blockIdx.x == 0 && " in plan.stage_sources()[0]
     assert plan.waits_expired() >= 1
     # the same shapes without the injected fault: correct results, nothing counted
     healthy, got = _run(4096, 8192, {}, backward)
-    _, want = _run(4096, 8192, {"THOR_B200_ROWPROG_RING": "0"}, backward)
+    _, want = _run(4096, 8192, RING_OFF, backward)
     for g, w in zip(got, want):
         assert np.array_equal(g, w)
     assert healthy.waits_expired() == 0

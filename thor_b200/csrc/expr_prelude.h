@@ -203,6 +203,14 @@ __device__ __forceinline__ void tb_bulk_load(void* smem, const void* gmem, unsig
                  "r"(tb_smem_addr(bar))
                  : "memory");
 }
+__device__ __forceinline__ void tb_mbar_arrive(tb_u64* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tb_smem_addr(bar)) : "memory"); }
+// Barrier among the first THREADS threads of the CTA (a multiple of 32), leaving __syncthreads' barrier 0 alone.
+template <int ID, int THREADS>
+__device__ __forceinline__ void tb_named_barrier() { asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(THREADS) : "memory"); }
+// Register hand-over between warpgroups (every warp of a warpgroup must execute the same one): the copy warpgroup keeps
+// 24 registers per thread, the two team warpgroups grow to 240 (per SM sub-partition: 2 x 240 + 24 <= 512 per lane).
+__device__ __forceinline__ void tb_release_registers() { asm volatile("setmaxnreg.dec.sync.aligned.u32 24;"); }
+__device__ __forceinline__ void tb_claim_registers() { asm volatile("setmaxnreg.inc.sync.aligned.u32 240;"); }
 __device__ __forceinline__ tb_u64 tb_now_ns() {
     tb_u64 ns;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));

@@ -13,6 +13,7 @@
 // persistent: they walk rows r, r + grid, ..., keep the per-column operands in registers and
 // accumulate per-column fp32 partials, which a small fold kernel sums in CTA order.
 #include <algorithm>
+#include <cctype>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -60,11 +61,11 @@ struct Program {
     int vec = 4, team = 256, cta = 256, vpt = 1;
     bool persistent = false;
     bool prefetch = false;  // persistent programs: load row r + stride while row r is being computed
-    bool prefetch_l2 = false;  // persistent programs: only pull row r + stride into L2 (costs no registers)
     int min_ctas = 0;       // second __launch_bounds__ argument, 0 = none
     bool pairs = false;     // element loops handle two neighbouring elements per step; fp32 + - * map onto the packed f32x2 instructions
     int ring_stages = 0;  // persistent programs: > 0 = rows arrive by bulk copies in a ring of this many shared-memory buffers
     size_t ring_stage_bytes = 0;
+    bool producer = false;  // ring mode: a warpgroup of its own requests the copies; the teams only wait, compute and release buffers
     std::vector<size_t> ring_offset;         // ring mode: byte offset of each [rows, cols] input inside a buffer, by input slot
     std::vector<uint8_t> cache_state;  // per node: 1 = its [rows, cols] fp32 value is kept in registers once computed, 2 = it has been
     bool cache_wanted = true;
@@ -74,7 +75,6 @@ struct Program {
     bool pipeline_wanted = true;
     bool pipelined = false;                  // ring mode: round 1 of the next row shares the last round of the current row
     bool elements_from_next_buffer = false;  // emission state: element operands come from the next ring buffer, not from registers
-    bool stage_smem = false;  // persistent programs: rows are staged in shared memory with cp.async (double buffer)
     size_t smem_bytes = 0;
     uint32_t grid = 0;
     std::string source;
@@ -534,7 +534,7 @@ std::string elemTypeOfInput(const Program& p, size_t slot) { return cTypeName(p.
 
 // Declarations of the element values x<slot> that `ids` read, for lane j of pack k.
 void emitElementInputs(const Program& p, const std::vector<uint32_t>& ids, const std::string& indent, std::ostringstream& os) {
-    const bool staged = (p.persistent && p.stage_smem) || p.elements_from_next_buffer;
+    const bool staged = p.elements_from_next_buffer;
     std::vector<bool> done(p.inputs.size(), false);
     for (uint32_t k : ids) {
         const auto& nd = p.nodes[k];
@@ -567,21 +567,6 @@ void emitColumnPackLoads(const Program& p, const std::vector<uint32_t>& ids, con
             const size_t es = dtypeSize(p.inputs[nd.input_slot].dtype);
             os << indent << "const tb_pack<VEC * " << es << "> g" << nd.input_slot << " = *reinterpret_cast<const tb_pack<VEC * " << es << ">*>(tb_ring + nstage * STAGE_BYTES + "
                << p.ring_offset[nd.input_slot] << "u + ((tb_u32)team_id * (tb_u32)COLS + q * VEC) * " << es << "u);\n";
-        }
-        return;
-    }
-    if (p.persistent && p.stage_smem) {
-        // this thread's pack k of the current row, from its private slot of the staging buffer
-        std::vector<bool> done(p.inputs.size(), false);
-        size_t fi = 0;
-        std::vector<size_t> full_index(p.inputs.size(), 0);
-        for (size_t s = 0; s < p.inputs.size(); ++s)
-            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) full_index[s] = fi++;
-        for (uint32_t k : ids) {
-            const auto& nd = p.nodes[k];
-            if (nd.op != THOR_B200_OP_INPUT || p.input_shape[nd.input_slot] != FULL || done[nd.input_slot]) continue;
-            done[nd.input_slot] = true;
-            os << indent << "const uint4 g" << nd.input_slot << " = tb_stage[((" << full_index[nd.input_slot] << " * 2 + buf) * VPT + k) * " << p.cta << " + threadIdx.x];\n";
         }
         return;
     }
@@ -660,7 +645,9 @@ std::string emit(Program& p) {
     }
     os << "#include \"tb_prelude.cuh\"\n#include \"tb_rowprog.cuh\"\n\n";
     // kernel signature
-    os << "extern \"C\" __global__ void __launch_bounds__(" << CTA << (p.min_ctas > 0 ? ", " + std::to_string(p.min_ctas) : std::string()) << ") row_kernel(";
+    os << "extern \"C\" __global__ void __launch_bounds__(" << (p.ring_stages > 0 && p.producer ? CTA + 128 : CTA)
+       << (p.ring_stages > 0 && p.producer ? std::string(", 1") : (p.min_ctas > 0 ? ", " + std::to_string(p.min_ctas) : std::string()))
+       << ") row_kernel(";
     bool first = true;
     for (size_t s = 0; s < p.inputs.size(); ++s) {
         os << (first ? "" : ", ");
@@ -693,24 +680,29 @@ std::string emit(Program& p) {
     for (size_t s = 0; s < p.inputs.size(); ++s)
         if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR_RUNTIME_SCALAR || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == SCALAR))
             os << "    const " << cTypeName(p.inputs[s].dtype) << (p.inputs[s].kind == THOR_B200_INPUT_TENSOR ? " x" : " s") << s << " = in" << s << "[0];\n";
-    // per-column operands: registers for the whole kernel when persistent
-    for (size_t s = 0; s < p.inputs.size(); ++s)
-        if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL) {
-            os << "    tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> c" << s << "[VPT];\n";
-            if (p.persistent) {
-                os << "#pragma unroll\n    for (int k = 0; k < VPT; ++k) {\n        const tb_u32 q = t + k * TEAM;\n        if (q < PPR) tb_load_keep(c" << s
-                   << "[k], in" << s << " + (tb_u64)q * VEC);\n    }\n";
+    // per-column operands and column accumulators live in registers for the whole kernel; in producer mode they are
+    // declared after the copy warpgroup has left, so that they belong to the teams' enlarged register allowance
+    auto emitColumnState = [&]() {
+        // per-column operands: registers for the whole kernel when persistent
+        for (size_t s = 0; s < p.inputs.size(); ++s)
+            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL) {
+                os << "    tb_pack<VEC * " << dtypeSize(p.inputs[s].dtype) << "> c" << s << "[VPT];\n";
+                if (p.persistent) {
+                    os << "#pragma unroll\n    for (int k = 0; k < VPT; ++k) {\n        const tb_u32 q = t + k * TEAM;\n        if (q < PPR) tb_load_keep(c" << s
+                       << "[k], in" << s << " + (tb_u64)q * VEC);\n    }\n";
+                }
             }
+        // column-reduction accumulators
+        for (uint32_t k : p.col_reduces) {
+            if (p.pairs)
+                os << "    float2 acc" << k << "[VPT][VEC / 2];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC / 2; ++j) acc" << k
+                   << "[k][j] = make_float2(0.0f, 0.0f);\n";
+            else
+                os << "    float acc" << k << "[VPT][VEC];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC; ++j) acc" << k
+                   << "[k][j] = 0.0f;\n";
         }
-    // column-reduction accumulators
-    for (uint32_t k : p.col_reduces) {
-        if (p.pairs)
-            os << "    float2 acc" << k << "[VPT][VEC / 2];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC / 2; ++j) acc" << k
-               << "[k][j] = make_float2(0.0f, 0.0f);\n";
-        else
-            os << "    float acc" << k << "[VPT][VEC];\n#pragma unroll\n    for (int k = 0; k < VPT; ++k)\n#pragma unroll\n        for (int j = 0; j < VEC; ++j) acc" << k
-               << "[k][j] = 0.0f;\n";
-    }
+    };
+    if (!(p.ring_stages > 0 && p.producer)) emitColumnState();
     // row loop
     const std::string I = "        ";
     auto declareFull = [&](const std::string& prefix, const std::string& indent) {
@@ -726,36 +718,22 @@ std::string emit(Program& p) {
         os << indent << "    }\n" << indent << "}\n";
     };
     const std::string guard = "row_ok && q < PPR";
+    // the barrier of a reduction round: the whole CTA, or -- with a copy warpgroup beside the teams -- the team threads only
+    const std::string team_sync = p.ring_stages > 0 && p.producer ? "if (TEAM > 32) tb_named_barrier<1, CONSUMERS>();\n" : "if (TEAM > 32) __syncthreads();\n";
     std::string ring_refill;  // ring mode: statements that refill the consumed buffer, emitted after the first barrier of the iteration
-    if (p.persistent && p.stage_smem) {
-        os << "    extern __shared__ uint4 tb_stage[];  // [full input][2 buffers][VPT][CTA threads] 16-byte packs, slot private to its thread\n";
-        os << "    const tb_u64 row_first = (tb_u64)blockIdx.x * TEAMS + team_id, row_stride = (tb_u64)gridDim.x * TEAMS;\n";
-        auto issue = [&](const std::string& row, const std::string& bufexpr, const std::string& indent) {
-            os << indent << "if (" << row << " < ROWS) {\n#pragma unroll\n" << indent << "    for (int k = 0; k < VPT; ++k) {\n" << indent << "        const tb_u32 q = t + k * TEAM;\n"
-               << indent << "        if (q < PPR) {\n";
-            size_t fi = 0;
-            for (size_t s = 0; s < p.inputs.size(); ++s)
-                if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
-                    os << indent << "            tb_cp_async16(&tb_stage[((" << fi << " * 2 + " << bufexpr << ") * VPT + k) * " << p.cta << " + threadIdx.x], in" << s << " + (" << row
-                       << ") * COLS + (tb_u64)q * VEC);\n";
-                    ++fi;
-                }
-            os << indent << "        }\n" << indent << "    }\n" << indent << "}\n" << indent << "tb_cp_async_commit();\n";
-        };
-        os << "    int buf = 0;\n";
-        issue("row_first", "0", "    ");
-        os << "    for (tb_u64 row0 = (tb_u64)blockIdx.x * TEAMS; row0 < ROWS; row0 += row_stride) {  // same trip count for every team of the CTA\n";
-        os << I << "const tb_u64 row = row0 + team_id;\n" << I << "const bool row_ok = " << (teams_per_cta == 1 ? "true" : "row < ROWS") << ";\n";
-        os << I << "// the copy of this team's next row runs while the current row is computed\n";
-        issue("row + row_stride", "(buf ^ 1)", I);
-        os << I << "tb_cp_async_wait<1>();\n";
-    } else if (p.persistent && p.ring_stages > 0) {
+    if (p.persistent && p.ring_stages > 0) {
         // Rows of all [rows, cols] inputs arrive by bulk copies (one per input and iteration, covering the CTA's TEAMS
         // consecutive rows) in a ring of STAGES buffers; a buffer is copied to registers, then refilled for the
         // iteration STAGES ahead, so STAGES iterations of traffic are in flight per SM at no register cost.
+        // Who requests the copies: thread 0 of the CTA after the first barrier of an iteration, or -- producer mode -- one
+        // thread of a warpgroup that does nothing else.  Issuing a bulk copy stalls its thread for a few hundred cycles;
+        // in a CTA whose warps all wait for each other twice per row that stall is on every row's critical path, so
+        // programs that run one CTA per SM give the copies a warpgroup of their own: it hands its registers to the teams
+        // (setmaxnreg) and waits on per-buffer "empty" barriers on which every team thread arrives once it holds its packs.
         os << "    constexpr int STAGES = " << p.ring_stages << ";\n    constexpr tb_u32 STAGE_BYTES = " << p.ring_stage_bytes << "u;\n";
         os << "    extern __shared__ __align__(128) unsigned char tb_ring[];  // [STAGES][full input][TEAMS][COLS]\n";
         os << "    __shared__ tb_u64 tb_full[STAGES];\n    __shared__ int tb_gave_up;\n";
+        if (p.producer) os << "    __shared__ tb_u64 tb_empty[STAGES];\n    constexpr int CONSUMERS = TEAM * TEAMS;  // threads " << CTA << " and up are the copy warpgroup\n";
         os << "    const tb_u64 row_stride = (tb_u64)gridDim.x * TEAMS;\n";
         std::ostringstream fill;  // body of: refill buffer `stage` with the rows from `r0`
         {
@@ -774,17 +752,33 @@ std::string emit(Program& p) {
                     off += row_bytes * teams_per_cta;
                 }
         }
-        auto emitFill = [&](const std::string& indent) {
+        auto emitFill = [&](const std::string& indent, std::ostringstream& to) {
             std::istringstream lines(fill.str());
             std::string line;
-            while (std::getline(lines, line)) os << indent << line << "\n";
+            while (std::getline(lines, line)) to << indent << line << "\n";
         };
-        os << "    if (threadIdx.x == 0) {\n#pragma unroll\n        for (int s = 0; s < STAGES; ++s) tb_mbar_init(&tb_full[s], 1);\n        tb_gave_up = 0;\n        tb_mbar_init_fence();\n    }\n";
+        os << "    if (threadIdx.x == 0) {\n#pragma unroll\n        for (int s = 0; s < STAGES; ++s) {\n            tb_mbar_init(&tb_full[s], 1);\n";
+        if (p.producer) os << "            tb_mbar_init(&tb_empty[s], CONSUMERS);\n";
+        os << "        }\n        tb_gave_up = 0;\n        tb_mbar_init_fence();\n    }\n";
         os << "    __syncthreads();\n";
-        os << "    if (threadIdx.x == 0) {\n        for (int stage = 0; stage < STAGES; ++stage) {\n            const tb_u64 r0 = (tb_u64)blockIdx.x * TEAMS + stage * row_stride;\n"
-           << "            if (r0 < ROWS) {\n";
-        emitFill("                ");
-        os << "            }\n        }\n    }\n";
+        if (p.producer) {
+            // host-side fault injection for the tests of the bounded waits: the generated kernel simply lacks one copy
+            // request (CTA 0, one iteration), so that the wait on that buffer's barrier runs out and the counter is raised
+            os << "    if (threadIdx.x >= CONSUMERS) {\n        tb_release_registers();\n        if (threadIdx.x == CONSUMERS) {\n            tb_u32 stage = 0, it = 0;\n"
+               << "            for (tb_u64 r0 = (tb_u64)blockIdx.x * TEAMS; r0 < ROWS; r0 += row_stride, ++it) {\n"
+               << "                // the buffer is free once every team thread holds its packs of the iteration that used it last\n"
+               << "                if (it >= STAGES) tb_mbar_wait(&tb_empty[stage], ((it / STAGES) + 1u) & 1u, &tb_gave_up);\n";
+            if (p.drop_fill_iteration >= 0) os << "                if (!(blockIdx.x == 0 && it == " << p.drop_fill_iteration << "u)) {\n";
+            else os << "                {\n";
+            emitFill("                    ", os);
+            os << "                }\n                if (++stage == STAGES) stage = 0;\n            }\n        }\n        return;\n    }\n    tb_claim_registers();\n";
+            emitColumnState();
+        } else {
+            os << "    if (threadIdx.x == 0) {\n        for (int stage = 0; stage < STAGES; ++stage) {\n            const tb_u64 r0 = (tb_u64)blockIdx.x * TEAMS + stage * row_stride;\n"
+               << "            if (r0 < ROWS) {\n";
+            emitFill("                ", os);
+            os << "            }\n        }\n    }\n";
+        }
         declareFull("f", "    ");
         os << "    tb_u32 stage = 0, parity = 0;\n";
         if (p.pipelined) {
@@ -808,19 +802,17 @@ std::string emit(Program& p) {
                 }
         }
         os << I << "    }\n" << I << "}\n";
-        // the buffer can take the rows of the iteration STAGES ahead once every thread holds its packs: after the
-        // barrier of the first reduction round when the program has one, after a barrier of its own otherwise
-        {
+        if (p.producer) {
+            os << I << "tb_mbar_arrive(&tb_empty[stage]);  // this thread is done with the buffer\n";
+        } else {
+            // the buffer can take the rows of the iteration STAGES ahead once every thread holds its packs: after the
+            // barrier of the first reduction round when the program has one, after a barrier of its own otherwise
             std::ostringstream refill;
             refill << I << "if (threadIdx.x == 0) {\n" << I << "    const tb_u64 r0 = row0 + STAGES * row_stride;\n";
-            // host-side fault injection for the tests of the bounded waits: the generated kernel simply lacks one copy
-            // (CTA 0, one iteration), so that a wait on its barrier runs out and the counter is raised
             if (p.drop_fill_iteration >= 0)
                 refill << I << "    if (r0 < ROWS && !(blockIdx.x == 0 && r0 == (tb_u64)" << p.drop_fill_iteration << " * row_stride)) {\n";
             else refill << I << "    if (r0 < ROWS) {\n";
-            std::istringstream lines(fill.str());
-            std::string line;
-            while (std::getline(lines, line)) refill << I << "        " << line << "\n";
+            emitFill(I + "        ", refill);
             refill << I << "    }\n" << I << "}\n";
             if (TEAM > 32 && max_depth >= (p.pipelined ? 2 : 1)) ring_refill = refill.str();
             else os << I << "__syncthreads();\n" << refill.str();
@@ -839,14 +831,6 @@ std::string emit(Program& p) {
         os << I << "const tb_u64 row = row0 + team_id;\n" << I << "const bool row_ok = " << (teams_per_cta == 1 ? "true" : "row < ROWS") << ";\n";
         declareFull("f", I);
         loadFull("f", "row", guard, I);
-        if (p.prefetch_l2) {
-            os << I << "{\n" << I << "    const tb_u64 next = row + (tb_u64)gridDim.x * TEAMS;\n" << I << "    if (next < ROWS) {\n#pragma unroll\n" << I
-               << "        for (int k = 0; k < VPT; ++k) {\n" << I << "            const tb_u32 q = t + k * TEAM;\n" << I << "            if (q < PPR) {\n";
-            for (size_t s2 = 0; s2 < p.inputs.size(); ++s2)
-                if (p.inputs[s2].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s2] == FULL)
-                    os << I << "                tb_prefetch_l2(in" << s2 << " + next * COLS + (tb_u64)q * VEC);\n";
-            os << I << "            }\n" << I << "        }\n" << I << "    }\n" << I << "}\n";
-        }
     } else {
         os << "    {\n        const tb_u64 row = (tb_u64)blockIdx.x * TEAMS + team_id;\n        const bool row_ok = row < ROWS;\n";
         declareFull("f", I);
@@ -1049,7 +1033,7 @@ std::string emit(Program& p) {
         p.elements_from_next_buffer = false;
         roundLaneFold(first_round);
         roundBeforeBarrier(first_round);
-        os << I << "if (TEAM > 32) __syncthreads();\n";
+        os << I << team_sync;
         roundAfterBarrier(first_round, true);
         os << "    }\n";
         std::swap(pro, os);
@@ -1092,7 +1076,7 @@ std::string emit(Program& p) {
         // team combine: all reductions of the round share one shared-memory exchange
         roundBeforeBarrier(round);
         if (carries_next) roundBeforeBarrier(first_round);
-        os << I << "if (TEAM > 32) __syncthreads();\n";
+        os << I << team_sync;
         if (!ring_refill.empty()) {
             os << ring_refill;
             ring_refill.clear();
@@ -1147,9 +1131,7 @@ std::string emit(Program& p) {
         if (p.shape[p.outputs[o].node] == ROW) os << I << "if (t == 0 && row_ok) out" << o << "[row] = "
                                                       << convertExpression("v" + std::to_string(p.outputs[o].node), vdt(p, p.outputs[o].node), p.outputs[o].dtype) << ";\n";
     if (p.persistent) os << I << "red_set ^= 1;\n";
-    if (p.persistent && p.stage_smem) {
-        os << I << "buf ^= 1;\n";
-    } else if (p.persistent && p.ring_stages > 0) {
+    if (p.persistent && p.ring_stages > 0) {
         os << I << "if (++stage == STAGES) {\n" << I << "    stage = 0;\n" << I << "    parity ^= 1;\n" << I << "}\n";
     } else if (p.persistent && p.prefetch) {
         os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n";
@@ -1388,12 +1370,10 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     mergeDuplicates(p);
     std::string why = analyse(p);
     if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
-    if (getenv("THOR_B200_ROWPROG_HOIST") == nullptr || atoi(getenv("THOR_B200_ROWPROG_HOIST")) != 0) {
-        for (int pass = 0; pass < 4 && hoistLinearRowSums(p); ++pass) {
-            mergeDuplicates(p);
-            why = analyse(p);
-            if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
-        }
+    for (int pass = 0; pass < 4 && hoistLinearRowSums(p); ++pass) {
+        mergeDuplicates(p);
+        why = analyse(p);
+        if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
     }
 
     // geometry: pack width from the narrowest FULL / COL tensor, team size from the row length
@@ -1437,85 +1417,65 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     if (p.cols % vec != 0) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: cols (%llu) is not a multiple of the pack width %d", static_cast<unsigned long long>(p.cols), vec);
     const uint64_t packs = p.cols / vec;
     if (packs > 1024ull * 8) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: rows of %llu elements do not fit one CTA's registers", static_cast<unsigned long long>(p.cols));
-    // Packs per thread: up to 4.
-    const auto envInt = [](const char* name, int fallback) {
-        const char* v = getenv(name);
-        return v && *v ? atoi(v) : fallback;
-    };
+    const thor_b200_rowprog_tuning& tune = d->tuning;
+    TB_REQUIRE(tune.reserved == 0, "rowprog_compile: tuning.reserved must be zero");
+    TB_REQUIRE(tune.ring_buffers >= -2 && tune.ring_buffers != 1 && tune.ring_buffers != 2, "rowprog_compile: tuning.ring_buffers must be 0, -1, -2 or at least 3");
     const int vpt_target = 4;  // measured: 4 packs per thread beat 2 even with column accumulators in registers
     int team = 32;
     while (team < 1024 && packs > static_cast<uint64_t>(team) * vpt_target) team *= 2;
     if (team == 64) team = 128;
-    // tuning overrides for experiments: THOR_B200_ROWPROG_TEAM / _PREFETCH / _CTAS_PER_SM
-    {
-        const int forced = envInt("THOR_B200_ROWPROG_TEAM", 0);
-        if ((forced == 32 || forced == 128 || forced == 256 || forced == 512 || forced == 1024) && packs <= static_cast<uint64_t>(forced) * 8) team = forced;
-    }
     p.vec = vec;
     p.team = team;
     p.cta = team < 256 ? 256 : team;
     p.vpt = static_cast<int>((packs + team - 1) / team);
     bool has_col_input = false;
     for (size_t s = 0; s < p.inputs.size(); ++s) has_col_input = has_col_input || (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == COL);
-    p.persistent = has_col_input || !p.col_reduces.empty() || envInt("THOR_B200_ROWPROG_PERSISTENT", 0) != 0;
-    const int prefetch_mode = envInt("THOR_B200_ROWPROG_PREFETCH", 1);  // 0 none, 1 registers, 2 L2 only
-    p.prefetch = p.persistent && prefetch_mode == 1;
-    p.prefetch_l2 = p.persistent && prefetch_mode == 2;
-    p.min_ctas = envInt("THOR_B200_ROWPROG_MIN_CTAS", d->options.min_ctas_per_sm);
-    p.pairs = envInt("THOR_B200_ROWPROG_PAIRS", 1) != 0;
-    p.cache_wanted = envInt("THOR_B200_ROWPROG_CACHE", 1) != 0;
+    p.persistent = has_col_input || !p.col_reduces.empty();
+    p.prefetch = p.persistent;  // register double buffer, unless the ring below takes over
+    p.min_ctas = d->options.min_ctas_per_sm;
+    p.pairs = true;
+    p.cache_wanted = tune.keep_values >= 0;
     // off unless the caller asked for fast math: the reference divides, and so do we (measured: softmax + argmax in one
     // pass 352 us with the division, 310 us with the reciprocal; softmax alone is at the memory bound either way)
-    p.reciprocal_division = envInt("THOR_B200_ROWPROG_RCP", p.fast_math ? 1 : 0) != 0;
-    {
-        // Staging rows in shared memory (cp.async, thread-private slots) frees the registers of both row buffers.
-        bool packs16 = true;
-        size_t n_full = 0;
-        for (size_t s = 0; s < p.inputs.size(); ++s)
-            if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
-                ++n_full;
-                packs16 = packs16 && dtypeSize(p.inputs[s].dtype) * p.vec == 16;
-            }
-        const size_t bytes = n_full * 2 * static_cast<size_t>(p.vpt) * p.cta * 16;
-        // measured on B200 (LayerNorm backward [32768, 8192] bf16): 435 us staged against 348 us with the register double buffer,
-        // so staging is opt-in
-        const bool wanted = envInt("THOR_B200_ROWPROG_STAGE", 0) != 0;
-        p.stage_smem = p.persistent && wanted && packs16 && n_full > 0 && bytes <= 200 * 1024;
-        p.smem_bytes = p.stage_smem ? bytes : 0;
-    }
+    p.reciprocal_division = tune.reciprocal_division != 0 ? tune.reciprocal_division > 0 : p.fast_math;
     {
         // Ring of bulk-copied row buffers: needs 16-byte rows, as many stages as fit in 200 KB (at least 3, at most 8).
         const uint64_t teams = p.cta / p.team;
-        size_t stage_bytes = 0;
+        size_t slot_bytes = 0;  // one row group of the CTA: every [rows, cols] input, TEAMS consecutive rows
         bool rows16 = true;
         for (size_t s = 0; s < p.inputs.size(); ++s)
             if (p.inputs[s].kind == THOR_B200_INPUT_TENSOR && p.input_shape[s] == FULL) {
                 const size_t row_bytes = p.cols * dtypeSize(p.inputs[s].dtype);
                 rows16 = rows16 && row_bytes % 16 == 0;
-                stage_bytes += row_bytes * teams;
+                slot_bytes += row_bytes * teams;
             }
         // Measured on B200, LayerNorm [32768, 8192] bf16.  Forward (two CTAs per SM): 3 buffers with round 1 pipelined
         // 164 us, against 175 us for the register double buffer, 183 us for 4 buffers and 186 us for 3 buffers
         // without the pipelining.  Backward (one CTA per SM, 64 accumulator registers): 4 buffers without pipelining
         // 311 us, against 321 us for the register double buffer, 316 / 314 us for 3 / 5 buffers and 324 us pipelined.
         const bool with_columns = !p.col_reduces.empty();
-        const bool pipeline = envInt("THOR_B200_ROWPROG_PIPELINE", with_columns ? 0 : 1) != 0 && canPipeline(p);
-        int wanted = envInt("THOR_B200_ROWPROG_RING", -2);  // -2 the measured default, 0 off, -1 as many buffers as fit, n > 0 at most n
-        if (wanted == -2) wanted = with_columns ? 4 : (pipeline ? 3 : 0);
-        if (p.persistent && !p.stage_smem && wanted != 0 && rows16 && stage_bytes > 0 && stage_bytes < (1u << 20)) {
+        const bool pipeline = (tune.pipeline_round_one != 0 ? tune.pipeline_round_one > 0 : !with_columns) && canPipeline(p);
+        // A copy warpgroup beside the teams (see emit()): for programs that run one CTA of 256 team threads per SM, where
+        // 2 x 240 + 24 registers per lane fit an SM sub-partition.  Measured on the backward program: 295 -> 285 us.
+        const bool producer = (tune.copy_warpgroup != 0 ? tune.copy_warpgroup > 0 : with_columns) && with_columns && p.cta == 256;
+        int wanted = tune.ring_buffers;  // 0 the measured default, -1 off, -2 as many buffers as fit, n >= 3 at most n
+        if (wanted == 0) wanted = with_columns ? 4 : (pipeline ? 3 : -1);
+        if (p.persistent && wanted != -1 && rows16 && slot_bytes > 0 && slot_bytes < (1u << 20)) {
             // programs without column reductions run two CTAs per SM, which share the SM's shared memory
-            int ctas_per_sm = p.col_reduces.empty() ? 2 : 1;
-            if (const int per_sm = envInt("THOR_B200_ROWPROG_CTAS_PER_SM", 0)) ctas_per_sm = per_sm;
-            int stages = static_cast<int>(std::min<size_t>(8, (200 * 1024 / ctas_per_sm) / stage_bytes));
+            const int ctas_per_sm = p.col_reduces.empty() ? 2 : 1;
+            const size_t budget = 200 * 1024 / ctas_per_sm;
+            const size_t stage_bytes = slot_bytes;
+            int stages = static_cast<int>(std::min<size_t>(8, budget / stage_bytes));
             if (wanted > 0) stages = std::min(stages, wanted);
             if (stages >= 3) {
                 p.ring_stages = stages;
                 p.ring_stage_bytes = stage_bytes;
+                p.producer = producer;
                 p.smem_bytes = stage_bytes * stages;
-                p.prefetch = p.prefetch_l2 = false;
+                p.prefetch = false;
                 p.pipeline_wanted = pipeline;
-                p.wait_limit_ms = envInt("THOR_B200_ROWPROG_WAIT_LIMIT_MS", 0);
-                p.drop_fill_iteration = envInt("THOR_B200_ROWPROG_TEST_DROP_FILL", -1);
+                p.wait_limit_ms = tune.wait_limit_ms;
+                p.drop_fill_iteration = tune.test_skip_fill > 0 ? tune.test_skip_fill : -1;
             }
         }
     }
@@ -1531,8 +1491,7 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         // every extra CTA of a program with column reductions costs a [cols] fp32 partial row
         // measured on B200 (LayerNorm [32768, 8192] bf16): 2 CTAs per SM for the forward program, 1 for the
         // backward program whose per-column accumulators take most of the register file
-        uint64_t resident = p.col_reduces.empty() ? static_cast<uint64_t>(sms) * 2 : static_cast<uint64_t>(sms);
-        if (const int per_sm = envInt("THOR_B200_ROWPROG_CTAS_PER_SM", 0)) resident = static_cast<uint64_t>(sms) * per_sm;
+        const uint64_t resident = p.col_reduces.empty() ? static_cast<uint64_t>(sms) * 2 : static_cast<uint64_t>(sms);
         p.grid = static_cast<uint32_t>(std::min<uint64_t>(ctas_for_rows, resident));
     } else {
         if (ctas_for_rows > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: too many rows for one grid");
@@ -1600,7 +1559,7 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
             h->smem_opted_in[dev & 63] = true;
         }
     }
-    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta)), args, p.smem_bytes, stream));
+    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta + (p.ring_stages > 0 && p.producer ? 128 : 0))), args, p.smem_bytes, stream));
     countLaunch();
     if (!p.all_reduces.empty()) {
         size_t idx = 0;

@@ -275,13 +275,15 @@ class Expression:
     # ---- compilation ------------------------------------------------------------------------------
     @staticmethod
     def compile(expr: Union["Expression", Mapping[str, "Expression"]], device_num: Optional[int] = None, use_fast_math: bool = False,
-                fuse_row_reductions: bool = True) -> "FusedEquation":
+                fuse_row_reductions: bool = True, row_program: Optional[Mapping[str, int]] = None) -> "FusedEquation":
         """FusedEquation::compile: one Expression (output named "output") or a dict of named outputs.
-        device_num defaults to the current CUDA device of the calling process."""
+        device_num defaults to the current CUDA device of the calling process.  row_program sets fields of
+        FusedEquationOptions::row_program (ROW_PROGRAM_TUNING_FIELDS; layout choices of row programs, all computing the same
+        values), which backward equations compiled from this one inherit."""
         named = {"output": expr} if isinstance(expr, Expression) else dict(expr)
         if device_num is None:
             device_num = torch.cuda.current_device() if torch.cuda.is_available() else 0
-        return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions)
+        return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions, row_program)
 
 
 def _bind_tensor(name: str, t: torch.Tensor, dtype: Optional[DataType] = None) -> _Binding:
@@ -373,8 +375,11 @@ class StampedExecutionPlan:
         return raw.view(to_torch(dt)).reshape(shape)
 
 
+ROW_PROGRAM_TUNING_FIELDS = ("ring_buffers", "pipeline_round_one", "copy_warpgroup", "keep_values", "reciprocal_division", "wait_limit_ms", "test_skip_fill")
+
+
 class FusedEquation:
-    def __init__(self, named: Mapping[str, Expression], device_num: int, use_fast_math: bool, fuse_row_reductions: bool, _handle=None):
+    def __init__(self, named: Mapping[str, Expression], device_num: int, use_fast_math: bool, fuse_row_reductions: bool, row_program=None, _handle=None):
         self.device_num = device_num
         if _handle is not None:
             self._h = _handle
@@ -383,7 +388,13 @@ class FusedEquation:
         arr_n = (C.c_char_p * len(names))(*[n.encode() for n in names])
         arr_e = (C.c_void_p * len(names))(*[named[n]._h for n in names])
         out = C.c_void_p()
-        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), C.byref(out)))
+        tuning = None
+        if row_program:
+            unknown = set(row_program) - set(ROW_PROGRAM_TUNING_FIELDS)
+            if unknown:
+                raise _native.ThorB200InvalidArgument(f"unknown row_program field(s): {sorted(unknown)}")
+            tuning = (C.c_int32 * len(ROW_PROGRAM_TUNING_FIELDS))(*[int(row_program.get(f, 0)) for f in ROW_PROGRAM_TUNING_FIELDS])
+        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, C.byref(out)))
         self._h = out
 
     def __del__(self):
@@ -397,7 +408,7 @@ class FusedEquation:
         arr = (C.c_char_p * len(wrt))(*[w.encode() for w in wrt])
         out = C.c_void_p()
         _check(_host.thb_compile_backward(self._h, arr, len(wrt), upstream_prefix.encode(), C.byref(out)))
-        return FusedEquation({}, self.device_num, False, True, _handle=out)
+        return FusedEquation({}, self.device_num, False, True, None, _handle=out)
 
     def stamp(self, inputs: Mapping[str, Union[torch.Tensor, float]], stream: Optional[torch.cuda.Stream] = None,
               outputs: Optional[Mapping[str, torch.Tensor]] = None, dtypes: Optional[Mapping[str, DataType]] = None) -> StampedExecutionPlan:
@@ -426,10 +437,19 @@ class FusedEquation:
             _check(_host.thb_stamp(self._h, in_arr, len(ins), out_arr, len(outs), _native.stream_handle(stream), C.byref(plan)))
         return StampedExecutionPlan(plan, keep)
 
-    def plan(self, inputs: Mapping[str, Union[tuple, float]]) -> StampedExecutionPlan:
-        """Stamps without a GPU: `inputs` maps each tensor name to (shape, DataType) and each runtime
-        scalar to a float.  The returned plan lists its stages, kernel shapes, emitted sources and
-        intermediate bytes exactly as a real stamp on those shapes would; run() and output() refuse."""
+    def graph(self, inputs: Mapping[str, Union[tuple, float]]) -> dict:
+        """The dtype-resolved SSA graph this equation evaluates for tensors of the given (shape, DataType): inputs by slot,
+        named outputs and every node (ExprOp integer, parents, literal, axes lists, output / compute dtype).  For a backward
+        equation it is the differentiated graph for those forward shapes.  Needs no GPU."""
+        import json
+
+        in_arr, n = self._shape_bindings(inputs)
+        text = C.c_char_p()
+        _check(_host.thb_equation_graph(self._h, in_arr, n, C.byref(text)))
+        return json.loads(text.value.decode())
+
+    @staticmethod
+    def _shape_bindings(inputs):
         ins = []
         for name, v in inputs.items():
             b = _Binding()
@@ -447,9 +467,15 @@ class FusedEquation:
                     b.dims[i] = int(d)
                 b.is_scalar = 0
             ins.append(b)
-        in_arr = (_Binding * max(1, len(ins)))(*ins)
+        return (_Binding * max(1, len(ins)))(*ins), len(ins)
+
+    def plan(self, inputs: Mapping[str, Union[tuple, float]]) -> StampedExecutionPlan:
+        """Stamps without a GPU: `inputs` maps each tensor name to (shape, DataType) and each runtime
+        scalar to a float.  The returned plan lists its stages, kernel shapes, emitted sources and
+        intermediate bytes exactly as a real stamp on those shapes would; run() and output() refuse."""
+        in_arr, n_in = self._shape_bindings(inputs)
         plan = C.c_void_p()
-        _check(_host.thb_stamp_plan_only(self._h, in_arr, len(ins), C.byref(plan)))
+        _check(_host.thb_stamp_plan_only(self._h, in_arr, n_in, C.byref(plan)))
         return StampedExecutionPlan(plan, [], plan_only=True)
 
     def run(self, inputs: Mapping[str, Union[torch.Tensor, float]], output: Union[torch.Tensor, Mapping[str, torch.Tensor]],

@@ -328,6 +328,51 @@ struct Planner {
 
 }  // namespace
 
+std::string FusedEquation::describeGraph(const std::unordered_map<std::string, std::vector<uint64_t>>& input_dims,
+                                         const std::unordered_map<std::string, DataType>& input_dtypes) const {
+    Outputs outputs = outputs_;
+    if (deferred_backward_) outputs = buildBackwardOutputs(deferred_backward_->forward, deferred_backward_->wrt, deferred_backward_->upstream_prefix, input_dims, input_dtypes);
+    PhysicalOutputs phys = outputs.physicalOutputs();
+    phys.expr = std::make_shared<PhysicalExpression>(*phys.expr);
+    std::vector<DataType> slot_dtypes(phys.expr->inputs.size(), DataType::FP32);
+    for (const NamedInput& in : phys.expr->inputs) {
+        if (in.kind == NamedInput::Kind::RuntimeScalarFp32) continue;
+        auto it = input_dtypes.find(in.name);
+        if (it == input_dtypes.end()) throw std::invalid_argument("describeGraph: no dtype given for input '" + in.name + "'");
+        slot_dtypes[in.slot] = it->second;
+    }
+    resolveOutputsDTypesInPlace(phys, slot_dtypes);
+    std::ostringstream os;
+    os.precision(17);
+    auto list = [&](const char* key, const std::vector<uint64_t>& v) {
+        os << ",\"" << key << "\":[";
+        for (size_t i = 0; i < v.size(); ++i) os << (i ? "," : "") << v[i];
+        os << "]";
+    };
+    auto parent = [](uint32_t p) { return p == UINT32_MAX ? -1ll : static_cast<long long>(p); };
+    os << "{\"inputs\":[";
+    for (size_t i = 0; i < phys.expr->inputs.size(); ++i) {
+        const NamedInput& in = phys.expr->inputs[i];
+        os << (i ? "," : "") << "{\"name\":\"" << in.name << "\",\"slot\":" << in.slot << ",\"kind\":" << static_cast<int>(in.kind) << "}";
+    }
+    os << "],\"outputs\":[";
+    for (size_t i = 0; i < phys.outputs.size(); ++i) os << (i ? "," : "") << "{\"name\":\"" << phys.outputs[i].name << "\",\"node\":" << phys.outputs[i].node_idx << "}";
+    os << "],\"nodes\":[";
+    for (size_t k = 0; k < phys.expr->nodes.size(); ++k) {
+        const ExprNode& n = phys.expr->nodes[k];
+        os << (k ? "," : "") << "{\"op\":" << static_cast<int>(n.op) << ",\"lhs\":" << parent(n.lhs) << ",\"rhs\":" << parent(n.rhs) << ",\"aux\":" << parent(n.aux)
+           << ",\"slot\":" << parent(n.input_slot) << ",\"scalar\":" << n.scalar_fp << ",\"out\":" << (n.output_dtype ? static_cast<int>(*n.output_dtype) : 0)
+           << ",\"compute\":" << (n.compute_dtype ? static_cast<int>(*n.compute_dtype) : 0);
+        list("reduction_axes", n.reduction_axes);
+        list("squeeze_axes", n.squeeze_axes);
+        list("unsqueeze_axes", n.unsqueeze_axes);
+        list("reshape_dims", n.reshape_dims);
+        os << "}";
+    }
+    os << "]}";
+    return os.str();
+}
+
 StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, RuntimeInputValue>& inputs, const Stream& stream,
                                           const std::unordered_map<std::string, Tensor>& preallocated_outputs) {
     Outputs outputs = outputs_;
@@ -450,7 +495,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
     // Optional physical fusion of row-reduction chains (softmax / LayerNorm class).
     std::vector<bool> covered(g.nodes.size(), false);  // nodes whose values a super-stage already produced or made unnecessary
     if (options_.fuse_row_reductions) {
-        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_, options_.use_fast_math};
+        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_, options_.use_fast_math, options_.row_program};
         std::vector<RowFusionMatch> matches = matchRowFusions(ctx);
         for (RowFusionMatch& m : matches) {
             PhysicalStage st;

@@ -34,8 +34,21 @@ struct RuntimeInputValue {
 
 enum class StageKind { FusedKernel, Reduction, ArgMinMax, View, FusedRows, ReduceMinMaxBackward };
 
+// Layout choices of persistent row programs (thor_b200_rowprog_tuning of the C ABI, field for field); all zero = the
+// measured defaults.  Every combination computes the same values.
+struct RowProgramTuning {
+    int ring_buffers = 0;
+    int pipeline_round_one = 0;
+    int copy_warpgroup = 0;
+    int keep_values = 0;
+    int reciprocal_division = 0;
+    int wait_limit_ms = 0;
+    int test_skip_fill = 0;
+};
+
 struct FusedEquationOptions {
     bool use_fast_math = false;
+    RowProgramTuning row_program;
     // Execute "elementwise -> row reduction -> elementwise" chains over the innermost axis (softmax,
     // LayerNorm forward / backward) as one single-pass kernel instead of the reference's stage list.
     // The logical stage list is still reported by stageKindNames().
@@ -91,6 +104,12 @@ class FusedEquation {
     // an equation whose outputs are "<wrt>_grad" for every requested input, taking the forward inputs
     // plus the upstream gradient(s) "<upstream_prefix><output name>" (one output: just upstream_prefix).
     FusedEquation compileBackward(const std::vector<std::string>& wrt_names, const std::string& upstream_prefix = "__grad_output") const;
+
+    // The dtype-resolved SSA graph this equation evaluates for the given tensor shapes and dtypes, as JSON text: inputs by
+    // slot, named outputs, and every node with its ExprOp integer, parents, literal, axes lists and resolved output /
+    // compute dtypes.  For a backward equation this is the graph that stamp() differentiates for those shapes.  No GPU.
+    std::string describeGraph(const std::unordered_map<std::string, std::vector<uint64_t>>& input_dims,
+                              const std::unordered_map<std::string, DataType>& input_dtypes) const;
 
     const Outputs& outputs() const { return outputs_; }
     int deviceNum() const { return device_num_; }

@@ -175,13 +175,17 @@ THB_API int thb_shape_op(const Expression* a, int op, const uint64_t* values, ui
 THB_API uint32_t thb_expr_node_count(const Expression* a) { return static_cast<uint32_t>(a->graph()->nodes.size()); }
 
 // ---- equations --------------------------------------------------------------------------------------
-THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint32_t n, int device, int fast_math, int fuse_rows, FusedEquation** out) {
+// row_tuning: NULL or the seven RowProgramTuning fields in declaration order
+THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint32_t n, int device, int fast_math, int fuse_rows, const int32_t* row_tuning,
+                        FusedEquation** out) {
     return guarded([&] {
         std::vector<std::pair<std::string, Expression>> named;
         for (uint32_t i = 0; i < n; ++i) named.emplace_back(names[i], *exprs[i]);
         FusedEquationOptions opt;
         opt.use_fast_math = fast_math != 0;
         opt.fuse_row_reductions = fuse_rows != 0;
+        if (row_tuning != nullptr)
+            opt.row_program = RowProgramTuning{row_tuning[0], row_tuning[1], row_tuning[2], row_tuning[3], row_tuning[4], row_tuning[5], row_tuning[6]};
         *out = new FusedEquation(FusedEquation::compile(Expression::outputs(named), device, opt));
     });
 }
@@ -225,6 +229,22 @@ THB_API int thb_stamp(FusedEquation* eq, const thb_binding* inputs, uint32_t n_i
             throw;
         }
         *out = p;
+    });
+}
+// JSON description of the dtype-resolved graph the equation evaluates for the bound shapes and dtypes (ptr ignored).
+// The text lives until the next call on the calling thread.
+THB_API int thb_equation_graph(FusedEquation* eq, const thb_binding* inputs, uint32_t n_inputs, const char** text) {
+    static thread_local std::string g_graph;
+    return guarded([&] {
+        std::unordered_map<std::string, std::vector<uint64_t>> dims;
+        std::unordered_map<std::string, DataType> dtypes;
+        for (uint32_t i = 0; i < n_inputs; ++i) {
+            if (inputs[i].is_scalar) continue;
+            dims[inputs[i].name] = std::vector<uint64_t>(inputs[i].dims, inputs[i].dims + inputs[i].rank);
+            dtypes[inputs[i].name] = static_cast<DataType>(inputs[i].dtype);
+        }
+        g_graph = eq->describeGraph(dims, dtypes);
+        *text = g_graph.c_str();
     });
 }
 // Same as thb_stamp, but nothing touches a GPU: bindings carry shapes and dtypes only (their ptr is

@@ -273,6 +273,13 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
     d.cols = cols;
     d.options.use_fast_math = ctx.use_fast_math;
     d.options.compile_only = Tensor::planOnly() ? 1 : 0;
+    d.tuning.ring_buffers = ctx.tuning.ring_buffers;
+    d.tuning.pipeline_round_one = ctx.tuning.pipeline_round_one;
+    d.tuning.copy_warpgroup = ctx.tuning.copy_warpgroup;
+    d.tuning.keep_values = ctx.tuning.keep_values;
+    d.tuning.reciprocal_division = ctx.tuning.reciprocal_division;
+    d.tuning.wait_limit_ms = ctx.tuning.wait_limit_ms;
+    d.tuning.test_skip_fill = ctx.tuning.test_skip_fill;
     auto prog = std::make_shared<ProgHandle>();
     size_t ws_bytes = 1;
     const int status = thor_b200_rowprog_compile(&d, &prog->h, &ws_bytes);

@@ -21,6 +21,7 @@ struct RowFusionContext {
     const std::vector<RuntimeInputValue>& bound;  // by input slot
     int device_num;
     bool use_fast_math;
+    RowProgramTuning tuning;
 };
 
 struct RowFusionMatch {
