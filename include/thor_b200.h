@@ -385,6 +385,14 @@ typedef struct thor_b200_rowprog thor_b200_rowprog;
 THOR_B200_API int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* desc, thor_b200_rowprog** out_prog, size_t* workspace_bytes);
 THOR_B200_API int thor_b200_rowprog_launch(thor_b200_rowprog* prog, const void* const* input_ptrs, const float* runtime_scalars,
                                            void* const* output_ptrs, void* workspace, size_t workspace_bytes, void* stream);
+/* The same launch for a caller that holds only a SHARD of the rows (rows split across GPUs): column_sums_f32, when not
+ * NULL, receives the program's column reductions unrounded, fp32 [number of column reductions][cols] in the order of the
+ * program's outputs, next to the rounded outputs.  The caller adds the shards' sums (thor_b200_comm_allreduce_f32) and
+ * rounds once, instead of adding values that were already rounded to a 16-bit output dtype.  A mean over rows divides
+ * by this program's own row count.  No counterpart in the reference, which is single-GPU on this path. */
+THOR_B200_API int thor_b200_rowprog_launch_sharded(thor_b200_rowprog* prog, const void* const* input_ptrs, const float* runtime_scalars,
+                                                   void* const* output_ptrs, void* workspace, size_t workspace_bytes, void* column_sums_f32,
+                                                   void* stream);
 THOR_B200_API const char* thor_b200_rowprog_source(const thor_b200_rowprog* prog);
 /* Kernels one launch of the program runs (1, or 2 when column reductions need the fold kernel). */
 THOR_B200_API uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* prog);

@@ -135,7 +135,7 @@ def test_layernorm_forward_and_backward_plans():
     bwd = fwd_eq.compile_backward(["x", "gamma", "beta"]).plan({**shapes, "__grad_output": ((32768, 8192), DT.bf16)})
     assert sorted(bwd.output_names()) == ["beta_grad", "gamma_grad", "x_grad"]
     # one row kernel plus one fold per column reduction; gradients come back in the dtype of their input
-    assert bwd.physical_stage_names() == ["row_program"] and bwd.kernel_launches_per_run() == 3
+    assert bwd.physical_stage_names() == ["row_program"] and bwd.kernel_launches_per_run() == 2  # the row kernel + one fold of both column sums
     assert bwd.output_spec("x_grad") == ([32768, 8192], DT.bf16)
     assert bwd.output_spec("gamma_grad") == ([8192], DT.bf16)
     src = bwd.stage_sources()[0]

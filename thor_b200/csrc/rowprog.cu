@@ -1298,22 +1298,68 @@ __global__ void __launch_bounds__(1024) foldFullPartials(const float* __restrict
     }
 }
 
-// Folds column partials [parts][cols] in part order and stores in the output dtype.
-__global__ void __launch_bounds__(256) foldColumnPartials(const float* __restrict__ ws, uint32_t parts, uint64_t cols, void* out, int out_dtype, float divisor) {
+// Folds the column partials of every column reduction of a program in ONE launch.  ws holds [reduction][parts][cols]
+// fp32.  A CTA of 8 warps owns 32 * VEC neighbouring columns of one reduction: warp w adds parts w, w + 8, ... (coalesced
+// VEC-wide loads, all of a thread's loads independent), the eight warp sums meet in shared memory and are added in warp
+// order, so the result does not depend on timing.  The value is divided (means), optionally written unrounded to
+// sums_f32[reduction][cols] -- what a caller that combines several GPUs' shards adds up before rounding once -- and
+// stored in the output's dtype.
+constexpr int kMaxColumnFolds = 8;
+struct ColumnFoldArgs {
+    void* out[kMaxColumnFolds];
+    int out_dtype[kMaxColumnFolds];
+    float divisor[kMaxColumnFolds];
+};
+
+__device__ __forceinline__ void storeAs(void* out, uint64_t i, int dtype, float v) {
+    switch (dtype) {
+        case THOR_B200_FP32: static_cast<float*>(out)[i] = v; break;
+        case THOR_B200_FP16: static_cast<__half*>(out)[i] = __float2half_rn(v); break;
+        case THOR_B200_BF16: static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v); break;
+        case THOR_B200_FP8_E4M3: static_cast<__nv_fp8_storage_t*>(out)[i] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); break;
+        case THOR_B200_FP8_E5M2: static_cast<__nv_fp8_storage_t*>(out)[i] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2); break;
+        default: break;
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(256) foldColumnPartials(const float* __restrict__ ws, uint32_t parts, uint64_t cols, ColumnFoldArgs args, float* __restrict__ sums_f32) {
     gridDependencyWait();
     gridLaunchDependents();
-    const uint64_t c = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
-    if (c >= cols) return;
-    float v = 0.0f;
-    for (uint32_t s = 0; s < parts; ++s) v += ws[static_cast<uint64_t>(s) * cols + c];
-    if (divisor != 1.0f) v = v / divisor;
-    switch (out_dtype) {
-        case THOR_B200_FP32: static_cast<float*>(out)[c] = v; break;
-        case THOR_B200_FP16: static_cast<__half*>(out)[c] = __float2half_rn(v); break;
-        case THOR_B200_BF16: static_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(v); break;
-        case THOR_B200_FP8_E4M3: static_cast<__nv_fp8_storage_t*>(out)[c] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); break;
-        case THOR_B200_FP8_E5M2: static_cast<__nv_fp8_storage_t*>(out)[c] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2); break;
-        default: break;
+    __shared__ float sm[8][32 * VEC];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.y;
+    const uint64_t c0 = (static_cast<uint64_t>(blockIdx.x) * 32 + lane) * VEC;
+    const float* base = ws + static_cast<uint64_t>(r) * parts * cols;
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.0f;
+    if (c0 < cols) {
+        for (uint32_t s = warp; s < parts; s += 8) {
+            if (VEC == 4) {
+                const float4 v = *reinterpret_cast<const float4*>(base + static_cast<uint64_t>(s) * cols + c0);
+                acc[0] += v.x;
+                acc[1 % VEC] += v.y;
+                acc[2 % VEC] += v.z;
+                acc[3 % VEC] += v.w;
+            } else {
+                acc[0] += base[static_cast<uint64_t>(s) * cols + c0];
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) sm[warp][lane * VEC + j] = acc[j];
+    __syncthreads();
+    // thread t of the CTA finishes column t of the CTA's 32 * VEC (VEC = 4: the first 128 threads)
+    if (threadIdx.x < 32 * VEC) {
+        const uint64_t c = static_cast<uint64_t>(blockIdx.x) * 32 * VEC + threadIdx.x;
+        if (c < cols) {
+            float v = sm[0][threadIdx.x];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) v += sm[w][threadIdx.x];
+            if (args.divisor[r] != 1.0f) v = v / args.divisor[r];
+            if (sums_f32 != nullptr) sums_f32[static_cast<uint64_t>(r) * cols + c] = v;
+            storeAs(args.out[r], c, args.out_dtype[r], v);
+        }
     }
 }
 
@@ -1497,6 +1543,8 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         if (ctas_for_rows > 0x7FFFFFFFull) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: too many rows for one grid");
         p.grid = static_cast<uint32_t>(ctas_for_rows);
     }
+    if (p.col_reduces.size() > static_cast<size_t>(kMaxColumnFolds))
+        return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: at most %d column reductions per program", kMaxColumnFolds);
     const std::string err = emit(p);
     if (!err.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", err.c_str());
     h->workspace_bytes = p.col_reduces.empty() ? 1 : p.col_reduces.size() * static_cast<size_t>(p.grid) * teams_per_cta * p.cols * sizeof(float);
@@ -1510,6 +1558,11 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
 
 int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs, const float* runtime_scalars, void* const* output_ptrs, void* workspace,
                              size_t workspace_bytes, void* stream_v) {
+    return thor_b200_rowprog_launch_sharded(h, input_ptrs, runtime_scalars, output_ptrs, workspace, workspace_bytes, nullptr, stream_v);
+}
+
+int thor_b200_rowprog_launch_sharded(thor_b200_rowprog* h, const void* const* input_ptrs, const float* runtime_scalars, void* const* output_ptrs, void* workspace,
+                                     size_t workspace_bytes, void* column_sums_f32, void* stream_v) {
     using namespace tb;
     using namespace tb::rowprog;
     TB_REQUIRE(h != nullptr, "rowprog_launch: null handle");
@@ -1582,18 +1635,27 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
     }
     if (!p.col_reduces.empty()) {
         const uint32_t parts = p.grid * static_cast<uint32_t>(p.cta / p.team);
+        ColumnFoldArgs fold{};
         size_t ci = 0;
         for (uint32_t k : p.col_reduces) {
             size_t o = 0;
             for (; o < p.outputs.size(); ++o)
                 if (p.outputs[o].node == k) break;
-            const float divisor = p.nodes[k].op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows) : 1.0f;
-            const float* part = static_cast<const float*>(workspace) + ci * static_cast<size_t>(parts) * p.cols;
-            (void)launchDependent(foldColumnPartials, dim3(static_cast<unsigned>((p.cols + 255) / 256)), dim3(256), 0, stream, part, parts, p.cols, output_ptrs[o], p.outputs[o].dtype, divisor);
-            TB_CUDA(cudaGetLastError());
+            fold.out[ci] = output_ptrs[o];
+            fold.out_dtype[ci] = p.outputs[o].dtype;
+            fold.divisor[ci] = p.nodes[k].op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows) : 1.0f;
             ++ci;
         }
-        countLaunch(p.col_reduces.size());
+        const float* part = static_cast<const float*>(workspace);
+        float* sums = static_cast<float*>(column_sums_f32);
+        if (p.cols % 4 == 0)
+            (void)launchDependent(foldColumnPartials<4>, dim3(static_cast<unsigned>((p.cols + 127) / 128), static_cast<unsigned>(ci)), dim3(256), 0, stream, part, parts, p.cols, fold, sums);
+        else
+            (void)launchDependent(foldColumnPartials<1>, dim3(static_cast<unsigned>((p.cols + 31) / 32), static_cast<unsigned>(ci)), dim3(256), 0, stream, part, parts, p.cols, fold, sums);
+        TB_CUDA(cudaGetLastError());
+        countLaunch();
+    } else {
+        TB_REQUIRE(column_sums_f32 == nullptr, "rowprog_launch: the program has no column reductions to report unrounded");
     }
     return THOR_B200_OK;
 }
@@ -1601,7 +1663,7 @@ int thor_b200_rowprog_launch(thor_b200_rowprog* h, const void* const* input_ptrs
 const char* thor_b200_rowprog_source(const thor_b200_rowprog* h) { return h ? h->prog.source.c_str() : ""; }
 
 uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) {
-    return h ? 1u + static_cast<uint32_t>(h->prog.col_reduces.size() + h->prog.all_reduces.size()) : 0u;
+    return h ? 1u + static_cast<uint32_t>((h->prog.col_reduces.empty() ? 0 : 1) + h->prog.all_reduces.size()) : 0u;
 }
 
 int thor_b200_rowprog_waits_expired(thor_b200_rowprog* h, uint32_t* count) {

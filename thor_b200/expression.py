@@ -275,15 +275,18 @@ class Expression:
     # ---- compilation ------------------------------------------------------------------------------
     @staticmethod
     def compile(expr: Union["Expression", Mapping[str, "Expression"]], device_num: Optional[int] = None, use_fast_math: bool = False,
-                fuse_row_reductions: bool = True, row_program: Optional[Mapping[str, int]] = None) -> "FusedEquation":
+                fuse_row_reductions: bool = True, row_program: Optional[Mapping[str, int]] = None,
+                unrounded_column_sums: bool = False) -> "FusedEquation":
         """FusedEquation::compile: one Expression (output named "output") or a dict of named outputs.
         device_num defaults to the current CUDA device of the calling process.  row_program sets fields of
         FusedEquationOptions::row_program (ROW_PROGRAM_TUNING_FIELDS; layout choices of row programs, all computing the same
-        values), which backward equations compiled from this one inherit."""
+        values), which backward equations compiled from this one inherit.  unrounded_column_sums (for callers that hold
+        one shard of the rows): row programs with column reductions also deliver those sums as the fp32 output
+        "__column_sums" [reductions, cols], rows named by StampedExecutionPlan.column_sum_names()."""
         named = {"output": expr} if isinstance(expr, Expression) else dict(expr)
         if device_num is None:
             device_num = torch.cuda.current_device() if torch.cuda.is_available() else 0
-        return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions, row_program)
+        return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions, row_program, unrounded_column_sums)
 
 
 def _bind_tensor(name: str, t: torch.Tensor, dtype: Optional[DataType] = None) -> _Binding:
@@ -333,6 +336,7 @@ class StampedExecutionPlan:
     def physical_stage_names(self): return self._strings(1)
     def stage_sources(self): return self._strings(2)
     def output_names(self): return self._strings(3)
+    def column_sum_names(self): return self._strings(4)
     def output_spec(self, name: str = "output"):
         """(shape, DataType) of the named output."""
         b = _Binding()
@@ -379,7 +383,7 @@ ROW_PROGRAM_TUNING_FIELDS = ("ring_buffers", "pipeline_round_one", "copy_warpgro
 
 
 class FusedEquation:
-    def __init__(self, named: Mapping[str, Expression], device_num: int, use_fast_math: bool, fuse_row_reductions: bool, row_program=None, _handle=None):
+    def __init__(self, named: Mapping[str, Expression], device_num: int, use_fast_math: bool, fuse_row_reductions: bool, row_program=None, unrounded_column_sums=False, _handle=None):
         self.device_num = device_num
         if _handle is not None:
             self._h = _handle
@@ -394,7 +398,7 @@ class FusedEquation:
             if unknown:
                 raise _native.ThorB200InvalidArgument(f"unknown row_program field(s): {sorted(unknown)}")
             tuning = (C.c_int32 * len(ROW_PROGRAM_TUNING_FIELDS))(*[int(row_program.get(f, 0)) for f in ROW_PROGRAM_TUNING_FIELDS])
-        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, C.byref(out)))
+        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, int(unrounded_column_sums), C.byref(out)))
         self._h = out
 
     def __del__(self):
@@ -408,7 +412,7 @@ class FusedEquation:
         arr = (C.c_char_p * len(wrt))(*[w.encode() for w in wrt])
         out = C.c_void_p()
         _check(_host.thb_compile_backward(self._h, arr, len(wrt), upstream_prefix.encode(), C.byref(out)))
-        return FusedEquation({}, self.device_num, False, True, None, _handle=out)
+        return FusedEquation({}, self.device_num, False, True, None, False, _handle=out)
 
     def stamp(self, inputs: Mapping[str, Union[torch.Tensor, float]], stream: Optional[torch.cuda.Stream] = None,
               outputs: Optional[Mapping[str, torch.Tensor]] = None, dtypes: Optional[Mapping[str, DataType]] = None) -> StampedExecutionPlan:

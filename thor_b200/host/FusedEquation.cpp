@@ -169,6 +169,7 @@ struct StampedExecutionPlan::Impl {
     std::map<std::string, Tensor> outputs;
     std::vector<Tensor> keep_alive;
     uint64_t intermediate_bytes = 0;
+    std::vector<std::string> column_sum_names;
     bool plan_only = false;  // stamped with placeholder memory: describes the plan, cannot run
 };
 
@@ -248,6 +249,7 @@ uint64_t StampedExecutionPlan::waitsExpired() const {
         if (s.waits_expired) n += s.waits_expired();
     return n;
 }
+std::vector<std::string> StampedExecutionPlan::columnSumNames() const { return impl_->column_sum_names; }
 uint64_t StampedExecutionPlan::kernelLaunchesPerRun() const {
     uint64_t n = 0;
     for (const auto& s : impl_->stages)
@@ -495,7 +497,7 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
     // Optional physical fusion of row-reduction chains (softmax / LayerNorm class).
     std::vector<bool> covered(g.nodes.size(), false);  // nodes whose values a super-stage already produced or made unnecessary
     if (options_.fuse_row_reductions) {
-        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_, options_.use_fast_math, options_.row_program};
+        RowFusionContext ctx{g, phys.outputs, shape, bound, device_num_, options_.use_fast_math, options_.row_program, options_.unrounded_column_sums};
         std::vector<RowFusionMatch> matches = matchRowFusions(ctx);
         for (RowFusionMatch& m : matches) {
             PhysicalStage st;
@@ -514,6 +516,10 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             }
             for (uint32_t node : m.absorbed) covered[node] = true;
             st.custom_launch = m.bind(node_tensor, impl->keep_alive, impl->intermediate_bytes);
+            if (m.column_sums) {
+                impl->outputs["__column_sums"] = *m.column_sums;
+                impl->column_sum_names = m.column_sum_names;
+            }
             st.waits_expired = m.waits_expired;
             impl->stages.push_back(std::move(st));
         }

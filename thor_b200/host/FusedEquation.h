@@ -49,6 +49,11 @@ struct RowProgramTuning {
 struct FusedEquationOptions {
     bool use_fast_math = false;
     RowProgramTuning row_program;
+    // For callers that hold one SHARD of the rows (rows split across GPUs): a row program with column reductions (LayerNorm
+    // dgamma / dbeta) also delivers those sums unrounded, as the fp32 output "__column_sums" of shape [reductions, cols]
+    // in the order of columnSumNames(), so that the shards' sums can be added before the single rounding to the gradient's
+    // dtype.  The reference is single-GPU on this path and has no counterpart.
+    bool unrounded_column_sums = false;
     // Execute "elementwise -> row reduction -> elementwise" chains over the innermost axis (softmax,
     // LayerNorm forward / backward) as one single-pass kernel instead of the reference's stage list.
     // The logical stage list is still reported by stageKindNames().
@@ -80,6 +85,9 @@ class StampedExecutionPlan {
     // Kernels that wait on device-side barriers bound every wait in time; this is how many such waits ran out in the
     // launches so far (synchronises with the device).  Anything but 0 means the outputs are not to be trusted.
     uint64_t waitsExpired() const;
+    // Names of the outputs whose unrounded sums the rows of "__column_sums" hold (empty unless the equation was compiled
+    // with unrounded_column_sums and runs as a row program with column reductions).
+    std::vector<std::string> columnSumNames() const;
 
    private:
     std::shared_ptr<Impl> impl_;

@@ -177,13 +177,14 @@ THB_API uint32_t thb_expr_node_count(const Expression* a) { return static_cast<u
 // ---- equations --------------------------------------------------------------------------------------
 // row_tuning: NULL or the seven RowProgramTuning fields in declaration order
 THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint32_t n, int device, int fast_math, int fuse_rows, const int32_t* row_tuning,
-                        FusedEquation** out) {
+                        int unrounded_column_sums, FusedEquation** out) {
     return guarded([&] {
         std::vector<std::pair<std::string, Expression>> named;
         for (uint32_t i = 0; i < n; ++i) named.emplace_back(names[i], *exprs[i]);
         FusedEquationOptions opt;
         opt.use_fast_math = fast_math != 0;
         opt.fuse_row_reductions = fuse_rows != 0;
+        opt.unrounded_column_sums = unrounded_column_sums != 0;
         if (row_tuning != nullptr)
             opt.row_program = RowProgramTuning{row_tuning[0], row_tuning[1], row_tuning[2], row_tuning[3], row_tuning[4], row_tuning[5], row_tuning[6]};
         *out = new FusedEquation(FusedEquation::compile(Expression::outputs(named), device, opt));
@@ -285,11 +286,11 @@ THB_API int thb_plan_output(Plan* p, const char* name, thb_binding* out) {
         out->is_scalar = 0;
     });
 }
-// kind: 0 logical stage names, 1 physical stage names, 2 stage sources, 3 output names; items are joined by '\x1e'
+// kind: 0 logical stage names, 1 physical stage names, 2 stage sources, 3 output names, 4 column-sum names; items are joined by '\x1e'
 THB_API const char* thb_plan_strings(Plan* p, int kind) {
     std::vector<std::string> items;
     try {
-        items = kind == 0 ? p->plan.stageKindNames() : kind == 1 ? p->plan.physicalStageNames() : kind == 2 ? p->plan.stageSources() : p->plan.getOutputNames();
+        items = kind == 0 ? p->plan.stageKindNames() : kind == 1 ? p->plan.physicalStageNames() : kind == 2 ? p->plan.stageSources() : kind == 4 ? p->plan.columnSumNames() : p->plan.getOutputNames();
     } catch (...) {
     }
     std::string joined;

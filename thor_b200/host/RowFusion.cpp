@@ -301,13 +301,19 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
     for (const auto& o : ctx.outputs) {
         m.produced.push_back({o.node_idx, true});
         out_nodes.push_back(o.node_idx);
+        const thor_b200_expr_node& pn = nodes[remap.at(o.node_idx)];
+        const bool column_reduction = (pn.op == THOR_B200_OP_REDUCE_SUM || pn.op == THOR_B200_OP_REDUCE_AVG) && pn.input_slot == 1;
+        if (ctx.unrounded_column_sums && column_reduction) m.column_sum_names.push_back(o.name);
     }
+    if (!m.column_sum_names.empty()) m.column_sums = std::make_shared<Tensor>();
+    const std::shared_ptr<Tensor> column_sums = m.column_sums;
+    const uint64_t n_column_sums = m.column_sum_names.size(), n_cols = cols;
     for (uint32_t k = 0; k < n; ++k)
         if (needed[k] && !isLeafOp(g.nodes[k].op)) m.absorbed.push_back(k);
     const int device = ctx.device_num;
     std::vector<Tensor> in_tensors;
     for (uint32_t gs : input_graph_slot) in_tensors.push_back(ctx.bound[gs].tensor);
-    m.bind = [prog, ws_bytes, out_nodes, in_tensors, scalars, device](std::vector<Tensor>& node_tensor, std::vector<Tensor>& keep_alive,
+    m.bind = [prog, ws_bytes, out_nodes, in_tensors, scalars, device, column_sums, n_column_sums, n_cols](std::vector<Tensor>& node_tensor, std::vector<Tensor>& keep_alive,
                                                                        uint64_t& intermediate_bytes) -> std::function<void(void*)> {
         Tensor ws = Tensor::allocate(DataType::UINT8, {static_cast<uint64_t>(ws_bytes)}, device);
         if (ws_bytes > 1) intermediate_bytes += ws_bytes;
@@ -319,8 +325,13 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
         std::vector<void*> out_ptrs;
         for (uint32_t k : out_nodes) out_ptrs.push_back(node_tensor[k].getMemPtr());
         keep_alive.push_back(ws);
-        return [prog, in_ptrs, out_ptrs, ws, ws_bytes, scalars](void* stream) {
-            const int st = thor_b200_rowprog_launch(prog->h, in_ptrs.data(), scalars->data(), out_ptrs.data(), ws.getMemPtr(), ws_bytes, stream);
+        void* sums_ptr = nullptr;
+        if (column_sums) {
+            *column_sums = Tensor::allocate(DataType::FP32, {n_column_sums, n_cols}, device);
+            sums_ptr = column_sums->getMemPtr();
+        }
+        return [prog, in_ptrs, out_ptrs, ws, ws_bytes, scalars, sums_ptr](void* stream) {
+            const int st = thor_b200_rowprog_launch_sharded(prog->h, in_ptrs.data(), scalars->data(), out_ptrs.data(), ws.getMemPtr(), ws_bytes, sums_ptr, stream);
             if (st != THOR_B200_OK) throw std::runtime_error(std::string("row program launch: ") + thor_b200_last_error());
         };
     };

@@ -22,6 +22,7 @@ struct RowFusionContext {
     int device_num;
     bool use_fast_math;
     RowProgramTuning tuning;
+    bool unrounded_column_sums = false;
 };
 
 struct RowFusionMatch {
@@ -36,6 +37,9 @@ struct RowFusionMatch {
     std::function<std::function<void(void*)>(std::vector<Tensor>& node_tensor, std::vector<Tensor>& keep_alive, uint64_t& intermediate_bytes)> bind;
     // Device-side waits of the program that ran out of time so far (synchronises; 0 for programs without such waits).
     std::function<uint32_t()> waits_expired;
+    // unrounded_column_sums: output names of the program's column reductions, and (after bind) the fp32 [names, cols] tensor
+    std::vector<std::string> column_sum_names;
+    std::shared_ptr<Tensor> column_sums;
 };
 
 // Tries to run the whole equation as one row program; returns no match when it does not fit.
