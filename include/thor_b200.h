@@ -435,8 +435,17 @@ THOR_B200_API int thor_b200_reduce_full_noalloc(int op, const void* input, int i
 typedef struct thor_b200_comm thor_b200_comm;
 THOR_B200_API int thor_b200_comm_unique_id(void* out_id_128_bytes);
 THOR_B200_API int thor_b200_comm_init(int nranks, int rank, const void* unique_id_128_bytes, thor_b200_comm** out_comm);
-/* op: 0 = sum, 1 = max, 2 = min.  Asynchronous on `stream`; every rank must make the same calls in the same order. */
+/* op: 0 = sum, 1 = max, 2 = min (NCCL's floating-point min / max: what they return when a shard holds a NaN is not
+ * specified -- use thor_b200_comm_allreduce_stats_f32 for extremes).  Asynchronous on `stream`; every rank must make the
+ * same calls in the same order. */
 THOR_B200_API int thor_b200_comm_allreduce_f32(thor_b200_comm* comm, void* buffer, uint64_t count, int op, void* stream);
+/* The statistics of one sharded reduction step in ONE NCCL group (ncclGroupStart / ncclGroupEnd): `sums` (n_sums fp32:
+ * sum, sum of squares, column sums ...) combined with +, `maxima` with max, `minima` with min, each in place; a count of 0
+ * skips that part.  Minima and maxima follow the reduction seam's rule that a NaN in any shard is the result (NCCL's own
+ * floating-point min / max leave that open): they cross the ranks as order-preserving integer keys in which NaN wins.
+ * Asynchronous on `stream`; every rank makes the same call. */
+THOR_B200_API int thor_b200_comm_allreduce_stats_f32(thor_b200_comm* comm, void* sums, uint64_t n_sums, void* maxima, uint64_t n_maxima, void* minima,
+                                                     uint64_t n_minima, void* stream);
 THOR_B200_API void thor_b200_comm_destroy(thor_b200_comm* comm);
 
 #ifdef __cplusplus

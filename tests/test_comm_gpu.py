@@ -21,6 +21,15 @@ def test_single_rank_allreduce_is_the_identity():
         comm.allreduce(x, op)
     torch.cuda.synchronize()
     assert torch.equal(x, want)
+    # the grouped statistics call: sums, NaN-propagating maxima and minima through ordered keys, identity on one rank
+    mx = torch.tensor([float("-inf"), -2.5, -0.0, 0.0, 3.0, float("inf"), float("nan")], device="cuda")
+    mn = mx.clone()
+    keep = mx.clone()
+    comm.allreduce_stats(sums=x, maxima=mx, minima=mn)
+    torch.cuda.synchronize()
+    assert torch.equal(x, want)
+    for got in (mx, mn):
+        assert torch.equal(got[:-1].view(torch.int32), keep[:-1].view(torch.int32)) and torch.isnan(got[-1])
     comm.close()
 
 
@@ -46,6 +55,14 @@ comm.allreduce(maxima, "max")
 torch.cuda.synchronize()
 assert bool((sums == sum(range(1, world + 1))).all()), sums[:4]
 assert maxima.tolist() == [float(world - 1), 0.0], maxima
+# one group for a step's statistics; a NaN in exactly one rank's shard is the global extreme
+s2 = torch.full((2,), float(rank + 1), device="cuda")
+mx = torch.tensor([float(rank), float("nan") if rank == world - 1 else 1.0], device="cuda")
+mn = torch.tensor([float(rank), float("nan") if rank == 0 else 1.0], device="cuda")
+comm.allreduce_stats(sums=s2, maxima=mx, minima=mn)
+torch.cuda.synchronize()
+assert s2.tolist() == [float(sum(range(1, world + 1)))] * 2, s2
+assert mx[0].item() == world - 1 and torch.isnan(mx[1]) and mn[0].item() == 0 and torch.isnan(mn[1]), (mx, mn)
 comm.close()
 print("rank", rank, "ok")
 """

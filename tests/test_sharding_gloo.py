@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from thor_b200.sharding import combine_partials, shard_range
+from thor_b200.sharding import combine_partials, from_ordered_keys, ordered_keys, shard_range
 
 
 def test_shard_ranges_cover_and_align():
@@ -21,6 +21,17 @@ def test_shard_ranges_cover_and_align():
                 assert a1 == b0 and (a1 % 8 == 0 or a1 == n)
             sizes = [b - a for a, b in ranges]
             assert max(sizes) - min(sizes) < 16  # one block of 8 plus the ragged last block
+
+
+def test_ordered_keys_keep_the_float_order_and_let_nan_win():
+    v = torch.tensor([float("-inf"), -3.5, -0.0, 0.0, 1e-40, 2.0, float("inf")], dtype=torch.float32)
+    for high in (True, False):
+        keys = ordered_keys(v, high)
+        assert torch.all(keys[1:] >= keys[:-1]) and keys[1] < keys[2] and keys[4] < keys[5]
+        assert torch.equal(from_ordered_keys(keys).view(torch.int32), v.view(torch.int32))
+    nan = torch.tensor([float("nan"), -float("nan")], dtype=torch.float32)
+    assert torch.all(ordered_keys(nan, True) > ordered_keys(v, True).max()) and torch.all(ordered_keys(nan, False) < ordered_keys(v, False).min())
+    assert torch.isnan(from_ordered_keys(ordered_keys(nan, True))).all() and torch.isnan(from_ordered_keys(ordered_keys(nan, False))).all()
 
 
 def _free_port():
@@ -50,12 +61,17 @@ def _worker(rank, world, port, n, rows, cols, out_path):
     cols_sum = torch.from_numpy(np.concatenate([dg, db]))
     combine_partials(sums=sums, maxima=mx)
     combine_partials(sums=cols_sum)
+    # a NaN in exactly one rank's shard is the global maximum and minimum, as in the single-GPU reductions
+    nan_mx = torch.tensor([float("nan") if rank == 1 else 5.0, float(rank)], dtype=torch.float32)
+    nan_mn = torch.tensor([float("nan") if rank == 0 else -5.0, float(rank)], dtype=torch.float32)
+    combine_partials(maxima=nan_mx, minima=nan_mn)
+    nan_ok = bool(torch.isnan(nan_mx[0]) and nan_mx[1] == world - 1 and torch.isnan(nan_mn[0]) and nan_mn[1] == 0)
     if rank == 0:
         s_all, q_all, m_all = oracle.c4_stats(x, threads=1)
         _, dg_all, db_all = oracle.layernorm_bwd(xs, gamma, dy, threads=1)
         ok = (abs(sums[0].item() - s_all) <= 1e-9 * abs(s_all) + 1e-6 and abs(sums[1].item() - q_all) <= 1e-9 * q_all and mx.item() == m_all
               and np.allclose(cols_sum.numpy(), np.concatenate([dg_all, db_all]), rtol=1e-9, atol=1e-12))
-        open(out_path, "w").write("ok" if ok else "mismatch")
+        open(out_path, "w").write("ok" if ok and nan_ok else "mismatch")
     dist.barrier()
     dist.destroy_process_group()
 

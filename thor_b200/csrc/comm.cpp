@@ -24,6 +24,8 @@ struct NcclApi {
     int (*CommInitRank)(NcclComm*, int, NcclId, int) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*CommDestroy)(NcclComm) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     std::string error;
 };
@@ -50,9 +52,31 @@ NcclApi& nccl() {
         api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
         api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
         api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
-        if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString) api.error = "NCCL library lacks a required symbol";
+        api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+        api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+        if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy || !api.GetErrorString || !api.GroupStart || !api.GroupEnd) api.error = "NCCL library lacks a required symbol";
     });
     return api;
+}
+
+// Minima and maxima cross the ranks as 32-bit integer keys whose signed order is the float order, with every NaN mapped
+// to the key that wins (the largest key for a maximum, the smallest for a minimum): the rule of the reduction seam --
+// a NaN in any shard is the result -- which NCCL's own floating-point min / max do not promise.  Decoding needs no flag:
+// the winning keys are themselves NaN bit patterns.
+__global__ void encodeOrderedKeys(float* values, uint64_t n, int nan_wins_high) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = values[i];
+    const int b = __float_as_int(v);
+    int key = b >= 0 ? b : (b ^ 0x7fffffff);
+    if (v != v) key = nan_wins_high ? 0x7fffffff : static_cast<int>(0x80000000u);
+    reinterpret_cast<int*>(values)[i] = key;
+}
+__global__ void decodeOrderedKeys(float* values, uint64_t n) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int key = reinterpret_cast<const int*>(values)[i];
+    values[i] = __int_as_float(key >= 0 ? key : (key ^ 0x7fffffff));
 }
 
 int ncclFail(const char* what, int rc) { return tb::fail(THOR_B200_CUDA_ERROR, "%s failed: %s", what, nccl().GetErrorString(rc)); }
@@ -107,6 +131,35 @@ int thor_b200_comm_allreduce_f32(thor_b200_comm* comm, void* buffer, uint64_t co
     const int red = op == 0 ? 0 : (op == 1 ? 2 : 3);  // ncclSum, ncclMax, ncclMin
     if (int rc = nccl().AllReduce(buffer, buffer, static_cast<size_t>(count), kFloat32, red, comm->comm, static_cast<cudaStream_t>(stream)))
         return ncclFail("ncclAllReduce", rc);
+    return THOR_B200_OK;
+}
+
+int thor_b200_comm_allreduce_stats_f32(thor_b200_comm* comm, void* sums, uint64_t n_sums, void* maxima, uint64_t n_maxima, void* minima, uint64_t n_minima,
+                                       void* stream_v) {
+    using namespace tb;
+    TB_REQUIRE(comm != nullptr && comm->comm != nullptr, "comm_allreduce_stats_f32: null communicator");
+    TB_REQUIRE((sums != nullptr || n_sums == 0) && (maxima != nullptr || n_maxima == 0) && (minima != nullptr || n_minima == 0),
+               "comm_allreduce_stats_f32: a buffer with a non-zero count is null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    NcclApi& api = nccl();
+    constexpr int kInt32 = 2, kFloat32 = 7, kSum = 0, kMax = 2, kMin = 3;  // ncclInt32, ncclFloat32, ncclSum, ncclMax, ncclMin
+    auto blocks = [](uint64_t n) { return static_cast<unsigned>((n + 255) / 256); };
+    if (n_maxima) encodeOrderedKeys<<<blocks(n_maxima), 256, 0, stream>>>(static_cast<float*>(maxima), n_maxima, 1);
+    if (n_minima) encodeOrderedKeys<<<blocks(n_minima), 256, 0, stream>>>(static_cast<float*>(minima), n_minima, 0);
+    TB_CUDA(cudaGetLastError());
+    // one group: NCCL launches the (up to three) small collectives together
+    if (int rc = api.GroupStart()) return ncclFail("ncclGroupStart", rc);
+    int rc = 0;
+    if (n_sums) rc = api.AllReduce(sums, sums, static_cast<size_t>(n_sums), kFloat32, kSum, comm->comm, stream);
+    if (!rc && n_maxima) rc = api.AllReduce(maxima, maxima, static_cast<size_t>(n_maxima), kInt32, kMax, comm->comm, stream);
+    if (!rc && n_minima) rc = api.AllReduce(minima, minima, static_cast<size_t>(n_minima), kInt32, kMin, comm->comm, stream);
+    const int end = api.GroupEnd();
+    if (rc) return ncclFail("ncclAllReduce", rc);
+    if (end) return ncclFail("ncclGroupEnd", end);
+    if (n_maxima) decodeOrderedKeys<<<blocks(n_maxima), 256, 0, stream>>>(static_cast<float*>(maxima), n_maxima);
+    if (n_minima) decodeOrderedKeys<<<blocks(n_minima), 256, 0, stream>>>(static_cast<float*>(minima), n_minima);
+    TB_CUDA(cudaGetLastError());
+    countLaunch((n_maxima ? 2 : 0) + (n_minima ? 2 : 0));
     return THOR_B200_OK;
 }
 

@@ -26,18 +26,38 @@ def shard_range(n: int, rank: int, world: int, multiple: int = 8) -> Tuple[int, 
     return min(n, start_block * multiple), min(n, stop_block * multiple)
 
 
+def ordered_keys(values: torch.Tensor, nan_wins_high: bool) -> torch.Tensor:
+    """int32 keys whose signed order is the float order of `values` (fp32), with every NaN mapped to the key that wins a
+    maximum (nan_wins_high) or a minimum.  The reduction seam's rule -- a NaN in any shard is the result -- survives an
+    integer max / min across ranks, which the backends' floating-point max / min do not promise."""
+    bits = values.contiguous().view(torch.int32)
+    keys = torch.where(bits >= 0, bits, bits ^ 0x7FFFFFFF)
+    nan_key = 0x7FFFFFFF if nan_wins_high else -0x80000000
+    return torch.where(torch.isnan(values), torch.full_like(keys, nan_key), keys)
+
+
+def from_ordered_keys(keys: torch.Tensor) -> torch.Tensor:
+    """Inverse of ordered_keys (the winning NaN keys are NaN bit patterns themselves)."""
+    return torch.where(keys >= 0, keys, keys ^ 0x7FFFFFFF).view(torch.float32)
+
+
 def combine_partials(sums: Optional[torch.Tensor] = None, maxima: Optional[torch.Tensor] = None, minima: Optional[torch.Tensor] = None,
                      group=None) -> None:
     """In-place allreduce of per-rank fp32 partials: `sums` with SUM (sum, sum of squares, dgamma, dbeta ...),
-    `maxima` with MAX, `minima` with MIN.  No-op without an initialised process group."""
+    `maxima` with MAX, `minima` with MIN; extremes are NaN-propagating like the single-GPU reductions (they cross the
+    ranks as ordered integer keys).  No-op without an initialised process group."""
     if not (dist.is_available() and dist.is_initialized()):
         return
     if sums is not None:
         dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
     if maxima is not None:
-        dist.all_reduce(maxima, op=dist.ReduceOp.MAX, group=group)
+        keys = ordered_keys(maxima, True)
+        dist.all_reduce(keys, op=dist.ReduceOp.MAX, group=group)
+        maxima.copy_(from_ordered_keys(keys).reshape(maxima.shape))
     if minima is not None:
-        dist.all_reduce(minima, op=dist.ReduceOp.MIN, group=group)
+        keys = ordered_keys(minima, False)
+        dist.all_reduce(keys, op=dist.ReduceOp.MIN, group=group)
+        minima.copy_(from_ordered_keys(keys).reshape(minima.shape))
 
 
 def finalize_mean(total: torch.Tensor, global_count: int) -> torch.Tensor:
@@ -58,6 +78,7 @@ class Communicator:
         self._lib = _native.lib
         self._lib.thor_b200_comm_init.argtypes = [C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)]
         self._lib.thor_b200_comm_allreduce_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
+        self._lib.thor_b200_comm_allreduce_stats_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p]
         self._lib.thor_b200_comm_destroy.argtypes = [C.c_void_p]
         self._lib.thor_b200_comm_destroy.restype = None
         if len(unique_id) != 128:
@@ -82,6 +103,19 @@ class Communicator:
         if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
             raise ValueError("allreduce takes a contiguous fp32 CUDA tensor")
         _native.check(self._lib.thor_b200_comm_allreduce_f32(self._h, t.data_ptr(), t.numel(), {"sum": 0, "max": 1, "min": 2}[op], _native.stream_handle(stream)))
+
+    def allreduce_stats(self, sums: Optional[torch.Tensor] = None, maxima: Optional[torch.Tensor] = None, minima: Optional[torch.Tensor] = None,
+                        stream=None) -> None:
+        """One NCCL group for the statistics of a sharded reduction step: `sums` added, `maxima` / `minima` combined with
+        NaN-propagating max / min, all in place (thor_b200_comm_allreduce_stats_f32)."""
+        from . import _native
+
+        args = []
+        for t in (sums, maxima, minima):
+            if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
+                raise ValueError("allreduce_stats takes contiguous fp32 CUDA tensors")
+            args += [t.data_ptr() if t is not None else None, t.numel() if t is not None else 0]
+        _native.check(self._lib.thor_b200_comm_allreduce_stats_f32(self._h, *args, _native.stream_handle(stream)))
 
     def close(self) -> None:
         if self._h:
