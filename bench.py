@@ -3,17 +3,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2] [--no-extras]
 
-A step is one pass of the hot path over one batch of synthetic input resident in HBM.  The headline
-workload is configuration 2 (y = relu(a*x + b) * sigmoid(z), fp16 [8192, 8192], a per column, b an
-fp32 runtime scalar); with N > 1 every rank owns its own [8192, 8192] row shard of a [8192*N, 8192]
-problem (weak scaling, no data-path collective).  The other configurations are timed the same way
-and reported under "all_configs" (their full-reduction / dgamma partials are combined with one NCCL
-allreduce when N > 1).
+A step is one pass of the hot path over one batch of synthetic input resident in HBM.  The headline workload is
+configuration 2 (y = relu(a*x + b) * sigmoid(z), fp16 [8192, 8192], a per column, b an fp32 runtime scalar).  With N > 1
+the FIXED global problem of every configuration is sharded along its leading dimension (rows / flat index) over the N
+ranks -- strong scaling: `value` is the global problem's algorithmic bytes over the slowest rank's time.  Elementwise,
+cast and row-wise configurations need no communication; the full reductions (configuration 4) and the LayerNorm
+dgamma / dbeta column sums (configuration 5 backward) combine per-GPU fp32 partials with one NCCL allreduce per step
+through the library's own communicator, inside the timed region, and the combined results are checked against the CPU
+oracle of the global problem after the timed region ("multi_gpu_check").  Every configuration is reported under
+roofline.per_config (time per step, fraction of the HBM roofline per GPU, at N > 1 the allreduce timed alone and the
+1-GPU time of the same global problem measured on rank 0 in the same run); "all_configs" carries the detail.
 
-Timing: W >= 3 warm-up steps, then exactly K steps between a barrier + synchronize on both sides,
-bracketed by CUDA events on the launching stream; the max over ranks is reported.  Buffers rotate
-over several disjoint sets whose total size is several times the 126 MB L2, so no step finds its
-inputs in cache.  SM clocks and throttle reasons are sampled with nvidia-smi during the timed region.
+Timing: W >= 3 warm-up steps, then exactly K steps between a barrier + synchronize on both sides, bracketed by CUDA events
+on the launching stream; the max over ranks is reported.  Buffers rotate over several disjoint sets whose total size is
+several times the 126 MB L2, so no step finds its inputs in cache.  After the timed region the same load keeps running in
+11 timed groups (at least 400 ms in all) while nvidia-smi samples SM clocks and throttle reasons: roofline.sustained holds
+the median / p10 / p90 per-step time of those groups and roofline.frac_sustained the fraction at the clocks that were
+sampled.
 
 Rank 0 prints ONE JSON line.
 """
@@ -146,23 +152,78 @@ class Dist:
         if self.enabled:
             self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM if op == "sum" else self.dist.ReduceOp.MAX)
 
+    def communicator(self):
+        """The library's own NCCL communicator (thor_b200_comm_*) over the ranks of this job; the id travels through the
+        process group that torchrun set up.  Data-path collectives of the benchmark go through it."""
+        if not self.enabled:
+            return None
+        if getattr(self, "_comm", None) is None:
+            import torch
+
+            from thor_b200.sharding import Communicator
+
+            uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+            if self.rank == 0:
+                uid.copy_(torch.frombuffer(bytearray(Communicator.unique_id()), dtype=torch.uint8))
+            self.dist.broadcast(uid, src=0)
+            self._comm = Communicator(self.world, self.rank, bytes(uid.cpu().numpy().tobytes()))
+        return self._comm
+
+    def sum_f64(self, values):
+        """Sum / of float64 host values over the ranks (oracle partials of the result check)."""
+        import torch
+
+        t = torch.tensor(values, dtype=torch.float64, device="cuda")
+        if self.enabled:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return t.cpu().numpy()
+
+    def max_f64(self, values):
+        import torch
+
+        t = torch.tensor(values, dtype=torch.float64, device="cuda")
+        if self.enabled:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.cpu().numpy()
+
     def close(self):
+        if getattr(self, "_comm", None) is not None:
+            self._comm.close()
         if self.enabled:
             self.dist.destroy_process_group()
 
 
-def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler | None = None, sample: bool = False, drain=None):
-    """W untimed + K timed calls of step(i); returns (device ms per step as max over ranks, wall ms per step).
-    `drain` (optional) makes the timing stream wait for work the steps put on side streams, so that it ends inside the
-    timed region."""
+class SingleRank:
+    """Stands in for Dist when rank 0 times the WHOLE global problem alone (the 1-GPU time of the strong-scaling ratio)."""
+    enabled, world, rank = False, 1, 0
+
+    def __init__(self, local_rank):
+        self.local_rank = local_rank
+
+    def barrier(self):
+        import torch
+
+        torch.cuda.synchronize()
+
+    def max(self, v): return v
+    def communicator(self): return None
+
+
+def time_steps(dist, step, steps: int, warmup: int, drain=None):
+    """W untimed + K timed calls of step(i).  Returns {"ms": device ms per step (max over ranks), "wall_ms": host ms per step,
+    "launches": kernels this library launched inside the timed region (read from its own counter)}.  `drain` makes the timing
+    stream wait for work the steps put on side streams, so that it ends inside the timed region."""
     import torch
+
+    import thor_b200
 
     for i in range(warmup):
         step(i)
+    if drain is not None:
+        drain()
     dist.barrier()
-    if sampler:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = thor_b200.launch_count()
     t0 = time.perf_counter()
     e0.record()
     for i in range(steps):
@@ -170,24 +231,37 @@ def time_steps(dist: Dist, step, steps: int, warmup: int, sampler: ClockSampler 
     if drain is not None:
         drain()
     e1.record()
+    issued = (time.perf_counter() - t0) * 1e3 / steps
+    launches = thor_b200.launch_count() - before
     dist.barrier()
-    wall = (time.perf_counter() - t0) * 1e3 / steps
-    ms = dist.max(e0.elapsed_time(e1) / steps)
-    clocks = None
-    if sample:
-        # nvidia-smi cannot sample faster than every ~20 ms: when the timed region was shorter than 400 ms every rank
-        # keeps the identical load running (untimed; the count derives from the rank-maximum time, so all ranks agree
-        # and collectives stay matched) until a handful of samples under load exist
-        extended = 0
-        if steps * ms < 400.0:
-            extended = int(400.0 / max(ms, 1e-3)) + 1
-            for i in range(extended):
-                step(warmup + steps + i)
-            dist.barrier()
-        if sampler:
-            clocks = sampler.stop()
-            clocks["untimed_extension_steps"] = extended
-    return ms, wall, clocks
+    return {"ms": dist.max(e0.elapsed_time(e1) / steps), "host_issue_ms": dist.max(issued), "launches": int(launches)}
+
+
+def time_sustained(dist, step, steps: int, first: int, ms_hint: float, sampler: ClockSampler | None, drain=None, groups: int = 11, min_total_ms: float = 400.0):
+    """The same load kept running after the timed region: `groups` groups of equal length, each bracketed by its own event
+    pair, at least min_total_ms in all (nvidia-smi cannot sample faster than every ~20 ms).  Every rank derives the group
+    length from the rank-maximum time of the timed region, so collectives stay matched.  Returns per-step statistics over
+    the groups (rank maximum per group) and the clocks sampled while they ran."""
+    import torch
+
+    per_group = max(steps, int(min_total_ms / groups / max(ms_hint, 1e-4)) + 1)
+    if sampler:
+        sampler.start()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(groups + 1)]
+    i = first
+    events[0].record()
+    for g in range(groups):
+        for _ in range(per_group):
+            step(i)
+            i += 1
+        if drain is not None:
+            drain()
+        events[g + 1].record()
+    dist.barrier()
+    times = sorted(dist.max(events[g].elapsed_time(events[g + 1]) / per_group) for g in range(groups))
+    clocks = sampler.stop() if sampler else None
+    pick = lambda q: times[min(groups - 1, max(0, int(round(q * (groups - 1)))))]
+    return {"groups": groups, "steps_per_group": per_group, "ms_median": pick(0.5), "ms_p10": pick(0.1), "ms_p90": pick(0.9)}, clocks
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -199,26 +273,52 @@ class Workload:
     dtype = ""
     unit_name = "elements"
 
-    def __init__(self, dist: Dist, scale: float = 1.0):
+    def __init__(self, dist, scale: float = 1.0):
+        from thor_b200.sharding import shard_range
+
         self.dist = dist
         self.scale = scale  # fraction of the leading dimension (profiling captures use a smaller case)
         self.sets = []
         self.launches_per_step = 0
-        for attr in ("ROWS", "N"):
-            if hasattr(self, attr) and scale != 1.0:
-                setattr(self, attr, max(8, int(getattr(type(self), attr) * scale) // 8 * 8))
+        # ROWS / N of the class is the GLOBAL problem; the instance works on this rank's contiguous shard of it
+        self.lead = "ROWS" if hasattr(self, "ROWS") else "N"
+        total = getattr(type(self), self.lead)
+        if scale != 1.0:
+            total = max(8, int(total * scale) // 8 * 8)
+        self.global_lead = total
+        self.shard = shard_range(total, dist.rank, dist.world, 8 if self.lead == "N" else 1)
+        setattr(self, self.lead, self.shard[1] - self.shard[0])
 
     def algorithmic_bytes(self) -> int: raise NotImplementedError
     def units(self) -> int: raise NotImplementedError
     def setup(self): raise NotImplementedError
     def step(self, i: int): raise NotImplementedError
+
+    def _of_global(self, fn):
+        local = getattr(self, self.lead)
+        setattr(self, self.lead, self.global_lead)
+        try:
+            return fn()
+        finally:
+            setattr(self, self.lead, local)
+
+    def global_algorithmic_bytes(self) -> int: return self._of_global(self.algorithmic_bytes)
+    def global_units(self) -> int: return self._of_global(self.units)
+
     def n_sets(self, bytes_per_set: int) -> int:
-        return max(2, min(8, -(-4 * L2_BYTES // max(1, bytes_per_set))))
+        return max(2, min(16, -(-4 * L2_BYTES // max(1, bytes_per_set))))
+
+    def sharding(self) -> str:
+        if self.dist.world == 1:
+            return "single GPU"
+        return f"{self.lead.lower()} {self.global_lead} split over {self.dist.world} ranks ({getattr(self, self.lead)} on this rank), {self.collective}"
+
+    collective = "no collective"
 
 
 class C1Cast(Workload):
     name = "c1_cast_fp32_fp16"
-    description = "TypeConverter fp32->fp16, 1-D, n=2^24, U(-4,4) with edge values at 0.1% (per GPU)"
+    description = "TypeConverter fp32->fp16, 1-D, n=2^24, U(-4,4) with edge values at 0.1%"
     dtype = "f32->f16"
     N = 1 << 24
 
@@ -284,7 +384,7 @@ class C1CastReferenceGpu(C1Cast):
 
 class C2FusedExpr(Workload):
     name = "c2_fused_relu_axb_sigmoid"
-    description = "y = relu(a*x + b) * sigmoid(z): x,z,y fp16 [8192,8192] per GPU, a fp16 [8192] per column, b fp32 runtime scalar 0.1"
+    description = "y = relu(a*x + b) * sigmoid(z): x,z,y fp16 [8192,8192], a fp16 [8192] per column, b fp32 runtime scalar 0.1"
     dtype = "f16"
     ROWS, COLS = 8192, 8192
 
@@ -413,7 +513,7 @@ class C2ReferenceGpu(C2FusedExpr):
 
 class C3Softmax(Workload):
     name = "c3_softmax_rows_fp32"
-    description = "exp(x - max_row) / sum_row(exp(x - max_row)) on fp32 [65536,4096] per GPU (composed expression)"
+    description = "exp(x - max_row) / sum_row(exp(x - max_row)) on fp32 [65536,4096] (composed expression)"
     dtype = "f32"
     ROWS, COLS = 65536, 4096
 
@@ -447,7 +547,7 @@ class C3SoftmaxWithArgmax(C3Softmax):
     """Softmax and row argmax of the same tensor as ONE equation: the arg reduction joins the first round of the row
     program, so x is read once for both results (reported beside the two separate operations)."""
     name = "c3_softmax_and_argmax_one_pass_fp32"
-    description = "softmax rows + row argmax of fp32 [65536,4096] per GPU in one row program"
+    description = "softmax rows + row argmax of fp32 [65536,4096] in one row program"
 
     def build(self, ex):
         x = ex.input("x")
@@ -537,7 +637,7 @@ class C3ReferenceStagePipeline(C3Softmax):
 
 class C3Argmax(C3Softmax):
     name = "c3_row_argmax_fp32"
-    description = "row argmax of fp32 [65536,4096] per GPU -> uint32 [65536]"
+    description = "row argmax of fp32 [65536,4096] -> uint32 [65536]"
 
     def build(self, ex):
         return {"idx": ex.input("x").argmax([1], [1])}
@@ -560,11 +660,71 @@ class C3Argmax(C3Softmax):
     def algorithmic_bytes(self): return self.ROWS * self.COLS * 4 + self.ROWS * 4
 
 
+class _ShardCombiner:
+    """Combines this rank's fp32 partials with the other ranks' through the library's communicator
+    (thor_b200_comm_allreduce_stats_f32: one NCCL group) on a side stream.  The partial buffers are double-buffered with
+    the plans that write them, so the collective of step i overlaps the kernel of step i + 1; a buffer's next kernel
+    waits for that buffer's last collective."""
+
+    def __init__(self, comm, buffers: int):
+        import torch
+
+        self.comm = comm
+        self.stream = torch.cuda.Stream()
+        self.ready = [torch.cuda.Event() for _ in range(buffers)]
+        self.done = [torch.cuda.Event() for _ in range(buffers)]
+        self.used = [False] * buffers
+
+    def before_kernel(self, b: int):
+        import torch
+
+        if self.used[b]:
+            torch.cuda.current_stream().wait_event(self.done[b])
+
+    def after_kernel(self, b: int, sums=None, maxima=None, then=None):
+        import torch
+
+        self.ready[b].record()
+        self.stream.wait_event(self.ready[b])
+        self.comm.allreduce_stats(sums=sums, maxima=maxima, stream=self.stream)
+        if then is not None:
+            with torch.cuda.stream(self.stream):
+                then()
+        self.done[b].record(self.stream)
+        self.used[b] = True
+
+    def drain(self):
+        import torch
+
+        torch.cuda.current_stream().wait_stream(self.stream)
+
+    def time_alone(self, dist, sums=None, maxima=None, iters: int = 50) -> float:
+        """Microseconds of one collective with nothing else on the GPU (events around `iters` back-to-back calls on the side
+        stream, max over ranks): the NVLink time of the step."""
+        import torch
+
+        scratch_s = sums.clone() if sums is not None else None
+        scratch_m = maxima.clone() if maxima is not None else None
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(self.stream):
+            for _ in range(5):
+                self.comm.allreduce_stats(sums=scratch_s, maxima=scratch_m, stream=self.stream)
+            e0.record(self.stream)
+            for _ in range(iters):
+                self.comm.allreduce_stats(sums=scratch_s, maxima=scratch_m, stream=self.stream)
+            e1.record(self.stream)
+        self.stream.synchronize()
+        return dist.max(e0.elapsed_time(e1) / iters * 1e3)
+
+
 class C4FullReduce(Workload):
     name = "c4_full_reductions_bf16"
-    description = "sum, sum of squares ((x*x).reduce_sum()) and max over bf16 n=2^31 per GPU, fp32 accumulation"
+    description = "sum, sum of squares ((x*x).reduce_sum()) and max over bf16 n=2^31, fp32 accumulation"
     dtype = "bf16->f32"
     N = 1 << 31
+    collective = "per-GPU {sum, sum of squares} and {max} combined in one NCCL group per step"
+    combiner = None
 
     def setup(self):
         import torch
@@ -579,25 +739,50 @@ class C4FullReduce(Workload):
             self.x[s:s + n] = (torch.randn(n, device="cuda", generator=gen) + 0.01).bfloat16()
         x = ex.input("x")
         eq = ex.compile({"sum": x.reduce_sum(), "sumsq": (x * x).reduce_sum(), "max": x.reduce_max()})
-        self.plan = eq.stamp({"x": self.x})
-        self.launches_per_step = self.plan.kernel_launches_per_run()
-        self.kernel_kind = self.plan.physical_stage_names()
-        self.outs = [self.plan.output(n) for n in ("sum", "sumsq", "max")]
+        # two stamped plans over the same input, each with its own [sum, sumsq, max] fp32 result buffer
+        self.stats = [torch.zeros(3, device="cuda") for _ in range(2)]
+        self.plans = [eq.stamp({"x": self.x}, outputs={"sum": st[0:1], "sumsq": st[1:2], "max": st[2:3]}) for st in self.stats]
+        self.sets = self.plans
+        self.launches_per_step = self.plans[0].kernel_launches_per_run()
+        self.kernel_kind = self.plans[0].physical_stage_names()
+        comm = self.dist.communicator()
+        self.combiner = _ShardCombiner(comm, 2) if comm is not None else None
 
     def algorithmic_bytes(self): return self.N * 2
     def units(self): return self.N
     def step(self, i):
-        self.plan.run()
-        if self.dist.enabled:
-            # per-GPU fp32 partials -> one allreduce each (sum for the additive statistics, max for the maximum), on a side
-            # stream: the collective of step i overlaps the kernel of step i + 1
-            if not hasattr(self, "side"):
-                self.side = _SideCollective()
-            self.side.submit(sums=torch_cat(self.outs[:2]), maxima=self.outs[2].clone())
+        b = i & 1
+        if self.combiner is None:
+            self.plans[b].run()
+            return
+        self.combiner.before_kernel(b)
+        self.plans[b].run()
+        self.combiner.after_kernel(b, sums=self.stats[b][0:2], maxima=self.stats[b][2:3])
 
     def drain(self):
-        if hasattr(self, "side"):
-            self.side.drain()
+        if self.combiner is not None:
+            self.combiner.drain()
+
+    def collective_us(self):
+        return self.combiner.time_alone(self.dist, sums=self.stats[0][0:2].clone(), maxima=self.stats[0][2:3].clone()) if self.combiner else None
+
+    def check(self):
+        """The combined statistics against the CPU oracle of the GLOBAL problem: every rank's host cores reduce its own shard
+        in float64, the float64 partials are added / maximised across the ranks."""
+        import torch
+
+        import oracle
+
+        self.step(0)
+        self.drain()
+        torch.cuda.synchronize()
+        got = self.stats[0].cpu().numpy().astype("float64")
+        s, q, m = oracle.c4_stats(self.x.view(torch.uint16).cpu().numpy())
+        s, q = self.dist.sum_f64([s, q]) if self.dist.enabled else (s, q)
+        m = float(self.dist.max_f64([m])[0]) if self.dist.enabled else m
+        n = self.global_lead
+        ok = abs(got[0] - s) <= 1e-5 * abs(s) + 2e-7 * n and abs(got[1] - q) <= 1e-5 * abs(q) and got[2] == m
+        return bool(ok), f"sum {got[0]:.6g} vs {s:.6g}, sumsq {got[1]:.6g} vs {q:.6g}, max {got[2]:.6g} vs {m:.6g}"
 
 
 class C3ArgmaxReferenceGpu(C3Argmax):
@@ -675,40 +860,6 @@ class C4ReferenceStagePipeline(C4FullReduce):
         self.r_max.run()
 
 
-class _SideCollective:
-    """Allreduce of a step's packed partials on a side stream, so that it overlaps the next step's kernel (the partials
-    are packed on the main stream first, which also frees the step's output buffers for the next launch)."""
-
-    def __init__(self):
-        import torch
-
-        self.stream = torch.cuda.Stream()
-
-    def submit(self, **partials):
-        import torch
-
-        from thor_b200.sharding import combine_partials
-
-        ready = torch.cuda.Event()
-        ready.record()
-        self.stream.wait_event(ready)
-        with torch.cuda.stream(self.stream):
-            combine_partials(**partials)
-        for t in partials.values():
-            t.record_stream(self.stream)
-
-    def drain(self):
-        import torch
-
-        torch.cuda.current_stream().wait_stream(self.stream)
-
-
-def torch_cat(ts):
-    import torch
-
-    return torch.cat([t.reshape(-1) for t in ts])
-
-
 def _layernorm_expr(ex, eps=1e-5):
     from thor_b200 import DataType
 
@@ -722,7 +873,7 @@ def _layernorm_expr(ex, eps=1e-5):
 
 class C5LayerNormFwd(Workload):
     name = "c5_layernorm_forward_bf16"
-    description = "Expression-authored LayerNorm forward over bf16 [32768,8192] per GPU (mean/var row reductions fused with the elementwise terms)"
+    description = "Expression-authored LayerNorm forward over bf16 [32768,8192] (mean/var row reductions fused with the elementwise terms)"
     dtype = "bf16"
     ROWS, COLS = 32768, 8192
 
@@ -803,37 +954,84 @@ class C5FwdReferenceStagePipeline(C5LayerNormFwd):
 
 class C5LayerNormBwd(C5LayerNormFwd):
     name = "c5_layernorm_backward_bf16"
-    description = "autodiff-generated LayerNorm backward (dx, dgamma, dbeta) over bf16 [32768,8192] per GPU; dgamma/dbeta allreduced when N > 1"
+    description = ("autodiff-generated LayerNorm backward (dx, dgamma, dbeta) over bf16 [32768,8192]; per-GPU fp32 dgamma/dbeta sums allreduced "
+                   "and rounded once when N > 1")
+    collective = "per-GPU fp32 [2, 8192] dgamma / dbeta sums combined by one allreduce per step, rounded to bf16 once after it"
+    combiner = None
 
     def setup(self):
         import torch
 
+        from thor_b200 import TypeConverter
         from thor_b200.expression import Expression as ex
 
         gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
-        bwd = ex.compile({"y": _layernorm_expr(ex)}, row_program=ROW_PROGRAM).compile_backward(["x", "gamma", "beta"])
+        sharded = self.dist.enabled
+        bwd = ex.compile({"y": _layernorm_expr(ex)}, row_program=ROW_PROGRAM, unrounded_column_sums=sharded).compile_backward(["x", "gamma", "beta"])
         self.sets = []
         for _ in range(2):
             x, gamma, beta = self._inputs(gen)
             dy = (torch.randn(self.ROWS, self.COLS, device="cuda", generator=gen) * 1e-2).bfloat16()
             plan = bwd.stamp({"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy})
-            self.sets.append((plan, x, dy, torch_cat([plan.output("gamma_grad"), plan.output("beta_grad")])))
+            grads = torch.empty(2, self.COLS, device="cuda", dtype=torch.bfloat16) if sharded else None  # the combined gradients
+            self.sets.append((plan, x, dy, gamma, plan.output("__column_sums") if sharded else None, grads))
         self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
         self.kernel_kind = self.sets[0][0].physical_stage_names()
+        comm = self.dist.communicator()
+        self.combiner = _ShardCombiner(comm, 2) if comm is not None else None
+        self.round_once = TypeConverter.convert_type
 
     def algorithmic_bytes(self): return 3 * self.ROWS * self.COLS * 2 + 3 * self.COLS * 2
     def step(self, i):
-        plan = self.sets[i % len(self.sets)][0]
+        b = i & 1
+        plan, _, _, _, sums, grads = self.sets[b]
+        if self.combiner is None:
+            plan.run()
+            return
+        self.combiner.before_kernel(b)
         plan.run()
-        if self.dist.enabled:
-            # the packed fp32 [dgamma, dbeta] partials are allreduced on a side stream, overlapping the next step's kernel
-            if not hasattr(self, "side"):
-                self.side = _SideCollective()
-            self.side.submit(sums=torch_cat([plan.output("gamma_grad").float(), plan.output("beta_grad").float()]))
+        # the unrounded fp32 sums of this rank's rows are added across the ranks, then rounded to the gradients' dtype once
+        self.combiner.after_kernel(b, sums=sums, then=lambda: self.round_once(sums.view(-1), grads.view(-1)))
 
     def drain(self):
-        if hasattr(self, "side"):
-            self.side.drain()
+        if self.combiner is not None:
+            self.combiner.drain()
+
+    def collective_us(self):
+        return self.combiner.time_alone(self.dist, sums=self.sets[0][4].clone()) if self.combiner else None
+
+    def check(self):
+        """dgamma / dbeta of the GLOBAL problem: every rank's host cores compute the float64 column sums of its own rows
+        (the oracle's LayerNorm backward), the float64 partials are added across the ranks and compared with the allreduced,
+        once-rounded bf16 gradients; dx is compared on a sample of this rank's rows."""
+        import numpy as np
+        import torch
+
+        import oracle
+        from oracle import expr_oracle as eo
+
+        self.step(0)
+        self.drain()
+        torch.cuda.synchronize()
+        plan, x, dy, gamma, sums, grads = self.sets[0]
+        u16 = lambda t: t.contiguous().view(torch.uint16).cpu().numpy()
+        want_dx, dg, db = oracle.layernorm_bwd(u16(x), u16(gamma), u16(dy), 1e-5)
+        want = np.concatenate([dg, db])
+        if self.dist.enabled:
+            want = self.dist.sum_f64(want.tolist())
+            got = grads.float().cpu().numpy().astype(np.float64).reshape(-1)
+        else:
+            got = np.concatenate([plan.output("gamma_grad").float().cpu().numpy().reshape(-1), plan.output("beta_grad").float().cpu().numpy().reshape(-1)]).astype(np.float64)
+        rows_global = self.global_lead
+        d = eo.ulp_distance(got, eo.round_to(want, oracle.BF16), oracle.BF16)
+        d = np.where(np.abs(got - want) <= 1e-5 * np.abs(want) + 2e-7 * rows_global * 1e-2 + 2.0 ** -9 * np.abs(want), 0.0, d)
+        sample = slice(0, min(64, self.ROWS))
+        got_dx = plan.output("x_grad")[sample].float().cpu().numpy().astype(np.float64).reshape(-1)
+        w_dx = oracle.to_float64(want_dx[sample].reshape(-1), oracle.BF16)
+        ddx = eo.ulp_distance(got_dx, w_dx, oracle.BF16)
+        ddx = np.where(np.abs(got_dx - w_dx) <= 2e-8, 0.0, ddx)
+        ok = float(d.max()) <= 1.0 and float(ddx.max()) <= 1.0
+        return bool(ok), f"dgamma/dbeta max {float(d.max()):.2f} bf16 ulp beyond tolerance, dx max {float(ddx.max()):.2f} ulp"
 
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
@@ -874,24 +1072,173 @@ def reference_arm(args):
     sample = f"{rows} of 8192 rows x {cols} cols per step (oracle C port, OpenMP)"
     print(json.dumps({
         "impl": "reference", "metric": "fused_expr_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": {"workload": C2FusedExpr.name, "description": C2FusedExpr.description, "sample": sample},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
     }))
 
 
-def run_workload(dist: Dist, cls, steps: int, warmup: int, sample_clocks: bool, scale: float = 1.0):
-    import thor_b200
+def load_traffic():
+    """DRAM bytes per launch of each workload's dominant kernel, from the committed summary of the ncu captures
+    (profiles/traffic.json: read and written bytes of ONE captured launch of a reduced case and the fraction of the full
+    workload that case is; traffic grows in proportion because every input byte is read exactly once)."""
+    try:
+        return json.loads((ROOT / "profiles" / "traffic.json").read_text())
+    except Exception:
+        return {}
 
+
+def traffic_of(table, wl):
+    t = table.get(wl.name)
+    if not t:
+        return None, None
+    k = 1.0 / float(t.get("fraction_of_workload", 1.0))
+    total = (t["dram_read_bytes"] + t["dram_write_bytes"]) * k
+    read_ratio = t["dram_read_bytes"] * k / max(1, t.get("algorithmic_read_bytes_full", 0)) if t.get("algorithmic_read_bytes_full") else None
+    return total, read_ratio
+
+
+def measure(dist, cls, steps: int, warmup: int, scale: float, sustained: bool, sampler=None):
+    """Sets the workload up on this rank's shard and times it.  Returns (workload, result dict)."""
     wl = cls(dist, scale)
     wl.setup()
-    before = thor_b200.launch_count()
-    sampler = ClockSampler(dist.local_rank if dist.enabled else 0) if (sample_clocks and dist.rank == 0) else None
-    ms, wall, clocks = time_steps(dist, wl.step, steps, warmup, sampler, sample_clocks, getattr(wl, "drain", None))
-    del before
-    launches = wl.launches_per_step * steps  # kernels of this library inside the timed region
-    return wl, ms, wall, clocks, launches
+    drain = getattr(wl, "drain", None)
+    r = time_steps(dist, wl.step, steps, warmup, drain)
+    if sustained:
+        stats, clocks = time_sustained(dist, wl.step, steps, warmup + steps + (warmup + steps) % 2, r["ms"], sampler, drain)
+        r["sustained"], r["clocks"] = stats, clocks
+    return wl, r
+
+
+def config_entry(wl, r, peak, world):
+    per_gpu = wl.algorithmic_bytes() / (r["ms"] * 1e-3) / 1e9  # this rank's shard over the slowest rank's time
+    e = {"us": round(r["ms"] * 1e3, 3), "frac": round(per_gpu / peak, 4), "gbps_total": round(wl.global_algorithmic_bytes() / (r["ms"] * 1e-3) / 1e9, 1),
+         "launches": round(r["launches"] / max(1, r["steps"]), 2)}
+    if "sustained" in r:
+        e["us_sustained_median"] = round(r["sustained"]["ms_median"] * 1e3, 3)
+    return e
+
+
+def one_gpu_time(dist, cls, steps: int, warmup: int, scale: float):
+    """Microseconds per step of the WHOLE global problem on one GPU, measured by rank 0 alone while the other ranks wait:
+    the T(1) of the strong-scaling ratio, from the same run and the same box."""
+    import torch
+
+    us = 0.0
+    if dist.rank == 0:
+        alone = SingleRank(dist.local_rank)
+        w1 = cls(alone, scale)
+        w1.setup()
+        us = time_steps(alone, w1.step, steps, warmup, getattr(w1, "drain", None))["ms"] * 1e3
+        del w1
+        torch.cuda.empty_cache()
+    dist.barrier()
+    return dist.max(us)
+
+
+def c1_cpu_reference(n: int):
+    """The reference's own CPU converter (TypeConverter::cpuConvertTypeImpl compiled from its checkout into oracle/_ref) on
+    the full 2^24-element input with its own thread rule, min(processors, n / 500000) (TypeConverter.cpp:919-925)."""
+    import numpy as np
+
+    import oracle
+    from thor_b200.workloads import cast_input
+
+    if oracle.reference_cast_lib() is None:
+        return None
+    x = cast_input(n, seed=0)
+    oracle.reference_cast(x[: 1 << 20], oracle.FP32, oracle.FP16)
+    best = None
+    for _ in range(5):
+        t0 = time.perf_counter()
+        oracle.reference_cast(x, oracle.FP32, oracle.FP16)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": n * 6 / best / 1e9, "unit": "GB/s", "cores": int(oracle.reference_cast_lib().thor_ref_omp_threads_for(n)), "kind": "reference",
+            "sample": f"all {n} elements, best of 5 passes of the reference's cpuConvertTypeImpl"}
+
+
+def extras(args, dist, wl, line, per_config, peak, traffic):
+    """Everything beside the headline's device-timed number: its end-to-end leg and CPU baseline, the strong-scaling 1-GPU
+    time, every other configuration, the reference's GPU baselines (one GPU only) and the check of the combined results."""
+    import torch
+
+    world = dist.world
+    steps = max(20, args.steps)
+    checks = {}
+
+    def finish(key, cls, w, entry):
+        if world > 1:
+            coll = w.collective_us() if hasattr(w, "collective_us") else None
+            if coll is not None:
+                entry["allreduce_us"] = round(coll, 2)
+            if hasattr(w, "check"):
+                ok, detail = w.check()
+                ok = bool(dist.max(0.0 if ok else 1.0) == 0.0)
+                checks[w.name] = "ok" if ok else "MISMATCH: " + detail
+                entry["check"] = checks[w.name]
+        return entry
+
+    # end to end: pinned host buffers -> H2D -> kernel -> D2H inside the timed region, through the public API
+    if hasattr(wl, "e2e_step") and not getattr(wl, "is_baseline", False):
+        k = max(3, min(10, args.steps))
+        e = time_steps(dist, wl.e2e_step, k, 3)
+        h2d, d2h = wl.e2e_bytes()
+        line["e2e"] = {"value": wl.global_algorithmic_bytes() / (e["ms"] * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "ms_per_step": e["ms"]}
+    if world == 1 and hasattr(wl, "cpu_sample") and not getattr(wl, "is_baseline", False):
+        import oracle
+
+        threads = oracle.host_threads()
+        wl.cpu_sample(64, threads)  # warm
+        v, sample = wl.cpu_sample(1024, threads)
+        line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample}
+    finish(args.workload, WORKLOADS[args.workload], wl, per_config[wl.name])
+    del wl
+    torch.cuda.empty_cache()
+    if world > 1:
+        t1 = one_gpu_time(dist, WORKLOADS[args.workload], steps, 5, args.scale)
+        first = per_config[next(iter(per_config))]
+        first["one_gpu_us"], first["speedup"] = round(t1, 3), round(t1 / first["us"], 3)
+
+    detail = {}
+    for key, cls in WORKLOADS.items():
+        if key == args.workload or (world > 1 and getattr(cls, "is_baseline", False)):
+            continue
+        try:
+            w2, r2 = measure(dist, cls, steps, 5, 1.0, False)
+            r2["steps"] = steps
+            entry = config_entry(w2, r2, peak, world)
+            t_bytes, read_ratio = traffic_of(traffic, w2)
+            detail[w2.name] = {"description": w2.description, "sharding": w2.sharding(), "kernels": getattr(w2, "kernel_kind", None),
+                               "algorithmic_bytes_per_gpu": w2.algorithmic_bytes(), "elements_per_s": w2.global_units() / (r2["ms"] * 1e-3),
+                               "host_issue_us": round(r2["host_issue_ms"] * 1e3, 2), "traffic": t_bytes, "dram_read_over_algorithmic_read": read_ratio}
+            if key == "c1" and world == 1:
+                e = time_steps(dist, w2.e2e_step, 10, 3)
+                entry["e2e_gbps"] = round(w2.global_algorithmic_bytes() / (e["ms"] * 1e-3) / 1e9, 2)
+                cpu = c1_cpu_reference(w2.global_lead)
+                if cpu:
+                    entry["cpu_baseline"] = cpu
+            finish(key, cls, w2, entry)
+            per_config[w2.name] = entry
+            del w2
+            torch.cuda.empty_cache()
+            if world > 1:
+                t1 = one_gpu_time(dist, cls, steps, 5, 1.0)
+                entry["one_gpu_us"], entry["speedup"] = round(t1, 3), round(t1 / entry["us"], 3)
+        except Exception as exc:  # a configuration that cannot run must not hide the headline number
+            per_config[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            if world > 1:
+                raise
+    line["all_configs"] = detail
+    if world > 1:
+        bad = {k: v for k, v in checks.items() if v != "ok"}
+        line["multi_gpu_check"] = "ok" if not bad else bad
+        if bad:
+            if dist.rank == 0:
+                print(json.dumps(line))
+            raise SystemExit(f"multi-GPU results differ from the oracle of the global problem: {bad}")
 
 
 def main():
@@ -901,9 +1248,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations, the end-to-end leg and the CPU baseline")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations, the end-to-end leg, the baselines and the result check")
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of the workload's leading dimension (smaller cases for profiler captures only)")
-    ap.add_argument("--row-program", default="", help="row-program layout fields, e.g. rows_per_iteration=1,ring_buffers=4 (comparison runs)")
+    ap.add_argument("--row-program", default="", help="row-program layout fields, e.g. copy_warpgroup=-1,ring_buffers=4 (comparison runs)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.row_program:
@@ -915,83 +1262,47 @@ def main():
 
     import torch
 
-    import thor_b200
-
     dist = Dist(args.gpus)
-    peak, peak_kind = measured_peak()
-    wl, ms, wall, clocks, launches = run_workload(dist, WORKLOADS[args.workload], args.steps, args.warmup, True, args.scale)
     world = dist.world
-    total_bytes = wl.algorithmic_bytes() * world
-    value = total_bytes / (ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    traffic = load_traffic()
+    sampler = ClockSampler(dist.local_rank if dist.enabled else 0) if dist.rank == 0 else None
+    wl, r = measure(dist, WORKLOADS[args.workload], args.steps, args.warmup, args.scale, True, sampler)
+    r["steps"] = args.steps
+    ms = r["ms"]
+    global_bytes = wl.global_algorithmic_bytes()
+    value = global_bytes / (ms * 1e-3) / 1e9
     per_gpu_gbs = wl.algorithmic_bytes() / (ms * 1e-3) / 1e9
+    sus = r["sustained"]
+    traffic_bytes, read_ratio = traffic_of(traffic, wl)
+    kernel_launches = max(1, wl.launches_per_step)
     line = {
         "metric": "fused_expr_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "description": wl.description, "sharding": f"rows x{world}, no collective" if world > 1 else "single GPU",
-                   "cache": f"{len(wl.sets) or 1} rotating buffer sets, {wl.algorithmic_bytes() * max(1, len(wl.sets)) >> 20} MiB per GPU > 4 x L2",
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "description": wl.description, "sharding": wl.sharding(),
+                   "cache": f"{len(wl.sets) or 1} rotating buffer sets, {wl.algorithmic_bytes() * max(1, len(wl.sets)) >> 20} MiB on this GPU, more than 4 x L2",
                    "kernel": getattr(wl, "kernel_kind", None), "scale": args.scale},
-        "elements_per_s": wl.units() * world / (ms * 1e-3),
-        "wall_ms_per_step": wall,
-        "clocks": clocks,
-        "gpu_launches": launches,
+        "elements_per_s": wl.global_units() / (ms * 1e-3),
+        "host_issue_ms_per_step": r["host_issue_ms"],
+        "clocks": r["clocks"],
+        "gpu_launches": r["launches"],
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
-                     "traffic": TRAFFIC_BYTES.get(wl.name), "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": wl.algorithmic_bytes(),
-                     "launch_us": ms * 1e3 / max(1, wl.launches_per_step)},
+                     "traffic": traffic_bytes, "dram_read_over_algorithmic_read": read_ratio, "peak_source": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": wl.algorithmic_bytes(), "launch_us": ms * 1e3 / kernel_launches,
+                     "frac_sustained": wl.algorithmic_bytes() / (sus["ms_median"] * 1e-3) / 1e9 / peak,
+                     "sustained": {"us_median": sus["ms_median"] * 1e3, "us_p10": sus["ms_p10"] * 1e3, "us_p90": sus["ms_p90"] * 1e3, "groups": sus["groups"],
+                                   "steps_per_group": sus["steps_per_group"], "sm_mhz": (r["clocks"] or {}).get("sm_mhz")},
+                     "per_config": {}},
     }
+    per_config = line["roofline"]["per_config"]
+    per_config[wl.name] = config_entry(wl, r, peak, world)
 
     if not args.no_extras:
-        # end to end: pinned host buffers -> H2D -> kernel -> D2H inside the timed region
-        if hasattr(wl, "e2e_step") and not getattr(wl, "is_baseline", False):
-            k = max(3, min(10, args.steps))
-            e_ms, _, _ = time_steps(dist, wl.e2e_step, k, 3)
-            h2d, d2h = wl.e2e_bytes()
-            line["e2e"] = {"value": total_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                           "ms_per_step": e_ms}
-        # CPU baseline on rank 0 at N = 1: bounded sample of the same workload
-        if world == 1 and hasattr(wl, "cpu_sample") and not getattr(wl, "is_baseline", False):
-            import oracle
-
-            threads = oracle.host_threads()
-            wl.cpu_sample(64, threads)  # warm
-            v, sample = wl.cpu_sample(1024, threads)
-            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample}
-        del wl
-        torch.cuda.empty_cache()
-        extras = {}
-        for key, cls in WORKLOADS.items():
-            if key == args.workload:
-                continue
-            try:
-                w2, ms2, _, _, l2 = run_workload(dist, cls, max(20, args.steps), 5, False)
-                g = w2.algorithmic_bytes() / (ms2 * 1e-3) / 1e9
-                extras[w2.name] = {"ms_per_step": ms2, "gbps_per_gpu": g, "gbps_total": g * world, "frac_of_peak": g / peak, "launches_per_step": w2.launches_per_step,
-                                   "kernels": getattr(w2, "kernel_kind", None), "algorithmic_bytes": w2.algorithmic_bytes(),
-                                   "elements_per_s": w2.units() * world / (ms2 * 1e-3)}
-                del w2
-                torch.cuda.empty_cache()
-            except Exception as exc:  # a configuration that cannot run must not hide the headline number
-                extras[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
-        line["all_configs"] = extras
+        extras(args, dist, wl, line, per_config, peak, traffic)
     if dist.rank == 0:
         print(json.dumps(line))
     dist.close()
 
-
-# DRAM bytes of the dominant kernel per launch, measured with ncu on a reduced case of the same kernel (one
-# captured launch, summaries under profiles/) and scaled to the full launch by the elements processed: traffic
-# grows in proportion (every input byte is read once).  Written bytes undercount outputs that are still dirty
-# in the 126 MB L2 when a small case ends, so values below the algorithmic bytes mean "no re-reads", not less work.
-TRAFFIC_BYTES = {
-    "c1_cast_fp32_fp16": 71_600_000,                 # full size captured; most of the 33.5 MB output is still in L2 at kernel end
-    "c2_fused_relu_axb_sigmoid": 2 * 161_700_000,    # 4096 of 8192 rows captured
-    "c3_softmax_rows_fp32": 8 * 215_500_000,
-    "c3_softmax_and_argmax_one_pass_fp32": 8 * 217_300_000,         # 8192 of 65536 rows captured
-    "c3_row_argmax_fp32": 8 * 138_300_000,
-    "c4_full_reductions_bf16": 16 * 272_400_000,     # 2^27 of 2^31 elements captured
-    "c5_layernorm_forward_bf16": 8 * 78_900_000,     # 4096 of 32768 rows captured
-    "c5_layernorm_backward_bf16": 8 * 170_100_000,
-    "c2_fused_relu_axb_sigmoid_reference_gpu_kernel": 2 * 173_900_000,
-}
 
 if __name__ == "__main__":
     main()

@@ -203,3 +203,17 @@ def test_layernorm_programs_take_rows_through_the_bulk_copy_ring_and_softmax_kee
     e = (xi - xi.reduce_max([1])).exp()
     sm = ex.compile(e / e.reduce_sum([1])).plan({"x": ((65536, 4096), DT.fp32)}).stage_sources()[0]
     assert sm.count("expf(") == 2 and "kept from the first element loop" in sm  # two lanes of one pair, once
+
+
+def test_constant_subtrees_become_one_literal_and_identities_compute_nothing():
+    """The reference's emitter folds literal subtrees in double and emits one float literal, and x + 0, x * 1, x / 1 alias
+    their operand (CudaSourceEmitter.cpp:1965-2076, 3745-3782); the fused stage and the row program do the same."""
+    x, z = ex.input("x"), ex.input("z")
+    e = x * (ex.scalar(0.1) * ex.scalar(3.0)) + (ex.scalar(1.0) / ex.scalar(3.0)) + (z + 0.0) * 1.0 / (ex.scalar(2.0) - ex.scalar(1.0))
+    body = ex.compile(e).plan({"x": ((1 << 16,), DT.fp16), "z": ((1 << 16,), DT.fp16)}).stage_sources()[0].split('extern "C"')[0]
+    assert "0.300000012f" in body and "0.333333343f" in body  # (float)(0.1 * 3.0) and (float)(1.0 / 3.0), not fp16 products
+    assert "0.100000001f" not in body and "3.0f" not in body and "2.0f" not in body and "1.0f" not in body
+    # one multiplication (x by the folded literal) and two additions are all the arithmetic that is left
+    assert body.count(" * ") == 1 and body.count(" + ") == 2 and " / " not in body and " - " not in body
+    row = ex.compile({"y": (x * 1.0 + 0.0) / x.reduce_sum([1])}).plan({"x": ((64, 512), DT.fp32)}).stage_sources()[0]
+    assert "1.0f" not in row.split("row_kernel")[1] and "0.0f)" not in row.split("// outputs")[1]

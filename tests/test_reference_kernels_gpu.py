@@ -37,6 +37,10 @@ PROGRAMS = [
     ("div_pow", "in:x in:a abs lit:0.5 add div in:z abs lit:1.5 pow add", {}),
     ("minmax_neg", "in:x in:z min in:a neg max lit:0.25 mul", {}),
     ("erf_expm1", "in:x erf in:z lit:0.5 mul expm1 sub", {}),
+    # constant subtrees (folded in double to one float literal) and identities (x + 0, x * 1, x / 1 compute nothing):
+    # CudaSourceEmitter.cpp:1965-2076, 3745-3782 -- in 16-bit stages a per-node evaluation would round differently
+    ("const_fold", "in:x lit:0.1 lit:3 mul mul lit:1 lit:3 div add lit:0.7 neg in:z mul sub", {}),
+    ("identities", "in:x lit:0 add lit:1 mul in:z lit:2 lit:1 sub div sub lit:0 in:a add add", {}),
 ]
 
 

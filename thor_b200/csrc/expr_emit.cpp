@@ -160,7 +160,6 @@ struct Plan {
     int v2_dtype = 0;
     // value-range facts used to pick cheaper bit-identical routines: "<= 0 or NaN" / ">= 0 or NaN"
     std::vector<bool> nonpos, nonneg;
-    bool lean_pair_math = true;
     // half2 bodies: node k = exp(-max(-z, 0)) takes its value from node exp_twin[k] = exp(-|z|) of the same z (node
     // exp_twin_z[k]) where z < 0 and is 1 elsewhere; `order` is the emission order (such a node moves behind its twin)
     std::vector<int> exp_twin;
@@ -411,11 +410,11 @@ std::string v2NodeExpr(const Plan& p, size_t k) {
         case THOR_B200_OP_ADD: return "__hadd2(" + a + ", " + b + ")";
         case THOR_B200_OP_SUB: return "__hsub2(" + a + ", " + b + ")";
         case THOR_B200_OP_MUL: return "__hmul2(" + a + ", " + b + ")";
-        case THOR_B200_OP_DIV: return (!bf && p.lean_pair_math ? "tb_h2div(" : "__h2div(") + a + ", " + b + ")";
+        case THOR_B200_OP_DIV: return (!bf ? "tb_h2div(" : "__h2div(") + a + ", " + b + ")";
         case THOR_B200_OP_NEG: return "__hneg2(" + a + ")";
         case THOR_B200_OP_ABS: return "__hmax2(" + a + ", __hneg2(" + a + "))";
         case THOR_B200_OP_EXP:
-            if (!bf && p.lean_pair_math) return std::string(p.nonpos[nd.lhs] ? "tb_h2exp_nonpos(" : "tb_h2exp(") + a + ")";
+            if (!bf) return std::string(p.nonpos[nd.lhs] ? "tb_h2exp_nonpos(" : "tb_h2exp(") + a + ")";
             return "h2exp(" + a + ")";
         case THOR_B200_OP_EXP2: return "h2exp2(" + a + ")";
         case THOR_B200_OP_EXP10: return "h2exp10(" + a + ")";
@@ -881,20 +880,67 @@ std::string validate(const Stage& st) {
     return "";
 }
 
-std::string emit(const Stage& st, bool force_generic, Emitted* out) {
-    std::string why = validate(st);
+size_t foldConstantsAndIdentities(std::vector<thor_b200_expr_node>& nodes, const std::vector<uint32_t>& keep) {
+    const size_t n = nodes.size();
+    std::vector<bool> is_const(n, false), kept(n, false);
+    std::vector<double> value(n, 0.0);
+    for (uint32_t k : keep)
+        if (k < n) kept[k] = true;
+    size_t rewritten = 0;
+    for (size_t k = 0; k < n; ++k) {
+        thor_b200_expr_node& nd = nodes[k];
+        auto constant = [&](uint32_t i) { return i != THOR_B200_NO_NODE && i < k && is_const[i]; };
+        if (nd.op == THOR_B200_OP_SCALAR_FP) {
+            is_const[k] = true;
+            value[k] = nd.scalar_fp;
+            continue;
+        }
+        const bool arith4 = nd.op == THOR_B200_OP_ADD || nd.op == THOR_B200_OP_SUB || nd.op == THOR_B200_OP_MUL || nd.op == THOR_B200_OP_DIV;
+        // the dtype the node's value is held in: what the literal or the aliased value is converted to
+        const uint16_t held = isArithCompute(nd.compute_dtype) ? nd.compute_dtype : nd.output_dtype;
+        if ((nd.op == THOR_B200_OP_NEG && constant(nd.lhs)) || (arith4 && constant(nd.lhs) && constant(nd.rhs))) {
+            const double a = value[nd.lhs], b = arith4 ? value[nd.rhs] : 0.0;
+            is_const[k] = true;
+            value[k] = nd.op == THOR_B200_OP_NEG ? -a : nd.op == THOR_B200_OP_ADD ? a + b : nd.op == THOR_B200_OP_SUB ? a - b : nd.op == THOR_B200_OP_MUL ? a * b : a / b;
+            nd.op = THOR_B200_OP_SCALAR_FP;
+            nd.scalar_fp = value[k];
+            nd.lhs = nd.rhs = nd.aux = THOR_B200_NO_NODE;
+            if (!kept[k]) nd.output_dtype = held;
+            ++rewritten;
+            continue;
+        }
+        if (!arith4) continue;
+        uint32_t source = THOR_B200_NO_NODE;
+        const bool lhs_zero = constant(nd.lhs) && value[nd.lhs] == 0.0, rhs_zero = constant(nd.rhs) && value[nd.rhs] == 0.0;
+        const bool lhs_one = constant(nd.lhs) && value[nd.lhs] == 1.0, rhs_one = constant(nd.rhs) && value[nd.rhs] == 1.0;
+        if (nd.op == THOR_B200_OP_ADD) source = lhs_zero ? nd.rhs : (rhs_zero ? nd.lhs : THOR_B200_NO_NODE);
+        else if (nd.op == THOR_B200_OP_SUB) source = rhs_zero ? nd.lhs : THOR_B200_NO_NODE;
+        else if (nd.op == THOR_B200_OP_MUL) source = lhs_one ? nd.rhs : (rhs_one ? nd.lhs : THOR_B200_NO_NODE);
+        else source = rhs_one ? nd.lhs : THOR_B200_NO_NODE;
+        if (source == THOR_B200_NO_NODE) continue;
+        nd.op = THOR_B200_OP_CAST;  // a conversion of the source's value and nothing else
+        nd.lhs = source;
+        nd.rhs = nd.aux = THOR_B200_NO_NODE;
+        if (!kept[k]) nd.output_dtype = held;
+        ++rewritten;
+    }
+    return rewritten;
+}
+
+std::string emit(const Stage& original, bool force_generic, Emitted* out) {
+    std::string why = validate(original);
     if (!why.empty()) return why;
+    Stage st = original;
+    {
+        std::vector<uint32_t> keep;
+        for (const auto& o : st.outputs) keep.push_back(o.node);
+        foldConstantsAndIdentities(st.nodes, keep);
+    }
     Plan p(st);
     markLive(p);
     decideV2(p);
     analyseSigns(p);
-    if (const char* e = getenv("THOR_B200_LEAN_PAIR_MATH")) p.lean_pair_math = atoi(e) != 0;
     findExpTwins(p);
-    if (const char* e = getenv("THOR_B200_EXP_TWINS"))
-        if (atoi(e) == 0) {
-            std::fill(p.exp_twin.begin(), p.exp_twin.end(), -1);
-            std::sort(p.order.begin(), p.order.end());
-        }
     std::ostringstream os;
     os << "// generated by thor_b200: fused stage, " << st.nodes.size() << " nodes, " << st.inputs.size() << " inputs, " << st.outputs.size() << " outputs\n";
     os << "#include \"tb_prelude.cuh\"\n\n";

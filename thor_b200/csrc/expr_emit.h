@@ -49,6 +49,14 @@ std::string emit(const Stage& stage, bool force_generic, Emitted* out);
 
 const char* kindName(Kind k);
 
+// What the reference's emitter does to constants and identities before it emits a node
+// (CudaSourceEmitter.cpp:1965-2076, 3478-3485, 3745-3782), applied to the node list itself:
+//   - a subtree of literals under NEG / ADD / SUB / MUL / DIV is evaluated in double and becomes ONE literal, emitted as
+//     a float literal and converted to the dtype the node's value is held in (not computed per node in a 16-bit type);
+//   - x + 0, 0 + x, x - 0, x * 1, 1 * x and x / 1 compute nothing: the node's value is x converted to the node's dtype.
+// Nodes listed in `keep` (stage outputs) keep their declared output dtype.  Returns how many nodes were rewritten.
+size_t foldConstantsAndIdentities(std::vector<thor_b200_expr_node>& nodes, const std::vector<uint32_t>& keep);
+
 // Building blocks shared with the row-program emitter.  A node's value lives in the variable "v<k>"
 // typed as its output dtype; tensor inputs are "x<slot>", scalars "s<slot>".
 std::string scalarNodeExpression(const std::vector<thor_b200_expr_node>& nodes, const std::vector<thor_b200_expr_input>& inputs, size_t k);

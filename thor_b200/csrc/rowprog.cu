@@ -1413,6 +1413,12 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
             }
         }
     }
+    {
+        // constants and identities first, as in the fused stages (the reference's emitter rule)
+        std::vector<uint32_t> keep;
+        for (const auto& o : p.outputs) keep.push_back(o.node);
+        tb::expr::foldConstantsAndIdentities(p.nodes, keep);
+    }
     mergeDuplicates(p);
     std::string why = analyse(p);
     if (!why.empty()) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: %s", why.c_str());
