@@ -237,7 +237,7 @@ def time_steps(dist, step, steps: int, warmup: int, drain=None):
     return {"ms": dist.max(e0.elapsed_time(e1) / steps), "host_issue_ms": dist.max(issued), "launches": int(launches)}
 
 
-def time_sustained(dist, step, steps: int, first: int, ms_hint: float, sampler: ClockSampler | None, drain=None, groups: int = 11, min_total_ms: float = 400.0):
+def time_sustained(dist, step, steps: int, first: int, ms_hint: float, sampler: ClockSampler | None, drain=None, groups: int = 11, min_total_ms: float = 1500.0):
     """The same load kept running after the timed region: `groups` groups of equal length, each bracketed by its own event
     pair, at least min_total_ms in all (nvidia-smi cannot sample faster than every ~20 ms).  Every rank derives the group
     length from the rank-maximum time of the timed region, so collectives stay matched.  Returns per-step statistics over
@@ -661,59 +661,42 @@ class C3Argmax(C3Softmax):
 
 
 class _ShardCombiner:
-    """Combines this rank's fp32 partials with the other ranks' through the library's communicator
-    (thor_b200_comm_allreduce_stats_f32: one NCCL group) on a side stream.  The partial buffers are double-buffered with
-    the plans that write them, so the collective of step i overlaps the kernel of step i + 1; a buffer's next kernel
-    waits for that buffer's last collective."""
+    """Combines this rank's fp32 partials with the other ranks' through the library's overlapped combiner
+    (thor_b200_combiner_*: one NCCL group per step on a high-priority stream of its own).  The partial buffers are
+    double-buffered with the plans that write them, so the collective of step i overlaps the kernel of step i + 1; a
+    buffer's next kernel waits for that buffer's last collective."""
 
     def __init__(self, comm, buffers: int):
-        import torch
+        from thor_b200.sharding import Combiner
 
         self.comm = comm
-        self.stream = torch.cuda.Stream()
-        self.ready = [torch.cuda.Event() for _ in range(buffers)]
-        self.done = [torch.cuda.Event() for _ in range(buffers)]
-        self.used = [False] * buffers
+        self.native = Combiner(comm, buffers)
+        self.stream = self.native.stream
 
-    def before_kernel(self, b: int):
-        import torch
+    # Three slots, not two: a persistent kernel fills every SM, so the collective of step i only gets to run when the kernel of
+    # step i + 1 drains; with two slots the kernel of step i + 2 would wait for it at every boundary (measured at N = 2,
+    # LayerNorm backward: 177 us per step against 156 us), with three it never does.
+    SLOTS = 3
 
-        if self.used[b]:
-            torch.cuda.current_stream().wait_event(self.done[b])
-
-    def after_kernel(self, b: int, sums=None, maxima=None, then=None):
-        import torch
-
-        self.ready[b].record()
-        self.stream.wait_event(self.ready[b])
-        self.comm.allreduce_stats(sums=sums, maxima=maxima, stream=self.stream)
-        if then is not None:
-            with torch.cuda.stream(self.stream):
-                then()
-        self.done[b].record(self.stream)
-        self.used[b] = True
-
-    def drain(self):
-        import torch
-
-        torch.cuda.current_stream().wait_stream(self.stream)
+    def before_kernel(self, b: int): self.native.wait(b)
+    def after_kernel(self, b: int, sums=None, maxima=None, rounded=None): self.native.submit(b, sums=sums, maxima=maxima, rounded_sums=rounded)
+    def drain(self): self.native.drain()
 
     def time_alone(self, dist, sums=None, maxima=None, iters: int = 50) -> float:
-        """Microseconds of one collective with nothing else on the GPU (events around `iters` back-to-back calls on the side
-        stream, max over ranks): the NVLink time of the step."""
+        """Microseconds of one collective with nothing else on the GPU (events around `iters` back-to-back calls on the
+        combiner's stream, max over ranks): the NVLink time of the step."""
         import torch
 
         scratch_s = sums.clone() if sums is not None else None
         scratch_m = maxima.clone() if maxima is not None else None
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(self.stream):
-            for _ in range(5):
-                self.comm.allreduce_stats(sums=scratch_s, maxima=scratch_m, stream=self.stream)
-            e0.record(self.stream)
-            for _ in range(iters):
-                self.comm.allreduce_stats(sums=scratch_s, maxima=scratch_m, stream=self.stream)
-            e1.record(self.stream)
+        for _ in range(5):
+            self.comm.allreduce_stats(sums=scratch_s, maxima=scratch_m, stream=self.stream)
+        e0.record(self.stream)
+        for _ in range(iters):
+            self.comm.allreduce_stats(sums=scratch_s, maxima=scratch_m, stream=self.stream)
+        e1.record(self.stream)
         self.stream.synchronize()
         return dist.max(e0.elapsed_time(e1) / iters * 1e3)
 
@@ -739,19 +722,19 @@ class C4FullReduce(Workload):
             self.x[s:s + n] = (torch.randn(n, device="cuda", generator=gen) + 0.01).bfloat16()
         x = ex.input("x")
         eq = ex.compile({"sum": x.reduce_sum(), "sumsq": (x * x).reduce_sum(), "max": x.reduce_max()})
-        # two stamped plans over the same input, each with its own [sum, sumsq, max] fp32 result buffer
-        self.stats = [torch.zeros(3, device="cuda") for _ in range(2)]
+        # one stamped plan per combiner slot over the same input, each with its own [sum, sumsq, max] fp32 result buffer
+        self.stats = [torch.zeros(3, device="cuda") for _ in range(_ShardCombiner.SLOTS)]
         self.plans = [eq.stamp({"x": self.x}, outputs={"sum": st[0:1], "sumsq": st[1:2], "max": st[2:3]}) for st in self.stats]
         self.sets = self.plans
         self.launches_per_step = self.plans[0].kernel_launches_per_run()
         self.kernel_kind = self.plans[0].physical_stage_names()
         comm = self.dist.communicator()
-        self.combiner = _ShardCombiner(comm, 2) if comm is not None else None
+        self.combiner = _ShardCombiner(comm, _ShardCombiner.SLOTS) if comm is not None else None
 
     def algorithmic_bytes(self): return self.N * 2
     def units(self): return self.N
     def step(self, i):
-        b = i & 1
+        b = i % _ShardCombiner.SLOTS
         if self.combiner is None:
             self.plans[b].run()
             return
@@ -962,14 +945,13 @@ class C5LayerNormBwd(C5LayerNormFwd):
     def setup(self):
         import torch
 
-        from thor_b200 import TypeConverter
         from thor_b200.expression import Expression as ex
 
         gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
         sharded = self.dist.enabled
         bwd = ex.compile({"y": _layernorm_expr(ex)}, row_program=ROW_PROGRAM, unrounded_column_sums=sharded).compile_backward(["x", "gamma", "beta"])
         self.sets = []
-        for _ in range(2):
+        for _ in range(_ShardCombiner.SLOTS if sharded else 2):
             x, gamma, beta = self._inputs(gen)
             dy = (torch.randn(self.ROWS, self.COLS, device="cuda", generator=gen) * 1e-2).bfloat16()
             plan = bwd.stamp({"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy})
@@ -978,12 +960,11 @@ class C5LayerNormBwd(C5LayerNormFwd):
         self.launches_per_step = self.sets[0][0].kernel_launches_per_run()
         self.kernel_kind = self.sets[0][0].physical_stage_names()
         comm = self.dist.communicator()
-        self.combiner = _ShardCombiner(comm, 2) if comm is not None else None
-        self.round_once = TypeConverter.convert_type
+        self.combiner = _ShardCombiner(comm, _ShardCombiner.SLOTS) if comm is not None else None
 
     def algorithmic_bytes(self): return 3 * self.ROWS * self.COLS * 2 + 3 * self.COLS * 2
     def step(self, i):
-        b = i & 1
+        b = i % len(self.sets)
         plan, _, _, _, sums, grads = self.sets[b]
         if self.combiner is None:
             plan.run()
@@ -991,7 +972,7 @@ class C5LayerNormBwd(C5LayerNormFwd):
         self.combiner.before_kernel(b)
         plan.run()
         # the unrounded fp32 sums of this rank's rows are added across the ranks, then rounded to the gradients' dtype once
-        self.combiner.after_kernel(b, sums=sums, then=lambda: self.round_once(sums.view(-1), grads.view(-1)))
+        self.combiner.after_kernel(b, sums=sums, rounded=grads)
 
     def drain(self):
         if self.combiner is not None:
@@ -1106,7 +1087,7 @@ def measure(dist, cls, steps: int, warmup: int, scale: float, sustained: bool, s
     drain = getattr(wl, "drain", None)
     r = time_steps(dist, wl.step, steps, warmup, drain)
     if sustained:
-        stats, clocks = time_sustained(dist, wl.step, steps, warmup + steps + (warmup + steps) % 2, r["ms"], sampler, drain)
+        stats, clocks = time_sustained(dist, wl.step, steps, warmup + steps, r["ms"], sampler, drain)
         r["sustained"], r["clocks"] = stats, clocks
     return wl, r
 
@@ -1237,7 +1218,7 @@ def extras(args, dist, wl, line, per_config, peak, traffic):
         line["multi_gpu_check"] = "ok" if not bad else bad
         if bad:
             if dist.rank == 0:
-                print(json.dumps(line))
+                sys.stderr.write(json.dumps(line) + "\n")
             raise SystemExit(f"multi-GPU results differ from the oracle of the global problem: {bad}")
 
 
@@ -1262,6 +1243,9 @@ def main():
 
     import torch
 
+    # stdout carries the one JSON line and nothing else: whatever libraries print (NCCL's version banner) goes to stderr
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     dist = Dist(args.gpus)
     world = dist.world
     peak, peak_kind = measured_peak()
@@ -1300,7 +1284,8 @@ def main():
     if not args.no_extras:
         extras(args, dist, wl, line, per_config, peak, traffic)
     if dist.rank == 0:
-        print(json.dumps(line))
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
     dist.close()
 
 

@@ -361,7 +361,8 @@ typedef struct thor_b200_rowprog_tuning {
     int32_t wait_limit_ms;       /* time limit of a wait on a ring buffer's barrier; 0 = two seconds */
     int32_t test_skip_fill;      /* tests of the bounded waits only: n > 0 makes CTA 0's code lack the copy request of loop
                                   * iteration n, so the wait for that buffer runs out; 0 = none */
-    int32_t reserved;            /* must be zero */
+    int32_t reserve_sms;         /* persistent programs leave this many SMs without a CTA, for a kernel that has to run beside
+                                  * them (the allreduce of the previous step's partials on another stream): 0 = none */
 } thor_b200_rowprog_tuning;
 
 typedef struct thor_b200_rowprog_desc {
@@ -446,6 +447,25 @@ THOR_B200_API int thor_b200_comm_allreduce_f32(thor_b200_comm* comm, void* buffe
  * Asynchronous on `stream`; every rank makes the same call. */
 THOR_B200_API int thor_b200_comm_allreduce_stats_f32(thor_b200_comm* comm, void* sums, uint64_t n_sums, void* maxima, uint64_t n_maxima, void* minima,
                                                      uint64_t n_minima, void* stream);
+/* Overlapped combine for a stepping job: the statistics of step i cross the ranks on a high-priority stream of the
+ * combiner's own while the kernel of step i + 1 runs.  The caller keeps `slots` copies of its partial buffers and uses
+ * slot i % slots in step i:
+ *     thor_b200_combiner_wait(c, slot, stream);      -- the kernel may overwrite the slot's partials only after their last combine
+ *     ... launch the step's kernels on `stream` ...
+ *     thor_b200_combiner_submit(c, slot, stream, sums, n_sums, maxima, n_maxima, minima, n_minima, rounded_sums, dtype);
+ * submit orders the combine behind everything `stream` holds so far, runs thor_b200_comm_allreduce_stats_f32 and then,
+ * when rounded_sums is not NULL, converts the combined fp32 sums to `rounded_dtype` there (the single rounding of a
+ * sharded column sum).  thor_b200_combiner_drain makes `stream` wait for every combine submitted so far.  No call
+ * blocks the host or allocates after create. */
+typedef struct thor_b200_combiner thor_b200_combiner;
+THOR_B200_API int thor_b200_combiner_create(thor_b200_comm* comm, int slots, thor_b200_combiner** out_combiner);
+THOR_B200_API int thor_b200_combiner_wait(thor_b200_combiner* combiner, int slot, void* stream);
+THOR_B200_API int thor_b200_combiner_submit(thor_b200_combiner* combiner, int slot, void* producer_stream, void* sums, uint64_t n_sums, void* maxima,
+                                            uint64_t n_maxima, void* minima, uint64_t n_minima, void* rounded_sums, int rounded_dtype);
+THOR_B200_API int thor_b200_combiner_drain(thor_b200_combiner* combiner, void* stream);
+/* The combiner's own stream (cudaStream_t), e.g. to time the collective alone. */
+THOR_B200_API void* thor_b200_combiner_stream(thor_b200_combiner* combiner);
+THOR_B200_API void thor_b200_combiner_destroy(thor_b200_combiner* combiner);
 THOR_B200_API void thor_b200_comm_destroy(thor_b200_comm* comm);
 
 #ifdef __cplusplus

@@ -63,6 +63,28 @@ comm.allreduce_stats(sums=s2, maxima=mx, minima=mn)
 torch.cuda.synchronize()
 assert s2.tolist() == [float(sum(range(1, world + 1)))] * 2, s2
 assert mx[0].item() == world - 1 and torch.isnan(mx[1]) and mn[0].item() == 0 and torch.isnan(mn[1]), (mx, mn)
+# the overlapped combiner: four steps over two slots, sums rounded to bf16 once after the combine
+from thor_b200.sharding import Combiner
+cb = Combiner(comm, 2)
+sums = [torch.zeros(2, 4096, device="cuda") for _ in range(2)]
+rounded = [torch.zeros(2, 4096, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+mx = [torch.zeros(1, device="cuda") for _ in range(2)]
+for step in range(4):
+    b = step & 1
+    cb.wait(b)
+    sums[b].fill_(float(rank + 1) * (step + 1) + 0.001)
+    mx[b].fill_(float(rank * (step + 1)))
+    cb.submit(b, sums=sums[b], maxima=mx[b], rounded_sums=rounded[b])
+cb.drain()
+torch.cuda.synchronize()
+total = sum(range(1, world + 1))
+for b, step in ((0, 2), (1, 3)):
+    want = torch.full((2, 4096), 0.0, device="cuda")
+    for r in range(world):
+        want += float(r + 1) * (step + 1) + 0.001
+    assert torch.equal(sums[b], want), (sums[b][0, :2], want[0, :2])
+    assert torch.equal(rounded[b], want.bfloat16()) and mx[b].item() == (world - 1) * (step + 1)
+cb.close()
 comm.close()
 print("rank", rank, "ok")
 """

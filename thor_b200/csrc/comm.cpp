@@ -163,6 +163,84 @@ int thor_b200_comm_allreduce_stats_f32(thor_b200_comm* comm, void* sums, uint64_
     return THOR_B200_OK;
 }
 
+// ---- overlapped combine ---------------------------------------------------------------------------
+// A step of a row-sharded job ends with small fp32 partials (two or three statistics, or a [2, cols] block of column
+// sums) that have to be combined across the ranks while the NEXT step's kernel already runs.  The combiner owns a
+// high-priority side stream and one (ready, done) event pair per slot; the caller double-buffers its partials over the
+// slots.  Everything is stream-ordered: no call blocks the host.
+struct thor_b200_combiner {
+    thor_b200_comm* comm = nullptr;
+    cudaStream_t side = nullptr;
+    int slots = 0;
+    cudaEvent_t ready[8] = {}, done[8] = {};
+    bool used[8] = {};
+};
+
+int thor_b200_combiner_create(thor_b200_comm* comm, int slots, thor_b200_combiner** out) {
+    using namespace tb;
+    TB_REQUIRE(comm != nullptr && out != nullptr, "combiner_create: null argument");
+    TB_REQUIRE(slots >= 1 && slots <= 8, "combiner_create: between 1 and 8 slots");
+    *out = nullptr;
+    auto c = new thor_b200_combiner();
+    c->comm = comm;
+    c->slots = slots;
+    int least = 0, greatest = 0;
+    cudaError_t e = cudaDeviceGetStreamPriorityRange(&least, &greatest);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&c->side, cudaStreamNonBlocking, greatest);
+    for (int i = 0; i < slots && e == cudaSuccess; ++i) {
+        e = cudaEventCreateWithFlags(&c->ready[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->done[i], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) {
+        thor_b200_combiner_destroy(c);
+        return fail(THOR_B200_CUDA_ERROR, "combiner_create: %s", cudaGetErrorString(e));
+    }
+    *out = c;
+    return THOR_B200_OK;
+}
+
+int thor_b200_combiner_wait(thor_b200_combiner* c, int slot, void* stream) {
+    using namespace tb;
+    TB_REQUIRE(c != nullptr && slot >= 0 && slot < c->slots, "combiner_wait: bad combiner or slot");
+    if (c->used[slot]) TB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), c->done[slot], 0));
+    return THOR_B200_OK;
+}
+
+int thor_b200_combiner_submit(thor_b200_combiner* c, int slot, void* producer_stream, void* sums, uint64_t n_sums, void* maxima, uint64_t n_maxima,
+                              void* minima, uint64_t n_minima, void* rounded_sums, int rounded_dtype) {
+    using namespace tb;
+    TB_REQUIRE(c != nullptr && slot >= 0 && slot < c->slots, "combiner_submit: bad combiner or slot");
+    TB_REQUIRE(rounded_sums == nullptr || (sums != nullptr && n_sums > 0), "combiner_submit: rounded_sums needs sums");
+    TB_CUDA(cudaEventRecord(c->ready[slot], static_cast<cudaStream_t>(producer_stream)));
+    TB_CUDA(cudaStreamWaitEvent(c->side, c->ready[slot], 0));
+    if (int st = thor_b200_comm_allreduce_stats_f32(c->comm, sums, n_sums, maxima, n_maxima, minima, n_minima, c->side)) return st;
+    if (rounded_sums != nullptr)
+        if (int st = thor_b200_cast_launch(sums, rounded_sums, THOR_B200_FP32, rounded_dtype, static_cast<int64_t>(n_sums), c->side)) return st;
+    TB_CUDA(cudaEventRecord(c->done[slot], c->side));
+    c->used[slot] = true;
+    return THOR_B200_OK;
+}
+
+int thor_b200_combiner_drain(thor_b200_combiner* c, void* stream) {
+    using namespace tb;
+    TB_REQUIRE(c != nullptr, "combiner_drain: null combiner");
+    for (int i = 0; i < c->slots; ++i)
+        if (c->used[i]) TB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), c->done[i], 0));
+    return THOR_B200_OK;
+}
+
+void* thor_b200_combiner_stream(thor_b200_combiner* c) { return c ? c->side : nullptr; }
+
+void thor_b200_combiner_destroy(thor_b200_combiner* c) {
+    if (!c) return;
+    for (int i = 0; i < 8; ++i) {
+        if (c->ready[i]) cudaEventDestroy(c->ready[i]);
+        if (c->done[i]) cudaEventDestroy(c->done[i]);
+    }
+    if (c->side) cudaStreamDestroy(c->side);
+    delete c;
+}
+
 void thor_b200_comm_destroy(thor_b200_comm* comm) {
     if (!comm) return;
     if (comm->comm) nccl().CommDestroy(comm->comm);

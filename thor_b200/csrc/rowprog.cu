@@ -1470,7 +1470,7 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
     const uint64_t packs = p.cols / vec;
     if (packs > 1024ull * 8) return fail(THOR_B200_UNSUPPORTED, "rowprog_compile: rows of %llu elements do not fit one CTA's registers", static_cast<unsigned long long>(p.cols));
     const thor_b200_rowprog_tuning& tune = d->tuning;
-    TB_REQUIRE(tune.reserved == 0, "rowprog_compile: tuning.reserved must be zero");
+    TB_REQUIRE(tune.reserve_sms >= 0 && tune.reserve_sms <= 64, "rowprog_compile: tuning.reserve_sms must be between 0 and 64");
     TB_REQUIRE(tune.ring_buffers >= -2 && tune.ring_buffers != 1 && tune.ring_buffers != 2, "rowprog_compile: tuning.ring_buffers must be 0, -1, -2 or at least 3");
     const int vpt_target = 4;  // measured: 4 packs per thread beat 2 even with column accumulators in registers
     int team = 32;
@@ -1538,6 +1538,7 @@ int thor_b200_rowprog_compile(const thor_b200_rowprog_desc* d, thor_b200_rowprog
         int dev = 0, v = 0;
         if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sms = v;
         else (void)cudaGetLastError();
+        if (tune.reserve_sms < sms) sms -= tune.reserve_sms;
     }
     if (p.persistent) {
         // every extra CTA of a program with column reductions costs a [cols] fp32 partial row

@@ -379,7 +379,7 @@ class StampedExecutionPlan:
         return raw.view(to_torch(dt)).reshape(shape)
 
 
-ROW_PROGRAM_TUNING_FIELDS = ("ring_buffers", "pipeline_round_one", "copy_warpgroup", "keep_values", "reciprocal_division", "wait_limit_ms", "test_skip_fill")
+ROW_PROGRAM_TUNING_FIELDS = ("ring_buffers", "pipeline_round_one", "copy_warpgroup", "keep_values", "reciprocal_division", "wait_limit_ms", "test_skip_fill", "reserve_sms")
 
 
 class FusedEquation:

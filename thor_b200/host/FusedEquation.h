@@ -44,6 +44,7 @@ struct RowProgramTuning {
     int reciprocal_division = 0;
     int wait_limit_ms = 0;
     int test_skip_fill = 0;
+    int reserve_sms = 0;
 };
 
 struct FusedEquationOptions {

@@ -175,7 +175,7 @@ THB_API int thb_shape_op(const Expression* a, int op, const uint64_t* values, ui
 THB_API uint32_t thb_expr_node_count(const Expression* a) { return static_cast<uint32_t>(a->graph()->nodes.size()); }
 
 // ---- equations --------------------------------------------------------------------------------------
-// row_tuning: NULL or the seven RowProgramTuning fields in declaration order
+// row_tuning: NULL or the eight RowProgramTuning fields in declaration order
 THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint32_t n, int device, int fast_math, int fuse_rows, const int32_t* row_tuning,
                         int unrounded_column_sums, FusedEquation** out) {
     return guarded([&] {
@@ -186,7 +186,7 @@ THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint
         opt.fuse_row_reductions = fuse_rows != 0;
         opt.unrounded_column_sums = unrounded_column_sums != 0;
         if (row_tuning != nullptr)
-            opt.row_program = RowProgramTuning{row_tuning[0], row_tuning[1], row_tuning[2], row_tuning[3], row_tuning[4], row_tuning[5], row_tuning[6]};
+            opt.row_program = RowProgramTuning{row_tuning[0], row_tuning[1], row_tuning[2], row_tuning[3], row_tuning[4], row_tuning[5], row_tuning[6], row_tuning[7]};
         *out = new FusedEquation(FusedEquation::compile(Expression::outputs(named), device, opt));
     });
 }

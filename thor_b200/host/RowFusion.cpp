@@ -280,6 +280,7 @@ std::vector<RowFusionMatch> matchOutputs(const RowFusionContext& ctx) {
     d.tuning.reciprocal_division = ctx.tuning.reciprocal_division;
     d.tuning.wait_limit_ms = ctx.tuning.wait_limit_ms;
     d.tuning.test_skip_fill = ctx.tuning.test_skip_fill;
+    d.tuning.reserve_sms = ctx.tuning.reserve_sms;
     auto prog = std::make_shared<ProgHandle>();
     size_t ws_bytes = 1;
     const int status = thor_b200_rowprog_compile(&d, &prog->h, &ws_bytes);

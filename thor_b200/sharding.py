@@ -127,3 +127,70 @@ class Communicator:
             self.close()
         except Exception:
             pass
+
+
+class Combiner:
+    """Overlapped combine of a stepping job's partials (thor_b200_combiner_*): the statistics of step i cross the ranks on
+    the combiner's own high-priority stream while the kernel of step i + 1 runs.  The caller keeps `slots` copies of its
+    partial buffers and uses slot i % slots in step i: wait(slot) before the step's kernels, submit(slot, ...) after them."""
+
+    def __init__(self, comm: Communicator, slots: int = 2):
+        import ctypes as C
+
+        from . import _native
+
+        self._lib = _native.lib
+        L = self._lib
+        L.thor_b200_combiner_create.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]
+        L.thor_b200_combiner_wait.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.thor_b200_combiner_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_int]
+        L.thor_b200_combiner_drain.argtypes = [C.c_void_p, C.c_void_p]
+        L.thor_b200_combiner_stream.argtypes = [C.c_void_p]
+        L.thor_b200_combiner_stream.restype = C.c_void_p
+        L.thor_b200_combiner_destroy.argtypes = [C.c_void_p]
+        L.thor_b200_combiner_destroy.restype = None
+        self._comm = comm  # keeps the communicator alive
+        self._h = C.c_void_p()
+        _native.check(L.thor_b200_combiner_create(comm._h, slots, C.byref(self._h)))
+        self.stream = torch.cuda.ExternalStream(L.thor_b200_combiner_stream(self._h))
+
+    def wait(self, slot: int, stream=None) -> None:
+        from . import _native
+
+        _native.check(self._lib.thor_b200_combiner_wait(self._h, slot, _native.stream_handle(stream)))
+
+    def submit(self, slot: int, sums: Optional[torch.Tensor] = None, maxima: Optional[torch.Tensor] = None, minima: Optional[torch.Tensor] = None,
+               rounded_sums: Optional[torch.Tensor] = None, stream=None) -> None:
+        """Combine behind everything `stream` (default: the current stream) holds so far; rounded_sums, when given, receives
+        the combined sums converted to its dtype."""
+        from . import _native
+        from .dtypes import from_torch
+
+        def pair(t):
+            if t is None:
+                return None, 0
+            if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+                raise ValueError("partials are contiguous fp32 CUDA tensors")
+            return t.data_ptr(), t.numel()
+
+        if rounded_sums is not None and (sums is None or rounded_sums.numel() != sums.numel() or not rounded_sums.is_contiguous()):
+            raise ValueError("rounded_sums must be contiguous and hold as many elements as sums")
+        _native.check(self._lib.thor_b200_combiner_submit(self._h, slot, _native.stream_handle(stream), *pair(sums), *pair(maxima), *pair(minima),
+                                                          rounded_sums.data_ptr() if rounded_sums is not None else None,
+                                                          int(from_torch(rounded_sums.dtype)) if rounded_sums is not None else 0))
+
+    def drain(self, stream=None) -> None:
+        from . import _native
+
+        _native.check(self._lib.thor_b200_combiner_drain(self._h, _native.stream_handle(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.thor_b200_combiner_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
