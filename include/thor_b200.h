@@ -189,6 +189,11 @@ THOR_B200_API const char* thor_b200_expr_source(const thor_b200_expr* expr);
 /* "flat_v2", "flat_scalar", "bcast_tiled_v2", "bcast_tiled_scalar" or "bcast_generic": which kernel shape was chosen. */
 THOR_B200_API const char* thor_b200_expr_launch_kind(const thor_b200_expr* expr);
 THOR_B200_API void thor_b200_expr_destroy(thor_b200_expr* expr);
+/* The process-wide cache of compiled stages and row programs keeps the most recently used modules, at most `entries`
+ * (default 10 000, the bound of the reference's LRU caches, EquationCompiler.cpp:123-157; 0 turns caching off).  A module
+ * that leaves the cache is unloaded once the last handle that uses it is destroyed.  Returns the previous bound. */
+THOR_B200_API size_t thor_b200_jit_cache_capacity(size_t entries);
+THOR_B200_API size_t thor_b200_jit_cache_size(void);
 /* 16-bit stages evaluate exp and division with leaner routines than cuda_fp16.hpp's h2exp / __h2div, the
  * intrinsics the reference emits (CudaSourceEmitter.cpp:4376-4377).  This self-check runs both over every fp16
  * input (exp) and every ordered input pair in both lanes (division) and writes four counters to device
@@ -412,14 +417,14 @@ THOR_B200_API void thor_b200_rowprog_destroy(thor_b200_rowprog* prog);
  * arithmetic as thor_b200_reduce_launch for outer = inner = 1.  The scratch the two-phase reduction
  * needs is a fixed 256 KiB array inside the library instead of a caller workspace, so the call
  * performs no cudaMalloc / cudaFree and uses no allocating library routine.  It exists for callers
- * that have no point at which they could allocate: a step that is being captured into a CUDA graph,
- * a process that distributed all of its device memory at start-up, a latency-critical loop that must
- * not hit cudaMalloc's device-wide synchronisation.
+ * that have no point at which they could allocate: a process that distributed all of its device memory
+ * at start-up, a plug-in whose host application forbids it the allocator, a latency-critical loop that
+ * must not hit cudaMalloc's device-wide synchronisation.
  *
  * Limit: at most 65536 partials, i.e. n <= 65536 * 4096 * (16 / element size) elements (2^30 for fp32,
  * 2^31 for fp16 / bf16, 2^32 for fp8); larger inputs are rejected with THOR_B200_INVALID_ARGUMENT.
- * The first call on each device looks up the array's device address; make that first call outside
- * of any stream capture.  All calls on a device share the one array: two calls whose kernels can
+ * The first call on each device looks up the array's device address; make that first call before
+ * any stream capture begins, and do not use the entry point on a device after cudaDeviceReset.  All calls on a device share the one array: two calls whose kernels can
  * overlap on the GPU (different streams, no dependency) race on it and must be ordered by the caller.
  * ------------------------------------------------------------------------------------------- */
 THOR_B200_API int thor_b200_reduce_full_noalloc(int op, const void* input, int input_dtype, uint64_t n, void* output, int output_dtype,

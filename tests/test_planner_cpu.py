@@ -217,3 +217,26 @@ def test_constant_subtrees_become_one_literal_and_identities_compute_nothing():
     assert body.count(" * ") == 1 and body.count(" + ") == 2 and " / " not in body and " - " not in body
     row = ex.compile({"y": (x * 1.0 + 0.0) / x.reduce_sum([1])}).plan({"x": ((64, 512), DT.fp32)}).stage_sources()[0]
     assert "1.0f" not in row.split("row_kernel")[1] and "0.0f)" not in row.split("// outputs")[1]
+
+
+def test_the_compile_cache_is_bounded_and_evicts_the_least_recently_used():
+    """Compiled modules live in a process-wide LRU cache (10 000 entries like the reference's, EquationCompiler.cpp:123-157):
+    with the bound lowered, distinct stages push the oldest out and the count never exceeds the bound."""
+    import ctypes
+
+    from thor_b200 import _native
+
+    lib = _native.lib
+    lib.thor_b200_jit_cache_capacity.argtypes = [ctypes.c_size_t]
+    lib.thor_b200_jit_cache_capacity.restype = ctypes.c_size_t
+    lib.thor_b200_jit_cache_size.restype = ctypes.c_size_t
+    previous = lib.thor_b200_jit_cache_capacity(3)
+    try:
+        assert previous == 10000 and lib.thor_b200_jit_cache_size() <= 3
+        x = ex.input("x")
+        for k in range(6):  # six different stages
+            ex.compile(x * float(k + 2) + 0.5).plan({"x": ((4096,), DT.fp32)})
+            assert lib.thor_b200_jit_cache_size() <= 3
+        assert lib.thor_b200_jit_cache_size() == 3
+    finally:
+        lib.thor_b200_jit_cache_capacity(previous)

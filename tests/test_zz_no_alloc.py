@@ -1,7 +1,7 @@
 """The allocation-free full reduction (thor_b200_reduce_full_noalloc) against the planned reduction.
 
-Some users of this library never get a chance to allocate device memory: their step is recorded into a
-CUDA graph, or all device memory was handed out when the process started, or a cudaMalloc (which
+Some users of this library never get a chance to allocate device memory: all of it was handed out when the
+process started, or they run as a plug-in that may not call the allocator, or a cudaMalloc (which
 synchronises the device) is not acceptable inside their loop.  For them one entry point keeps its
 scratch in a fixed array inside the library.  This file is collected last on purpose, so that a failure
 here cannot hide the result of any other test in a stop-at-first-failure run.
@@ -49,6 +49,22 @@ def test_two_calls_in_a_row_match_the_planned_reduction(dtype):
                 assert torch.equal(got, want), op
             else:
                 assert torch.allclose(got, want, rtol=1e-5, atol=1e-6), (op, float(got), float(want))
+
+
+@pytest.mark.parametrize("n", [1000, (1 << 21) + 17, 1 << 24])
+def test_against_an_independent_fp64_sum_and_torch_extremes(n):
+    """Not the library against itself: float64 sums and torch's own max / min of the same values, including an fp8 input
+    (converted to fp32 per element, accumulated in fp32 like the reduction seam) and sizes on both sides of the point
+    where the two-phase form needs its fold."""
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(n, device="cuda", generator=gen) + 0.01
+    for t in (x, x.bfloat16(), x.to(torch.float8_e4m3fn)):
+        wide = t.double() if t.dtype != torch.float8_e4m3fn else t.float().double()
+        got = float(_noalloc(CubReductionOp.Sum, t))
+        assert abs(got - float(wide.sum())) <= 1e-5 * abs(float(wide.sum())) + 2e-7 * float(wide.abs().sum())
+        assert float(_noalloc(CubReductionOp.Max, t)) == float(wide.max()) and float(_noalloc(CubReductionOp.Min, t)) == float(wide.min())
+        want_l2 = float(wide.pow(2).sum().sqrt())
+        assert abs(float(_noalloc(CubReductionOp.L2Norm, t)) - want_l2) <= 1e-5 * want_l2
 
 
 def test_small_input_and_output_scale_and_dtype():

@@ -7,6 +7,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <list>
 #include <memory>
 #include <mutex>
 #include <unordered_map>
@@ -104,8 +105,18 @@ int loadNvrtc(Nvrtc** out) {
     return THOR_B200_OK;
 }
 
-std::mutex g_cache_mutex;
-std::unordered_map<std::string, std::shared_ptr<jit::Module>> g_cache;  // key: fast-math flag + source
+// Least-recently-used cache of compiled modules, key: fast-math flag + source.  Heap-allocated and never destroyed: at
+// process exit no module destructor runs against a CUDA runtime that is already shutting down.
+struct ModuleCache {
+    std::mutex mutex;
+    size_t capacity = 10000;
+    std::list<std::string> order;  // most recently used first
+    std::unordered_map<std::string, std::pair<std::shared_ptr<jit::Module>, std::list<std::string>::iterator>> entries;
+};
+ModuleCache& cache() {
+    static ModuleCache* c = new ModuleCache();
+    return *c;
+}
 
 }  // namespace
 }  // namespace tb::expr
@@ -115,11 +126,13 @@ using namespace tb::expr;
 
 int compileSource(const std::string& source, bool fast_math, const char* kernel_name, std::shared_ptr<Module>* out) {
     const std::string key = (fast_math ? "F" : "P") + source;
+    ModuleCache& mc = cache();
     {
-        std::lock_guard<std::mutex> lock(g_cache_mutex);
-        auto it = g_cache.find(key);
-        if (it != g_cache.end()) {
-            *out = it->second;
+        std::lock_guard<std::mutex> lock(mc.mutex);
+        auto it = mc.entries.find(key);
+        if (it != mc.entries.end()) {
+            mc.order.splice(mc.order.begin(), mc.order, it->second.second);
+            *out = it->second.first;
             return THOR_B200_OK;
         }
     }
@@ -153,25 +166,64 @@ int compileSource(const std::string& source, bool fast_math, const char* kernel_
     }
     rt->destroyProgram(&prog);
     if (r != NVRTC_SUCCESS || mod->cubin.empty()) return fail(THOR_B200_JIT_ERROR, "nvrtcGetCUBIN: %s", rt->errorString(r));
+    std::vector<std::shared_ptr<Module>> evicted;  // released after the lock: unloading a library is slow
     {
-        std::lock_guard<std::mutex> lock(g_cache_mutex);
-        auto ins = g_cache.emplace(key, mod);
-        *out = ins.first->second;
+        std::lock_guard<std::mutex> lock(mc.mutex);
+        auto it = mc.entries.find(key);
+        if (it != mc.entries.end()) {  // another thread compiled the same source meanwhile: share its module
+            *out = it->second.first;
+            return THOR_B200_OK;
+        }
+        *out = mod;
+        if (mc.capacity > 0) {
+            mc.order.push_front(key);
+            mc.entries.emplace(key, std::make_pair(mod, mc.order.begin()));
+            while (mc.entries.size() > mc.capacity) {
+                auto victim = mc.entries.find(mc.order.back());
+                evicted.push_back(victim->second.first);
+                mc.entries.erase(victim);
+                mc.order.pop_back();
+            }
+        }
     }
     return THOR_B200_OK;
 }
 
+size_t setCacheCapacity(size_t entries) {
+    ModuleCache& mc = cache();
+    std::vector<std::shared_ptr<Module>> evicted;
+    std::lock_guard<std::mutex> lock(mc.mutex);
+    const size_t before = mc.capacity;
+    mc.capacity = entries;
+    while (mc.entries.size() > mc.capacity) {
+        auto victim = mc.entries.find(mc.order.back());
+        evicted.push_back(victim->second.first);
+        mc.entries.erase(victim);
+        mc.order.pop_back();
+    }
+    return before;
+}
+size_t cacheSize() {
+    ModuleCache& mc = cache();
+    std::lock_guard<std::mutex> lock(mc.mutex);
+    return mc.entries.size();
+}
+
+Module::~Module() {
+    if (library != nullptr) (void)cudaLibraryUnload(library);
+}
+
 int ensureLoaded(Module& m) {
-    if (m.kernel) return THOR_B200_OK;
+    if (m.kernel.load(std::memory_order_acquire) != nullptr) return THOR_B200_OK;
     std::lock_guard<std::mutex> lock(m.load_mutex);
-    if (m.kernel) return THOR_B200_OK;
+    if (m.kernel.load(std::memory_order_relaxed) != nullptr) return THOR_B200_OK;
     TB_CUDA(cudaFree(nullptr));  // make sure the primary context exists
     cudaLibrary_t lib = nullptr;
     TB_CUDA(cudaLibraryLoadData(&lib, m.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
     cudaKernel_t k = nullptr;
     TB_CUDA(cudaLibraryGetKernel(&k, lib, m.kernel_name.c_str()));
     m.library = lib;
-    m.kernel = k;
+    m.kernel.store(k, std::memory_order_release);
     return THOR_B200_OK;
 }
 
@@ -258,7 +310,7 @@ int launchVariant(const thor_b200_expr& e, const Variant& v, const void* const* 
             grid.x = static_cast<unsigned>(blocks == 0 ? 1 : blocks);
         } break;
     }
-    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(m.kernel), grid, block, args, 0, stream));
+    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(m.kernel.load()), grid, block, args, 0, stream));
     countLaunch();
     return THOR_B200_OK;
 }
@@ -385,7 +437,7 @@ int thor_b200_selfcheck_pair_math(unsigned long long* device_counters, void* str
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     TB_CUDA(cudaMemsetAsync(device_counters, 0, 4 * sizeof(unsigned long long), stream));
     void* args[] = {&device_counters};
-    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(mod->kernel), dim3(65536), dim3(256), args, 0, stream));
+    TB_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(mod->kernel.load()), dim3(65536), dim3(256), args, 0, stream));
     countLaunch();
     return THOR_B200_OK;
 }
@@ -395,5 +447,8 @@ const char* thor_b200_expr_source(const thor_b200_expr* e) { return e ? e->fast.
 const char* thor_b200_expr_launch_kind(const thor_b200_expr* e) { return e ? tb::expr::kindName(e->fast.em.kind) : ""; }
 
 void thor_b200_expr_destroy(thor_b200_expr* e) { delete e; }
+
+size_t thor_b200_jit_cache_capacity(size_t entries) { return tb::jit::setCacheCapacity(entries); }
+size_t thor_b200_jit_cache_size(void) { return tb::jit::cacheSize(); }
 
 }  // extern "C"

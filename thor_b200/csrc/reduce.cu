@@ -480,10 +480,10 @@ void thor_b200_reduce_plan_destroy(thor_b200_reduce_plan* p) { delete p; }
 // Full reduction without any allocation by anybody.
 //
 // thor_b200_reduce_launch needs a workspace that somebody allocated beforehand.  Some callers have no
-// such moment: code that is being recorded into a CUDA graph (cudaMalloc is illegal while a stream
-// is capturing), code that runs under a fixed device-memory budget where every byte was handed out
-// at start-up, and code on a latency-critical path where cudaMalloc's implicit device
-// synchronisation is not acceptable.  For them the per-CTA partials of the two-phase full reduction
+// such moment: code that runs under a fixed device-memory budget where every byte was handed out at
+// start-up, a plug-in that its host application does not allow to call the allocator, and code on a
+// latency-critical path where cudaMalloc's implicit device synchronisation is not acceptable.  For
+// them the per-CTA partials of the two-phase full reduction
 // live in the fixed array below, which is part of the library image: every GPU that loads the
 // library carries these 256 KiB until the process exits.
 // ---------------------------------------------------------------------------------------------------
@@ -495,7 +495,9 @@ static __device__ __align__(256) float g_noalloc_partials[kNoAllocMaxPartials];
 
 // Device address of g_noalloc_partials per device ordinal.  In host code the array's name is only a
 // handle for the runtime, never a pointer a kernel could use, so the address is looked up once per
-// device with cudaGetSymbolAddress while that device is current.
+// device with cudaGetSymbolAddress while that device is current (the first call on a device does this;
+// make it before any stream capture begins).  The cached address belongs to the device's context: a
+// process that calls cudaDeviceReset must not use this entry point on that device afterwards.
 std::mutex g_noalloc_mutex;
 float* g_noalloc_ptr[64] = {};
 

@@ -1615,11 +1615,11 @@ int thor_b200_rowprog_launch_sharded(thor_b200_rowprog* h, const void* const* in
         int dev = 0;
         TB_CUDA(cudaGetDevice(&dev));
         if (!h->smem_opted_in[dev & 63]) {
-            TB_CUDA(cudaKernelSetAttributeForDevice(h->module->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem_bytes), dev));
+            TB_CUDA(cudaKernelSetAttributeForDevice(h->module->kernel.load(), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem_bytes), dev));
             h->smem_opted_in[dev & 63] = true;
         }
     }
-    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(h->module->kernel), dim3(p.grid), dim3(static_cast<unsigned>(p.cta + (p.ring_stages > 0 && p.producer ? 128 : 0))), args, p.smem_bytes, stream));
+    TB_CUDA(launchDependentC(reinterpret_cast<const void*>(h->module->kernel.load()), dim3(p.grid), dim3(static_cast<unsigned>(p.cta + (p.ring_stages > 0 && p.producer ? 128 : 0))), args, p.smem_bytes, stream));
     countLaunch();
     if (!p.all_reduces.empty()) {
         size_t idx = 0;
@@ -1676,7 +1676,7 @@ uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) {
 int thor_b200_rowprog_waits_expired(thor_b200_rowprog* h, uint32_t* count) {
     TB_REQUIRE(h != nullptr && count != nullptr, "rowprog_waits_expired: null argument");
     *count = 0;
-    if (h->prog.ring_stages == 0 || !h->module || h->module->library == nullptr) return THOR_B200_OK;
+    if (h->prog.ring_stages == 0 || !h->module || h->module->kernel.load(std::memory_order_acquire) == nullptr) return THOR_B200_OK;  // never loaded
     void* flag = nullptr;
     size_t bytes = 0;
     TB_CUDA(cudaLibraryGetGlobal(&flag, &bytes, h->module->library, "tb_wait_expired"));
