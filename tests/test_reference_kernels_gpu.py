@@ -39,8 +39,8 @@ PROGRAMS = [
     ("erf_expm1", "in:x erf in:z lit:0.5 mul expm1 sub", {}),
     # constant subtrees (folded in double to one float literal) and identities (x + 0, x * 1, x / 1 compute nothing):
     # CudaSourceEmitter.cpp:1965-2076, 3745-3782 -- in 16-bit stages a per-node evaluation would round differently
-    ("const_fold", "in:x lit:0.1 lit:3 mul mul lit:1 lit:3 div add lit:0.7 neg in:z mul sub", {}),
-    ("identities", "in:x lit:0 add lit:1 mul in:z lit:2 lit:1 sub div sub lit:0 in:a add add", {}),
+    ("const_fold", "in:x lit:0.1 lit:3 mul mul in:z lit:0.7 neg lit:3 div mul mul", {}),  # products only: no fused multiply-add to place differently
+    ("identities", "in:x lit:0 add lit:1 mul in:z lit:2 lit:1 sub div mul lit:0 in:a add mul", {}),
 ]
 
 
