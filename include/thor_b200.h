@@ -82,6 +82,17 @@ THOR_B200_API uint64_t thor_b200_launch_count(void);
  * ------------------------------------------------------------------------------------------- */
 THOR_B200_API int thor_b200_cast_launch(const void* src, void* dst, int src_dtype, int dst_dtype, int64_t n, void* stream);
 
+/* Copy with an optional dtype change between placements: the data path of Tensor::copyFromAsync
+ * (DeepLearning/Implementation/Tensor/Tensor.cpp:769-792, 842-851).  A device of -1 means host memory (pinned for a truly
+ * asynchronous copy), otherwise a GPU ordinal; the destination's GPU is current and owns `stream`.  Same dtype: one
+ * copy.  Same GPU, different dtypes: thor_b200_cast_launch.  Different placements and dtypes: the bytes travel in the
+ * SOURCE dtype into the destination buffer and are converted there in place (one more launch), which requires the
+ * destination array to be at least as large as the source's -- the reference refuses the shrinking case too because it
+ * would need a hidden temporary (THOR_B200_INVALID_ARGUMENT).  Conversions INTO host memory are CPU work and are not
+ * done here (THOR_B200_UNSUPPORTED). */
+THOR_B200_API int thor_b200_copy_convert_launch(void* dst, int dst_dtype, int dst_device, const void* src, int src_dtype, int src_device, int64_t n,
+                                                void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * S3  fused elementwise / broadcast expression stage
  * Replaces EquationCompiler::compileFusedStage / compileSpecializedBroadcastStage

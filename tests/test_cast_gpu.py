@@ -183,3 +183,55 @@ def test_unaligned_views_use_the_scalar_path():
     TypeConverter.convert_type_raw(d.data_ptr() + 4, out.data_ptr() + 2, DataType.fp32, DataType.fp16, 4999)
     torch.cuda.synchronize()
     assert np.array_equal(out[1:5000].cpu().numpy().view(np.uint16), o.cast(x[1:], o.FP32, o.FP16).view(np.uint16))
+
+
+def test_in_place_resize_is_one_launch_and_matches_out_of_place_at_the_configured_size():
+    """Same-address fp32 -> fp16 of 2^24 elements (and back up): one cooperative launch that walks the buffer in waves,
+    instead of a chain of log(n) passes; bit-identical to the out-of-place cast."""
+    import thor_b200
+    from thor_b200.workloads import cast_input
+
+    n = (1 << 24) + 3
+    x = torch.from_numpy(cast_input(n, seed=3)).cuda()
+    want = torch.empty(n, dtype=torch.float16, device="cuda")
+    TypeConverter.convert_type(x, want)
+    buf = x.clone()
+    before = thor_b200.launch_count()
+    TypeConverter.convert_type_raw(buf.data_ptr(), buf.data_ptr(), DataType.fp32, DataType.fp16, n)
+    torch.cuda.synchronize()
+    assert thor_b200.launch_count() - before == 1
+    assert torch.equal(buf.view(torch.float16)[:n].view(torch.int16), want.view(torch.int16))
+    # and up again, in place, from the narrow view at the start of the same buffer
+    widened_want = want.float()
+    before = thor_b200.launch_count()
+    TypeConverter.convert_type_raw(buf.data_ptr(), buf.data_ptr(), DataType.fp16, DataType.fp32, n)
+    torch.cuda.synchronize()
+    assert thor_b200.launch_count() - before == 1
+    assert torch.equal(buf.view(torch.int32), widened_want.view(torch.int32))
+
+
+def test_copy_from_host_with_a_wider_destination_dtype_converts_in_place_on_the_gpu():
+    """Tensor::copyFromAsync across placements (Tensor.cpp:769-792): fp16 host values into an fp32 device tensor travel as
+    fp16 and are widened where they land; the shrinking direction is refused, as in the reference."""
+    from thor_b200.type_converter import tensor_copy_from
+
+    n = (1 << 20) + 7
+    host = torch.randn(n).half().pin_memory()
+    dev = torch.empty(n, dtype=torch.float32, device="cuda")
+    tensor_copy_from(dev, host)
+    torch.cuda.synchronize()
+    assert torch.equal(dev.cpu(), host.float())
+    same = torch.empty(n, dtype=torch.float16, device="cuda")
+    tensor_copy_from(same, host)  # same dtype: a plain upload
+    back = torch.empty(n, dtype=torch.float16).pin_memory()
+    tensor_copy_from(back, same)  # and a plain download
+    torch.cuda.synchronize()
+    assert torch.equal(back, host)
+    on_gpu = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    tensor_copy_from(on_gpu, dev)  # same GPU, different dtypes: the cast seam
+    torch.cuda.synchronize()
+    assert torch.equal(on_gpu, dev.bfloat16())
+    with pytest.raises(Exception, match="hidden temporary"):
+        tensor_copy_from(torch.empty(n, dtype=torch.float16, device="cuda"), torch.randn(n).pin_memory())
+    with pytest.raises(Exception, match="CPU"):
+        tensor_copy_from(torch.empty(n, dtype=torch.float32).pin_memory(), same)

@@ -7,6 +7,8 @@
 // for this access pattern (6.7-6.8 TB/s against 6.0-6.2 TB/s at 1.5 GB of traffic), so the grid
 // is sized to the tensor.  The last n % P elements are converted one by one by the first CTA,
 // which means the kernel touches exactly n elements on both sides.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace tb {
@@ -142,8 +144,78 @@ __global__ void __launch_bounds__(256) castInPlaceHeadKernel(void* buf, int coun
     }
 }
 
+// Same-address conversion between element sizes in ONE launch.  All CTAs of the grid are resident together (cooperative
+// launch) and walk the buffer in waves of gridDim.x * 256 * UW packs: every thread reads its packs of the wave into
+// registers, the grid meets at a barrier, every thread writes.  Waves go upwards when the elements shrink and downwards
+// when they grow, so the bytes a wave writes hold only values that this or an earlier wave has already read, and the
+// next wave's reads never touch bytes that a straggler of this wave still writes: one barrier per wave is enough
+// (4 waves for 2^24 fp32 -> fp16 on 148 SMs).  The last, partial pack is moved element by element by its thread.
+template <class F, class T, int P, int UW>
+__global__ void __launch_bounds__(256) castInPlaceWavesKernel(void* buf, int64_t n) {
+    namespace cg = cooperative_groups;
+    cg::grid_group grid = cg::this_grid();
+    const int64_t threads = static_cast<int64_t>(gridDim.x) * 256, tid = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    const int64_t packs = (n + P - 1) / P, wave_packs = threads * UW, waves = (packs + wave_packs - 1) / wave_packs;
+    const F* src = static_cast<const F*>(buf);
+    T* dst = static_cast<T*>(buf);
+    for (int64_t w = 0; w < waves; ++w) {
+        const int64_t wave = sizeof(F) > sizeof(T) ? w : waves - 1 - w;
+        Pack<P * sizeof(F)> in[UW];
+#pragma unroll
+        for (int u = 0; u < UW; ++u) {
+            const int64_t p = wave * wave_packs + static_cast<int64_t>(u) * threads + tid;
+            if (p >= packs) continue;
+            if ((p + 1) * P <= n) {
+                loadPack<P * sizeof(F), false>(in[u], src + p * P);
+            } else {
+                for (int e = 0; e < P; ++e)
+                    if (p * P + e < n) reinterpret_cast<F*>(&in[u])[e] = src[p * P + e];
+            }
+        }
+        grid.sync();
+#pragma unroll
+        for (int u = 0; u < UW; ++u) {
+            const int64_t p = wave * wave_packs + static_cast<int64_t>(u) * threads + tid;
+            if (p >= packs) continue;
+            Pack<P * sizeof(T)> out;
+#pragma unroll
+            for (int e = 0; e < P; ++e) reinterpret_cast<T*>(&out)[e] = Cvt<F, T>::run(reinterpret_cast<const F*>(&in[u])[e]);
+            if ((p + 1) * P <= n) {
+                storePack(dst + p * P, out);
+            } else {
+                for (int e = 0; e < P; ++e)
+                    if (p * P + e < n) dst[p * P + e] = reinterpret_cast<const T*>(&out)[e];
+            }
+        }
+    }
+}
+
 template <class F, class T>
 int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream);
+
+// Grid of the wave kernel: as many CTAs as are resident at once, but no more than one wave needs.
+template <class F, class T>
+int launchInPlaceWaves(void* buf, int64_t n, cudaStream_t stream) {
+    using G = CastGeom<F, T>;
+    constexpr int P = G::P, UW = 2;
+    const DeviceInfo* dev = nullptr;
+    if (int st = currentDeviceInfo(&dev)) return st;
+    static int per_sm = 0;  // the same for every device this library supports (one architecture)
+    if (per_sm == 0) {
+        int v = 0;
+        TB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, castInPlaceWavesKernel<F, T, P, UW>, 256, 0));
+        TB_REQUIRE(v > 0, "in-place cast: the wave kernel does not fit an SM");
+        per_sm = v;
+    }
+    const int64_t packs = (n + P - 1) / P;
+    int64_t blocks = (packs + 256 * UW - 1) / (256 * UW);
+    const int64_t resident = static_cast<int64_t>(dev->sm_count) * per_sm;
+    blocks = blocks < 1 ? 1 : (blocks > resident ? resident : blocks);
+    void* args[] = {&buf, &n};
+    TB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(castInPlaceWavesKernel<F, T, P, UW>), dim3(static_cast<unsigned>(blocks)), dim3(256), args, 0, stream));
+    countLaunch();
+    return THOR_B200_OK;
+}
 
 // Same-address conversion between element sizes (element i of the source view becomes element i of
 // the destination view; TypeConverterKernels.cu:846-904 has the reference's semantics).  The range
@@ -208,6 +280,9 @@ int launchCast(const void* src_v, void* dst_v, int64_t n, cudaStream_t stream) {
             TB_CUDA(cudaGetLastError());
             return THOR_B200_OK;
         } else {
+            // one cooperative launch when the buffer allows 16-byte packs (every allocation does); a foreign sub-view
+            // that is not aligned takes the chain of out-of-place passes
+            if (isAligned(dst_v, 16)) return launchInPlaceWaves<F, T>(dst_v, n, stream);
             return launchInPlaceResize<F, T>(dst_v, n, stream);
         }
     }
@@ -300,4 +375,35 @@ extern "C" int thor_b200_cast_launch(const void* src, void* dst, int src_dtype, 
     }
 #undef TB_SRC
     return fail(THOR_B200_INVALID_ARGUMENT, "cast: unsupported source dtype %d", src_dtype);
+}
+
+// Tensor::copyFromAsync across placements with a dtype change (Tensor.cpp:769-792, 842-851): the bytes travel in the
+// SOURCE dtype into the destination buffer, which is then converted where it lies.  Only destinations whose array is
+// at least as large as the source's are accepted, as in the reference: shrinking would need a hidden temporary.
+extern "C" int thor_b200_copy_convert_launch(void* dst, int dst_dtype, int dst_device, const void* src, int src_dtype, int src_device, int64_t n,
+                                             void* stream_v) {
+    using namespace tb;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    TB_REQUIRE(n >= 0, "copy_convert: numElements must be >= 0 (got %lld)", static_cast<long long>(n));
+    const size_t ss = dtypeSize(src_dtype), ds = dtypeSize(dst_dtype);
+    TB_REQUIRE(ss != 0 && ds != 0, "copy_convert: unknown dtype (%d -> %d)", src_dtype, dst_dtype);
+    if (n == 0) return THOR_B200_OK;
+    TB_REQUIRE(dst != nullptr && src != nullptr, "copy_convert: null pointer");
+    TB_REQUIRE(dst_device >= -1 && src_device >= -1, "copy_convert: a device is -1 (host memory) or a GPU ordinal");
+    const bool same_place = dst_device == src_device;
+    if (dst_device < 0 && (src_device < 0 || src_dtype != dst_dtype))
+        return fail(THOR_B200_UNSUPPORTED, "copy_convert: conversions into host memory run on the CPU, which this library does not do");
+    if (src_dtype == dst_dtype) {
+        const size_t bytes = static_cast<size_t>(n) * ss;
+        if (dst_device >= 0 && src_device >= 0 && !same_place) TB_CUDA(cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, stream));
+        else TB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, stream));
+        return THOR_B200_OK;
+    }
+    if (same_place) return thor_b200_cast_launch(src, dst, src_dtype, dst_dtype, n, stream_v);  // on one GPU: the cast seam, possibly in place
+    TB_REQUIRE(ss <= ds, "copy_convert: a copy across placements into a smaller dtype (%s -> %s) would need a hidden temporary; stage it explicitly",
+               dtypeName(src_dtype), dtypeName(dst_dtype));
+    const size_t bytes = static_cast<size_t>(n) * ss;
+    if (src_device >= 0) TB_CUDA(cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, stream));
+    else TB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream));
+    return thor_b200_cast_launch(dst, dst, src_dtype, dst_dtype, n, stream_v);
 }

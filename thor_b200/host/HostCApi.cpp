@@ -367,6 +367,14 @@ THB_API uint64_t thb_cub_reduction_workspace_bytes(StampedCubReduction* s) { ret
 THB_API void thb_cub_reduction_free(StampedCubReduction* s) { delete s; }
 THB_API float thb_cub_empty_value(int op) { return CubReduction::getFp32EmptyReductionValue(static_cast<CubReductionOp>(op)); }
 
+// Tensor::copyFromAsync between two bound tensors; device -1 = pinned host memory.
+THB_API int thb_tensor_copy_from(const thb_binding* dst, int dst_device, const thb_binding* src, int src_device, void* stream) {
+    return guarded([&] {
+        Tensor d = Tensor::wrap(dst->ptr, static_cast<DataType>(dst->dtype), std::vector<uint64_t>(dst->dims, dst->dims + dst->rank), dst_device);
+        Tensor s = Tensor::wrap(src->ptr, static_cast<DataType>(src->dtype), std::vector<uint64_t>(src->dims, src->dims + src->rank), src_device);
+        d.copyFromAsync(s, Stream(stream, dst_device >= 0 ? dst_device : src_device));
+    });
+}
 THB_API int thb_type_convert(void* src, void* dst, int src_dtype, int dst_dtype, long n, void* stream, int device) {
     return guarded([&] { TypeConverter::convertType(src, dst, static_cast<DataType>(src_dtype), static_cast<DataType>(dst_dtype), n, Stream(stream, device)); });
 }

@@ -43,4 +43,14 @@ Tensor Tensor::allocate(DataType dtype, std::vector<uint64_t> dims, int gpu_num)
     return t;
 }
 
+void Tensor::copyFromAsync(const Tensor& source, const Stream& stream) {
+    if (!isInitialized() || !source.isInitialized()) throw std::logic_error("Tensor::copyFromAsync: uninitialised tensor");
+    if (source.getTotalNumElements() != getTotalNumElements()) throw std::logic_error("Tensor::copyFromAsync: total number of elements does not match");
+    if (gpu_num_ >= 0 && gpu_num_ != stream.getGpuNum()) throw std::logic_error("Tensor::copyFromAsync: the stream belongs to another GPU than the destination");
+    const int status = thor_b200_copy_convert_launch(ptr_, static_cast<int>(dtype_), gpu_num_, source.ptr_, static_cast<int>(source.dtype_), source.gpu_num_,
+                                                     static_cast<int64_t>(getTotalNumElements()), stream.handle);
+    if (status == THOR_B200_INVALID_ARGUMENT || status == THOR_B200_UNSUPPORTED) throw std::logic_error(std::string("Tensor::copyFromAsync: ") + thor_b200_last_error());
+    if (status != THOR_B200_OK) throw std::runtime_error(std::string("Tensor::copyFromAsync: ") + thor_b200_last_error());
+}
+
 }  // namespace ThorB200

@@ -35,6 +35,13 @@ class Tensor {
     static void setPlanOnly(bool on);
     static bool planOnly();
 
+    // Host (pinned) memory owned by the caller: gpu_num is -1.
+    static Tensor wrapHost(void* host_ptr, DataType dtype, std::vector<uint64_t> dims) { return wrap(host_ptr, dtype, std::move(dims), -1); }
+    // Tensor::copyFromAsync (Tensor.cpp:700-860) for dense tensors: same element count; a dtype change across placements
+    // copies in the source dtype and converts in place on the destination GPU, and is refused when the destination
+    // dtype is the smaller one; conversions into host memory are refused (no CPU path here).
+    void copyFromAsync(const Tensor& source, const Stream& stream);
+
     bool isInitialized() const { return ptr_ != nullptr; }
     void* getMemPtr() const { return ptr_; }
     DataType getDataType() const { return dtype_; }

@@ -33,3 +33,33 @@ class TypeConverter:
         with torch.cuda.device(src.device):
             TypeConverter.convert_type_raw(src.data_ptr(), dst.data_ptr(), sd, dd, src.numel(), stream)
         return dst
+
+
+def tensor_copy_from(dst: torch.Tensor, src: torch.Tensor, dst_dtype: DataType | None = None, src_dtype: DataType | None = None, stream=None) -> torch.Tensor:
+    """Tensor::copyFromAsync of the reference (Tensor.cpp:700-860) through the host layer: `dst` and `src` hold the same
+    number of elements; either may be a pinned host tensor.  A dtype change across placements copies in the source dtype
+    and converts in place on the destination GPU (refused when the destination dtype is the smaller one, like the
+    reference; conversions into host memory are refused because this library has no CPU path).  Pass dtypes explicitly for
+    raw storage (a bf16 tensor whose first half holds fp8 bytes and the like)."""
+    import ctypes as C
+
+    from .expression import _Binding, _check, _host
+
+    def bind(t, dt):
+        b = _Binding()
+        b.name = b"t"
+        b.ptr = t.data_ptr()
+        b.dtype = int(dt if dt is not None else from_torch(t.dtype))
+        b.rank = 1
+        b.dims[0] = t.numel()
+        b.is_scalar = 0
+        return b
+
+    if not (dst.is_contiguous() and src.is_contiguous()):
+        raise _native.ThorB200InvalidArgument("tensor_copy_from: tensors must be contiguous")
+    device = lambda t: t.device.index if t.is_cuda else -1
+    d, s = bind(dst, dst_dtype), bind(src, src_dtype)
+    on = dst.device if dst.is_cuda else src.device
+    with torch.cuda.device(on):
+        _check(_host.thb_tensor_copy_from(C.byref(d), device(dst), C.byref(s), device(src), _native.stream_handle(stream)))
+    return dst
