@@ -290,7 +290,9 @@ THOR_B200_API void thor_b200_argreduce_plan_destroy(thor_b200_argreduce_plan* pl
  * Reductions over axes that are not adjacent (the reference's StridedFixedSegment path:
  * CubReductionOperation.cuh:2946-2958, 3038-3050; index map CubReductionIndexing.cuh:33-53;
  * arg variant CubArgReductionOperation.cuh:1119-1178).  input is a dense row-major tensor of
- * `rank` dims; output is dense over the kept axes in their order.  Stateless: no plan, no
+ * `rank` dims or, with has_strides, any strided view of storage (permuted, gapped, broadcast: the
+ * reference never materialises a view to regain a dense path, CubReduction.cpp:903-907); output is
+ * dense over the kept axes in their order.  Stateless: no plan, no
  * workspace, one kernel, the same numeric rules as the planned reductions (fp32 accumulation in
  * a fixed order, NaN-propagating min / max; arg: NaN wins, lowest flattened index of the reduced
  * axes in row-major order among equals).  Geometries that reduce one adjacent block of axes are
@@ -302,9 +304,11 @@ typedef struct thor_b200_strided_reduce_desc {
     int32_t input_dtype;  /* fp8 / fp16 / bf16 / fp32 */
     int32_t output_dtype; /* value reductions: fp8 / fp16 / bf16 / fp32; arg reductions: uint32 or uint64 */
     uint32_t rank;        /* 1..8 */
-    uint32_t reserved;
+    uint32_t has_strides; /* 0: the input is dense row-major; 1: `strides` describes a view (Tensor::aliasView, Tensor.h:146-152) */
     uint64_t dims[THOR_B200_MAX_RANK];
     uint8_t reduced[THOR_B200_MAX_RANK]; /* 1 = the axis is reduced */
+    uint64_t strides[THOR_B200_MAX_RANK]; /* element strides of the view: any values, 0 (broadcast) and overlapping included;
+                                           * `input` points at the view's first element */
 } thor_b200_strided_reduce_desc;
 
 THOR_B200_API int thor_b200_strided_reduce_launch(const thor_b200_strided_reduce_desc* desc, const void* input, void* output, float output_scale,

@@ -104,3 +104,54 @@ def test_expression_reduction_over_non_adjacent_axes_runs_the_strided_stage():
     np.testing.assert_allclose(plan.output("s").double().cpu().numpy(), want, rtol=1e-5, atol=1e-4)
     moved = x.cpu().numpy().transpose(1, 3, 0, 2).reshape(40, 64, -1)
     assert np.array_equal(plan.output("a").cpu().numpy().reshape(40, 64), moved.argmax(axis=-1).astype(np.uint32))
+
+
+CubReductionOp = Op
+
+
+# ---- views of storage: stamped as they are, nothing is materialised (CubReduction.cpp:868-907) ------------------------
+def _view_cases():
+    g = torch.Generator(device="cuda").manual_seed(21)
+    dense = torch.randn(7, 5, 32, device="cuda", generator=g)               # physical [I, J, K]
+    big = torch.randn(40, 48, 64, device="cuda", generator=g)
+    return [
+        ("permuted_inner_outer", dense.permute(2, 0, 1), [2], "cols"),       # logical [K, I, J], reduce J: output [K, I] written rotated
+        ("permuted_natural", dense.permute(1, 0, 2), [0], "cols"),           # logical [J, I, K], reduce J: output [I, K] in physical order
+        ("permuted_large", big.permute(2, 0, 1), [2], "cols"),
+        ("one_physical_block", torch.randn(2, 3, 5, 7, device="cuda", generator=g).permute(1, 0, 2, 3), [0, 2], "cols"),
+        ("gapped", big[:, ::2, ::3], [1], None),
+        ("broadcast", torch.randn(1, 48, 64, device="cuda", generator=g).expand(40, 48, 64), [2], None),
+        ("split_block", torch.randn(2, 3, 5, 7, device="cuda", generator=g).permute(1, 2, 0, 3), [1, 2], None),
+        ("diagonal", torch.randn(33, 33, device="cuda", generator=g).diagonal(), [0], None),
+        ("offset_view", big[3:, 1:, :].permute(2, 0, 1), [2], None),
+    ]
+
+
+@pytest.mark.parametrize("op,torch_fn", [(CubReductionOp.Sum, torch.sum), (CubReductionOp.Max, torch.amax), (CubReductionOp.Mean, torch.mean)])
+def test_views_reduce_without_a_copy_and_match_torch(op, torch_fn):
+    for name, view, axes, kind in _view_cases():
+        assert not view.is_contiguous() or view.dim() == 1
+        plan = CubReduction(op, axes, DataType.fp32).stamp(view)
+        plan.run()
+        torch.cuda.synchronize()
+        want = torch_fn(view.double(), dim=axes, keepdim=True).float()
+        assert plan.output.shape == want.shape, name
+        if op == CubReductionOp.Max:
+            assert torch.equal(plan.output, want), name
+        else:
+            assert torch.allclose(plan.output, want, rtol=1e-5, atol=1e-5), (name, float((plan.output - want).abs().max()))
+        if kind is not None:  # dense permutations whose reduced axes are one physical block keep the dense tiled kernels
+            assert plan.kernel_kind().startswith(kind), (name, plan.kernel_kind())
+        else:
+            assert plan.kernel_kind() == "strided", (name, plan.kernel_kind())
+
+
+def test_a_bf16_permuted_view_writes_its_rotated_output_in_the_requested_dtype():
+    x = torch.randn(64, 96, 256, device="cuda").bfloat16()
+    view = x.permute(2, 0, 1)  # [256, 64, 96] over dense [64, 96, 256]
+    plan = CubReduction(CubReductionOp.Sum, [2], DataType.bf16).stamp(view)
+    plan.run()
+    torch.cuda.synchronize()
+    want = view.float().sum(dim=2, keepdim=True)
+    assert plan.output.dtype == torch.bfloat16 and plan.kernel_kind().startswith("cols")
+    assert torch.allclose(plan.output.float(), want, rtol=2 ** -7, atol=1e-2)

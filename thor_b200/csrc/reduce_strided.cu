@@ -228,11 +228,12 @@ extern "C" int thor_b200_strided_reduce_launch(const thor_b200_strided_reduce_de
     // merge adjacent axes of one kind (singleton axes join whatever surrounds them)
     StridedArgs a{};
     Groups& g = a.g;
+    TB_REQUIRE(d->has_strides <= 1, "strided_reduce: has_strides must be 0 or 1");
     uint64_t stride[THOR_B200_MAX_RANK];
     uint64_t s = 1;
     for (uint32_t i = d->rank; i-- > 0;) {
         TB_REQUIRE(d->dims[i] > 0, "strided_reduce: zero-sized dimension");
-        stride[i] = s;
+        stride[i] = d->has_strides ? d->strides[i] : s;
         s *= d->dims[i];
     }
     g.n_out = g.n_red_total = 1;
@@ -244,7 +245,8 @@ extern "C" int thor_b200_strided_reduce_launch(const thor_b200_strided_reduce_de
         uint64_t* dim = kind ? g.red_dim : g.kept_dim;
         uint64_t* str = kind ? g.red_stride : g.kept_stride;
         uint32_t& n = kind ? g.n_red : g.n_kept;
-        if (kind == last_kind) {
+        // an axis joins the group before it when it is of the same kind and continues it in memory
+        if (kind == last_kind && str[n - 1] == d->dims[i] * stride[i]) {
             dim[n - 1] *= d->dims[i];
             str[n - 1] = stride[i];
         } else {

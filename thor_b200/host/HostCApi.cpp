@@ -1,6 +1,7 @@
 // Flat C surface over the C++ host layer, for the ctypes binding (the role nanobind plays in the
 // reference's bindings/python/src/core/physical/expression.cpp).  Every function catches C++
 // exceptions: logic errors return 1, runtime errors 2, and thb_last_error() holds the message.
+#include <sstream>
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -349,6 +350,72 @@ THB_API int thb_reduction_geometry(const uint64_t* dims, uint32_t rank, const ui
     });
 }
 
+// Every field of CubReduction::analyzeGeometry for a (possibly strided) view, as JSON text; strides may be NULL (dense).
+THB_API int thb_reduction_geometry_json(const uint64_t* dims, const uint64_t* strides, uint32_t rank, const uint32_t* axes, uint32_t n_axes, const char** text) {
+    static thread_local std::string g_text;
+    return guarded([&] {
+        const std::vector<uint64_t> d(dims, dims + rank);
+        const std::vector<uint32_t> a(axes, axes + n_axes);
+        const CubReductionGeometry g = strides ? CubReduction::analyzeGeometry(d, std::vector<uint64_t>(strides, strides + rank), a) : CubReduction::analyzeGeometry(d, a);
+        std::ostringstream os;
+        auto list = [&](const char* key, const auto& v) {
+            os << "\"" << key << "\":[";
+            for (size_t i = 0; i < v.size(); ++i) os << (i ? "," : "") << v[i];
+            os << "],";
+        };
+        os << "{\"path\":" << static_cast<int>(g.path) << ",\"rank\":" << g.rank << ",\"reduced_axes_are_contiguous\":" << (g.reduced_axes_are_contiguous ? 1 : 0)
+           << ",\"outer_size\":" << g.outer_size << ",\"reduction_size\":" << g.reduction_size << ",\"inner_size\":" << g.inner_size << ",\"input_elements\":"
+           << g.input_elements << ",\"output_elements\":" << g.output_elements << ",";
+        list("output_dimensions", g.output_dimensions);
+        list("squeezed_output_dimensions", g.squeezed_output_dimensions);
+        list("input_strides", g.indexing.input_strides);
+        list("reduced_axes", g.indexing.reduced_axes);
+        list("physical_non_singleton_axis_order", g.physical_non_singleton_axis_order);
+        os << "\"physical_layout_is_dense_permutation\":" << (g.physical_layout_is_dense_permutation ? 1 : 0) << ",\"tiled_output_permuted\":" << (g.tiled_output_permuted ? 1 : 0)
+           << ",\"tiled_output_shared_transpose\":" << (g.tiled_output_shared_transpose ? 1 : 0) << ",\"tiled_output_outer_stride\":" << g.tiled_output_outer_stride
+           << ",\"tiled_output_inner_stride\":" << g.tiled_output_inner_stride << ",\"device_transform_uses_affine_stride\":" << (g.device_transform_uses_affine_stride ? 1 : 0)
+           << ",\"affine_input_stride\":" << g.affine_input_stride << ",\"permutation_aware_tiled_geometry\":";
+        if (g.permutation_aware_tiled_geometry) {
+            const auto& c = *g.permutation_aware_tiled_geometry;
+            os << "{";
+            list("physical_outer_axes", c.physical_outer_axes);
+            list("physical_reduction_axes", c.physical_reduction_axes);
+            list("physical_inner_axes", c.physical_inner_axes);
+            list("logical_non_singleton_retained_axes", c.logical_non_singleton_retained_axes);
+            os << "\"outer_size\":" << c.outer_size << ",\"reduction_size\":" << c.reduction_size << ",\"inner_size\":" << c.inner_size << ",\"retained_output_order\":"
+               << static_cast<int>(c.retained_output_order) << "}";
+        } else {
+            os << "null";
+        }
+        os << "}";
+        g_text = os.str();
+        *text = g_text.c_str();
+    });
+}
+THB_API int thb_reduction_map_index(const uint64_t* dims, const uint64_t* strides, uint32_t rank, const uint32_t* axes, uint32_t n_axes, uint64_t output_index,
+                                    uint64_t reduction_index, uint64_t* physical) {
+    return guarded([&] {
+        const std::vector<uint64_t> d(dims, dims + rank);
+        const std::vector<uint32_t> a(axes, axes + n_axes);
+        const CubReductionGeometry g = strides ? CubReduction::analyzeGeometry(d, std::vector<uint64_t>(strides, strides + rank), a) : CubReduction::analyzeGeometry(d, a);
+        *physical = CubReduction::mapLogicalReductionIndexToPhysicalIndex(g, output_index, reduction_index);
+    });
+}
+// Stamp on a strided VIEW: `input` binds the view's first element and dims, view_strides its element strides.
+THB_API int thb_cub_reduction_stamp_view(int op, const uint32_t* axes, uint32_t n_axes, int output_dtype, float output_scale, const thb_binding* input,
+                                         const uint64_t* view_strides, const thb_binding* output, void* stream, int device, StampedCubReduction** out) {
+    return guarded([&] {
+        std::optional<DataType> od = output_dtype ? std::optional<DataType>(static_cast<DataType>(output_dtype)) : std::nullopt;
+        CubReduction r(static_cast<CubReductionOp>(op), std::vector<uint32_t>(axes, axes + n_axes), od, output_scale);
+        const std::vector<uint64_t> dims(input->dims, input->dims + input->rank), strides(view_strides, view_strides + input->rank);
+        uint64_t extent = 1;
+        for (size_t i = 0; i < dims.size(); ++i) extent += (dims[i] - 1) * strides[i];
+        Tensor storage = Tensor::wrap(input->ptr, static_cast<DataType>(input->dtype), {extent}, device);
+        Tensor in = storage.aliasView(dims, strides, 0);
+        Tensor o = Tensor::wrap(output->ptr, static_cast<DataType>(output->dtype), std::vector<uint64_t>(output->dims, output->dims + output->rank), device);
+        *out = new StampedCubReduction(r.stamp(in, o, Stream(stream, device)));
+    });
+}
 THB_API int thb_cub_reduction_stamp(int op, const uint32_t* axes, uint32_t n_axes, int output_dtype, float output_scale, const thb_binding* input,
                                     const thb_binding* output, void* stream, int device, StampedCubReduction** out) {
     return guarded([&] {

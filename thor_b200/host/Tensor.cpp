@@ -43,6 +43,44 @@ Tensor Tensor::allocate(DataType dtype, std::vector<uint64_t> dims, int gpu_num)
     return t;
 }
 
+Tensor Tensor::aliasView(std::vector<uint64_t> dims, std::vector<uint64_t> strides_elements, uint64_t element_offset) const {
+    if (!isInitialized()) throw std::logic_error("Tensor::aliasView: uninitialised tensor");
+    if (dims.size() != strides_elements.size()) throw std::invalid_argument("Tensor::aliasView: one stride per dimension");
+    // the view must stay inside the storage this tensor describes
+    uint64_t last = element_offset;
+    for (size_t i = 0; i < dims.size(); ++i) {
+        if (dims[i] == 0) throw std::invalid_argument("Tensor::aliasView: zero-sized dimension");
+        last += (dims[i] - 1) * strides_elements[i];
+    }
+    uint64_t extent = 1;
+    const std::vector<uint64_t> own = getStridesElements();
+    for (size_t i = 0; i < dims_.size(); ++i) extent += (dims_[i] - 1) * own[i];
+    if (last >= extent) throw std::invalid_argument("Tensor::aliasView: the view reaches beyond the tensor's storage");
+    Tensor v = *this;
+    v.dims_ = std::move(dims);
+    v.strides_ = std::move(strides_elements);
+    v.storage_offset_ = storage_offset_ + element_offset;
+    v.ptr_ = static_cast<char*>(ptr_) + element_offset * dataTypeSize(dtype_);
+    return v;
+}
+
+std::vector<uint64_t> Tensor::getStridesElements() const {
+    if (!strides_.empty()) return strides_;
+    std::vector<uint64_t> s(dims_.size(), 1);
+    for (size_t i = dims_.size(); i-- > 1;) s[i - 1] = s[i] * dims_[i];
+    return s;
+}
+
+bool Tensor::isDenseRowMajor() const {
+    if (strides_.empty()) return true;
+    uint64_t expect = 1;
+    for (size_t i = dims_.size(); i-- > 0;) {
+        if (dims_[i] != 1 && strides_[i] != expect) return false;
+        expect *= dims_[i];
+    }
+    return true;
+}
+
 void Tensor::copyFromAsync(const Tensor& source, const Stream& stream) {
     if (!isInitialized() || !source.isInitialized()) throw std::logic_error("Tensor::copyFromAsync: uninitialised tensor");
     if (source.getTotalNumElements() != getTotalNumElements()) throw std::logic_error("Tensor::copyFromAsync: total number of elements does not match");

@@ -54,11 +54,22 @@ class Tensor {
     }
     uint64_t getArraySizeInBytes() const { return getTotalNumElements() * dataTypeSize(dtype_); }
 
+    // Zero-copy view of this tensor's storage (Tensor::aliasView, Tensor.h:146-152): dims and element strides of the
+    // view, element offset of its first element from this tensor's first element.  getMemPtr() of the view already
+    // includes the offset; the view keeps the storage alive.
+    Tensor aliasView(std::vector<uint64_t> dims, std::vector<uint64_t> strides_elements, uint64_t element_offset = 0) const;
+    // Element strides: those of the view, or the dense row-major strides of dims.
+    std::vector<uint64_t> getStridesElements() const;
+    uint64_t getStorageElementOffset() const { return storage_offset_; }
+    bool isDenseRowMajor() const;
+
    private:
     void* ptr_ = nullptr;
     DataType dtype_ = DataType::FP32;
     std::vector<uint64_t> dims_;
     int gpu_num_ = 0;
+    std::vector<uint64_t> strides_;  // empty = dense row-major
+    uint64_t storage_offset_ = 0;
     std::shared_ptr<void> owner_;
 };
 

@@ -39,7 +39,7 @@ _lib.thor_b200_argreduce_plan_destroy.restype = None
 
 class _StridedDesc(C.Structure):
     _fields_ = [("op", C.c_int32), ("arg_op", C.c_int32), ("input_dtype", C.c_int32), ("output_dtype", C.c_int32), ("rank", C.c_uint32),
-                ("reserved", C.c_uint32), ("dims", C.c_uint64 * 8), ("reduced", C.c_uint8 * 8)]
+                ("has_strides", C.c_uint32), ("dims", C.c_uint64 * 8), ("reduced", C.c_uint8 * 8), ("strides", C.c_uint64 * 8)]
 
 
 _lib.thor_b200_strided_reduce_launch.argtypes = [C.POINTER(_StridedDesc), C.c_void_p, C.c_void_p, C.c_float, C.c_void_p]
@@ -88,6 +88,29 @@ def analyze_geometry(dims: Sequence[int], axes: Sequence[int]):
     return int(ori[0]), int(ori[1]), int(ori[2]), CubReductionPath(path.value)
 
 
+def analyze_geometry_full(dims: Sequence[int], axes: Sequence[int], strides: Optional[Sequence[int]] = None) -> dict:
+    """Every field of CubReduction::analyzeGeometry for a dense tensor or, with element `strides`, a view of storage
+    (permutation-aware tiled geometry, output strides, affine rank-1 views; CubReduction.h:107-153).  Needs no GPU."""
+    import json
+
+    d = (C.c_uint64 * max(1, len(dims)))(*dims)
+    s = (C.c_uint64 * max(1, len(dims)))(*strides) if strides is not None else None
+    a = (C.c_uint32 * max(1, len(axes)))(*axes)
+    text = C.c_char_p()
+    _check(_host.thb_reduction_geometry_json(d, s, len(dims), a, len(axes), C.byref(text)))
+    return json.loads(text.value.decode())
+
+
+def map_logical_reduction_index(dims: Sequence[int], axes: Sequence[int], output_index: int, reduction_index: int, strides: Optional[Sequence[int]] = None) -> int:
+    """CubReduction::mapLogicalReductionIndexToPhysicalIndex: element offset of one element of one output's reduction domain."""
+    d = (C.c_uint64 * max(1, len(dims)))(*dims)
+    s = (C.c_uint64 * max(1, len(dims)))(*strides) if strides is not None else None
+    a = (C.c_uint32 * max(1, len(axes)))(*axes)
+    out = C.c_uint64()
+    _check(_host.thb_reduction_map_index(d, s, len(dims), a, len(axes), C.c_uint64(output_index), C.c_uint64(reduction_index), C.byref(out)))
+    return int(out.value)
+
+
 def empty_reduction_value(op: CubReductionOp) -> float:
     return float(_host.thb_cub_empty_value(int(op)))
 
@@ -125,10 +148,21 @@ class CubReduction:
         out_shape = [1 if i in self.axes else d for i, d in enumerate(input_t.shape)]
         if output is None:
             output = torch.empty(out_shape, dtype=to_torch(out_dt), device=input_t.device)
-        ib = _bind_tensor("input", input_t, in_dt)
         ob = _bind_tensor("output", output, out_dt)
         axes = (C.c_uint32 * max(1, len(self.axes)))(*self.axes)
         h = C.c_void_p()
+        if not input_t.is_contiguous():
+            # a view of storage (permuted, sliced with a step, expanded ...): stamped as it is, nothing is copied
+            ib = _Binding()
+            ib.name, ib.ptr, ib.dtype, ib.rank, ib.is_scalar = b"input", input_t.data_ptr(), int(in_dt), input_t.dim(), 0
+            for i, d in enumerate(input_t.shape):
+                ib.dims[i] = d
+            strides = (C.c_uint64 * max(1, input_t.dim()))(*input_t.stride())
+            with torch.cuda.device(input_t.device):
+                _check(_host.thb_cub_reduction_stamp_view(int(self.op), axes, len(self.axes), int(self.output_dtype or 0), C.c_float(self.output_scale),
+                                                          C.byref(ib), strides, C.byref(ob), _native.stream_handle(stream), input_t.device.index or 0, C.byref(h)))
+            return StampedCubReduction(h, input_t, output)
+        ib = _bind_tensor("input", input_t, in_dt)
         with torch.cuda.device(input_t.device):
             _check(_host.thb_cub_reduction_stamp(int(self.op), axes, len(self.axes), int(self.output_dtype or 0), C.c_float(self.output_scale),
                                                  C.byref(ib), C.byref(ob), _native.stream_handle(stream), input_t.device.index or 0, C.byref(h)))
