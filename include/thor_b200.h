@@ -220,6 +220,16 @@ THOR_B200_API int thor_b200_selfcheck_pair_math(unsigned long long* device_count
 THOR_B200_API int thor_b200_device_alloc(size_t bytes, void** out_ptr);
 THOR_B200_API int thor_b200_device_free(void* ptr);
 
+/* Helper streams (non-blocking) and events (no timing) for a stamped plan whose independent branches run beside the
+ * caller's stream (StampedExecutionPlan::runOn, Utilities/Expression/StampedEquation.cpp:4057-4205): created at stamp
+ * time on the current device, reused by every run; recording and waiting are stream-ordered and never block the host. */
+THOR_B200_API int thor_b200_stream_create(void** out_stream);
+THOR_B200_API void thor_b200_stream_destroy(void* stream);
+THOR_B200_API int thor_b200_event_create(void** out_event);
+THOR_B200_API void thor_b200_event_destroy(void* event);
+THOR_B200_API int thor_b200_event_record(void* event, void* stream);
+THOR_B200_API int thor_b200_stream_wait_event(void* stream, void* event);
+
 /* ---------------------------------------------------------------------------------------------
  * S2  dense value reductions and arg reductions
  * Replaces CubReductionInternal::query*ReductionBytes / launch*Reduction and the ArgMin/ArgMax

@@ -93,4 +93,40 @@ size_t thor_b200_dtype_size(int dtype) { return tb::dtypeSize(dtype); }
 
 uint64_t thor_b200_launch_count(void) { return tb::g_launches.load(std::memory_order_relaxed); }
 
+// Helper streams and events for stamped plans whose independent branches run beside the caller's stream.
+int thor_b200_stream_create(void** out_stream) {
+    using namespace tb;
+    TB_REQUIRE(out_stream != nullptr, "stream_create: null output");
+    cudaStream_t s = nullptr;
+    TB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *out_stream = s;
+    return THOR_B200_OK;
+}
+void thor_b200_stream_destroy(void* stream) {
+    if (stream) (void)cudaStreamDestroy(static_cast<cudaStream_t>(stream));
+}
+int thor_b200_event_create(void** out_event) {
+    using namespace tb;
+    TB_REQUIRE(out_event != nullptr, "event_create: null output");
+    cudaEvent_t e = nullptr;
+    TB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    *out_event = e;
+    return THOR_B200_OK;
+}
+void thor_b200_event_destroy(void* event) {
+    if (event) (void)cudaEventDestroy(static_cast<cudaEvent_t>(event));
+}
+int thor_b200_event_record(void* event, void* stream) {
+    using namespace tb;
+    TB_REQUIRE(event != nullptr, "event_record: null event");
+    TB_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+    return THOR_B200_OK;
+}
+int thor_b200_stream_wait_event(void* stream, void* event) {
+    using namespace tb;
+    TB_REQUIRE(event != nullptr, "stream_wait_event: null event");
+    TB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+    return THOR_B200_OK;
+}
+
 }  // extern "C"

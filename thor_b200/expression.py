@@ -276,17 +276,18 @@ class Expression:
     @staticmethod
     def compile(expr: Union["Expression", Mapping[str, "Expression"]], device_num: Optional[int] = None, use_fast_math: bool = False,
                 fuse_row_reductions: bool = True, row_program: Optional[Mapping[str, int]] = None,
-                unrounded_column_sums: bool = False) -> "FusedEquation":
+                unrounded_column_sums: bool = False, branch_streams: bool = True) -> "FusedEquation":
         """FusedEquation::compile: one Expression (output named "output") or a dict of named outputs.
         device_num defaults to the current CUDA device of the calling process.  row_program sets fields of
         FusedEquationOptions::row_program (ROW_PROGRAM_TUNING_FIELDS; layout choices of row programs, all computing the same
         values), which backward equations compiled from this one inherit.  unrounded_column_sums (for callers that hold
         one shard of the rows): row programs with column reductions also deliver those sums as the fp32 output
-        "__column_sums" [reductions, cols], rows named by StampedExecutionPlan.column_sum_names()."""
+        "__column_sums" [reductions, cols], rows named by StampedExecutionPlan.column_sum_names().  branch_streams: stages
+        that do not depend on each other run on helper streams joined by events (StampedExecutionPlan.stage_lanes())."""
         named = {"output": expr} if isinstance(expr, Expression) else dict(expr)
         if device_num is None:
             device_num = torch.cuda.current_device() if torch.cuda.is_available() else 0
-        return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions, row_program, unrounded_column_sums)
+        return FusedEquation(named, device_num, use_fast_math, fuse_row_reductions, row_program, unrounded_column_sums, branch_streams)
 
 
 def _bind_tensor(name: str, t: torch.Tensor, dtype: Optional[DataType] = None) -> _Binding:
@@ -337,6 +338,12 @@ class StampedExecutionPlan:
     def stage_sources(self): return self._strings(2)
     def output_names(self): return self._strings(3)
     def column_sum_names(self): return self._strings(4)
+
+    def stage_lanes(self):
+        """Lane of every physical stage: 0 = the caller's stream, 1.. = helper streams of independent branches."""
+        buf = (C.c_uint32 * 256)()
+        n = int(_host.thb_plan_stage_lanes(self._h, buf, 256))
+        return [int(buf[i]) for i in range(min(n, 256))]
     def output_spec(self, name: str = "output"):
         """(shape, DataType) of the named output."""
         b = _Binding()
@@ -383,7 +390,7 @@ ROW_PROGRAM_TUNING_FIELDS = ("ring_buffers", "pipeline_round_one", "copy_warpgro
 
 
 class FusedEquation:
-    def __init__(self, named: Mapping[str, Expression], device_num: int, use_fast_math: bool, fuse_row_reductions: bool, row_program=None, unrounded_column_sums=False, _handle=None):
+    def __init__(self, named: Mapping[str, Expression], device_num: int, use_fast_math: bool, fuse_row_reductions: bool, row_program=None, unrounded_column_sums=False, branch_streams=True, _handle=None):
         self.device_num = device_num
         if _handle is not None:
             self._h = _handle
@@ -398,7 +405,7 @@ class FusedEquation:
             if unknown:
                 raise _native.ThorB200InvalidArgument(f"unknown row_program field(s): {sorted(unknown)}")
             tuning = (C.c_int32 * len(ROW_PROGRAM_TUNING_FIELDS))(*[int(row_program.get(f, 0)) for f in ROW_PROGRAM_TUNING_FIELDS])
-        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, int(unrounded_column_sums), C.byref(out)))
+        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, int(unrounded_column_sums), int(branch_streams), C.byref(out)))
         self._h = out
 
     def __del__(self):
@@ -412,7 +419,7 @@ class FusedEquation:
         arr = (C.c_char_p * len(wrt))(*[w.encode() for w in wrt])
         out = C.c_void_p()
         _check(_host.thb_compile_backward(self._h, arr, len(wrt), upstream_prefix.encode(), C.byref(out)))
-        return FusedEquation({}, self.device_num, False, True, None, False, _handle=out)
+        return FusedEquation({}, self.device_num, False, True, None, False, True, _handle=out)
 
     def stamp(self, inputs: Mapping[str, Union[torch.Tensor, float]], stream: Optional[torch.cuda.Stream] = None,
               outputs: Optional[Mapping[str, torch.Tensor]] = None, dtypes: Optional[Mapping[str, DataType]] = None) -> StampedExecutionPlan:
@@ -506,3 +513,20 @@ def resolve_dtypes(named: Mapping[str, Expression], input_dtypes: Mapping[str, D
     n_nodes = C.c_uint32()
     _check(_host.thb_resolve_dtypes(arr_n, arr_e, len(names), arr_in, arr_dt, len(in_names), buf, cap, C.byref(n_nodes)))
     return [(buf[3 * k], DataType(buf[3 * k + 1]), DataType(buf[3 * k + 2])) for k in range(n_nodes.value)]
+
+
+def build_execution_schedule(dependencies: Sequence[Sequence[int]]):
+    """The pure lane-assignment function of stamped plans (the reference's detail::buildStampedExecutionSchedule,
+    StampedEquation.h:1634-1646): dependencies[s] lists the stages that stage s consumes.  Returns (lanes per stage,
+    completion-event flags per stage, number of lanes, needs_caller_ready_event).  Needs no GPU."""
+    flat, offsets = [], [0]
+    for d in dependencies:
+        flat += list(d)
+        offsets.append(len(flat))
+    n = len(dependencies)
+    lanes = (C.c_uint32 * max(1, n))()
+    events = (C.c_uint8 * max(1, n))()
+    n_lanes, ready = C.c_uint32(), C.c_int32()
+    _host.thb_plan_stage_lanes.restype = C.c_uint32
+    _check(_host.thb_build_schedule((C.c_uint32 * max(1, len(flat)))(*flat), (C.c_uint32 * len(offsets))(*offsets), n, lanes, events, C.byref(n_lanes), C.byref(ready)))
+    return [int(lanes[i]) for i in range(n)], [bool(events[i]) for i in range(n)], int(n_lanes.value), bool(ready.value)

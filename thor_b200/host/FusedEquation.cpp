@@ -10,6 +10,7 @@
 
 #include "AutoDiff.h"
 #include "RowFusion.h"
+#include "Schedule.h"
 #include "thor_b200.h"
 
 namespace ThorB200 {
@@ -160,6 +161,23 @@ struct PhysicalStage {
     std::shared_ptr<std::vector<float>> shared_scalars;  // FusedRows: runtime scalars the launch closure reads
     std::function<uint32_t()> waits_expired;             // FusedRows: bounded device-side waits that ran out
     uint64_t launches = 1;
+    // device buffers the stage reads and writes: what orders it against the other stages of the plan
+    std::vector<const void*> reads;
+    std::vector<const void*> writes;
+};
+
+// Streams and events of a plan whose stages occupy more than one lane; owned by the plan, reused by every run.
+struct LaneResources {
+    std::vector<void*> lane_streams;   // [lane], entry 0 unused (the caller's stream)
+    std::vector<void*> done_events;    // [scheduled stage], null where no other lane waits for the stage
+    std::vector<void*> lane_end;       // [lane], recorded behind a helper lane's last stage of a run
+    void* caller_ready = nullptr;
+    ~LaneResources() {
+        for (void* s : lane_streams) thor_b200_stream_destroy(s);
+        for (void* e : done_events) thor_b200_event_destroy(e);
+        for (void* e : lane_end) thor_b200_event_destroy(e);
+        thor_b200_event_destroy(caller_ready);
+    }
 };
 
 struct StampedExecutionPlan::Impl {
@@ -170,44 +188,82 @@ struct StampedExecutionPlan::Impl {
     std::vector<Tensor> keep_alive;
     uint64_t intermediate_bytes = 0;
     std::vector<std::string> column_sum_names;
+    // branch scheduling (StampedEquation.cpp:4057-4205): stages that launch something, their dependencies and lanes
+    std::vector<uint32_t> scheduled;  // indices into `stages` (views launch nothing and are left out)
+    std::vector<std::vector<uint32_t>> dependencies;
+    StampedExecutionSchedule schedule;
+    std::shared_ptr<LaneResources> lanes;  // null: everything runs on the caller's stream
     bool plan_only = false;  // stamped with placeholder memory: describes the plan, cannot run
 };
 
 void StampedExecutionPlan::run() { runOn(impl_->stream); }
 
+namespace {
+void launchStage(PhysicalStage& s, void* stream) {
+    switch (s.kind) {
+        case StageKind::FusedKernel:
+            check(thor_b200_expr_launch(s.expr->h, s.input_ptrs.data(), s.scalars.data(), s.output_ptrs.data(), s.numel, stream), "StampedExecutionPlan::run fused stage");
+            break;
+        case StageKind::Reduction:
+            if (s.custom_launch) {
+                s.custom_launch(stream);
+                break;
+            }
+            check(thor_b200_reduce_launch(s.reduce->h, s.in, s.out, s.workspace.getMemPtr(), s.workspace_bytes, 1.0f, stream), "StampedExecutionPlan::run reduction");
+            break;
+        case StageKind::ArgMinMax:
+            if (s.custom_launch) {
+                s.custom_launch(stream);
+                break;
+            }
+            check(thor_b200_argreduce_launch(s.argreduce->h, s.in, nullptr, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream),
+                  "StampedExecutionPlan::run arg reduction");
+            break;
+        case StageKind::ReduceMinMaxBackward:
+            check(thor_b200_minmax_backward_launch(s.minmax_backward->h, s.in, s.in2, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream),
+                  "StampedExecutionPlan::run min/max backward");
+            break;
+        case StageKind::FusedRows: s.custom_launch(stream); break;
+        case StageKind::View: break;
+    }
+}
+}  // namespace
+
 void StampedExecutionPlan::runOn(const Stream& stream) {
     if (!impl_) throw std::logic_error("StampedExecutionPlan is empty");
     if (impl_->plan_only) throw std::logic_error("StampedExecutionPlan was stamped in plan-only mode and cannot run");
-    for (PhysicalStage& s : impl_->stages) {
-        switch (s.kind) {
-            case StageKind::FusedKernel:
-                check(thor_b200_expr_launch(s.expr->h, s.input_ptrs.data(), s.scalars.data(), s.output_ptrs.data(), s.numel, stream.handle),
-                      "StampedExecutionPlan::run fused stage");
-                break;
-            case StageKind::Reduction:
-                if (s.custom_launch) {
-                    s.custom_launch(stream.handle);
-                    break;
-                }
-                check(thor_b200_reduce_launch(s.reduce->h, s.in, s.out, s.workspace.getMemPtr(), s.workspace_bytes, 1.0f, stream.handle),
-                      "StampedExecutionPlan::run reduction");
-                break;
-            case StageKind::ArgMinMax:
-                if (s.custom_launch) {
-                    s.custom_launch(stream.handle);
-                    break;
-                }
-                check(thor_b200_argreduce_launch(s.argreduce->h, s.in, nullptr, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream.handle),
-                      "StampedExecutionPlan::run arg reduction");
-                break;
-            case StageKind::ReduceMinMaxBackward:
-                check(thor_b200_minmax_backward_launch(s.minmax_backward->h, s.in, s.in2, s.out, s.workspace.getMemPtr(), s.workspace_bytes, stream.handle),
-                      "StampedExecutionPlan::run min/max backward");
-                break;
-            case StageKind::FusedRows: s.custom_launch(stream.handle); break;
-            case StageKind::View: break;
-        }
+    if (!impl_->lanes) {
+        for (PhysicalStage& s : impl_->stages) launchStage(s, stream.handle);
+        return;
     }
+    // Independent branches run on helper streams beside the caller's: a stage waits for the events of the stages it
+    // consumes that ran on other lanes, a helper lane's first stage without dependencies waits for the caller's stream as
+    // it stood at the start of the run, and the caller's stream waits for every helper lane at the end.
+    LaneResources& lr = *impl_->lanes;
+    const StampedExecutionSchedule& sch = impl_->schedule;
+    if (sch.needs_caller_ready_event) check(thor_b200_event_record(lr.caller_ready, stream.handle), "StampedExecutionPlan::run event");
+    std::vector<bool> lane_used(lr.lane_streams.size(), false);
+    for (size_t k = 0; k < impl_->scheduled.size(); ++k) {
+        const uint32_t lane = sch.stage_lane_indices[k];
+        void* lane_stream = lane == 0 ? stream.handle : lr.lane_streams[lane];
+        if (lane != 0 && impl_->dependencies[k].empty()) check(thor_b200_stream_wait_event(lane_stream, lr.caller_ready), "StampedExecutionPlan::run wait");
+        for (uint32_t dep : impl_->dependencies[k])
+            if (sch.stage_lane_indices[dep] != lane) check(thor_b200_stream_wait_event(lane_stream, lr.done_events[dep]), "StampedExecutionPlan::run wait");
+        launchStage(impl_->stages[impl_->scheduled[k]], lane_stream);
+        if (lr.done_events[k]) check(thor_b200_event_record(lr.done_events[k], lane_stream), "StampedExecutionPlan::run event");
+        lane_used[lane] = true;
+    }
+    for (size_t lane = 1; lane < lr.lane_streams.size(); ++lane)
+        if (lane_used[lane]) {
+            check(thor_b200_event_record(lr.lane_end[lane], lr.lane_streams[lane]), "StampedExecutionPlan::run event");
+            check(thor_b200_stream_wait_event(stream.handle, lr.lane_end[lane]), "StampedExecutionPlan::run wait");
+        }
+}
+
+std::vector<uint32_t> StampedExecutionPlan::stageLanes() const {
+    std::vector<uint32_t> lanes(impl_->stages.size(), 0);
+    for (size_t k = 0; k < impl_->scheduled.size(); ++k) lanes[impl_->scheduled[k]] = impl_->schedule.stage_lane_indices.empty() ? 0 : impl_->schedule.stage_lane_indices[k];
+    return lanes;
 }
 
 Tensor StampedExecutionPlan::getOutput(const std::string& name) const {
@@ -515,6 +571,9 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
                 covered[node] = true;
             }
             for (uint32_t node : m.absorbed) covered[node] = true;
+            for (auto& [node, is_out] : m.produced) st.writes.push_back(node_tensor[node].getMemPtr());
+            for (const RuntimeInputValue& v : bound)
+                if (!v.is_scalar && v.tensor.isInitialized()) st.reads.push_back(v.tensor.getMemPtr());
             st.custom_launch = m.bind(node_tensor, impl->keep_alive, impl->intermediate_bytes);
             if (m.column_sums) {
                 impl->outputs["__column_sums"] = *m.column_sums;
@@ -597,6 +656,8 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
                     check(thor_b200_strided_reduce_launch(d.get(), in_ptr, out_ptr, 1.0f, stream), "StampedExecutionPlan::run strided reduction");
                 };
                 impl->keep_alive.push_back(src);
+                st.reads.push_back(in_ptr);
+                st.writes.push_back(out_ptr);
                 impl->stages.push_back(std::move(st));
                 continue;
             }
@@ -665,6 +726,9 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
             st.workspace_bytes = ws;
             st.workspace = Tensor::allocate(DataType::UINT8, {static_cast<uint64_t>(ws)}, device_num_);
             if (ws > 1) impl->intermediate_bytes += ws;
+            st.reads.push_back(st.in);
+            if (st.in2) st.reads.push_back(st.in2);
+            st.writes.push_back(st.out);
             impl->stages.push_back(std::move(st));
             continue;
         }
@@ -821,6 +885,9 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
         st.scalar_names = scalar_names;
         st.output_ptrs = out_ptrs;
         st.numel = out_numel;
+        for (const void* q : in_ptrs)
+            if (q) st.reads.push_back(q);
+        for (void* q : out_ptrs) st.writes.push_back(q);
         impl->stages.push_back(std::move(st));
     }
 
@@ -832,6 +899,40 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
     }
     for (auto& t : node_tensor)
         if (t.isInitialized()) impl->keep_alive.push_back(t);
+
+    // Lanes: a stage depends on the earlier stages that wrote what it reads (and on those that read or wrote what it
+    // writes); stages that share no such edge run on different streams.  Views launch nothing and are left out.
+    for (uint32_t i = 0; i < impl->stages.size(); ++i)
+        if (impl->stages[i].kind != StageKind::View) impl->scheduled.push_back(i);
+    auto overlap = [](const std::vector<const void*>& a, const std::vector<const void*>& b) {
+        for (const void* x : a)
+            for (const void* y : b)
+                if (x == y) return true;
+        return false;
+    };
+    impl->dependencies.assign(impl->scheduled.size(), {});
+    for (uint32_t k = 0; k < impl->scheduled.size(); ++k) {
+        const PhysicalStage& later = impl->stages[impl->scheduled[k]];
+        for (uint32_t e = 0; e < k; ++e) {
+            const PhysicalStage& earlier = impl->stages[impl->scheduled[e]];
+            if (overlap(later.reads, earlier.writes) || overlap(later.writes, earlier.writes) || overlap(later.writes, earlier.reads)) impl->dependencies[k].push_back(e);
+        }
+    }
+    impl->schedule = buildStampedExecutionSchedule(impl->dependencies, static_cast<uint32_t>(device_num_));
+    if (options_.branch_streams && !Tensor::planOnly() && impl->schedule.lane_gpu_nums.size() > 1) {
+        auto lr = std::make_shared<LaneResources>();
+        lr->lane_streams.assign(impl->schedule.lane_gpu_nums.size(), nullptr);
+        lr->lane_end.assign(impl->schedule.lane_gpu_nums.size(), nullptr);
+        lr->done_events.assign(impl->scheduled.size(), nullptr);
+        for (size_t lane = 1; lane < lr->lane_streams.size(); ++lane) {
+            check(thor_b200_stream_create(&lr->lane_streams[lane]), "FusedEquation::stamp helper stream");
+            check(thor_b200_event_create(&lr->lane_end[lane]), "FusedEquation::stamp event");
+        }
+        for (size_t k = 0; k < impl->scheduled.size(); ++k)
+            if (impl->schedule.stage_needs_completion_event[k]) check(thor_b200_event_create(&lr->done_events[k]), "FusedEquation::stamp event");
+        check(thor_b200_event_create(&lr->caller_ready), "FusedEquation::stamp event");
+        impl->lanes = lr;
+    }
     return StampedExecutionPlan(impl);
 }
 

@@ -55,6 +55,8 @@ struct FusedEquationOptions {
     // in the order of columnSumNames(), so that the shards' sums can be added before the single rounding to the gradient's
     // dtype.  The reference is single-GPU on this path and has no counterpart.
     bool unrounded_column_sums = false;
+    // Stages that do not depend on each other run on helper streams joined by events, like the reference's stamped plans.
+    bool branch_streams = true;
     // Execute "elementwise -> row reduction -> elementwise" chains over the innermost axis (softmax,
     // LayerNorm forward / backward) as one single-pass kernel instead of the reference's stage list.
     // The logical stage list is still reported by stageKindNames().
@@ -89,6 +91,9 @@ class StampedExecutionPlan {
     // Names of the outputs whose unrounded sums the rows of "__column_sums" hold (empty unless the equation was compiled
     // with unrounded_column_sums and runs as a row program with column reductions).
     std::vector<std::string> columnSumNames() const;
+    // Lane of every physical stage: 0 = the caller's stream, 1.. = helper streams for branches that do not depend on
+    // each other (StampedExecutionPlan::runOn, StampedEquation.cpp:4057-4205; lane policy StampedEquation.h:1634-1646).
+    std::vector<uint32_t> stageLanes() const;
 
    private:
     std::shared_ptr<Impl> impl_;

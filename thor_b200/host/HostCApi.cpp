@@ -9,6 +9,7 @@
 
 #include "CubReduction.h"
 #include "FusedEquation.h"
+#include "Schedule.h"
 
 using namespace ThorB200;
 
@@ -178,7 +179,7 @@ THB_API uint32_t thb_expr_node_count(const Expression* a) { return static_cast<u
 // ---- equations --------------------------------------------------------------------------------------
 // row_tuning: NULL or the eight RowProgramTuning fields in declaration order
 THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint32_t n, int device, int fast_math, int fuse_rows, const int32_t* row_tuning,
-                        int unrounded_column_sums, FusedEquation** out) {
+                        int unrounded_column_sums, int branch_streams, FusedEquation** out) {
     return guarded([&] {
         std::vector<std::pair<std::string, Expression>> named;
         for (uint32_t i = 0; i < n; ++i) named.emplace_back(names[i], *exprs[i]);
@@ -186,6 +187,7 @@ THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint
         opt.use_fast_math = fast_math != 0;
         opt.fuse_row_reductions = fuse_rows != 0;
         opt.unrounded_column_sums = unrounded_column_sums != 0;
+        opt.branch_streams = branch_streams != 0;
         if (row_tuning != nullptr)
             opt.row_program = RowProgramTuning{row_tuning[0], row_tuning[1], row_tuning[2], row_tuning[3], row_tuning[4], row_tuning[5], row_tuning[6], row_tuning[7]};
         *out = new FusedEquation(FusedEquation::compile(Expression::outputs(named), device, opt));
@@ -301,6 +303,32 @@ THB_API const char* thb_plan_strings(Plan* p, int kind) {
     }
     p->strings.push_back(joined);
     return p->strings.back().c_str();
+}
+// Lane of every physical stage of the plan (0 = the caller's stream); returns the number written.
+THB_API uint32_t thb_plan_stage_lanes(Plan* p, uint32_t* lanes, uint32_t capacity) {
+    const std::vector<uint32_t> v = p->plan.stageLanes();
+    for (size_t i = 0; i < v.size() && i < capacity; ++i) lanes[i] = v[i];
+    return static_cast<uint32_t>(v.size());
+}
+// The pure lane-assignment function: deps is a flat list, stage s consuming deps[offsets[s] .. offsets[s + 1]).
+THB_API int thb_build_schedule(const uint32_t* deps, const uint32_t* offsets, uint32_t n_stages, uint32_t* lanes, uint8_t* completion_event, uint32_t* n_lanes,
+                               int32_t* needs_caller_ready) {
+    return guarded([&] {
+        std::vector<std::vector<uint32_t>> d(n_stages);
+        for (uint32_t s = 0; s < n_stages; ++s) d[s].assign(deps + offsets[s], deps + offsets[s + 1]);
+        StampedExecutionSchedule sch;
+        try {
+            sch = buildStampedExecutionSchedule(d, 0);
+        } catch (const std::runtime_error& e) {
+            throw std::logic_error(e.what());
+        }
+        for (uint32_t s = 0; s < n_stages; ++s) {
+            lanes[s] = sch.stage_lane_indices[s];
+            completion_event[s] = sch.stage_needs_completion_event[s] ? 1 : 0;
+        }
+        *n_lanes = static_cast<uint32_t>(sch.lane_gpu_nums.size());
+        *needs_caller_ready = sch.needs_caller_ready_event ? 1 : 0;
+    });
 }
 THB_API uint64_t thb_plan_intermediate_bytes(Plan* p) { return p->plan.intermediateBytes(); }
 THB_API uint64_t thb_plan_launches(Plan* p) { return p->plan.kernelLaunchesPerRun(); }
