@@ -1015,9 +1015,41 @@ class C5LayerNormBwd(C5LayerNormFwd):
         return bool(ok), f"dgamma/dbeta max {float(d.max()):.2f} bf16 ulp beyond tolerance, dx max {float(ddx.max()):.2f} ulp"
 
 
+
+class C5BwdStageList(C5LayerNormBwd):
+    """Baseline, not product: the reference's stage cut of the autodiff LayerNorm backward -- every reduction a stage of its
+    own, fused kernels between them, the fp32 [rows, cols] intermediates materialised in HBM (ten stages, twelve launches)
+    -- run with THIS library's fused and reduction kernels, which are at least as fast as the reference's own (see the
+    other reference baselines), so the ratio to the row program understates the reference's cost rather than inflating
+    it.  The reference's own emitted kernels are not used here because its multi-output fused stages cannot be driven
+    through the single-output launcher of the test infrastructure."""
+    is_baseline = True
+    name = "c5_layernorm_backward_bf16_reference_stage_list"
+    description = ("reference stage cut for the autodiff LayerNorm backward (Reduction / FusedKernel stages with materialised fp32 intermediates), "
+                   "this library's kernels per stage (baseline beside c5 backward)")
+    collective = None
+
+    def setup(self):
+        import torch
+
+        from thor_b200.expression import Expression as ex
+
+        gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
+        bwd = ex.compile({"y": _layernorm_expr(ex)}, fuse_row_reductions=False).compile_backward(["x", "gamma", "beta"])
+        x, gamma, beta = self._inputs(gen)
+        dy = (torch.randn(self.ROWS, self.COLS, device="cuda", generator=gen) * 1e-2).bfloat16()
+        plan = bwd.stamp({"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy})
+        self.sets = [(plan, x, dy, gamma, None, None)]
+        self.launches_per_step = plan.kernel_launches_per_run()
+        self.kernel_kind = plan.physical_stage_names()
+        self.combiner = None
+
+    def step(self, i): self.sets[0][0].run()
+    def collective_us(self): return None
+
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
              "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c3_argmax_ref_gpu": C3ArgmaxReferenceGpu, "c4_ref_stages": C4ReferenceStagePipeline,
-             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline}
+             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline, "c5_bwd_ref_stages": C5BwdStageList}
 
 
 # ---------------------------------------------------------------------------------------------------------

@@ -67,6 +67,12 @@ THOR_B200_API const char* thor_b200_last_error(void);
 THOR_B200_API size_t thor_b200_dtype_size(int dtype);
 /* Number of kernels this library has launched from the calling process (all threads). */
 THOR_B200_API uint64_t thor_b200_launch_count(void);
+/* Programmatic dependent launch: every kernel of this library is launched with stream serialisation relaxed and opens
+ * with griddepcontrol.wait, so its CTAs are placed while the previous kernel of the stream drains; stream-order
+ * semantics are unchanged.  On by default; set_dependent_launch(0) launches without the attribute (process-wide, for
+ * comparison runs and for tools that cannot follow overlapped launches).  dependent_launch() returns the setting. */
+THOR_B200_API void thor_b200_set_dependent_launch(int on);
+THOR_B200_API int thor_b200_dependent_launch(void);
 
 /* ---------------------------------------------------------------------------------------------
  * S1  dtype cast
@@ -353,6 +359,34 @@ THOR_B200_API int thor_b200_minmax_backward_plan_create(const thor_b200_minmax_b
 THOR_B200_API int thor_b200_minmax_backward_launch(const thor_b200_minmax_backward_plan* plan, const void* input, const void* grad_output,
                                                    void* grad_input, void* workspace, size_t workspace_bytes, void* stream);
 THOR_B200_API void thor_b200_minmax_backward_plan_destroy(thor_b200_minmax_backward_plan* plan);
+
+/* ---------------------------------------------------------------------------------------------
+ * Flat scatter-add without atomics (the step behind arg scans in scan min / max backward)
+ * Replaces prepareFlatScatterAdd / runFlatScatterAdd (Utilities/Expression/FlatScatterAddKernel.h:16-74; caller
+ * StampedScanMinMaxBackward::runOn, Utilities/Expression/StampedEquation.cpp:3134-3137).
+ *   output[:] = 0;  for i in [0, num_updates): dst = indices[i];
+ *                   if dst != 0xFFFFFFFF and dst < output_numel: output[dst] += updates[i]
+ * THOR_B200_SCATTER_CANONICALIZE (CanonicalizeDuplicatesAndSkipInvalid): duplicate destinations are summed and invalid
+ * ones skipped; the sum of a destination's updates is taken in the order of their positions i, so the result equals the
+ * sequential loop above bit for bit and is the same on every run (no atomics).  THOR_B200_SCATTER_UNIQUE_VALID
+ * (IndicesAreUniqueAndValid): the caller guarantees in-range, non-sentinel, pairwise different destinations; no
+ * workspace is used.  fp32 updates and output, uint32 indices (what the reference supports); num_updates < 2^31.
+ * The workspace size depends on num_updates only; launch() allocates nothing and does not synchronise.
+ * ------------------------------------------------------------------------------------------- */
+enum { THOR_B200_SCATTER_CANONICALIZE = 0, THOR_B200_SCATTER_UNIQUE_VALID = 1 };
+
+typedef struct thor_b200_scatter_add_desc {
+    int32_t value_dtype;  /* THOR_B200_FP32 */
+    int32_t index_policy; /* THOR_B200_SCATTER_* */
+    uint64_t num_updates;
+    uint64_t output_numel;
+} thor_b200_scatter_add_desc;
+
+THOR_B200_API int thor_b200_scatter_add_workspace_bytes(const thor_b200_scatter_add_desc* desc, size_t* bytes);
+THOR_B200_API int thor_b200_scatter_add_launch(const thor_b200_scatter_add_desc* desc, const void* updates, const void* indices, void* output,
+                                               void* workspace, size_t workspace_bytes, void* stream);
+/* Kernels one launch() issues (the zero fill is a memset, not a kernel). */
+THOR_B200_API int thor_b200_scatter_add_launch_count(const thor_b200_scatter_add_desc* desc);
 
 /* ---------------------------------------------------------------------------------------------
  * Row programs: "elementwise -> row reduction -> elementwise" chains as ONE single-pass kernel.

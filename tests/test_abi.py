@@ -52,6 +52,33 @@ def test_cast_argument_errors_need_no_gpu():
     native.check(native.lib.thor_b200_cast_launch(None, None, 11, 10, 0, None))
 
 
+def test_scatter_add_descriptions_are_validated_without_a_gpu():
+    """Workspace sizing of the flat scatter-add: fp32 only (as the reference, FlatScatterAddKernel.cu:236-247), four
+    ping-pong arrays of num_updates 32-bit words plus the [256][tiles] digit table; the unique-and-valid policy and an
+    empty update list need the one-byte placeholder only; the dependent-launch switch is a process-wide setting."""
+    import thor_b200._native as native
+    from thor_b200 import DataType
+    from thor_b200.reductions import FlatScatterAddIndexPolicy as Policy
+    from thor_b200.reductions import scatter_add_workspace_bytes as ws_bytes
+
+    n = 100_000
+    tiles = -(-n // 4096)
+    align = lambda v: (v + 255) // 256 * 256
+    assert ws_bytes(n, 1 << 20) == 4 * align(4 * n) + align(tiles * 256 * 4)
+    assert ws_bytes(n, 1 << 20, Policy.IndicesAreUniqueAndValid) == 1 and ws_bytes(0, 7) == 1
+    with pytest.raises(native.ThorB200InvalidArgument, match="only fp32"):
+        ws_bytes(4, 4, value_dtype=DataType.bf16)
+    with pytest.raises(native.ThorB200InvalidArgument, match="2\\^31"):
+        ws_bytes(1 << 31, 4)
+    with pytest.raises(native.ThorB200InvalidArgument, match="2\\^32"):
+        ws_bytes(4, 1 << 32)
+    native.lib.thor_b200_set_dependent_launch.restype = None
+    assert native.lib.thor_b200_dependent_launch() == 1
+    native.lib.thor_b200_set_dependent_launch(0)
+    assert native.lib.thor_b200_dependent_launch() == 0
+    native.lib.thor_b200_set_dependent_launch(1)
+
+
 def test_product_does_not_import_the_oracle():
     """The shipped package must never route through the CPU checker."""
     for path in list((ROOT / "thor_b200").rglob("*.py")) + list((ROOT / "thor_b200").rglob("*.cu")) + list((ROOT / "thor_b200").rglob("*.cpp")):

@@ -27,13 +27,8 @@ void clearError() { lastErrorSlot().clear(); }
 static std::atomic<uint64_t> g_launches{0};
 void countLaunch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-bool dependentLaunchEnabled() {
-    static const bool on = [] {
-        const char* v = getenv("THOR_B200_DEPENDENT_LAUNCH");
-        return !(v && *v && atoi(v) == 0);
-    }();
-    return on;
-}
+static std::atomic<bool> g_dependent_launch{true};
+bool dependentLaunchEnabled() { return g_dependent_launch.load(std::memory_order_relaxed); }
 
 int currentDeviceInfo(const DeviceInfo** out) {
     static DeviceInfo table[64];
@@ -92,6 +87,9 @@ const char* thor_b200_last_error(void) { return tb::lastErrorSlot().c_str(); }
 size_t thor_b200_dtype_size(int dtype) { return tb::dtypeSize(dtype); }
 
 uint64_t thor_b200_launch_count(void) { return tb::g_launches.load(std::memory_order_relaxed); }
+
+void thor_b200_set_dependent_launch(int on) { tb::g_dependent_launch.store(on != 0, std::memory_order_relaxed); }
+int thor_b200_dependent_launch(void) { return tb::g_dependent_launch.load(std::memory_order_relaxed) ? 1 : 0; }
 
 // Helper streams and events for stamped plans whose independent branches run beside the caller's stream.
 int thor_b200_stream_create(void** out_stream) {

@@ -51,7 +51,7 @@ void countLaunch(uint64_t n = 1);
 __device__ __forceinline__ void gridDependencyWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void gridLaunchDependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
-bool dependentLaunchEnabled();  // THOR_B200_DEPENDENT_LAUNCH=0 turns the launch attribute off
+bool dependentLaunchEnabled();  // thor_b200_set_dependent_launch(0) turns the launch attribute off
 
 template <class... KArgs, class... Args>
 cudaError_t launchDependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

@@ -272,3 +272,62 @@ class ReduceMinMaxBackward:
         _native.check(_lib.thor_b200_minmax_backward_launch(self._plan, self._input.data_ptr(), self._grad_output.data_ptr(), self.grad_input.data_ptr(),
                                                             self._workspace.data_ptr(), self._ws_bytes, _native.stream_handle(self._stream)))
         return self.grad_input
+
+
+# ---- flat scatter-add without atomics ------------------------------------------------------------------
+class _ScatterAddDesc(C.Structure):
+    _fields_ = [("value_dtype", C.c_int32), ("index_policy", C.c_int32), ("num_updates", C.c_uint64), ("output_numel", C.c_uint64)]
+
+
+_lib.thor_b200_scatter_add_workspace_bytes.argtypes = [C.POINTER(_ScatterAddDesc), C.POINTER(C.c_size_t)]
+_lib.thor_b200_scatter_add_launch.argtypes = [C.POINTER(_ScatterAddDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+_lib.thor_b200_scatter_add_launch_count.argtypes = [C.POINTER(_ScatterAddDesc)]
+
+
+class FlatScatterAddIndexPolicy(enum.IntEnum):
+    CanonicalizeDuplicatesAndSkipInvalid = 0
+    IndicesAreUniqueAndValid = 1
+
+
+def scatter_add_workspace_bytes(num_updates: int, output_numel: int, policy=FlatScatterAddIndexPolicy.CanonicalizeDuplicatesAndSkipInvalid,
+                                value_dtype: DataType = DataType.fp32) -> int:
+    """Workspace a FlatScatterAdd of this size needs; validates the description (no GPU needed)."""
+    d = _ScatterAddDesc(int(value_dtype), int(policy), num_updates, output_numel)
+    ws = C.c_size_t()
+    _native.check(_lib.thor_b200_scatter_add_workspace_bytes(C.byref(d), C.byref(ws)))
+    return int(ws.value)
+
+
+class FlatScatterAdd:
+    """output[:] = 0; output[indices[i]] += updates[i] for every valid i, duplicates added in the order of i, no atomics
+    (the reference's prepareFlatScatterAdd / runFlatScatterAdd, Utilities/Expression/FlatScatterAddKernel.h:61-74).
+    The plan owns its workspace; run() allocates nothing."""
+
+    def __init__(self, updates: torch.Tensor, flat_indices: torch.Tensor, output: torch.Tensor,
+                 index_policy=FlatScatterAddIndexPolicy.CanonicalizeDuplicatesAndSkipInvalid, stream=None):
+        if flat_indices.dtype != torch.uint32:
+            raise _native.ThorB200InvalidArgument("Flat scatter-add indices must be UINT32.")
+        if updates.dtype != output.dtype:
+            raise _native.ThorB200InvalidArgument("Flat scatter-add updates and output must have the same dtype.")
+        if tuple(updates.shape) != tuple(flat_indices.shape):
+            raise _native.ThorB200InvalidArgument("Flat scatter-add updates and indices must have the same shape.")
+        if not (updates.device == flat_indices.device == output.device):
+            raise _native.ThorB200InvalidArgument("Flat scatter-add updates, indices, and output must be on the same placement.")
+        self.index_policy = FlatScatterAddIndexPolicy(index_policy)
+        self._desc = _ScatterAddDesc(int(from_torch(updates.dtype)), int(self.index_policy), updates.numel(), output.numel())
+        ws = C.c_size_t()
+        _native.check(_lib.thor_b200_scatter_add_workspace_bytes(C.byref(self._desc), C.byref(ws)))
+        self.workspace_bytes = int(ws.value) if self.index_policy == FlatScatterAddIndexPolicy.CanonicalizeDuplicatesAndSkipInvalid else 0
+        self._ws_bytes = int(ws.value)
+        self._workspace = torch.empty(max(16, self._ws_bytes), dtype=torch.uint8, device=output.device)
+        self._stream = stream
+        self.kernel_launches = int(_lib.thor_b200_scatter_add_launch_count(C.byref(self._desc)))
+
+    def run(self, updates: torch.Tensor, flat_indices: torch.Tensor, output: torch.Tensor, stream=None) -> torch.Tensor:
+        if updates.numel() != self._desc.num_updates or flat_indices.numel() != self._desc.num_updates or output.numel() != self._desc.output_numel:
+            raise _native.ThorB200InvalidArgument("Flat scatter-add runtime tensors do not match the prepared plan shape.")
+        if int(from_torch(updates.dtype)) != self._desc.value_dtype or updates.dtype != output.dtype or flat_indices.dtype != torch.uint32:
+            raise _native.ThorB200InvalidArgument("Flat scatter-add runtime tensor dtypes do not match the prepared plan.")
+        _native.check(_lib.thor_b200_scatter_add_launch(C.byref(self._desc), updates.data_ptr(), flat_indices.data_ptr(), output.data_ptr(),
+                                                        self._workspace.data_ptr(), self._ws_bytes, _native.stream_handle(stream if stream is not None else self._stream)))
+        return output
