@@ -54,7 +54,7 @@ def test_cast_argument_errors_need_no_gpu():
 
 def test_scatter_add_descriptions_are_validated_without_a_gpu():
     """Workspace sizing of the flat scatter-add: fp32 only (as the reference, FlatScatterAddKernel.cu:236-247), four
-    ping-pong arrays of num_updates 32-bit words plus the [256][tiles] digit table; the unique-and-valid policy and an
+    ping-pong arrays of num_updates 32-bit words plus the [256][tiles] digit table and the per-digit totals of four passes; the unique-and-valid policy and an
     empty update list need the one-byte placeholder only; the dependent-launch switch is a process-wide setting."""
     import thor_b200._native as native
     from thor_b200 import DataType
@@ -64,7 +64,7 @@ def test_scatter_add_descriptions_are_validated_without_a_gpu():
     n = 100_000
     tiles = -(-n // 4096)
     align = lambda v: (v + 255) // 256 * 256
-    assert ws_bytes(n, 1 << 20) == 4 * align(4 * n) + align(tiles * 256 * 4)
+    assert ws_bytes(n, 1 << 20) == 4 * align(4 * n) + align(tiles * 256 * 4) + 4 * 256 * 4
     assert ws_bytes(n, 1 << 20, Policy.IndicesAreUniqueAndValid) == 1 and ws_bytes(0, 7) == 1
     with pytest.raises(native.ThorB200InvalidArgument, match="only fp32"):
         ws_bytes(4, 4, value_dtype=DataType.bf16)

@@ -55,8 +55,20 @@ def test_random_destinations_match_the_sequential_loop_bit_for_bit(n, out_n, inv
     plan, got = _run(updates, indices, out_n)
     want = _sequential(updates, indices, out_n)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
-    passes = max(1, (int(out_n).bit_length() + 7) // 8)
+    passes = max(1, (int(out_n - 1).bit_length() + 7) // 8)
     assert plan.kernel_launches == 3 * passes + 1
+
+
+def test_every_small_size_with_many_and_few_duplicates():
+    """Sizes around the chunk of eight pairs a thread walks and the 256 pairs of a warp's window, with three destinations
+    (runs span threads and warps) and with fifty (most runs inside one thread)."""
+    rng = np.random.default_rng(77)
+    for n in list(range(1, 41)) + [63, 64, 65, 255, 256, 257, 258, 511, 512, 513, 2047, 2048, 2049]:
+        for out_n in (3, 50):
+            updates = (rng.standard_normal(n) * 10.0 ** rng.integers(-3, 4, n)).astype(np.float32)
+            indices = rng.integers(0, out_n + 1, n).astype(np.uint32)  # out_n itself is out of range: skipped
+            _, got = _run(updates, indices, out_n)
+            assert np.array_equal(got.view(np.uint32), _sequential(updates, indices, out_n).view(np.uint32)), (n, out_n)
 
 
 def test_long_runs_of_one_destination_keep_the_order_of_the_updates():
