@@ -368,17 +368,41 @@ __global__ void __launch_bounds__(kApplyThreads) applyRunsKernel(const uint32_t*
     if (__ballot_sync(FULL, runs_on) != 0) {
         const uint32_t rk = __shfl_sync(FULL, tail_key, 31);
         float rs = __shfl_sync(FULL, tail_sum, 31);
+        // batches of 128 pairs (four coalesced loads per lane), the next batch in flight while this one is added
+        constexpr int kBatch = 4;
         uint64_t rj = window_end;
+        uint32_t bk[kBatch], nk[kBatch];
+        float bx[kBatch], nx[kBatch];
+        auto load = [&](uint64_t from, uint32_t (&kk)[kBatch], float (&xx)[kBatch]) {
+#pragma unroll
+            for (int t = 0; t < kBatch; ++t) {
+                const uint64_t p = from + static_cast<uint64_t>(t) * 32 + lane;
+                const bool live = p < n;
+                kk[t] = live ? keys[p] : ~rk;  // anything but the run's destination
+                xx[t] = live ? vals[p] : 0.0f;
+            }
+        };
+        load(rj, bk, bx);
         bool more = true;
         while (more) {
-            const uint64_t p = rj + lane;
-            const bool in = p < n && keys[p] == rk;
-            const float x = in ? vals[p] : 0.0f;
-            const uint32_t in_run = __ballot_sync(FULL, in);
-            const uint32_t len = in_run == FULL ? 32u : static_cast<uint32_t>(__ffs(~in_run) - 1);  // the leading set bits
-            for (uint32_t t = 0; t < len; ++t) rs += __shfl_sync(FULL, x, t);
-            rj += len;
-            more = len == 32u;
+            load(rj + 32ull * kBatch, nk, nx);
+#pragma unroll
+            for (int t = 0; t < kBatch; ++t) {
+                if (more) {
+                    const uint32_t in_run = __ballot_sync(FULL, bk[t] == rk);
+                    const uint32_t len = in_run == FULL ? 32u : static_cast<uint32_t>(__ffs(~in_run) - 1);  // the leading set bits
+                    if (len == 32u) {
+#pragma unroll
+                        for (int u = 0; u < 32; ++u) rs += __shfl_sync(FULL, bx[t], u);  // unrolled: the shuffles run ahead of the adds
+                    } else {
+                        for (uint32_t u = 0; u < len; ++u) rs += __shfl_sync(FULL, bx[t], u);
+                    }
+                    more = len == 32u;
+                }
+            }
+            rj += 32ull * kBatch;
+#pragma unroll
+            for (int t = 0; t < kBatch; ++t) bk[t] = nk[t], bx[t] = nx[t];
         }
         if (lane == 31) output[rk] = rs;
     }
