@@ -464,7 +464,8 @@ THOR_B200_API uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* p
 /* Programs whose rows arrive by bulk copies wait on shared-memory barriers; every such wait has a time limit, and a
  * wait that ran out is counted on the device instead of hanging the kernel.  Synchronises with the device and
  * stores the count since the program was loaded (0 for programs without such waits, or never launched); a
- * non-zero count means the outputs of the launches so far are not to be trusted. */
+ * non-zero count means the outputs of the launches so far are not to be trusted, and once this call has reported one
+ * the handle refuses further launches (THOR_B200_CUDA_ERROR): find the cause and compile the program again. */
 THOR_B200_API int thor_b200_rowprog_waits_expired(thor_b200_rowprog* prog, uint32_t* count);
 THOR_B200_API void thor_b200_rowprog_destroy(thor_b200_rowprog* prog);
 

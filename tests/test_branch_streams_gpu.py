@@ -29,7 +29,7 @@ def _softmax_argmax():
 @pytest.mark.parametrize("builder,shape,dtype", [(_statistics, (1 << 22,), torch.bfloat16), (_softmax_argmax, (2048, 1024), torch.float32)])
 def test_helper_lanes_give_the_single_stream_results_bit_for_bit(builder, shape, dtype):
     x = torch.randn(shape, device="cuda").to(dtype)
-    lanes = ex.compile(builder(), fuse_row_reductions=False, branch_streams=True).stamp({"x": x})
+    lanes = ex.compile(builder(), fuse_row_reductions=False, branch_streams="always").stamp({"x": x})
     single = ex.compile(builder(), fuse_row_reductions=False, branch_streams=False).stamp({"x": x})
     assert max(lanes.stage_lanes()) >= 1 and lanes.stage_lanes() == single.stage_lanes()  # the schedule is the same; only its use differs
     lanes.run()
@@ -43,7 +43,7 @@ def test_helper_lanes_give_the_single_stream_results_bit_for_bit(builder, shape,
 
 def test_statistics_on_helper_lanes_match_the_fp64_oracle():
     x = (torch.randn(1 << 22, device="cuda") * 2.0).to(torch.bfloat16)
-    plan = ex.compile(_statistics(), fuse_row_reductions=False).stamp({"x": x})
+    plan = ex.compile(_statistics(), fuse_row_reductions=False, branch_streams="always").stamp({"x": x})
     plan.run()
     torch.cuda.synchronize()
     v = x.float().cpu().numpy().astype(np.float64)
@@ -59,7 +59,7 @@ def test_repeated_runs_with_new_input_values_never_read_a_stale_or_half_written_
     run's results must belong to that run's input (the helper lanes start after the overwrite and finish before the next)."""
     rows, cols = 512, 1024
     x = torch.empty(rows, cols, device="cuda")
-    plan = ex.compile(_softmax_argmax(), fuse_row_reductions=False).stamp({"x": x})
+    plan = ex.compile(_softmax_argmax(), fuse_row_reductions=False, branch_streams="always").stamp({"x": x})
     assert max(plan.stage_lanes()) >= 1
     stream = torch.cuda.Stream()
     gen = torch.Generator(device="cuda").manual_seed(11)

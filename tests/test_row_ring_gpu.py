@@ -105,6 +105,8 @@ def test_a_wait_that_runs_out_is_counted_and_the_device_stays_usable(backward):
     plan, _ = _run(4096, 8192, {"wait_limit_ms": 20, "test_skip_fill": 6}, backward)
     assert "blockIdx.x == 0 && " in plan.stage_sources()[0]
     assert plan.waits_expired() >= 1
+    with pytest.raises(Exception, match="expired device-side waits"):
+        plan.run()  # a program that reported an expired wait refuses further launches
     # the same shapes without the injected fault: correct results, nothing counted
     healthy, got = _run(4096, 8192, {}, backward)
     _, want = _run(4096, 8192, RING_OFF, backward)

@@ -114,6 +114,23 @@ __device__ __forceinline__ Cand teamBest(Cand c, float* sv, unsigned long long* 
     return c;
 }
 
+// NaN-propagating extreme of two / three values in one instruction (three-input max / min exists from sm_100 on): a pack
+// of sixteen bytes is summarised by its extreme in VEC / 2 instructions instead of a compare-and-select per element.
+template <bool IS_MAX>
+__device__ __forceinline__ float extreme2(float a, float b) {
+    float r;
+    if constexpr (IS_MAX) asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    else asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+template <bool IS_MAX>
+__device__ __forceinline__ float extreme3(float a, float b, float c) {
+    float r;
+    if constexpr (IS_MAX) asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    else asm("min.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 template <class T, bool IS_MAX, int TEAM, bool IDX32>
 __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
     gridDependencyWait();
@@ -142,16 +159,22 @@ __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
             // A thread visits its elements in increasing index order, so inside a thread a strict comparison keeps
             // the earliest of equal values and the first NaN sticks; the full ordering rule is only needed when
             // candidates of different threads meet.
+            // Packs are compared through their extreme alone; a pack that wins is remembered by its first index and looked
+            // into once, after the loops (`in_pack`): the first element equal to the extreme -- or the first NaN -- is
+            // the candidate, with the value it really holds (the extreme of {-0, +0} may carry either sign).
             float bv = 0.0f;
             uint64_t bi = kNoIndex;
-            auto consider = [&](uint64_t idx, float v) {
-                const bool take = bi == kNoIndex || (bv == bv && (v != v || (IS_MAX ? v > bv : v < bv)));
+            bool have = false, in_pack = false;
+            auto consider = [&](uint64_t idx, float v, bool pack) {
+                const bool take = !have || (bv == bv && (v != v || (IS_MAX ? v > bv : v < bv)));
                 if (take) {
                     bv = v;
                     bi = idx;
+                    in_pack = pack;
+                    have = true;
                 }
             };
-            for (uint64_t i = lo + t; i < body0; i += TEAM) consider(i, toFloat(p[i]));
+            for (uint64_t i = lo + t; i < body0; i += TEAM) consider(i, toFloat(p[i]), false);
             for (uint64_t q = t; q < n_packs; q += static_cast<uint64_t>(TEAM) * U) {
                 Pack<16> pk[U];
 #pragma unroll
@@ -160,20 +183,32 @@ __global__ void __launch_bounds__(kThreads) argRowsKernel(ArgArgs a) {
 #pragma unroll
                 for (int u = 0; u < U; ++u)
                     if (q + static_cast<uint64_t>(u) * TEAM < n_packs) {
-                        // value-only scan of the pack; the index is materialised once per pack
-                        float pv = toFloat(reinterpret_cast<const T*>(&pk[u])[0]);
-                        int pj = 0;
+                        const T* e = reinterpret_cast<const T*>(&pk[u]);
+                        float m = toFloat(e[0]);
 #pragma unroll
-                        for (int j = 1; j < VEC; ++j) {
-                            const float v = toFloat(reinterpret_cast<const T*>(&pk[u])[j]);
-                            const bool take = pv == pv && (v != v || (IS_MAX ? v > pv : v < pv));
-                            pv = take ? v : pv;
-                            pj = take ? j : pj;
-                        }
-                        consider(body0 + (q + static_cast<uint64_t>(u) * TEAM) * VEC + pj, pv);
+                        for (int j = 1; j + 1 < VEC; j += 2) m = extreme3<IS_MAX>(m, toFloat(e[j]), toFloat(e[j + 1]));
+                        if constexpr (VEC % 2 == 0) m = extreme2<IS_MAX>(m, toFloat(e[VEC - 1]));
+                        consider(body0 + (q + static_cast<uint64_t>(u) * TEAM) * VEC, m, true);
                     }
             }
-            for (uint64_t i = tail0 + t; i < hi; i += TEAM) consider(i, toFloat(p[i]));
+            for (uint64_t i = tail0 + t; i < hi; i += TEAM) consider(i, toFloat(p[i]), false);
+            if (in_pack) {
+                Pack<16> pk;
+                loadPack(pk, p + bi);
+                const T* e = reinterpret_cast<const T*>(&pk);
+                const bool want_nan = bv != bv;
+                int pos = 0;
+                float val = bv;
+#pragma unroll
+                for (int j = VEC - 1; j >= 0; --j) {  // descending, so the lowest matching position is what remains
+                    const float v = toFloat(e[j]);
+                    const bool match = want_nan ? v != v : v == bv;
+                    pos = match ? j : pos;
+                    val = match ? v : val;
+                }
+                bi += static_cast<uint64_t>(pos);
+                bv = val;
+            }
             best = Cand{bv, bi};
         }
     }

@@ -1372,6 +1372,7 @@ struct thor_b200_rowprog {
     size_t workspace_bytes = 1;
     bool compile_only = false;
     bool smem_opted_in[64] = {};
+    std::atomic<uint32_t> expired_seen{0};  // what thor_b200_rowprog_waits_expired last reported
 };
 
 extern "C" {
@@ -1575,6 +1576,11 @@ int thor_b200_rowprog_launch_sharded(thor_b200_rowprog* h, const void* const* in
     TB_REQUIRE(h != nullptr, "rowprog_launch: null handle");
     TB_REQUIRE(!h->compile_only, "rowprog_launch: handle was compiled with compile_only");
     TB_REQUIRE(output_ptrs != nullptr, "rowprog_launch: output_ptrs is null");
+    if (const uint32_t seen = h->expired_seen.load(std::memory_order_relaxed))
+        return fail(THOR_B200_CUDA_ERROR,
+                    "rowprog_launch: earlier launches of this program recorded %u expired device-side waits, so their outputs were invalid; "
+                    "the program refuses further launches until the cause is found and it is compiled again",
+                    seen);
     const Program& p = h->prog;
     TB_REQUIRE(workspace_bytes >= h->workspace_bytes, "rowprog_launch: workspace too small");
     TB_REQUIRE((p.col_reduces.empty() && p.all_reduces.empty()) || (workspace != nullptr && isAligned(workspace, 16)),
@@ -1683,6 +1689,7 @@ int thor_b200_rowprog_waits_expired(thor_b200_rowprog* h, uint32_t* count) {
     TB_REQUIRE(bytes == sizeof(uint32_t), "rowprog_waits_expired: unexpected size of the device counter");
     TB_CUDA(cudaDeviceSynchronize());
     TB_CUDA(cudaMemcpy(count, flag, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    h->expired_seen.store(*count, std::memory_order_relaxed);
     return THOR_B200_OK;
 }
 

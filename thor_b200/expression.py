@@ -283,7 +283,8 @@ class Expression:
         values), which backward equations compiled from this one inherit.  unrounded_column_sums (for callers that hold
         one shard of the rows): row programs with column reductions also deliver those sums as the fp32 output
         "__column_sums" [reductions, cols], rows named by StampedExecutionPlan.column_sum_names().  branch_streams: stages
-        that do not depend on each other run on helper streams joined by events (StampedExecutionPlan.stage_lanes())."""
+        that do not depend on each other run on helper streams joined by events (StampedExecutionPlan.stage_lanes()) when the
+        plan's tensor inputs hold at least 64 MiB (the joins cost about 4 us per run); "always" uses them at any size."""
         named = {"output": expr} if isinstance(expr, Expression) else dict(expr)
         if device_num is None:
             device_num = torch.cuda.current_device() if torch.cuda.is_available() else 0
@@ -405,7 +406,7 @@ class FusedEquation:
             if unknown:
                 raise _native.ThorB200InvalidArgument(f"unknown row_program field(s): {sorted(unknown)}")
             tuning = (C.c_int32 * len(ROW_PROGRAM_TUNING_FIELDS))(*[int(row_program.get(f, 0)) for f in ROW_PROGRAM_TUNING_FIELDS])
-        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, int(unrounded_column_sums), int(branch_streams), C.byref(out)))
+        _check(_host.thb_compile(arr_n, arr_e, len(names), device_num, int(use_fast_math), int(fuse_row_reductions), tuning, int(unrounded_column_sums), 2 if branch_streams == "always" else int(bool(branch_streams)), C.byref(out)))
         self._h = out
 
     def __del__(self):

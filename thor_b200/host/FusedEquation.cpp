@@ -919,7 +919,10 @@ StampedExecutionPlan FusedEquation::stamp(const std::unordered_map<std::string, 
         }
     }
     impl->schedule = buildStampedExecutionSchedule(impl->dependencies, static_cast<uint32_t>(device_num_));
-    if (options_.branch_streams && !Tensor::planOnly() && impl->schedule.lane_gpu_nums.size() > 1) {
+    uint64_t input_bytes = 0;
+    for (const auto& kv : inputs)
+        if (!kv.second.is_scalar && kv.second.tensor.isInitialized()) input_bytes += kv.second.tensor.getArraySizeInBytes();
+    if (options_.branch_streams && !Tensor::planOnly() && impl->schedule.lane_gpu_nums.size() > 1 && input_bytes >= options_.branch_streams_min_input_bytes) {
         auto lr = std::make_shared<LaneResources>();
         lr->lane_streams.assign(impl->schedule.lane_gpu_nums.size(), nullptr);
         lr->lane_end.assign(impl->schedule.lane_gpu_nums.size(), nullptr);

@@ -57,6 +57,10 @@ struct FusedEquationOptions {
     bool unrounded_column_sums = false;
     // Stages that do not depend on each other run on helper streams joined by events, like the reference's stamped plans.
     bool branch_streams = true;
+    // Joining lanes costs a few event records and waits per run (about 4 us measured), which only pays when the stages
+    // are long: plans whose tensor inputs hold fewer bytes than this run on the caller's stream alone.  0 = always
+    // use the lanes.  The lane assignment itself (stageLanes()) does not depend on it.
+    uint64_t branch_streams_min_input_bytes = 64ull << 20;
     // Execute "elementwise -> row reduction -> elementwise" chains over the innermost axis (softmax,
     // LayerNorm forward / backward) as one single-pass kernel instead of the reference's stage list.
     // The logical stage list is still reported by stageKindNames().

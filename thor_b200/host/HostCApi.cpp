@@ -187,7 +187,8 @@ THB_API int thb_compile(const char* const* names, Expression* const* exprs, uint
         opt.use_fast_math = fast_math != 0;
         opt.fuse_row_reductions = fuse_rows != 0;
         opt.unrounded_column_sums = unrounded_column_sums != 0;
-        opt.branch_streams = branch_streams != 0;
+        opt.branch_streams = branch_streams != 0;  // 0 = off, 1 = on for plans above the default size, 2 = on for every plan
+        if (branch_streams == 2) opt.branch_streams_min_input_bytes = 0;
         if (row_tuning != nullptr)
             opt.row_program = RowProgramTuning{row_tuning[0], row_tuning[1], row_tuning[2], row_tuning[3], row_tuning[4], row_tuning[5], row_tuning[6], row_tuning[7]};
         *out = new FusedEquation(FusedEquation::compile(Expression::outputs(named), device, opt));
