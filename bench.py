@@ -1047,9 +1047,43 @@ class C5BwdStageList(C5LayerNormBwd):
     def step(self, i): self.sets[0][0].run()
     def collective_us(self): return None
 
+
+class F3ScatterAdd(Workload):
+    """Flat scatter-add without atomics (the step behind arg scans in scan min / max backward): 2^24 fp32 updates with
+    uniformly random uint32 destinations into 2^20 outputs, duplicates added in update order.  Algorithmic bytes = one
+    read of updates and destinations + one write of the output; the stable radix sort behind it moves 24 bytes per
+    update and pass on top, which is what bounds it.  One GPU only (shards of the updates would need the outputs added)."""
+    single_gpu_only = True
+    name = "f3_flat_scatter_add_fp32"
+    description = "flat scatter-add, 2^24 fp32 updates with random uint32 destinations into 2^20 outputs, no atomics, update order kept"
+    dtype = "f32"
+    N = 1 << 24
+    OUT = 1 << 20
+
+    def setup(self):
+        import torch
+
+        from thor_b200.reductions import FlatScatterAdd
+
+        gen = torch.Generator(device="cuda").manual_seed(77)
+        self.sets = []
+        for _ in range(2):
+            u = torch.randn(self.N, device="cuda", generator=gen)
+            i = torch.randint(0, self.OUT, (self.N,), device="cuda", generator=gen).to(torch.uint32)
+            self.sets.append((u, i, torch.empty(self.OUT, device="cuda")))
+        self.plan = FlatScatterAdd(*self.sets[0])
+        self.launches_per_step = self.plan.kernel_launches
+        self.kernel_kind = ["digitHistogramKernel", "tableScanKernel", "digitScatterKernel", "applyRunsKernel"]
+
+    def algorithmic_bytes(self): return self.N * 8 + self.OUT * 4
+    def units(self): return self.N
+    def step(self, i):
+        u, idx, out = self.sets[i % len(self.sets)]
+        self.plan.run(u, idx, out)
+
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
              "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c3_argmax_ref_gpu": C3ArgmaxReferenceGpu, "c4_ref_stages": C4ReferenceStagePipeline,
-             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline, "c5_bwd_ref_stages": C5BwdStageList}
+             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline, "c5_bwd_ref_stages": C5BwdStageList, "f3_scatter": F3ScatterAdd}
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -1217,7 +1251,7 @@ def extras(args, dist, wl, line, per_config, peak, traffic):
 
     detail = {}
     for key, cls in WORKLOADS.items():
-        if key == args.workload or (world > 1 and getattr(cls, "is_baseline", False)):
+        if key == args.workload or (world > 1 and (getattr(cls, "is_baseline", False) or getattr(cls, "single_gpu_only", False))):
             continue
         try:
             w2, r2 = measure(dist, cls, steps, 5, 1.0, False)
