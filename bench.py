@@ -333,15 +333,15 @@ class C1Cast(Workload):
         k = self.n_sets(self.algorithmic_bytes())
         self.sets = [(host.cuda(), torch.empty(self.n, dtype=torch.float16, device="cuda")) for _ in range(k)]
         self.convert = TypeConverter.convert_type
+        # the cast of a shard takes a few microseconds: the timed loop runs stamped conversions (one C call each)
+        self.stamped = [TypeConverter.stamp(src, dst) for src, dst in self.sets]
         self.launches_per_step = 1
         self.host_in = host.pin_memory()
         self.host_out = torch.empty(self.n, dtype=torch.float16).pin_memory()
 
     def algorithmic_bytes(self): return self.N * 6
     def units(self): return self.N
-    def step(self, i):
-        src, dst = self.sets[i % len(self.sets)]
-        self.convert(src, dst)
+    def step(self, i): self.stamped[i % len(self.stamped)].run()
 
     def e2e_step(self, i):
         src, dst = self.sets[i % len(self.sets)]
@@ -380,6 +380,10 @@ class C1CastReferenceGpu(C1Cast):
         self.convert = lambda s, d: oracle.reference_gpu_cast(s.data_ptr(), d.data_ptr(), oracle.FP32, oracle.FP16, self.n, stream)
         self.launches_per_step = 1
         self.kernel_kind = ["reference convertOutOfPlaceKernel"]
+
+    def step(self, i):
+        src, dst = self.sets[i % len(self.sets)]
+        self.convert(src, dst)
 
 
 class C2FusedExpr(Workload):
@@ -678,8 +682,10 @@ class _ShardCombiner:
     # LayerNorm backward: 177 us per step against 156 us), with three it never does.
     SLOTS = 3
 
-    def before_kernel(self, b: int): self.native.wait(b)
-    def after_kernel(self, b: int, sums=None, maxima=None, rounded=None): self.native.submit(b, sums=sums, maxima=maxima, rounded_sums=rounded)
+    def bind(self, b: int, sums=None, maxima=None, rounded=None):
+        """Slot b with its buffers resolved once: .wait() before the step's kernels, .submit() after them (one C call each)."""
+        return self.native.bind(b, sums=sums, maxima=maxima, rounded_sums=rounded)
+
     def drain(self): self.native.drain()
 
     def time_alone(self, dist, sums=None, maxima=None, iters: int = 50) -> float:
@@ -730,6 +736,7 @@ class C4FullReduce(Workload):
         self.kernel_kind = self.plans[0].physical_stage_names()
         comm = self.dist.communicator()
         self.combiner = _ShardCombiner(comm, _ShardCombiner.SLOTS) if comm is not None else None
+        self.slots = [self.combiner.bind(b, sums=st[0:2], maxima=st[2:3]) for b, st in enumerate(self.stats)] if self.combiner else None
 
     def algorithmic_bytes(self): return self.N * 2
     def units(self): return self.N
@@ -738,9 +745,9 @@ class C4FullReduce(Workload):
         if self.combiner is None:
             self.plans[b].run()
             return
-        self.combiner.before_kernel(b)
+        self.slots[b].wait()
         self.plans[b].run()
-        self.combiner.after_kernel(b, sums=self.stats[b][0:2], maxima=self.stats[b][2:3])
+        self.slots[b].submit()
 
     def drain(self):
         if self.combiner is not None:
@@ -961,6 +968,8 @@ class C5LayerNormBwd(C5LayerNormFwd):
         self.kernel_kind = self.sets[0][0].physical_stage_names()
         comm = self.dist.communicator()
         self.combiner = _ShardCombiner(comm, _ShardCombiner.SLOTS) if comm is not None else None
+        # the unrounded fp32 sums of this rank's rows are added across the ranks, then rounded to the gradients' dtype once
+        self.slots = [self.combiner.bind(b, sums=st[4], rounded=st[5]) for b, st in enumerate(self.sets)] if self.combiner else None
 
     def algorithmic_bytes(self): return 3 * self.ROWS * self.COLS * 2 + 3 * self.COLS * 2
     def step(self, i):
@@ -969,10 +978,9 @@ class C5LayerNormBwd(C5LayerNormFwd):
         if self.combiner is None:
             plan.run()
             return
-        self.combiner.before_kernel(b)
+        self.slots[b].wait()
         plan.run()
-        # the unrounded fp32 sums of this rank's rows are added across the ranks, then rounded to the gradients' dtype once
-        self.combiner.after_kernel(b, sums=sums, rounded=grads)
+        self.slots[b].submit()
 
     def drain(self):
         if self.combiner is not None:

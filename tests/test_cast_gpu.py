@@ -235,3 +235,20 @@ def test_copy_from_host_with_a_wider_destination_dtype_converts_in_place_on_the_
         tensor_copy_from(torch.empty(n, dtype=torch.float16, device="cuda"), torch.randn(n).pin_memory())
     with pytest.raises(Exception, match="CPU"):
         tensor_copy_from(torch.empty(n, dtype=torch.float32).pin_memory(), same)
+
+
+def test_a_stamped_conversion_repeats_the_cast_with_one_call():
+    """TypeConverter.stamp binds tensors, dtypes and stream once; run() gives what convert_type gives, and follows the
+    source's current contents."""
+    src = torch.randn(100_003, device="cuda")
+    dst = torch.empty(100_003, device="cuda", dtype=torch.float16)
+    stamped = TypeConverter.stamp(src, dst)
+    want = torch.empty_like(dst)
+    for _ in range(3):
+        src.normal_()
+        stamped.run()
+        TypeConverter.convert_type(src, want)
+        torch.cuda.synchronize()
+        assert torch.equal(dst.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(Exception, match="element counts differ"):
+        TypeConverter.stamp(src, dst[:5])

@@ -135,3 +135,15 @@ def test_dense_and_affine_path_selection():  # :380-397
     _check(g, path=P.DeviceTransformReduce, device_transform_uses_affine_stride=1, affine_input_stride=4, physical_layout_is_dense_permutation=0,
            permutation_aware_tiled_geometry=None)
     assert map_index([3], [0], 0, 2, strides=[4]) == 8
+
+
+def test_arg_reductions_take_dense_tensors_only():
+    """The reference's CubArgReduction::stamp starts with requireDenseContiguousGpuTensor (CubReduction.cpp:1310): a
+    view is refused before anything touches a device."""
+    import torch
+
+    from thor_b200 import ThorB200InvalidArgument
+    from thor_b200.reductions import CubArgReduction, CubArgReductionOp
+
+    with pytest.raises(ThorB200InvalidArgument, match="dense contiguous"):
+        CubArgReduction(CubArgReductionOp.ArgMax, [1]).stamp(torch.zeros(4, 6).t())

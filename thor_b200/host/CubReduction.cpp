@@ -297,6 +297,10 @@ CubArgReduction::CubArgReduction(CubArgReductionOp op, std::vector<uint32_t> axe
 }
 
 StampedCubArgReduction CubArgReduction::stamp(const Tensor& input, const Stream& stream) const {
+    // views are for value reductions; arg reductions take dense tensors only, like the reference's
+    // (CubReduction.cpp:1310, requireDenseContiguousGpuTensor)
+    if (!input.isInitialized()) throw std::invalid_argument("input must be initialized.");
+    if (!input.isDenseRowMajor()) throw std::invalid_argument("input must be dense contiguous.");
     const CubReductionGeometry g = CubReduction::analyzeGeometry(input.getDimensions(), axes_);
     StampedCubArgReduction s;
     if (g.path == CubReductionPath::StridedFixedSegment) {

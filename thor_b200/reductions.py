@@ -209,6 +209,9 @@ class CubArgReduction:
 
     def stamp(self, input_t: torch.Tensor, stream=None, input_dtype: Optional[DataType] = None) -> StampedCubArgReduction:
         in_dt = DataType(input_dtype) if input_dtype is not None else from_torch(input_t.dtype)
+        if not input_t.is_contiguous():
+            # the reference's arg reductions take dense tensors only (CubReduction.cpp:1310, requireDenseContiguousGpuTensor)
+            raise _native.ThorB200InvalidArgument("input must be dense contiguous.")
         outer, red, inner, path = analyze_geometry(list(input_t.shape), self.axes)
         if path == CubReductionPath.StridedFixedSegment:
             out_shape = [1 if i in self.axes else d for i, d in enumerate(input_t.shape)]

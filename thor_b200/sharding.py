@@ -129,6 +129,44 @@ class Communicator:
             pass
 
 
+class BoundCombinerSlot:
+    """One slot of a Combiner bound to its buffers: wait() and submit() are single C calls."""
+
+    def __init__(self, combiner, slot, sums, maxima, minima, rounded_sums, stream):
+        import ctypes as C
+
+        from . import _native
+        from .dtypes import from_torch
+
+        def pair(t):
+            if t is None:
+                return C.c_void_p(None), C.c_uint64(0)
+            if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+                raise ValueError("partials are contiguous fp32 CUDA tensors")
+            return C.c_void_p(t.data_ptr()), C.c_uint64(t.numel())
+
+        if rounded_sums is not None and (sums is None or rounded_sums.numel() != sums.numel() or not rounded_sums.is_contiguous()):
+            raise ValueError("rounded_sums must be contiguous and hold as many elements as sums")
+        self._keep = (combiner, sums, maxima, minima, rounded_sums)
+        st = _native.stream_handle(stream)
+        self._check = _native.check
+        self._wait, self._wait_args = combiner._lib.thor_b200_combiner_wait, (combiner._h, slot, st)
+        self._submit = combiner._lib.thor_b200_combiner_submit
+        self._submit_args = (combiner._h, slot, st, *pair(sums), *pair(maxima), *pair(minima),
+                             C.c_void_p(rounded_sums.data_ptr()) if rounded_sums is not None else C.c_void_p(None),
+                             int(from_torch(rounded_sums.dtype)) if rounded_sums is not None else 0)
+
+    def wait(self) -> None:
+        status = self._wait(*self._wait_args)
+        if status:
+            self._check(status)
+
+    def submit(self) -> None:
+        status = self._submit(*self._submit_args)
+        if status:
+            self._check(status)
+
+
 class Combiner:
     """Overlapped combine of a stepping job's partials (thor_b200_combiner_*): the statistics of step i cross the ranks on
     the combiner's own high-priority stream while the kernel of step i + 1 runs.  The caller keeps `slots` copies of its
@@ -183,6 +221,12 @@ class Combiner:
         from . import _native
 
         _native.check(self._lib.thor_b200_combiner_drain(self._h, _native.stream_handle(stream)))
+
+    def bind(self, slot: int, sums: Optional[torch.Tensor] = None, maxima: Optional[torch.Tensor] = None, minima: Optional[torch.Tensor] = None,
+             rounded_sums: Optional[torch.Tensor] = None, stream=None) -> "BoundCombinerSlot":
+        """wait / submit of one slot with its buffers and stream (the current one when none is given) resolved once, for
+        stepping loops in which the Python side of a call would cost as much as the step."""
+        return BoundCombinerSlot(self, slot, sums, maxima, minima, rounded_sums, stream)
 
     def close(self) -> None:
         if self._h:

@@ -34,6 +34,38 @@ class TypeConverter:
             TypeConverter.convert_type_raw(src.data_ptr(), dst.data_ptr(), sd, dd, src.numel(), stream)
         return dst
 
+    @staticmethod
+    def stamp(src: torch.Tensor, dst: torch.Tensor, src_dtype: DataType | None = None, dst_dtype: DataType | None = None,
+              stream=None) -> "StampedConversion":
+        """The same conversion with everything resolved once: run() is a single call into the library."""
+        return StampedConversion(src, dst, src_dtype, dst_dtype, stream)
+
+
+class StampedConversion:
+    """A cast bound to its tensors, dtypes and stream (the current one when none is given) at construction, for callers
+    that repeat it: run() makes one C call and no Python-side checks, which matters when the cast itself takes a few
+    microseconds.  The tensors must stay alive and the device current at construction must be current at run()."""
+
+    def __init__(self, src: torch.Tensor, dst: torch.Tensor, src_dtype=None, dst_dtype=None, stream=None):
+        if not (src.is_cuda and dst.is_cuda):
+            raise _native.ThorB200InvalidArgument("TypeConverter: both tensors must live on a CUDA device (no CPU path in this library)")
+        if not (src.is_contiguous() and dst.is_contiguous()):
+            raise _native.ThorB200InvalidArgument("TypeConverter: tensors must be contiguous")
+        if src.numel() != dst.numel():
+            raise _native.ThorB200InvalidArgument("TypeConverter: element counts differ")
+        if src.device != dst.device or src.device.index != torch.cuda.current_device():
+            raise _native.ThorB200InvalidArgument("TypeConverter.stamp: both tensors must live on the current device")
+        self.src, self.dst = src, dst
+        self._args = (ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()), int(DataType(src_dtype) if src_dtype is not None else from_torch(src.dtype)),
+                      int(DataType(dst_dtype) if dst_dtype is not None else from_torch(dst.dtype)), ctypes.c_int64(src.numel()), _native.stream_handle(stream))
+        self._launch = _native.lib.thor_b200_cast_launch
+
+    def run(self) -> torch.Tensor:
+        status = self._launch(*self._args)
+        if status:
+            _native.check(status)
+        return self.dst
+
 
 def tensor_copy_from(dst: torch.Tensor, src: torch.Tensor, dst_dtype: DataType | None = None, src_dtype: DataType | None = None, stream=None) -> torch.Tensor:
     """Tensor::copyFromAsync of the reference (Tensor.cpp:700-860) through the host layer: `dst` and `src` hold the same
