@@ -1346,6 +1346,7 @@ def main():
         "gpu_launches": r["launches"],
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "traffic": traffic_bytes, "dram_read_over_algorithmic_read": read_ratio, "peak_source": f"of {peak_kind}",
+                     "frac_of_nominal_8_tbs": per_gpu_gbs / 8000.0,
                      "algorithmic_bytes_per_launch": wl.algorithmic_bytes(), "launch_us": ms * 1e3 / kernel_launches,
                      "frac_sustained": wl.algorithmic_bytes() / (sus["ms_median"] * 1e-3) / 1e9 / peak,
                      "sustained": {"us_median": sus["ms_median"] * 1e3, "us_p10": sus["ms_p10"] * 1e3, "us_p90": sus["ms_p90"] * 1e3, "groups": sus["groups"],
