@@ -702,8 +702,10 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
         else cls[s] = outer_zero ? OneElem : RowScalar;
         dense += cls[s] == Dense;
     }
-    // rows per thread, measured on relu(a*x+b)*sigmoid(z) fp16 [8192, 8192] (two dense inputs): 1 -> 65.1 us, 2 -> 65.0 us, 4 -> 66.1 us, 8 -> 72.0 us
-    int U = dense <= 1 ? 4 : (dense <= 4 ? 2 : 1);
+    // rows per thread, measured on relu(a*x+b)*sigmoid(z) fp16 (two dense inputs): [8192, 8192] 1 -> 65.3 us, 2 -> 65.2 us, 4 -> 66.1 us,
+    // 8 -> 72.0 us; on shards of it one row per thread is ahead -- [4096, 8192] 34.1 / 34.4 / 35.3 us, [2048, 8192] 18.1 / 18.6 / 19.6 us,
+    // [1024, 8192] 10.4 / 10.9 / 11.8 us -- because the smaller grid leaves fewer CTAs to fill the last wave
+    int U = dense <= 1 ? 4 : 1;
     if (st.rows_per_thread == 1 || st.rows_per_thread == 2 || st.rows_per_thread == 4 || st.rows_per_thread == 8) U = st.rows_per_thread;
     while (U > 1 && static_cast<uint64_t>(ty) * (U / 2) >= rows) U /= 2;
     out->kind = p.v2 ? Kind::TiledV2 : Kind::TiledScalar;
