@@ -702,10 +702,10 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
         else cls[s] = outer_zero ? OneElem : RowScalar;
         dense += cls[s] == Dense;
     }
-    // rows per thread, measured on relu(a*x+b)*sigmoid(z) fp16 (two dense inputs): [8192, 8192] 1 -> 65.3 us, 2 -> 65.2 us, 4 -> 66.1 us,
-    // 8 -> 72.0 us; on shards of it one row per thread is ahead -- [4096, 8192] 34.1 / 34.4 / 35.3 us, [2048, 8192] 18.1 / 18.6 / 19.6 us,
-    // [1024, 8192] 10.4 / 10.9 / 11.8 us -- because the smaller grid leaves fewer CTAs to fill the last wave
-    int U = dense <= 1 ? 4 : 1;
+    // rows per thread, measured on relu(a*x+b)*sigmoid(z) fp16 (two dense inputs) in the linear CTA order below, 1 / 2 / 4 rows:
+    // [8192, 8192] 60.9 / 60.1 / 61.4 us, [4096, 8192] 31.6 / 31.7 / 32.7 us, [2048, 8192] 17.2 / 17.3 / 18.4 us, [1024, 8192]
+    // 9.9 / 10.2 / 11.0 us: two rows once the grid is large, one row on smaller tensors, where fewer CTAs fill the last wave worse
+    int U = dense <= 1 ? 4 : (rows * ((ppr + tx - 1) / tx) >= 32768 ? 2 : 1);
     if (st.rows_per_thread == 1 || st.rows_per_thread == 2 || st.rows_per_thread == 4 || st.rows_per_thread == 8) U = st.rows_per_thread;
     while (U > 1 && static_cast<uint64_t>(ty) * (U / 2) >= rows) U /= 2;
     out->kind = p.v2 ? Kind::TiledV2 : Kind::TiledScalar;
@@ -724,10 +724,26 @@ void emitTiled(const Plan& p, const Collapsed& c, Emitted* out, std::ostringstre
     os << "    constexpr int VEC = " << VEC << ", U = " << U << ", TX = " << tx << ", TY = " << ty << ";\n";
     os << "    constexpr tb_u64 ROWS = " << rows << "ull, COLS = " << cols << "ull, PPR = " << ppr << "ull;\n";
     os << "    const tb_u32 tx = threadIdx.x % TX, ty = threadIdx.x / TX;\n";
-    os << "    const tb_u64 cp = (tb_u64)blockIdx.y * TX + tx;\n";
+    const uint64_t gy = (ppr + tx - 1) / tx;
+    // CTA order: the column chunks of a row block sit in consecutive CTAs of a one-dimensional grid, so the CTAs that
+    // run at the same time stream one contiguous range of every dense tensor.  With the row block in blockIdx.x and the
+    // chunk in blockIdx.y, neighbouring CTAs read pieces a whole row apart: relu(a*x+b)*sigmoid(z) fp16 [8192, 8192]
+    // 65.3 us against 60.6 us in this order (0.944 -> 1.016 of the measured copy bandwidth), [4096, 8192] 34.1 -> 31.5 us.
+    {
+        const uint64_t rows_per_cta = static_cast<uint64_t>(ty) * U;
+        const uint64_t gx = (rows + rows_per_cta - 1) / rows_per_cta;
+        out->linear_grid = gx * gy <= 0x7FFFFFFFull;
+    }
+    if (out->linear_grid) {
+        os << "    constexpr tb_u32 GY = " << gy << "u;\n";
+        os << "    const tb_u32 by = blockIdx.x % GY, bx = blockIdx.x / GY;\n";
+    } else {
+        os << "    const tb_u32 by = blockIdx.y, bx = blockIdx.x;\n";
+    }
+    os << "    const tb_u64 cp = (tb_u64)by * TX + tx;\n";
     os << "    if (cp >= PPR) return;\n";
     os << "    const tb_u64 col = cp * VEC;\n";
-    os << "    const tb_u64 row0 = (tb_u64)blockIdx.x * (TY * U) + ty;\n";
+    os << "    const tb_u64 row0 = (tb_u64)bx * (TY * U) + ty;\n";
     emitScalarLoads(st, os);
     for (size_t s = 0; s < st.inputs.size(); ++s) {
         if (st.inputs[s].kind != THOR_B200_INPUT_TENSOR) continue;

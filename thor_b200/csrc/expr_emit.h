@@ -35,6 +35,7 @@ struct Emitted {
     // tiled / generic geometry (baked into the source as literals)
     uint64_t rows = 0, cols = 0, numel = 0;
     int tx = 0, ty = 0;
+    bool linear_grid = false;  // tiled kernels: one-dimensional grid, column chunks of a row block in consecutive CTAs
     // pointer alignment (bytes) the kernel assumes for each tensor input / output; 1 = none
     std::vector<int> input_align;
     std::vector<int> output_align;

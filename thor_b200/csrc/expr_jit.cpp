@@ -301,6 +301,10 @@ int launchVariant(const thor_b200_expr& e, const Variant& v, const void* const* 
             if (gx > 0x7FFFFFFFull || gy > 65535ull) return fail(THOR_B200_UNSUPPORTED, "broadcast stage exceeds the launch grid");
             grid.x = static_cast<unsigned>(gx);
             grid.y = static_cast<unsigned>(gy);
+            if (v.em.linear_grid) {
+                grid.x = static_cast<unsigned>(gx * gy);
+                grid.y = 1;
+            }
         } break;
         case Kind::Generic: {
             const uint64_t total = st.broadcast ? v.em.numel : numel;
