@@ -174,6 +174,21 @@ __device__ __forceinline__ float tb_digammaf(float x) {
 static const char* const kRowProgPrelude = R"TBROWPROG(
 __device__ __forceinline__ float tb_add(float a, float b) { return a + b; }
 __device__ __forceinline__ float tb_mul(float a, float b) { return a * b; }
+// NaN-propagating min / max in one instruction (the result for a NaN operand is the canonical NaN 0x7fffffff).
+__device__ __forceinline__ float tb_max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float tb_min_nan(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+// Three values: two instructions (the three-input form of sm_100 needs a newer PTX version than every NVRTC that may be
+// loaded at run time accepts, so generated code stays with the two-input form).
+__device__ __forceinline__ float tb_max3_nan(float a, float b, float c) { return tb_max_nan(a, tb_max_nan(b, c)); }
+__device__ __forceinline__ float tb_min3_nan(float a, float b, float c) { return tb_min_nan(a, tb_min_nan(b, c)); }
 // NaN-propagating min / max, the rule of the reduction seam.
 __device__ __forceinline__ float tb_nanmin(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
 __device__ __forceinline__ float tb_nanmax(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }

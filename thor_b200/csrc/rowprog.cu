@@ -878,7 +878,6 @@ std::string emit(Program& p) {
             }
             if (p.pairs) os << I << "float2 q" << k << " = tb_both(" << identityExpr(p.nodes[k].op) << ");  // one partial per lane\n";
             else os << I << "float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
-            if (isMinMax(k)) os << I << "bool nan" << k << " = false;  // min / max: fminf / fmaxf plus a sticky NaN predicate per element\n";
         }
     };
     auto roundElementLoop = [&](const std::vector<uint32_t>& round, const std::vector<uint32_t>& closure, const std::string& guard_expr) {
@@ -916,10 +915,11 @@ std::string emit(Program& p) {
                     const std::string arg = pairReduceArg(p, a, II, os);
                     os << I << "            { const float2 a" << k << " = " << arg << "; " << acc << " = __ffma2_rn(a" << k << ", a" << k << ", " << acc << "); }\n";
                 } else if (isMinMax(k)) {
-                    const char* fn = op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf";
+                    // both elements of the pair with the NaN-propagating max / min of the hardware, two instructions
+                    // (fmaxf per lane plus a sticky NaN predicate took five); only the .x lane of the partial is used
+                    const char* fn = op == THOR_B200_OP_REDUCE_MAX ? "tb_max3_nan" : "tb_min3_nan";
                     const std::string arg = pairReduceArg(p, a, II, os);
-                    os << I << "            { const float2 a" << k << " = " << arg << "; nan" << k << " = nan" << k << " || (a" << k << ".x != a" << k << ".x) || (a" << k
-                       << ".y != a" << k << ".y); " << acc << ".x = " << fn << "(" << acc << ".x, a" << k << ".x); " << acc << ".y = " << fn << "(" << acc << ".y, a" << k << ".y); }\n";
+                    os << I << "            { const float2 a" << k << " = " << arg << "; " << acc << ".x = " << fn << "(" << acc << ".x, a" << k << ".x, a" << k << ".y); }\n";
                 } else {
                     const std::string arg = pairReduceArg(p, a, II, os);
                     os << I << "            { const float2 a" << k << " = " << arg << "; " << acc << ".x = " << combineExpr(op) << "(" << acc << ".x, "
@@ -939,8 +939,7 @@ std::string emit(Program& p) {
                     os << I << "            tb_arg_scan<" << (p.nodes[k].op == THOR_B200_OP_REDUCE_ARGMAX ? "true" : "false") << ">(r" << k << ", i" << k << ", nan_i" << k << ", " << f
                        << ", q * VEC + j);\n";
                 else if (isMinMax(k))
-                    os << I << "            { const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
-                       << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
+                    os << I << "            r" << k << " = " << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "tb_max_nan" : "tb_min_nan") << "(r" << k << ", " << f << ");\n";
                 else
                     os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
             }
@@ -954,13 +953,12 @@ std::string emit(Program& p) {
             for (uint32_t k : round) {
                 if (isIndexReduce(p.nodes[k].op)) continue;
                 const bool mm = isMinMax(k);
-                os << I << "float r" << k << " = " << (mm ? (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") : combineExpr(p.nodes[k].op)) << "(q" << k << ".x, q" << k << ".y);\n";
+                os << I << "float r" << k << " = " << (mm ? (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "tb_max_nan" : "tb_min_nan") : combineExpr(p.nodes[k].op)) << "(q" << k << ".x, q" << k << ".y);\n";
             }
     };
     auto roundBeforeBarrier = [&](const std::vector<uint32_t>& round) {
         size_t slot = 0;
         for (uint32_t k : round) {
-            if (isMinMax(k)) os << I << "if (nan" << k << ") r" << k << " = __int_as_float(0x7fffffff);\n";
             const size_t idx = std::find(p.row_reduces.begin(), p.row_reduces.end(), k) - p.row_reduces.begin();
             if (p.nodes[k].op == kOpFirstMatch)
                 os << I << "tb_u64 key" << k << " = tb_team_arg_stage1<TEAM>((tb_u64)(tb_u32)~i" << k << ", red_key[" << idx << "][team_id]);  // max of ~index = lowest index\n";
@@ -1198,9 +1196,8 @@ std::string emitFlat(Program& p) {
     auto isMinMax = [&](uint32_t k) { return p.nodes[k].op == THOR_B200_OP_REDUCE_MIN || p.nodes[k].op == THOR_B200_OP_REDUCE_MAX; };
     for (uint32_t k : p.all_reduces) {
         os << "    float r" << k << " = " << identityExpr(p.nodes[k].op) << ";\n";
-        // min / max: the per-element step is fminf / fmaxf plus a sticky "saw a NaN" predicate (2 instructions);
-        // the NaN-propagating rule is restored once per thread before the CTA-wide combine
-        if (isMinMax(k)) os << "    bool nan" << k << " = false;\n";
+        // min / max: the per-element step is ONE instruction, the NaN-propagating min.NaN / max.NaN of the hardware
+        // (fminf / fmaxf plus a sticky "saw a NaN" predicate took three)
     }
     std::vector<uint32_t> args;
     for (uint32_t k : p.all_reduces) args.push_back(p.nodes[k].lhs);
@@ -1211,8 +1208,7 @@ std::string emitFlat(Program& p) {
             const uint32_t a = p.nodes[k].lhs;
             const std::string f = reduceArgF32(p, a, "v" + std::to_string(a));
             if (isMinMax(k)) {
-                os << indent << "{ const float a" << k << " = " << f << "; nan" << k << " = nan" << k << " || (a" << k << " != a" << k << "); r" << k << " = "
-                   << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "fmaxf" : "fminf") << "(r" << k << ", a" << k << "); }\n";
+                os << indent << "r" << k << " = " << (p.nodes[k].op == THOR_B200_OP_REDUCE_MAX ? "tb_max_nan" : "tb_min_nan") << "(r" << k << ", " << f << ");\n";
             } else {
                 os << indent << "r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
             }
@@ -1246,7 +1242,6 @@ std::string emitFlat(Program& p) {
     os << "        }\n    }\n";
     size_t idx = 0;
     for (uint32_t k : p.all_reduces) {
-        if (isMinMax(k)) os << "    if (nan" << k << ") r" << k << " = __int_as_float(0x7fffffff);\n";
         os << "    r" << k << " = tb_team_reduce_stage1<256, " << combineExpr(p.nodes[k].op) << ">(r" << k << ", red_smem[" << idx << "][0]);\n";
         ++idx;
     }
