@@ -3,8 +3,8 @@
 The graph is the JSON form that both dumpers produce: ``oracle/ref_autodiff.cpp`` for the graphs the REFERENCE's own
 autodiff builds (buildBackwardOutputs, AutoDiff.cpp:6210) and ``FusedEquation::describeGraph`` for the host layer's.
 Every node carries the reference's ExprOp integer (Expression.h:32-148), its parents and its resolved output / compute
-dtypes.  Evaluation follows the per-node rule of the reference's kernels (CudaSourceEmitter.cpp:1610-1959, 2077-2083;
-SURVEY appendix A): a node converts its operands to its compute dtype, computes (here in float64, rounded ONCE to the
+dtypes.  Evaluation follows the per-node rule of the reference's kernels (CudaSourceEmitter.cpp:1610-1959,
+2077-2083): a node converts its operands to its compute dtype, computes (here in float64, rounded ONCE to the
 compute dtype: correctly rounded + - * / sqrt, ideal transcendentals), holds the value in the compute dtype and rounds
 it to its output dtype where it is materialised (an output, the argument of a reduction or of a view).  Reductions
 convert to fp32, accumulate (here in float64), finalise and round once to the output dtype
