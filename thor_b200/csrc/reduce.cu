@@ -44,16 +44,27 @@ template <> struct OpTraits<THOR_B200_REDUCE_PRODUCT> {
     __device__ static float transform(float v) { return v; }
     __device__ static float combine(float a, float b) { return a * b; }
 };
-// NaN-propagating min / max (CubReductionOperation.cuh:106-129).
+// NaN-propagating min / max (CubReductionOperation.cuh:106-129) as ONE instruction, min.NaN / max.NaN; the result for a NaN
+// operand is the canonical NaN (the two compares and selects around fminf / fmaxf kept the payload of the first NaN).
+__device__ __forceinline__ float minNaN(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float maxNaN(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
 template <> struct OpTraits<THOR_B200_REDUCE_MIN> {
     __device__ static float identity() { return __int_as_float(0x7f800000); }
     __device__ static float transform(float v) { return v; }
-    __device__ static float combine(float a, float b) { return a != a ? a : (b != b ? b : fminf(a, b)); }
+    __device__ static float combine(float a, float b) { return minNaN(a, b); }
 };
 template <> struct OpTraits<THOR_B200_REDUCE_MAX> {
     __device__ static float identity() { return __int_as_float(0xff800000); }
     __device__ static float transform(float v) { return v; }
-    __device__ static float combine(float a, float b) { return a != a ? a : (b != b ? b : fmaxf(a, b)); }
+    __device__ static float combine(float a, float b) { return maxNaN(a, b); }
 };
 
 template <class T> __device__ __forceinline__ float toFloat(T v) { return static_cast<float>(v); }

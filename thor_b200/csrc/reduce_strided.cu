@@ -54,8 +54,16 @@ __device__ __forceinline__ float identityValue(int op) {
 __device__ __forceinline__ float combineValue(int op, float a, float b) {
     switch (op) {
         case THOR_B200_REDUCE_PRODUCT: return a * b;
-        case THOR_B200_REDUCE_MIN: return a != a ? a : (b != b ? b : fminf(a, b));
-        case THOR_B200_REDUCE_MAX: return a != a ? a : (b != b ? b : fmaxf(a, b));
+        case THOR_B200_REDUCE_MIN: {  // NaN-propagating, one instruction
+            float r;
+            asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+            return r;
+        }
+        case THOR_B200_REDUCE_MAX: {
+            float r;
+            asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+            return r;
+        }
         default: return a + b;
     }
 }

@@ -1257,7 +1257,7 @@ std::string emitFlat(Program& p) {
     return "";
 }
 
-// Folds the per-CTA partials of one full reduction: one CTA, thread t takes partials t, t + 1024, ...
+// Combine step of the folds below.
 template <int OP>
 __device__ __forceinline__ float foldCombine(float a, float b) {
     if (OP == 1) return a * b;
@@ -1265,24 +1265,44 @@ __device__ __forceinline__ float foldCombine(float a, float b) {
     if (OP == 3) return a != a ? a : (b != b ? b : fmaxf(a, b));
     return a + b;
 }
-template <int OP>
-__global__ void __launch_bounds__(1024) foldFullPartials(const float* __restrict__ ws, uint32_t parts, void* out, int out_dtype, float divisor, int take_sqrt) {
+// One launch folds every full reduction of a program: CTA i owns reduction i (thread t takes partials t, t + 1024, ...,
+// then a fixed shuffle / warp-order combine, so the result does not depend on timing).
+constexpr int kMaxFullFolds = 8;
+struct FullFoldArgs {
+    void* out[kMaxFullFolds];
+    int out_dtype[kMaxFullFolds];
+    float divisor[kMaxFullFolds];
+    int op[kMaxFullFolds];  // 0 sum, 1 product, 2 min, 3 max
+    int take_sqrt[kMaxFullFolds];
+};
+__device__ __forceinline__ float foldCombineAny(int op, float a, float b) {
+    switch (op) {
+        case 1: return foldCombine<1>(a, b);
+        case 2: return foldCombine<2>(a, b);
+        case 3: return foldCombine<3>(a, b);
+        default: return foldCombine<0>(a, b);
+    }
+}
+__global__ void __launch_bounds__(1024) foldFullPartials(const float* __restrict__ ws_all, uint32_t parts, FullFoldArgs a) {
     gridDependencyWait();
     gridLaunchDependents();
     __shared__ float sm[32];
-    const float identity = OP == 1 ? 1.0f : (OP == 2 ? __int_as_float(0x7f800000) : (OP == 3 ? __int_as_float(0xff800000) : 0.0f));
+    const int which = blockIdx.x, op = a.op[which];
+    const float* ws = ws_all + static_cast<size_t>(which) * parts;
+    const float identity = op == 1 ? 1.0f : (op == 2 ? __int_as_float(0x7f800000) : (op == 3 ? __int_as_float(0xff800000) : 0.0f));
     float v = identity;
-    for (uint32_t s = threadIdx.x; s < parts; s += 1024) v = foldCombine<OP>(v, ws[s]);
+    for (uint32_t s = threadIdx.x; s < parts; s += 1024) v = foldCombineAny(op, v, ws[s]);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = foldCombine<OP>(v, __shfl_xor_sync(0xffffffffu, v, off));
+    for (int off = 16; off > 0; off >>= 1) v = foldCombineAny(op, v, __shfl_xor_sync(0xffffffffu, v, off));
     if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
     __syncthreads();
     if (threadIdx.x == 0) {
         float r = sm[0];
-        for (int w = 1; w < 32; ++w) r = foldCombine<OP>(r, sm[w]);
-        if (divisor != 1.0f) r = r / divisor;
-        if (take_sqrt) r = sqrtf(r);
-        switch (out_dtype) {
+        for (int w = 1; w < 32; ++w) r = foldCombineAny(op, r, sm[w]);
+        if (a.divisor[which] != 1.0f) r = r / a.divisor[which];
+        if (a.take_sqrt[which]) r = sqrtf(r);
+        void* out = a.out[which];
+        switch (a.out_dtype[which]) {
             case THOR_B200_FP32: static_cast<float*>(out)[0] = r; break;
             case THOR_B200_FP16: static_cast<__half*>(out)[0] = __float2half_rn(r); break;
             case THOR_B200_BF16: static_cast<__nv_bfloat16*>(out)[0] = __float2bfloat16_rn(r); break;
@@ -1623,23 +1643,26 @@ int thor_b200_rowprog_launch_sharded(thor_b200_rowprog* h, const void* const* in
     TB_CUDA(launchDependentC(reinterpret_cast<const void*>(h->module->kernel.load()), dim3(p.grid), dim3(static_cast<unsigned>(p.cta + (p.ring_stages > 0 && p.producer ? 128 : 0))), args, p.smem_bytes, stream));
     countLaunch();
     if (!p.all_reduces.empty()) {
-        size_t idx = 0;
-        for (uint32_t k : p.all_reduces) {
-            size_t o = 0;
-            for (; o < p.outputs.size(); ++o)
-                if (p.outputs[o].node == k) break;
-            const uint16_t op = p.nodes[k].op;
-            const float divisor = op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows * p.cols) : 1.0f;
-            const int take_sqrt = op == THOR_B200_OP_REDUCE_NORM2;
-            const float* part = static_cast<const float*>(workspace) + idx * static_cast<size_t>(p.grid);
-            if (op == THOR_B200_OP_REDUCE_PROD) (void)launchDependent(foldFullPartials<1>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            else if (op == THOR_B200_OP_REDUCE_MIN) (void)launchDependent(foldFullPartials<2>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            else if (op == THOR_B200_OP_REDUCE_MAX) (void)launchDependent(foldFullPartials<3>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            else (void)launchDependent(foldFullPartials<0>, dim3(1), dim3(1024), 0, stream, part, p.grid, output_ptrs[o], p.outputs[o].dtype, divisor, take_sqrt);
-            TB_CUDA(cudaGetLastError());
-            ++idx;
+        // every group of up to kMaxFullFolds reductions is folded by one launch (one CTA per reduction)
+        for (size_t first = 0; first < p.all_reduces.size(); first += kMaxFullFolds) {
+            const size_t count = std::min<size_t>(kMaxFullFolds, p.all_reduces.size() - first);
+            FullFoldArgs fold{};
+            for (size_t i = 0; i < count; ++i) {
+                const uint32_t k = p.all_reduces[first + i];
+                size_t o = 0;
+                for (; o < p.outputs.size(); ++o)
+                    if (p.outputs[o].node == k) break;
+                const uint16_t op = p.nodes[k].op;
+                fold.out[i] = output_ptrs[o];
+                fold.out_dtype[i] = p.outputs[o].dtype;
+                fold.divisor[i] = op == THOR_B200_OP_REDUCE_AVG ? static_cast<float>(p.rows * p.cols) : 1.0f;
+                fold.take_sqrt[i] = op == THOR_B200_OP_REDUCE_NORM2;
+                fold.op[i] = op == THOR_B200_OP_REDUCE_PROD ? 1 : (op == THOR_B200_OP_REDUCE_MIN ? 2 : (op == THOR_B200_OP_REDUCE_MAX ? 3 : 0));
+            }
+            const float* part = static_cast<const float*>(workspace) + first * static_cast<size_t>(p.grid);
+            TB_CUDA(launchDependent(foldFullPartials, dim3(static_cast<unsigned>(count)), dim3(1024), 0, stream, part, p.grid, fold));
+            countLaunch();
         }
-        countLaunch(p.all_reduces.size());
     }
     if (!p.col_reduces.empty()) {
         const uint32_t parts = p.grid * static_cast<uint32_t>(p.cta / p.team);
@@ -1671,7 +1694,7 @@ int thor_b200_rowprog_launch_sharded(thor_b200_rowprog* h, const void* const* in
 const char* thor_b200_rowprog_source(const thor_b200_rowprog* h) { return h ? h->prog.source.c_str() : ""; }
 
 uint32_t thor_b200_rowprog_launch_count(const thor_b200_rowprog* h) {
-    return h ? 1u + static_cast<uint32_t>((h->prog.col_reduces.empty() ? 0 : 1) + h->prog.all_reduces.size()) : 0u;
+    return h ? 1u + static_cast<uint32_t>((h->prog.col_reduces.empty() ? 0 : 1) + (h->prog.all_reduces.size() + tb::rowprog::kMaxFullFolds - 1) / tb::rowprog::kMaxFullFolds) : 0u;
 }
 
 int thor_b200_rowprog_waits_expired(thor_b200_rowprog* h, uint32_t* count) {
