@@ -956,7 +956,13 @@ class C5LayerNormBwd(C5LayerNormFwd):
 
         gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
         sharded = self.dist.enabled
-        bwd = ex.compile({"y": _layernorm_expr(ex)}, row_program=ROW_PROGRAM, unrounded_column_sums=sharded).compile_backward(["x", "gamma", "beta"])
+        tuning = dict(ROW_PROGRAM or {})
+        if self.dist.world >= 8 and "reserve_sms" not in tuning:
+            # Eight ranks: the shard's kernel takes about 40 us and the collective about 26 us; a persistent grid over every
+            # SM leaves the collective's CTAs nowhere to run until it drains.  Measured per step at N = 8 with 0 / 4 / 8 / 16 /
+            # 32 SMs left free: 61.8 / 54.2 / 57.8 / 56.9 / 61.7 us.  At N = 2 it made no difference, so it stays 0 there.
+            tuning["reserve_sms"] = 4
+        bwd = ex.compile({"y": _layernorm_expr(ex)}, row_program=tuning or None, unrounded_column_sums=sharded).compile_backward(["x", "gamma", "beta"])
         self.sets = []
         for _ in range(_ShardCombiner.SLOTS if sharded else 2):
             x, gamma, beta = self._inputs(gen)
