@@ -1311,9 +1311,12 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations, the end-to-end leg, the baselines and the result check")
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of the workload's leading dimension (smaller cases for profiler captures only)")
+    ap.add_argument("--e2e-chunks", type=int, default=0, help="row chunks of the end-to-end leg of configuration 2 (comparison runs; 0 = the default)")
     ap.add_argument("--row-program", default="", help="row-program layout fields, e.g. copy_warpgroup=-1,ring_buffers=4 (comparison runs)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    if args.e2e_chunks > 0:
+        C2FusedExpr.E2E_CHUNKS = args.e2e_chunks
     if args.row_program:
         global ROW_PROGRAM
         ROW_PROGRAM = {k: int(v) for k, v in (kv.split("=") for kv in args.row_program.split(","))}
