@@ -883,6 +883,12 @@ std::string emit(Program& p) {
     auto roundElementLoop = [&](const std::vector<uint32_t>& round, const std::vector<uint32_t>& closure, const std::string& guard_expr) {
         os << "#pragma unroll\n" << I << "for (int k = 0; k < VPT; ++k) {\n" << I << "    const tb_u32 q = t + k * TEAM;\n" << I << "    if (" << guard_expr << ") {\n";
         emitColumnPackLoads(p, closure, I + "        ", os);
+        // "first column equal to the row extreme": the element loop only ORs one compare per element into a per-pack flag;
+        // the index arithmetic runs after the loop, for the few packs that hold a match (every pack of a row whose extreme is
+        // NaN, where the first NaN is what is looked for)
+        if (p.pairs)
+            for (uint32_t k : round)
+                if (p.nodes[k].op == kOpFirstMatch) os << I << "        bool hit" << k << " = mnan" << k << ";\n";
         os << "#pragma unroll\n" << I << "        for (int j = 0; j < VEC; " << (p.pairs ? "j += 2" : "++j") << ") {\n";
         emitElementInputs(p, closure, I + "            ", os);
         if (p.pairs) {
@@ -894,9 +900,7 @@ std::string emit(Program& p) {
                 const std::string II = I + "            ";
                 if (op == kOpFirstMatch) {
                     const std::string arg = pairReduceArg(p, a, II, os);
-                    os << II << "{ const float2 a" << k << " = " << arg << "; i" << k << " = min(i" << k << ", (a" << k << ".x == m" << k << " || (mnan" << k << " && a" << k << ".x != a" << k
-                       << ".x)) ? (tb_u32)(q * VEC + j) : 0xffffffffu); i" << k << " = min(i" << k << ", (a" << k << ".y == m" << k << " || (mnan" << k << " && a" << k << ".y != a" << k
-                       << ".y)) ? (tb_u32)(q * VEC + j + 1) : 0xffffffffu); }\n";
+                    os << II << "{ const float2 a" << k << " = " << arg << "; hit" << k << " = hit" << k << " | (a" << k << ".x == m" << k << ") | (a" << k << ".y == m" << k << "); }\n";
                     continue;
                 }
                 if (isArgReduce(op)) {
@@ -944,7 +948,23 @@ std::string emit(Program& p) {
                     os << I << "            r" << k << " = " << combineExpr(p.nodes[k].op) << "(r" << k << ", " << transformExpr(p.nodes[k].op, f) << ");\n";
             }
         }
-        os << I << "        }\n" << I << "    }\n" << I << "}\n";
+        os << I << "        }\n";
+        if (p.pairs)
+            for (uint32_t k : round) {
+                if (p.nodes[k].op != kOpFirstMatch) continue;
+                const uint32_t a = p.nodes[k].lhs;
+                const std::vector<uint32_t> arg_closure = elementClosure(p, std::vector<uint32_t>{a});
+                const std::string II = I + "                ";
+                os << I << "        if (hit" << k << ") {\n#pragma unroll\n" << I << "            for (int j = 0; j < VEC; j += 2) {\n";
+                emitElementInputs(p, arg_closure, II, os);
+                emitPairStatements(p, arg_closure, II, os);
+                const std::string arg = pairReduceArg(p, a, II, os);
+                os << II << "const float2 a" << k << " = " << arg << ";\n"
+                   << II << "i" << k << " = min(i" << k << ", (a" << k << ".x == m" << k << " || (mnan" << k << " && a" << k << ".x != a" << k << ".x)) ? (tb_u32)(q * VEC + j) : 0xffffffffu);\n"
+                   << II << "i" << k << " = min(i" << k << ", (a" << k << ".y == m" << k << " || (mnan" << k << " && a" << k << ".y != a" << k << ".y)) ? (tb_u32)(q * VEC + j + 1) : 0xffffffffu);\n";
+                os << I << "            }\n" << I << "        }\n";
+            }
+        os << I << "    }\n" << I << "}\n";
         for (uint32_t k : closure)
             if (p.cache_state[k] == 1) p.cache_state[k] = 2;  // later loops read the registers
     };
