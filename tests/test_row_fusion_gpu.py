@@ -204,6 +204,9 @@ def test_softmax_and_argmax_of_one_tensor_share_one_pass():
     x = torch.randint(-8, 8, (rows, cols), device="cuda").float()  # many ties
     x[7, 100] = float("nan")
     x[7, 50] = float("nan")
+    x[9, :] = -1.0  # signed zeros tie: the first of them wins whatever its sign
+    x[9, 20] = -0.0
+    x[9, 30] = 0.0
     xi = ex.input("x")
     e = (xi - xi.reduce_max([1])).exp()
     both = ex.compile({"y": e / e.reduce_sum([1]), "idx": xi.argmax([1], squeeze_axes=[1])}).stamp({"x": x})
@@ -217,7 +220,7 @@ def test_softmax_and_argmax_of_one_tensor_share_one_pass():
     assert idx.dtype == np.uint32
     assert np.array_equal(idx, alone.output().cpu().numpy())
     assert np.array_equal(idx, eo.arg_reduce_rows(x.cpu().numpy(), True).astype(np.uint32))
-    assert idx[7] == 50
+    assert idx[7] == 50 and idx[9] == 20
     y = both.output("y").cpu().numpy()
     want, _ = o.softmax_rows(np.delete(x.cpu().numpy(), 7, axis=0), want_argmax=False)
     np.testing.assert_allclose(np.delete(y, 7, axis=0), want, rtol=1e-5, atol=1e-12)
