@@ -1038,7 +1038,7 @@ class C5BwdStageList(C5LayerNormBwd):
     it.  The reference's own emitted kernels are not used here because its multi-output fused stages cannot be driven
     through the single-output launcher of the test infrastructure."""
     is_baseline = True
-    name = "c5_layernorm_backward_bf16_reference_stage_list"
+    name = "c5_layernorm_backward_bf16_reference_stage_cut_own_kernels"
     description = ("reference stage cut for the autodiff LayerNorm backward (Reduction / FusedKernel stages with materialised fp32 intermediates), "
                    "this library's kernels per stage (baseline beside c5 backward)")
     collective = None
@@ -1061,6 +1061,83 @@ class C5BwdStageList(C5LayerNormBwd):
     def step(self, i): self.sets[0][0].run()
     def collective_us(self): return None
 
+
+
+class C5BwdReferenceKernels(C5LayerNormBwd):
+    """Baseline, not product: the autodiff LayerNorm backward as the REFERENCE would run it.  The backward graph is the one
+    the reference's own buildBackwardOutputs builds (tests/golden/autodiff_reference_graphs.json, dumped from its AutoDiff.cpp);
+    oracle/stage_cut.py cuts it by the reference's planning rule (every reduction a stage over a tensor in memory, fused
+    stages between them); every fused stage is the kernel the reference's own emitter generates for it and every reduction its
+    own CUB call or tiled kernel (oracle/_ref).  One fused kernel per materialised tensor: where the reference would put two
+    outputs into one kernel this re-reads their shared inputs, which matters little next to the two column sums
+    ([1, 32768, 8192] over axis 0: its tiled kernel walks them on two CTAs)."""
+    is_baseline = True
+    name = "c5_layernorm_backward_bf16_reference_kernels"
+    description = ("reference stage list for the autodiff LayerNorm backward: its own backward graph cut by its planning rule, its emitted fused kernels + "
+                   "its CUB / tiled reductions (baseline beside c5 backward)")
+    collective = None
+
+    def setup(self):
+        import torch
+
+        import oracle
+        from oracle import stage_cut
+        from oracle.refkernel import ReferenceBroadcastKernel
+        from thor_b200.dtypes import DataType, to_torch
+
+        if oracle.reference_emitter_lib() is None or oracle.reference_cub_reduce_lib() is None:
+            raise RuntimeError("oracle/_ref holds no build of the reference's emitter / reductions")
+        R, C = self.ROWS, self.COLS
+        golden = json.loads((ROOT / "tests" / "golden" / "autodiff_reference_graphs.json").read_text())["layernorm_bf16_32768x8192"]
+        graph = stage_cut.merge_equal_nodes(golden["graph"])
+        shapes = {"x": (R, C), "gamma": (C,), "beta": (C,), "__grad_output": (R, C)}
+        gen = torch.Generator(device="cuda").manual_seed(56 + self.dist.rank)
+        x, gamma, beta = self._inputs(gen)
+        dy = (torch.randn(R, C, device="cuda", generator=gen) * 1e-2).bfloat16()
+        self.tensors = {"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy}
+        dtype_of = {"x": oracle.BF16, "gamma": oracle.BF16, "beta": oracle.BF16, "__grad_output": oracle.BF16}
+        self.stages, self.kernel_kind = [], []
+        for st in stage_cut.stage_list(graph, shapes):
+            out = torch.empty(st["shape"], device="cuda", dtype=to_torch(DataType(st["dtype"])))
+            self.tensors[st["name"]], dtype_of[st["name"]] = out, st["dtype"]
+            if st["kind"] == "reduction":
+                src = self.tensors[st["input"]]
+                rows, cols = st["input_shape"]
+                outer, n, inner = (rows, cols, 1) if st["axes"] == [1] else (1, rows, cols)
+                red = _ReferenceReduction(st["op"], src, out, outer, n, inner)
+                self.stages.append(red.run)
+                self.kernel_kind.append(f"reference reduction {st['op']} over axis {st['axes'][0]} -> {st['name']}")
+            else:
+                dims = {name: tuple(self.tensors[name].shape) for name in st["inputs"]}
+                dts = {name: dtype_of[name] for name in st["inputs"]}
+                kernel = ReferenceBroadcastKernel(st["program"], dts, dims)
+                if kernel.out_dtype != st["dtype"]:  # the graph stores this node in another dtype than the expression resolves to on its own
+                    kernel = ReferenceBroadcastKernel(st["program"] + f" cast:{st['dtype']}", dts, dims)
+                ins = {name: self.tensors[name] for name in st["inputs"]}
+                self.stages.append(lambda k=kernel, i=ins, o=out: k.launch(i, o))
+                self.kernel_kind.append(f"reference fused -> {st['name']}")
+        self.sets = [None]
+        self.launches_per_step = len(self.stages)
+        self.combiner = None
+        # sanity: the baseline computes the same gradients as the row program (same inputs), or it times nothing useful
+        from thor_b200.expression import Expression as ex
+
+        self.step(0)
+        ours = ex.compile({"y": _layernorm_expr(ex)}).compile_backward(["x", "gamma", "beta"]).stamp({"x": x, "gamma": gamma, "beta": beta, "__grad_output": dy})
+        ours.run()
+        torch.cuda.synchronize()
+        for name in ("x_grad", "gamma_grad", "beta_grad"):
+            a, b = self.tensors[name].float().reshape(-1), ours.output(name).float().reshape(-1)
+            worst = float((a - b).abs().max() / (b.abs().max() + 1e-30))
+            if not worst < 2e-2:
+                raise RuntimeError(f"reference-kernel baseline disagrees with the row program on {name}: {worst:.3e} of the largest value")
+        del ours
+
+    def step(self, i):
+        for run in self.stages:
+            run()
+
+    def collective_us(self): return None
 
 class F3ScatterAdd(Workload):
     """Flat scatter-add without atomics (the step behind arg scans in scan min / max backward): 2^24 fp32 updates with
@@ -1097,7 +1174,7 @@ class F3ScatterAdd(Workload):
 
 WORKLOADS = {"c1": C1Cast, "c2": C2FusedExpr, "c3": C3Softmax, "c3_argmax": C3Argmax, "c3_both": C3SoftmaxWithArgmax, "c4": C4FullReduce, "c5_fwd": C5LayerNormFwd,
              "c5_bwd": C5LayerNormBwd, "c1_ref_gpu": C1CastReferenceGpu, "c2_ref_gpu": C2ReferenceGpu, "c3_ref_stages": C3ReferenceStagePipeline, "c3_argmax_ref_gpu": C3ArgmaxReferenceGpu, "c4_ref_stages": C4ReferenceStagePipeline,
-             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline, "c5_bwd_ref_stages": C5BwdStageList, "f3_scatter": F3ScatterAdd}
+             "c5_fwd_ref_stages": C5FwdReferenceStagePipeline, "c5_bwd_ref_stages": C5BwdReferenceKernels, "c5_bwd_stage_cut": C5BwdStageList, "f3_scatter": F3ScatterAdd}
 
 
 # ---------------------------------------------------------------------------------------------------------
