@@ -127,3 +127,30 @@ def test_the_golden_graphs_are_what_the_reference_builds_today(name):
     case = GOLDEN[name]
     inputs = {k: (tuple(v[0]), v[1]) for k, v in case["inputs"].items()}
     assert o.reference_backward_graph(case["program"], inputs, case["wrt"], case["upstream_dtype"]) == case["graph"]
+
+
+def test_the_reference_backward_graph_cuts_into_its_stage_list():
+    """oracle/stage_cut.py applies the reference's planning rule (a reduction is a stage over a tensor in memory,
+    EquationCompiler.cpp:684-688, 4088-4173) to its LayerNorm backward graph: the benchmark's reference baseline runs
+    exactly these stages.  Equal nodes merge first (x - mean appears three times in the dump)."""
+    from oracle import stage_cut
+
+    case = GOLDEN["layernorm_bf16_32768x8192"]
+    graph = stage_cut.merge_equal_nodes(case["graph"])
+    assert len(case["graph"]["nodes"]) == 67 and len(graph["nodes"]) == 47
+    shapes = {k: tuple(v[0]) for k, v in case["inputs"].items()}
+    shapes[UPSTREAM] = (32768, 8192)
+    stages = stage_cut.stage_list(graph, shapes)
+    assert [s["kind"] for s in stages] == ["fused", "reduction"] + ["reduction", "fused"] * 6
+    assert stages[0]["program"] == f"in:{UPSTREAM} cast:11" and stages[0]["dtype"] == o.FP32
+    column_sums = [s for s in stages if s["kind"] == "reduction" and s["axes"] == [0]]
+    assert [s["name"] for s in column_sums] == ["beta_grad", "gamma_grad"] and all(s["dtype"] == o.BF16 and s["shape"] == (8192,) for s in column_sums)
+    row_stats = [s for s in stages if s["kind"] == "reduction" and s["axes"] == [1]]
+    assert len(row_stats) == 5 and all(s["shape"] == (32768, 1) and s["dtype"] == o.FP32 for s in row_stats)
+    last = stages[-1]
+    assert last["name"] == "x_grad" and last["dtype"] == o.BF16 and set(last["inputs"]) >= {"gamma", "x"}
+    # every fused stage reads only inputs and results of earlier stages
+    known = set(shapes)
+    for s in stages:
+        assert set(s["inputs"] if s["kind"] == "fused" else [s["input"]]) <= known, s["name"]
+        known.add(s["name"])
